@@ -1,0 +1,517 @@
+// Bandwidth-bound kernels of the training step: RMSNorm, RoPE, SwiGLU, fused
+// cross-entropy, AdamW over a flat bucket shard, dtype casts and the
+// descriptor-driven segment gather/cast/zero used by bucket packing.
+// All loads and stores are 16-byte vectors where alignment allows.
+#include "common.cuh"
+
+namespace {
+
+using namespace fsb;
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const bf16x8 t = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(t.v[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  bf16x8 t;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) t.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = t;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : -INFINITY;
+  if (w == 0) {
+    t = warp_max(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One CTA per row; D % 8 == 0. Optional residual: s = x + res is written to
+// `sum_out` and normalised (the pre-norm residual stream update in one pass).
+constexpr int NORM_THREADS = 256;
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd, int D, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * D;
+  const __nv_bfloat16* rr = res ? res + row * D : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
+    float f[8];
+    load8(xr + i, f);
+    if (rr) {
+      float g[8];
+      load8(rr + i, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+      // round through bf16 so the normalised value matches the stored sum
+      bf16x8 t;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) t.v[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+      *reinterpret_cast<bf16x8*>(sum_out + row * D + i) = t;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 q = __bfloat1622float2(t.v[j]);
+        f[2 * j] = q.x;
+        f[2 * j + 1] = q.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum<NORM_THREADS>(ss, red);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0) rstd[row] = r;
+  const __nv_bfloat16* src = rr ? sum_out + row * D : xr;
+  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
+    float f[8], g[8];
+    load8(src + i, f);
+    load8(w + i, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
+    store8(y + row * D + i, f);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); optional `dres` is added to dx
+// (gradient arriving on the residual branch). dw partials: each CTA handles
+// ROWS_PER_CTA rows and writes one fp32 partial row.
+constexpr int NORM_BWD_ROWS = 32;
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, long long T, int D) {
+  __shared__ float red[32];
+  // Per-thread dw accumulators for up to 4 column groups (D <= 8192).
+  float dwacc[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[a][j] = 0.f;
+  const long long row0 = static_cast<long long>(blockIdx.x) * NORM_BWD_ROWS;
+  for (int rr = 0; rr < NORM_BWD_ROWS; ++rr) {
+    const long long row = row0 + rr;
+    if (row >= T) break;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
+      float a[8], b[8], c[8];
+      load8(dy + row * D + i, a);
+      load8(x + row * D + i, b);
+      load8(w + i, c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * c[j] * b[j];
+    }
+    dot = block_sum<NORM_THREADS>(dot, red);
+    const float coef = dot * r * r * r / D;
+    int g = 0;
+    for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8, ++g) {
+      float a[8], b[8], c[8], o[8];
+      load8(dy + row * D + i, a);
+      load8(x + row * D + i, b);
+      load8(w + i, c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = a[j] * c[j] * r - b[j] * coef;
+        if (g < 4) dwacc[g][j] += a[j] * b[j] * r;
+      }
+      if (dres) {
+        float e[8];
+        load8(dres + row * D + i, e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += e[j];
+      }
+      store8(dx + row * D + i, o);
+    }
+  }
+  int g = 0;
+  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8, ++g) {
+    if (g < 4) {
+      float* p = dw_partial + static_cast<long long>(blockIdx.x) * D + i;
+      *reinterpret_cast<float4*>(p) = make_float4(dwacc[g][0], dwacc[g][1], dwacc[g][2], dwacc[g][3]);
+      *reinterpret_cast<float4*>(p + 4) =
+          make_float4(dwacc[g][4], dwacc[g][5], dwacc[g][6], dwacc[g][7]);
+    }
+  }
+}
+
+// Column sums of partial[P, D] in a fixed order (deterministic), out bf16 or fp32, optional accumulate.
+__global__ void colsum_kernel(const float* __restrict__ partial, void* __restrict__ out, int P, int D,
+                              int out_fp32, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[static_cast<long long>(p) * D + c];
+  if (out_fp32) {
+    float* o = static_cast<float*>(out);
+    o[c] = accumulate ? o[c] + s : s;
+  } else {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+    o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE
+// Interleaved-pair rotation (x[2i], x[2i+1]) * (cos_i + i sin_i), fp32 math, in
+// place on a [T, H, hd] view with row stride `row_stride` elements. `inverse`
+// rotates by the conjugate (the backward pass). table = [S, hd/2, 2] (cos, sin);
+// position of row t is t % S.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ table,
+                            long long T, int S, int H, int hd, long long row_stride, int inverse) {
+  const int half = hd / 2;
+  const long long total = T * H * (half / 4);  // 4 pairs (8 elements) per thread
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int p4 = idx % (half / 4);
+    const long long th = idx / (half / 4);
+    const int h = th % H;
+    const long long t = th / H;
+    const int pos = t % S;
+    __nv_bfloat16* px = x + t * row_stride + static_cast<long long>(h) * hd + p4 * 8;
+    float f[8];
+    load8(px, f);
+    const float4* tb = reinterpret_cast<const float4*>(table + (static_cast<long long>(pos) * half + p4 * 4) * 2);
+    const float4 cs0 = tb[0], cs1 = tb[1];
+    const float c[4] = {cs0.x, cs0.z, cs1.x, cs1.z};
+    float s[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float sj = inverse ? -s[j] : s[j];
+      o[2 * j] = f[2 * j] * c[j] - f[2 * j + 1] * sj;
+      o[2 * j + 1] = f[2 * j] * sj + f[2 * j + 1] * c[j];
+    }
+    store8(px, o);
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gu = [T, 2F] with gate in columns [0,F) and up in [F,2F); h = silu(gate) * up.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
+                                  long long T, int F) {
+  const long long total = T * (F / 8);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / (F / 8);
+    const int c = (idx % (F / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(h + t * F + c, o);
+  }
+}
+// dgu = [dgate, dup] from dh; written into a [T, 2F] buffer (may alias nothing).
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int F) {
+  const long long total = T * (F / 8);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / (F / 8);
+    const int c = (idx % (F / 8)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+    load8(dh + t * F + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * (sg + silu * (1.f - sg));
+    }
+    store8(dgu + t * 2 * F + c, dg);
+    store8(dgu + t * 2 * F + F + c, du);
+  }
+}
+
+// ------------------------------------------------------------------ cross entropy (forward + backward in one pass)
+// One CTA per row of logits [T, V] (bf16, V % 8 == 0). Writes loss[row] (fp32,
+// 0 for ignored targets) and overwrites the row with
+// dlogits = (softmax - onehot) * grad_scale.
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS)
+cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
+                     float* __restrict__ loss, int V, long long ld, float grad_scale,
+                     long long ignore_index) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long tgt = target[row];
+  float mx = -INFINITY;
+  for (int i = threadIdx.x * 8; i < V; i += CE_THREADS * 8) {
+    float f[8];
+    load8(lr + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+  }
+  mx = block_max<CE_THREADS>(mx, red);
+  float se = 0.f;
+  for (int i = threadIdx.x * 8; i < V; i += CE_THREADS * 8) {
+    float f[8];
+    load8(lr + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+  }
+  se = block_sum<CE_THREADS>(se, red);
+  const bool ignored = (tgt == ignore_index);
+  if (threadIdx.x == 0) {
+    loss[row] = ignored ? 0.f : (logf(se) + mx - __bfloat162float(lr[tgt]));
+  }
+  __syncthreads();
+  const float inv = ignored ? 0.f : grad_scale / se;
+  for (int i = threadIdx.x * 8; i < V; i += CE_THREADS * 8) {
+    float f[8];
+    load8(lr + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - mx) * inv;
+      if (!ignored && i + j == tgt) p -= grad_scale;
+      f[j] = p;
+    }
+    store8(lr + i, f);
+  }
+}
+
+// ------------------------------------------------------------------ AdamW over a flat shard
+// p: fp32 or bf16 master; g: fp32 or bf16; m, v: fp32. Optional `p_lowp`
+// receives the updated parameter as bf16 (the all-gather send buffer when the
+// master is fp32). Matches torch.optim.AdamW (decoupled decay, bias correction,
+// eps added after the sqrt), maximize=False, amsgrad=False.
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2_sqrt, grad_scale;
+};
+template <typename PT, typename GT>
+__global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ p_lowp, long long n,
+                             AdamArgs a) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float pv = static_cast<float>(p[i]);
+    const float gv = static_cast<float>(g[i]) * a.grad_scale;
+    pv *= (1.f - a.lr * a.weight_decay);
+    const float mv = m[i] + (1.f - a.beta1) * (gv - m[i]);           // lerp, as torch does
+    const float vv = a.beta2 * v[i] + (1.f - a.beta2) * gv * gv;
+    m[i] = mv;
+    v[i] = vv;
+    const float denom = sqrtf(vv) / a.bias2_sqrt + a.eps;
+    pv -= (a.lr / a.bias1) * (mv / denom);
+    p[i] = static_cast<PT>(pv);
+    if (p_lowp) p_lowp[i] = __float2bfloat16(pv);
+  }
+}
+
+// ------------------------------------------------------------------ casts
+template <typename ST, typename DT>
+__global__ void cast_scale_kernel(const ST* __restrict__ s, DT* __restrict__ d, long long n, float scale,
+                                  int accumulate) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float f = static_cast<float>(s[i]) * scale;
+    if (accumulate) f += static_cast<float>(d[i]);
+    d[i] = static_cast<DT>(f);
+  }
+}
+
+// ------------------------------------------------------------------ segment gather / cast / zero
+// One descriptor per segment chunk. mode: 0 copy bytes, 1 fp32->bf16,
+// 2 bf16->fp32, 3 zero-fill dst bytes. `n` counts bytes for modes 0/3 and
+// elements for modes 1/2. Descriptors live in device memory.
+struct SegDesc {
+  const void* src;
+  void* dst;
+  long long n;
+  int mode;
+  int pad;
+};
+__global__ void segment_kernel(const SegDesc* __restrict__ descs, int chunks_per_seg) {
+  const SegDesc d = descs[blockIdx.y];
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  (void)chunks_per_seg;
+  if (d.mode == 0 || d.mode == 3) {
+    const uintptr_t sa = reinterpret_cast<uintptr_t>(d.src), da = reinterpret_cast<uintptr_t>(d.dst);
+    uint8_t* dst = static_cast<uint8_t*>(d.dst);
+    const uint8_t* src = static_cast<const uint8_t*>(d.src);
+    const bool zero = d.mode == 3;
+    if (((da | (zero ? 0 : sa)) & 15) == 0) {
+      const long long nv = d.n / 16;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (long long i = tid; i < nv; i += stride)
+        reinterpret_cast<uint4*>(dst)[i] = zero ? z : reinterpret_cast<const uint4*>(src)[i];
+      for (long long i = nv * 16 + tid; i < d.n; i += stride) dst[i] = zero ? 0 : src[i];
+    } else if (((da | (zero ? 0 : sa)) & 3) == 0 && (d.n & 3) == 0) {
+      for (long long i = tid; i < d.n / 4; i += stride)
+        reinterpret_cast<uint32_t*>(dst)[i] = zero ? 0u : reinterpret_cast<const uint32_t*>(src)[i];
+    } else {
+      for (long long i = tid; i < d.n; i += stride) dst[i] = zero ? 0 : src[i];
+    }
+  } else if (d.mode == 1) {
+    const float* src = static_cast<const float*>(d.src);
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(d.dst);
+    for (long long i = tid; i < d.n; i += stride) dst[i] = __float2bfloat16(src[i]);
+  } else {
+    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(d.src);
+    float* dst = static_cast<float*>(d.dst);
+    for (long long i = tid; i < d.n; i += stride) dst[i] = __bfloat162float(src[i]);
+  }
+}
+
+inline int grid_for(long long n, int threads, int per_thread = 1) {
+  long long b = (n + static_cast<long long>(threads) * per_thread - 1) / (static_cast<long long>(threads) * per_thread);
+  if (b < 1) b = 1;
+  if (b > 148 * 16) b = 148 * 16;
+  return static_cast<int>(b);
+}
+inline int launch_ok() { return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH; }
+
+}  // namespace
+
+FSB_API int fsb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out,
+                            float* rstd, long long T, int D, float eps, cudaStream_t stream) {
+  if (D % 8 != 0 || T <= 0) return FSB_ERR_BAD_ARG;
+  rmsnorm_fwd_kernel<<<static_cast<unsigned>(T), NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<__nv_bfloat16*>(sum_out), rstd, D, eps);
+  return launch_ok();
+}
+
+// dw_partial must hold ceil(T/32) * D floats. dw_out: bf16 or fp32 [D].
+FSB_API int fsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                            const void* dres, void* dx, float* dw_partial, void* dw_out,
+                            int dw_fp32, int dw_accumulate, long long T, int D,
+                            cudaStream_t stream) {
+  if (D % 8 != 0 || D > 8192 || T <= 0) return FSB_ERR_BAD_ARG;
+  const int blocks = static_cast<int>((T + NORM_BWD_ROWS - 1) / NORM_BWD_ROWS);
+  rmsnorm_bwd_kernel<<<blocks, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
+      static_cast<__nv_bfloat16*>(dx), dw_partial, T, D);
+  colsum_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dw_partial, dw_out, blocks, D, dw_fp32,
+                                                      dw_accumulate);
+  return launch_ok();
+}
+
+FSB_API int fsb_rope(void* x, const float* table, long long T, int S, int H, int hd,
+                     long long row_stride, int inverse, cudaStream_t stream) {
+  if (hd % 16 != 0 || row_stride % 8 != 0) return FSB_ERR_BAD_ARG;
+  const long long total = T * H * (hd / 16);
+  rope_kernel<<<grid_for(total, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(x), table, T, S,
+                                                        H, hd, row_stride, inverse);
+  return launch_ok();
+}
+
+FSB_API int fsb_swiglu_fwd(const void* gu, void* h, long long T, int F, cudaStream_t stream) {
+  if (F % 8 != 0) return FSB_ERR_BAD_ARG;
+  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), T, F);
+  return launch_ok();
+}
+FSB_API int fsb_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long T, int F,
+                           cudaStream_t stream) {
+  if (F % 8 != 0) return FSB_ERR_BAD_ARG;
+  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh),
+      static_cast<__nv_bfloat16*>(dgu), T, F);
+  return launch_ok();
+}
+
+FSB_API int fsb_cross_entropy(void* logits, const long long* target, float* loss, long long T, int V,
+                              long long ld, float grad_scale, long long ignore_index,
+                              cudaStream_t stream) {
+  if (V % 8 != 0 || ld % 8 != 0) return FSB_ERR_BAD_ARG;
+  cross_entropy_kernel<<<static_cast<unsigned>(T), CE_THREADS, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(logits), target, loss, V, ld, grad_scale, ignore_index);
+  return launch_ok();
+}
+
+// step >= 1. p_fp32 / g_fp32 select the master and gradient dtypes.
+FSB_API int fsb_adamw(void* p, const void* g, float* m, float* v, void* p_lowp, long long n,
+                      int p_fp32, int g_fp32, float lr, float beta1, float beta2, float eps,
+                      float weight_decay, int step, float grad_scale, cudaStream_t stream) {
+  if (n <= 0) return FSB_OK;
+  AdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, static_cast<float>(step));
+  a.bias2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
+  a.grad_scale = grad_scale;
+  const int grid = grid_for(n, 256, 4);
+  __nv_bfloat16* lp = static_cast<__nv_bfloat16*>(p_lowp);
+  if (p_fp32 && g_fp32)
+    adamw_kernel<float, float><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const float*>(g), m, v, lp, n, a);
+  else if (p_fp32)
+    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, a);
+  else if (g_fp32)
+    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const float*>(g), m, v, lp, n, a);
+  else
+    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, a);
+  return launch_ok();
+}
+
+// mode: 1 fp32->bf16, 2 bf16->fp32, 4 fp32->fp32, 5 bf16->bf16 (scale / accumulate variants).
+FSB_API int fsb_cast_scale(const void* src, void* dst, long long n, int mode, float scale,
+                           int accumulate, cudaStream_t stream) {
+  if (n <= 0) return FSB_OK;
+  const int grid = grid_for(n, 256, 4);
+  switch (mode) {
+    case 1: cast_scale_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), n, scale, accumulate); break;
+    case 2: cast_scale_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), n, scale, accumulate); break;
+    case 4: cast_scale_kernel<float, float><<<grid, 256, 0, stream>>>(static_cast<const float*>(src), static_cast<float*>(dst), n, scale, accumulate); break;
+    case 5: cast_scale_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), n, scale, accumulate); break;
+    default: return FSB_ERR_BAD_ARG;
+  }
+  return launch_ok();
+}
+
+// descs: device array of `nseg` SegDesc records (32 bytes: src, dst, n, mode, pad).
+FSB_API int fsb_segment_op(const void* descs, int nseg, int blocks_per_seg, cudaStream_t stream) {
+  if (nseg <= 0) return FSB_OK;
+  if (nseg > 65535) return FSB_ERR_TOO_LARGE;
+  if (blocks_per_seg < 1) blocks_per_seg = 1;
+  dim3 grid(blocks_per_seg, nseg);
+  segment_kernel<<<grid, 256, 0, stream>>>(static_cast<const SegDesc*>(descs), blocks_per_seg);
+  return launch_ok();
+}

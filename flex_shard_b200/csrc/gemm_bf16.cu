@@ -1,0 +1,379 @@
+// Persistent bf16 GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma
+// issued by one thread, fp32 accumulators double-buffered in TMEM, epilogue
+// warps draining one accumulator while the tensor core fills the other.
+//
+//   D[M,N] = alpha * (A[M,K] . B[N,K]^T) + beta * C[M,N]  (+ D when accumulate)
+//
+// A and B may each be stored K-major (row = M/N index, K contiguous) or
+// MN-major (row = K index, M/N contiguous), which covers the three GEMMs of a
+// linear layer without a transpose pass:
+//   forward  y  = x W^T   : A = x  (K-major),  B = W  (K-major)
+//   dgrad    dx = dy W    : A = dy (K-major),  B = W  (MN-major)
+//   wgrad    dW = dy^T x  : A = dy (MN-major), B = x  (MN-major)
+// D and C are row-major, bf16 or fp32.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
+// issuer, warps 2..5 = epilogue (one TMEM lane quarter each).
+#include "common.cuh"
+
+namespace {
+
+using namespace fsb;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int TMEM_COLS = 512;              // two 256-column accumulators
+constexpr int GROUP_M = 8;                  // tile rasterisation group
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct GemmArgs {
+  int M, N, K;
+  int a_mn, b_mn;
+  void* d;
+  long long ldd;
+  int d_fp32;
+  const void* c;
+  long long ldc;
+  int c_fp32;
+  float alpha, beta;
+  int accumulate;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = min(tiles_m - first_m, GROUP_M);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (args.M + BM - 1) / BM;
+  const int tiles_n = (args.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!args.a_mn) {
+            tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &map_a, &full_bar[s], m0 + 64 * j, k0);
+          }
+          if (!args.b_mn) {
+            tma_load_2d(sb, &map_b, &full_bar[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &map_b, &full_bar[s], n0 + 64 * j, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN, 1, 1, args.a_mn ? 1u : 0u, args.b_mn ? 1u : 0u);
+      // K-major: 8-row groups 1024 B apart, K step of 16 elements = 32 B inside the atom.
+      // MN-major: 64-wide MN groups 8192 B apart (LBO), 8-deep K groups 1024 B apart (SBO),
+      //           K step of 16 = two K groups = 2048 B.
+      const uint32_t a_lbo = args.a_mn ? 8192u : 16u, b_lbo = args.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = args.a_mn ? 2048u : 32u, b_kstep = args.b_mn ? 2048u : 32u;
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
+          atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
+        if (lane == 0) {
+          atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = tn * BN + c0;
+        if (col >= args.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
+          const bool full = (col + 32 <= args.N);
+          if (args.c != nullptr) {
+            if (args.c_fp32) {
+              const float* cp = static_cast<const float*>(args.c) + row * args.ldc + col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (full || col + i < args.N) v[i] += args.beta * cp[i];
+            } else {
+              const __nv_bfloat16* cp =
+                  static_cast<const __nv_bfloat16*>(args.c) + row * args.ldc + col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (full || col + i < args.N) v[i] += args.beta * __bfloat162float(cp[i]);
+            }
+          }
+          if (args.d_fp32) {
+            float* dp = static_cast<float*>(args.d) + row * args.ldd + col;
+            if (full && (args.ldd % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (args.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dp + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dp + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col + i < args.N) dp[i] = args.accumulate ? dp[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(args.d) + row * args.ldd + col;
+            if (full && (args.ldd % 8 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                if (args.accumulate) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(dp + i);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(ob[j]);
+                    v[i + 2 * j] += f.x;
+                    v[i + 2 * j + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[i], v[i + 1]);
+                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(dp + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col + i < args.N) {
+                  const float o = args.accumulate ? __bfloat162float(dp[i]) + v[i] : v[i];
+                  dp[i] = __float2bfloat16(o);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // Common exit: every loop above is bounded, so all warps arrive here.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // Give copies that were already issued time to land before the CTA's
+      // shared memory and TMEM go away.
+      const unsigned long long t0 = clock64();
+      while (clock64() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int g_num_sms = 0;
+
+}  // namespace
+
+FsbEncodeTiledFn fsb_get_encode_tiled() {
+  static FsbEncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<FsbEncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+int fsb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_size,
+                     uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t box_cols) {
+  FsbEncodeTiledFn enc = fsb_get_encode_tiled();
+  if (enc == nullptr) return FSB_ERR_TMA_ENCODE;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_size) % 16 != 0)
+    return FSB_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_size)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FSB_OK : FSB_ERR_TMA_ENCODE;
+}
+
+// D = alpha * A.B^T + beta * C (+ D). Shapes in elements; see the header comment
+// for the meaning of a_mn / b_mn. `status` is a device int the kernel writes an
+// error code to when a bounded wait runs out (left untouched otherwise).
+FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
+                          long long lda, long long ldb, long long ldd, long long ldc, int a_mn,
+                          int b_mn, int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
+                          int* status, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
+  CUtensorMap map_a, map_b;
+  int rc;
+  if (!a_mn) {
+    rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  } else {
+    rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
+  }
+  if (rc != FSB_OK) return rc;
+  if (!b_mn) {
+    rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  } else {
+    rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  }
+  if (rc != FSB_OK) return rc;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess)
+      return FSB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate, status};
+  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args);
+  return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}

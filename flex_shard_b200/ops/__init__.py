@@ -1,0 +1,4 @@
+"""Hand-written sm_100a kernels (through a C ABI) and their autograd wrappers."""
+from . import _lib
+from ._lib import NativeError, available, check_status
+from .gemm import gemm, linear

@@ -1,0 +1,132 @@
+"""Loader for the native sm_100a library (``flex_shard_b200/lib/libfsb200.so``).
+
+The library exposes a C ABI; Python passes raw device pointers and the current
+CUDA stream. On a machine with a GPU a missing library is an error (the ops do
+not fall back to PyTorch silently); on a CPU-only machine ``available()`` is
+False and callers use their CPU reference paths.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libfsb200.so"
+_lib = None
+_lock = threading.Lock()
+_status: dict[int, torch.Tensor] = {}
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "bad argument",
+    2: "TMA descriptor encode failed",
+    3: "kernel launch failed",
+    16: "timeout waiting for a TMA stage",
+    17: "timeout waiting for a free stage",
+    18: "timeout waiting for a TMEM accumulator",
+    19: "timeout waiting for a free TMEM accumulator",
+    32: "timeout waiting for a peer signal",
+    64: "size beyond the supported maximum",
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load(required: bool = True):
+    """Return the ctypes handle of the native library, building it if asked by env."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not _LIB_PATH.exists() and os.environ.get("FSB200_BUILD_ON_IMPORT", "0") == "1":
+            from ..csrc.build import build
+
+            build()
+        if not _LIB_PATH.exists():
+            if required:
+                raise NativeError(
+                    f"native library {_LIB_PATH} is missing; run "
+                    "`python -m flex_shard_b200.csrc.build`"
+                )
+            return None
+        _lib = ctypes.CDLL(str(_LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def available() -> bool:
+    """True when CUDA kernels can run: a GPU is visible and the library loads."""
+    if not torch.cuda.is_available():
+        return False
+    return load(required=True) is not None
+
+
+def _declare(lib) -> None:
+    c = ctypes
+    vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+    sigs = {
+        "fsb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32,
+                          f32, f32, i32, vp, i32, vp],
+        "fsb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
+        "fsb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, vp],
+        "fsb_rope": [vp, vp, i64, i32, i32, i32, i64, i32, vp],
+        "fsb_swiglu_fwd": [vp, vp, i64, i32, vp],
+        "fsb_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
+        "fsb_cross_entropy": [vp, vp, vp, i64, i32, i64, f32, i64, vp],
+        "fsb_adamw": [vp, vp, vp, vp, vp, i64, i32, i32, f32, f32, f32, f32, f32, i32, f32, vp],
+        "fsb_cast_scale": [vp, vp, i64, i32, f32, i32, vp],
+        "fsb_segment_op": [vp, i32, i32, vp],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = c.c_int
+
+
+def declare(name: str, argtypes) -> None:
+    """Register the signature of a symbol added by a later source file."""
+    fn = getattr(load(), name)
+    fn.argtypes = argtypes
+    fn.restype = ctypes.c_int
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels write an error code to when a bounded wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a failed wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    t = status_word(dev)
+    code = int(t.item())
+    if code != 0:
+        t.zero_()
+        raise NativeError(f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what}: {STATUS_NAMES.get(rc, rc)} (code {rc})")

@@ -1,0 +1,108 @@
+"""bf16 tcgen05 GEMM and the linear-layer autograd function built on it.
+
+``gemm`` computes ``D = alpha * A @ B^T + beta * C (+ D)`` where A is
+``[M, K]`` and B is ``[N, K]`` logically; each may be handed over transposed
+in memory (``a_t`` / ``b_t``: the tensor passed is ``[K, M]`` / ``[K, N]``),
+which the kernel reads as an MN-major operand, so a linear layer's forward,
+dgrad and wgrad all run without a transpose copy.
+
+CPU tensors take a PyTorch fp32 reference path (used by the CPU test-suite).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+launch_count = 0  # native kernel launches issued through this package (all ops add to it)
+
+
+def count_launch(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    if t.stride(-1) != 1 or (t.dim() == 2 and t.stride(0) % 8 != 0) or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         c: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 1.0,
+         accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """``out = alpha * A @ B^T + beta * c (+ out)`` with bf16 operands, fp32 accumulation."""
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_t else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_t else b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    if not a.is_cuda:
+        af = (a.t() if a_t else a).float()
+        bf = (b.t() if b_t else b).float()
+        r = alpha * (af @ bf.t())
+        if c is not None:
+            r = r + beta * c.float()
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r)
+        return out
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    a = _rowmajor(a)
+    b = _rowmajor(b)
+    if c is not None:
+        assert c.shape == (M, N) and c.stride(1) == 1 and c.dtype in (torch.bfloat16, torch.float32)
+    if K % 8 != 0 or (a_t and M % 8 != 0) or (b_t and N % 8 != 0):
+        raise ValueError("gemm: K (and the contiguous dim of transposed operands) must be a multiple of 8")
+    lib = _lib.load()
+    status = _lib.status_word(a.device)
+    rc = lib.fsb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), c.data_ptr() if c is not None else None,
+        M, N, K, a.stride(0), b.stride(0), out.stride(0), c.stride(0) if c is not None else 0,
+        int(a_t), int(b_t), int(out.dtype == torch.float32),
+        int(c is not None and c.dtype == torch.float32), alpha, beta, int(accumulate),
+        status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
+    _lib.check(rc, "fsb_gemm_bf16")
+    count_launch()
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T on the tcgen05 GEMM; wgrad may accumulate straight into an fp32 buffer."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_t=True).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "main_grad", None)
+            if main is not None and main.dtype == torch.float32:
+                # Megatron-style: accumulate the weight gradient into the fp32 bucket view in
+                # the GEMM epilogue and hand autograd nothing to cast or add.
+                gemm(dy2, x2, a_t=True, b_t=True, out=main, accumulate=True)
+                weight.main_grad_written = True
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_t=True, b_t=True, out_dtype=weight.dtype
+                          if weight.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return _Linear.apply(x, weight)
