@@ -1,0 +1,596 @@
+"""The bucket runtime: hooks, prefetch, streams and the autograd choreography.
+
+Per root module one ``BucketCommContext`` (streams, learned orders, pending
+reductions) and per bucket one ``BucketRuntime``. Forward: the pre-forward hook
+gathers the bucket (consuming a prefetch if one is in flight), swaps the
+persistent unsharded ``nn.Parameter`` objects into the module and prefetches the
+next bucket; the post-forward hook registers backward hooks and reshards.
+Backward: a tensor hook on the outputs re-gathers, an identity autograd function
+on the inputs fires the post-backward step (take grads -> reshard -> reduce on
+the reduce stream -> accumulate into the sharded ``.grad``), and an engine
+callback drains the reductions at the end of backward.
+
+Parity: behaviour of ``flex_shard/bucket_runtime.py:210-1546`` of the reference
+(context, runtime, hooks, learned and explicit prefetch, persistent unsharded
+parameters with storage freed on reshard, no-sync accumulation, manual
+finalization, error poisoning after a raised backward).
+"""
+from __future__ import annotations
+
+import weakref
+from typing import Any, Sequence
+
+import torch
+import torch.nn as nn
+from torch.autograd import Variable
+from torch.utils._pytree import tree_flatten, tree_unflatten
+
+from .bucket_comm import (
+    PendingReduce,
+    PendingUnshard,
+    StreamHandoff,
+    begin_bucket_unshard,
+    begin_explicit_bucket_unshard,
+    begin_reduce_grad,
+)
+from .bucket_storage import ShardedBucketStorage
+from .utils.profiling import record
+
+
+def _in_backward() -> bool:
+    return torch._C._current_graph_task_id() != -1
+
+
+class BucketCommContext:
+    """State shared by the buckets of one root module."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            # high priority so collectives are not starved by queued compute kernels
+            self.unshard_stream = torch.cuda.Stream(device=device, priority=-1)
+            self.reduce_stream = torch.cuda.Stream(device=device, priority=-1)
+        else:
+            self.unshard_stream = None
+            self.reduce_stream = None
+        self.runtimes: list["BucketRuntime"] = []
+        self.forward_order: list["BucketRuntime"] = []
+        self.post_forward_order: list["BucketRuntime"] = []
+        self.learned = False
+        self.pending_reduces: list[PendingReduce] = []
+        self.max_pending_reduce_grads = 1
+        self.manual_finalization = False
+        self.backward_running = False
+        self.callback_queued = False
+        self.poisoned = False
+        self.pending_finalize_handle = None
+        self.stats = {"unshards": 0, "prefetch_hits": 0, "reduces": 0}
+
+    # ------------------------------------------------------------------ learned orders
+    def note_forward(self, rt: "BucketRuntime") -> None:
+        if not self.learned and rt not in self.forward_order:
+            self.forward_order.append(rt)
+
+    def note_post_forward(self, rt: "BucketRuntime") -> None:
+        if not self.learned:
+            if rt in self.post_forward_order:
+                self.post_forward_order.remove(rt)
+            self.post_forward_order.append(rt)
+
+    def next_forward_bucket(self, rt):
+        if rt in self.forward_order:
+            i = self.forward_order.index(rt)
+            if i + 1 < len(self.forward_order):
+                return self.forward_order[i + 1]
+        return None
+
+    def next_backward_bucket(self, rt):
+        order = self.post_forward_order
+        if rt in order:
+            i = order.index(rt)
+            if i - 1 >= 0:
+                return order[i - 1]
+        return None
+
+    # ------------------------------------------------------------------ reductions
+    def drain_reduces(self, keep: int = 0) -> None:
+        """Wait for (all but ``keep``) pending reductions on the current stream and release
+        their send buffers."""
+        while len(self.pending_reduces) > keep:
+            st = self.pending_reduces.pop(0)
+            if st.event is not None:
+                with record("FlexShard::post_backward_reduce_grad_wait"):
+                    torch.cuda.current_stream().wait_event(st.event)
+            st.keep.clear()
+
+    # ------------------------------------------------------------------ end of backward
+    def queue_final_callback(self) -> None:
+        if self.callback_queued:
+            return
+        self.callback_queued = True
+        self.backward_running = True
+        Variable._execution_engine.queue_callback(self._final_callback)
+
+    def _final_callback(self) -> None:
+        try:
+            if not self.manual_finalization:
+                for rt in reversed(self.post_forward_order or self.runtimes):
+                    rt.finish_backward()
+                for rt in self.runtimes:
+                    if rt not in self.post_forward_order:
+                        rt.finish_backward()
+                self.drain_reduces(0)
+            else:
+                for rt in self.runtimes:
+                    rt.end_of_backward_without_finalize()
+            for rt in self.runtimes:
+                rt.release_unused_prefetch()
+            if self.forward_order:
+                self.learned = True
+        finally:
+            self.callback_queued = False
+            self.backward_running = False
+            for rt in self.runtimes:
+                rt.reset_backward_state()
+
+    def check_not_poisoned(self) -> None:
+        if self.backward_running and not _in_backward():
+            self.poisoned = True
+        if self.poisoned:
+            raise RuntimeError(
+                "FlexShard: a previous backward raised before its gradient reduction finished; "
+                "the runtime state is not recoverable.")
+
+    def idle(self) -> bool:
+        return (not self.pending_reduces and not self.backward_running
+                and all(rt.pending is None for rt in self.runtimes))
+
+
+class _PostBackwardTrigger(torch.autograd.Function):
+    """Identity on a module's inputs; its backward runs after the module's parameter grads are
+    accumulated (AccumulateGrad nodes run as soon as they are ready), so it marks the end of the
+    bucket's backward."""
+
+    @staticmethod
+    def forward(ctx, rt_ref, *inputs):
+        ctx.rt_ref = rt_ref
+        return inputs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        rt = ctx.rt_ref()
+        if rt is not None:
+            rt.on_input_grads()
+        return (None, *grads)
+
+
+class BucketRuntime:
+    def __init__(self, storage: ShardedBucketStorage, context: BucketCommContext,
+                 modules: Sequence[nn.Module], is_group: bool):
+        self.storage = storage
+        self.context = context
+        self.modules = list(modules)
+        self.is_group = is_group or len(self.modules) > 1
+        storage.runtime = self
+        context.runtimes.append(self)
+        self.is_unsharded = False
+        self.unsharded_params: list[nn.Parameter] | None = None
+        self.persistent: list[torch.Tensor] | None = None
+        self.pending: PendingUnshard | None = None
+        self.keepalive: list = []
+        self._forwards_in_pass = 0     # member-module forwards since the last reshard
+        self._triggers_registered = 0
+        self._triggers_fired = 0
+        self._pre_backward_done = False
+        self._post_backward_done = False
+        self.needs_sync = False        # holds unreduced unsharded grads (no-sync accumulation)
+        self.deferred_params: set[int] = set()
+        self._handles: list = []
+
+    # ------------------------------------------------------------------ persistent unsharded params
+    def _alloc_persistent(self) -> list[torch.Tensor]:
+        st = self.storage
+        W = st.comm.world_size
+        if self.persistent is None:
+            self.persistent = []
+            for info in st.infos:
+                n = info.placement.unsharded_buffer_numel(info, W)
+                self.persistent.append(torch.empty(n, dtype=info.param_dtype, device=st.device))
+        else:
+            for info, buf in zip(st.infos, self.persistent):
+                n = info.placement.unsharded_buffer_numel(info, W)
+                nbytes = n * info.param_dtype.itemsize
+                if buf.untyped_storage().size() != nbytes:
+                    buf.untyped_storage().resize_(nbytes)
+        return self.persistent
+
+    def _free_persistent(self) -> None:
+        if self.persistent is None:
+            return
+        shared = getattr(self.storage.placement, "persistent_aliases_storage", False)
+        if shared:
+            return
+        for buf in self.persistent:
+            buf.untyped_storage().resize_(0)
+
+    def _create_unsharded_params(self, tensors: list[torch.Tensor]) -> None:
+        self.unsharded_params = []
+        for info, t, sp in zip(self.storage.infos, tensors, self.storage.sharded_params):
+            up = nn.Parameter(t, requires_grad=sp.requires_grad)
+            for k, v in info.param_attrs.items():
+                try:
+                    setattr(up, k, v)
+                except Exception:
+                    pass
+            up._fsb_sharded = weakref.ref(sp)
+            up._fsb_storage = self.storage
+            self.unsharded_params.append(up)
+
+    # ------------------------------------------------------------------ unshard / reshard
+    def begin_unshard(self, prefetch: bool = False) -> None:
+        if self.is_unsharded or self.pending is not None:
+            return
+        st = self.storage
+        persistent = None
+        if not st.placement.refills_persistent_buffers_in_finish:
+            persistent = self._alloc_persistent()
+        stream = self.context.unshard_stream
+        self.pending = begin_bucket_unshard(st, persistent, stream)
+        self.context.stats["unshards"] += 1
+
+    def finish_unshard(self) -> None:
+        p = self.pending
+        assert p is not None
+        self.pending = None
+        st = self.storage
+        if p.event is not None:
+            torch.cuda.current_stream().wait_event(p.event)
+        persistent = self._alloc_persistent()
+        # Refilling the persistent buffers must not look like an in-place edit to autograd: the
+        # tensors saved by the forward are these very buffers, re-gathered with the same values.
+        with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(tuple(persistent)):
+            res = st.placement.finish_prepared_unshard(p.prepared, st.comm, persistent)
+        if self.unsharded_params is None:
+            self._create_unsharded_params(res.tensors)
+        else:
+            # refresh requires_grad from the sharded parameters (freezing after wrap takes effect here)
+            for up, sp in zip(self.unsharded_params, st.sharded_params):
+                if up.requires_grad != sp.requires_grad and up.grad_fn is None:
+                    up.requires_grad_(sp.requires_grad)
+        keep = list(res.keepalive)
+        if p.prepared.recv is not None:
+            keep.append(p.prepared.recv)
+        StreamHandoff.release_after_current_stream(keep, p.stream)
+        self.is_unsharded = True
+
+    def unshard(self) -> None:
+        if self.is_unsharded:
+            return
+        if self.pending is not None:
+            self.context.stats["prefetch_hits"] += 1
+        else:
+            self.begin_unshard()
+        self.finish_unshard()
+
+    def explicit_unshard(self, async_op: bool = False):
+        if _in_backward():
+            raise RuntimeError("unshard() cannot run in backward; the runtime gathers buckets itself there.")
+        self.context.check_not_poisoned()
+        if self.is_unsharded:
+            return _UnshardHandle([])
+        if self.pending is None:
+            st = self.storage
+            persistent = None
+            if not st.placement.refills_persistent_buffers_in_finish:
+                persistent = self._alloc_persistent()
+            self.pending = begin_explicit_bucket_unshard(st, persistent, async_op)
+            self.context.stats["unshards"] += 1
+        handle = _UnshardHandle([self])
+        if not async_op:
+            handle.wait()
+        return handle
+
+    def swap_in_unsharded(self) -> None:
+        for up, slots in zip(self.unsharded_params, self.storage.param_slots):
+            for mod, attr in slots:
+                mod._parameters[attr] = up
+
+    def swap_in_sharded(self) -> None:
+        for sp, slots in zip(self.storage.sharded_params, self.storage.param_slots):
+            for mod, attr in slots:
+                mod._parameters[attr] = sp
+
+    def reshard(self) -> None:
+        if self.pending is not None and not self.is_unsharded:
+            self.release_unused_prefetch()
+        if not self.is_unsharded:
+            return
+        self.swap_in_sharded()
+        self._free_persistent()
+        self.is_unsharded = False
+        self._forwards_in_pass = 0
+
+    def release_unused_prefetch(self) -> None:
+        """Drop a prefetched gather that nothing consumed (its buffers return to the allocator)."""
+        p = self.pending
+        if p is None or self.is_unsharded:
+            return
+        with record("FlexShard::release_unused_prefetch"):
+            self.pending = None
+            if p.event is not None:
+                torch.cuda.current_stream().wait_event(p.event)
+            if p.prepared.work is not None:
+                p.prepared.work.wait()
+            self._free_persistent()
+
+    # ------------------------------------------------------------------ prefetch
+    def _prefetch(self, forward: bool) -> None:
+        st = self.storage
+        explicit = st.forward_prefetch if forward else st.backward_prefetch
+        if explicit is not None:
+            for other in explicit:
+                other.runtime.begin_unshard(prefetch=True)
+            return
+        ctx = self.context
+        if not ctx.learned:
+            return
+        nxt = ctx.next_forward_bucket(self) if forward else ctx.next_backward_bucket(self)
+        if nxt is not None and not nxt.is_unsharded:
+            nxt.begin_unshard(prefetch=True)
+
+    # ------------------------------------------------------------------ hooks
+    def pre_forward(self, module, args, kwargs):
+        ctx = self.context
+        ctx.check_not_poisoned()
+        in_bwd = _in_backward()
+        with record("FlexShard::pre_forward", self.storage.name):
+            if not in_bwd:
+                ctx.note_forward(self)
+            self.unshard()
+            self.swap_in_unsharded()
+            if not in_bwd:
+                self._prefetch(forward=True)
+        self._forwards_in_pass += 1
+        if torch.is_grad_enabled() and not (in_bwd and self._triggers_registered > 0):
+            flat, spec = tree_flatten((args, kwargs))
+            idx = [i for i, t in enumerate(flat) if isinstance(t, torch.Tensor) and t.requires_grad]
+            if idx:
+                outs = _PostBackwardTrigger.apply(weakref.ref(self), *[flat[i] for i in idx])
+                for i, o in zip(idx, outs):
+                    flat[i] = o
+                self._triggers_registered += 1
+                args, kwargs = tree_unflatten(flat, spec)
+        return args, kwargs
+
+    def post_forward(self, module, args, output):
+        ctx = self.context
+        in_bwd = _in_backward()
+        if not in_bwd:
+            ctx.note_post_forward(self)
+        if torch.is_grad_enabled():
+            flat, _ = tree_flatten(output)
+            for t in flat:
+                if isinstance(t, torch.Tensor) and t.requires_grad:
+                    t.register_hook(self._make_pre_backward_hook())
+        if in_bwd:
+            return output  # recompute inside backward: stay gathered until post-backward
+        all_ran = (not self.is_group) or self._forwards_in_pass >= len(self.modules)
+        if self.storage.reshard_after_forward and all_ran:
+            self.reshard()
+        return output
+
+    def _make_pre_backward_hook(self):
+        ref = weakref.ref(self)
+
+        def hook(grad):
+            rt = ref()
+            if rt is not None:
+                rt.pre_backward()
+            return grad
+
+        return hook
+
+    def pre_backward(self) -> None:
+        ctx = self.context
+        ctx.queue_final_callback()
+        if self._pre_backward_done:
+            return
+        self._pre_backward_done = True
+        self._post_backward_done = False
+        with record("FlexShard::pre_backward", self.storage.name):
+            self.unshard()
+            self.swap_in_unsharded()
+            hook = self.storage.spec.pre_backward_hook
+            if hook is not None:
+                hook(self.storage)
+            elif self.storage.placement.reduces_grads_in_param_layout(self.storage.infos):
+                from .utils.validation import alloc_grads_in_param_layout
+
+                alloc_grads_in_param_layout(self.storage)
+            self._prefetch(forward=False)
+
+    def on_input_grads(self) -> None:
+        self._triggers_fired += 1
+        if self._triggers_fired >= self._triggers_registered and not self.storage.spec.defer_post_backward:
+            self.post_backward()
+
+    def finish_deferred(self, param) -> None:
+        self.deferred_params.add(id(param))
+        if len(self.deferred_params) >= len([p for p in self.storage.sharded_params if p.requires_grad]):
+            self.deferred_params.clear()
+            self.post_backward()
+            self.context.drain_reduces(0)
+
+    # ------------------------------------------------------------------ post-backward
+    def _take_grads(self) -> list[torch.Tensor] | None:
+        grads = []
+        any_grad = False
+        for info, up in zip(self.storage.infos, self.unsharded_params):
+            if not info.requires_grad or not up.requires_grad:
+                continue
+            g = up.grad
+            mg = getattr(up, "main_grad", None)
+            if g is None and mg is not None and getattr(up, "main_grad_written", False):
+                g = mg
+                up.main_grad_written = False
+            if g is not None:
+                any_grad = True
+            grads.append(g)
+            up.grad = None
+        if not any_grad and self.storage.spec.fsdp2_compatible:
+            return None
+        out = []
+        trainable = [(i, u) for i, u in zip(self.storage.infos, self.unsharded_params)
+                     if i.requires_grad and u.requires_grad]
+        for (info, up), g in zip(trainable, grads):
+            if g is None:
+                g = torch.zeros(info.global_shape, dtype=info.param_dtype, device=self.storage.device)
+            if info.partial_grad_group is not None:
+                torch.distributed.all_reduce(g, group=info.partial_grad_group)
+            out.append(g)
+        return out
+
+    def post_backward(self) -> None:
+        if self._post_backward_done or self.unsharded_params is None:
+            return
+        st = self.storage
+        ctx = self.context
+        self._post_backward_done = True
+        with record("FlexShard::post_backward_reduce", st.name):
+            if not st.requires_gradient_sync or ctx.manual_finalization:
+                self.needs_sync = True
+                if st.reshard_after_backward:
+                    self.reshard()
+                return
+            self._reduce_now()
+
+    def _reduce_now(self) -> None:
+        st = self.storage
+        ctx = self.context
+        if not self.is_unsharded and self.unsharded_params is None:
+            return
+        grads = self._take_grads()
+        hook = st.spec.post_reduce_hook
+        if st.reshard_after_backward:
+            self.reshard()
+        self.needs_sync = False
+        if grads is None or not grads:
+            if hook is not None:
+                hook(st)
+            return
+        reduce_dtype = st.bucket_reduce_dtype
+        for g in grads:
+            reduce_dtype = torch.promote_types(reduce_dtype, g.dtype) if st.spec.mp_policy.reduce_dtype is None else reduce_dtype
+        ctx.drain_reduces(max(ctx.max_pending_reduce_grads - 1, 0))
+        stream = ctx.reduce_stream if st.reduce_comm.world_size > 1 else None
+        st.infos_for_reduce = [i for i, u in zip(st.infos, self.unsharded_params) if i.requires_grad and u.requires_grad]
+        state = begin_reduce_grad(self, grads, reduce_dtype, st.reduction, stream)
+        ctx.stats["reduces"] += 1
+        ctx.pending_reduces.append(state)
+        if hook is not None:
+            hook(st)
+
+    def accumulate_sharded_grads(self, result) -> None:
+        st = self.storage
+        with record("FlexShard::reduce_grad_accumulate", st.name):
+            sps = [sp for sp, i, u in zip(st.sharded_params, st.infos, self.unsharded_params)
+                   if i.requires_grad and u.requires_grad]
+            for sp, g in zip(sps, result.grads):
+                if g is None:
+                    continue
+                info = sp._fsb_info
+                gd = info.grad_dtype or sp.dtype
+                if sp.grad is None:
+                    sp.grad = g if g.dtype == gd else g.to(gd)
+                else:
+                    sp.grad.add_(g.to(sp.grad.dtype) if g.dtype != sp.grad.dtype else g)
+
+    def finish_backward(self) -> None:
+        """End of backward: run the post-backward step if its trigger never fired (inputs that
+        do not require grad) and the bucket took part in this backward."""
+        if self._pre_backward_done and not self._post_backward_done:
+            if self.storage.spec.defer_post_backward and self.storage.requires_gradient_sync:
+                raise RuntimeError(
+                    f"bucket {self.storage.name!r} has defer_post_backward=True but its backward ended "
+                    "without finish_deferred_backward() for every parameter")
+            self.post_backward()
+
+    def end_of_backward_without_finalize(self) -> None:
+        if self._pre_backward_done and not self._post_backward_done:
+            self._post_backward_done = True
+            self.needs_sync = True
+            if self.storage.reshard_after_backward:
+                self.reshard()
+
+    def reset_backward_state(self) -> None:
+        self._pre_backward_done = False
+        self._post_backward_done = False
+        self._triggers_registered = 0
+        self._triggers_fired = 0
+
+    def finalize(self) -> None:
+        """Reduce gradients accumulated by no-sync / manual-finalization backwards."""
+        if not self.needs_sync or self.unsharded_params is None:
+            return
+        self._reduce_now()
+
+
+class _UnshardHandle:
+    def __init__(self, runtimes):
+        self.runtimes = runtimes
+
+    def wait(self) -> None:
+        for rt in self.runtimes:
+            if rt.pending is not None and not rt.is_unsharded:
+                rt.finish_unshard()
+                rt.swap_in_unsharded()
+        self.runtimes = []
+
+
+class ModuleUnshardHandle(_UnshardHandle):
+    pass
+
+
+class GradientReductionHandle:
+    def __init__(self, context: BucketCommContext):
+        self.context = context
+        self.done = False
+
+    def wait(self) -> None:
+        if not self.done:
+            self.context.drain_reduces(0)
+            self.context.pending_finalize_handle = None
+            self.done = True
+
+
+# --------------------------------------------------------------------------- installation
+def install_bucket_hooks(root: nn.Module, storages: list[ShardedBucketStorage],
+                         hook_modules: list[tuple[list[nn.Module], bool]],
+                         context: BucketCommContext | None = None) -> BucketCommContext:
+    device = storages[0].device if storages else torch.device("cpu")
+    ctx = context or BucketCommContext(device)
+    for st, (mods, is_group) in zip(storages, hook_modules):
+        rt = BucketRuntime(st, ctx, mods, is_group)
+        st.modules = list(mods)
+        for m in mods:
+            rt._handles.append(m.register_forward_pre_hook(rt.pre_forward, with_kwargs=True, prepend=True))
+            rt._handles.append(m.register_forward_hook(rt.post_forward, prepend=False))
+
+    def root_post_forward(module, args, output):
+        if _in_backward():
+            return output
+        for rt in ctx.runtimes:
+            if rt.is_group and rt.is_unsharded and rt.storage.reshard_after_forward and rt._forwards_in_pass > 0:
+                rt.reshard()
+        return output
+
+    root.register_forward_hook(root_post_forward, prepend=False)
+
+    def state_dict_pre_hook(module, prefix, keep_vars):
+        for rt in ctx.runtimes:
+            rt.reshard()
+
+    root.register_state_dict_pre_hook(state_dict_pre_hook)
+    root._register_load_state_dict_pre_hook(lambda *a, **k: [rt.reshard() for rt in ctx.runtimes] and None)
+    return ctx

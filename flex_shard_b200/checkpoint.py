@@ -1,0 +1,224 @@
+"""Sharded checkpoints: layout tagging plus a save/load that reshards by global offset.
+
+Every tensor of a flex_shard ``state_dict()`` is a plain local shard. Tagging it
+with its ``GlobalLayout`` (placement layout composed with any outer TP/EP layout)
+makes a checkpoint loadable at another world size or under another placement:
+``save`` writes each rank's tagged tensors to ``rank{r}.pt`` and ``load`` fills
+every local box from whichever files overlap it.
+
+Parity: ``flex_shard/checkpoint.py:26-161`` of the reference (the three public
+helpers, Adam/AdamW optimizer hook, ``step`` left untagged). The reference hands
+the tagged tensors to ``torch.distributed.checkpoint``; the installed PyTorch has
+no ``CheckpointableTensor`` protocol, so the file format and the resharding reader
+live here.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Mapping
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .placement_contract import GlobalLayout, get_global_layout, set_global_layout
+from .sharded_param import is_flex_shard_param
+
+_ADAM_STATE_KEYS = ("exp_avg", "exp_avg_sq", "max_exp_avg_sq")
+
+
+def get_flex_shard_global_layouts(module: nn.Module) -> dict[str, GlobalLayout]:
+    """FQN -> layout for every managed parameter, including the extra names of tied weights."""
+    out: dict[str, GlobalLayout] = {}
+    for st in module.sharded_bucket_storages:
+        for info in st.infos:
+            lay = st.global_layout_of(info)
+            out[info.fqn] = lay
+            for other in info.shared_fqns:
+                out[other] = lay
+    return out
+
+
+def set_state_dict_global_layouts(module: nn.Module, state_dict: Mapping[str, Any]) -> None:
+    """Tag the tensors of ``module.state_dict()`` with their layouts (attributes do not survive a
+    copy such as ``.to(dtype)``: tag again afterwards)."""
+    layouts = get_flex_shard_global_layouts(module)
+    for k, v in state_dict.items():
+        if isinstance(v, torch.Tensor) and k in layouts:
+            set_global_layout(v, layouts[k])
+
+
+def register_optimizer_checkpoint_hook(optimizer: torch.optim.Optimizer, module: nn.Module):
+    """Tag Adam/AdamW state tensors in ``optimizer.state_dict()`` with their parameter's layout.
+    ``step`` stays untagged (replicated)."""
+    if not isinstance(optimizer, (torch.optim.Adam, torch.optim.AdamW)) and not getattr(
+            optimizer, "_fsb_adam_like", False):
+        raise ValueError("register_optimizer_checkpoint_hook supports Adam and AdamW only")
+    if getattr(optimizer, "_fsb_ckpt_hook", None) is not None:
+        raise ValueError("optimizer already has a flex_shard checkpoint hook")
+    layouts_by_param: dict[int, GlobalLayout] = {}
+    for st in module.sharded_bucket_storages:
+        for info, sp in zip(st.infos, st.sharded_params):
+            layouts_by_param[id(sp)] = st.global_layout_of(info)
+    managed = [p for g in optimizer.param_groups for p in g["params"]]
+    if not any(id(p) in layouts_by_param for p in managed):
+        raise ValueError("optimizer holds none of the module's flex_shard parameters; build it after flex_shard()")
+
+    def post_hook(opt, sd):
+        idx = 0
+        index_layout = {}
+        for g in opt.param_groups:
+            for p in g["params"]:
+                if id(p) in layouts_by_param:
+                    index_layout[idx] = layouts_by_param[id(p)]
+                idx += 1
+        for pid, st in sd.get("state", {}).items():
+            lay = index_layout.get(pid)
+            if lay is None:
+                continue
+            for key in _ADAM_STATE_KEYS:
+                t = st.get(key)
+                if isinstance(t, torch.Tensor):
+                    set_global_layout(t, lay)
+        return sd
+
+    handle = optimizer.register_state_dict_post_hook(post_hook)
+    optimizer._fsb_ckpt_hook = handle
+    return handle
+
+
+# --------------------------------------------------------------------------- file format
+def _flatten(d, prefix=""):
+    out = {}
+    if isinstance(d, Mapping):
+        for k, v in d.items():
+            out.update(_flatten(v, f"{prefix}{k}/" if isinstance(v, (Mapping,)) else f"{prefix}{k}"))
+    else:
+        out[prefix] = d
+    return out
+
+
+def _walk(d, path=()):
+    if isinstance(d, Mapping):
+        for k, v in d.items():
+            yield from _walk(v, path + (k,))
+    else:
+        yield path, d
+
+
+def save(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
+    """Write this rank's part of a (nested) state dict of tagged tensors."""
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    os.makedirs(checkpoint_id, exist_ok=True)
+    entries = {}
+    for path, v in _walk(state_dict):
+        key = "/".join(map(str, path))
+        if isinstance(v, torch.Tensor):
+            lay = get_global_layout(v)
+            if lay is None:
+                if rank == 0:
+                    entries[key] = {"kind": "replicated", "tensor": v.detach().cpu().clone()}
+                continue
+            chunks = []
+            for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
+                t = v.detach()
+                for d, (l, s) in enumerate(zip(loff, size)):
+                    t = t.narrow(d, l, s)
+                chunks.append((tuple(goff), tuple(size), t.cpu().clone()))
+            entries[key] = {"kind": "sharded", "global_shape": tuple(lay.global_shape), "dtype": v.dtype,
+                            "chunks": chunks}
+        elif rank == 0:
+            entries[key] = {"kind": "object", "value": v}
+    tmp = os.path.join(checkpoint_id, f"rank{rank}.pt.tmp")
+    torch.save({"world_size": world, "entries": entries}, tmp)
+    os.replace(tmp, os.path.join(checkpoint_id, f"rank{rank}.pt"))
+    if dist.is_initialized():
+        dist.barrier(group)
+
+
+def load(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
+    """Fill the tagged tensors of ``state_dict`` in place from a checkpoint written by ``save`` at
+    any world size / placement. Untagged tensors are loaded as replicated values."""
+    files = sorted(f for f in os.listdir(checkpoint_id) if f.startswith("rank") and f.endswith(".pt"))
+    if not files:
+        raise FileNotFoundError(f"no rank files under {checkpoint_id}")
+    blobs = [torch.load(os.path.join(checkpoint_id, f), map_location="cpu", weights_only=False) for f in files]
+    if len(blobs) != blobs[0]["world_size"]:
+        raise RuntimeError(f"checkpoint {checkpoint_id} is incomplete: {len(blobs)} of {blobs[0]['world_size']} rank files")
+
+    def assign(container, k, value):
+        container[k] = value
+
+    def visit(d):
+        for k in list(d.keys()) if isinstance(d, dict) else []:
+            yield d, k
+
+    def recurse(d, path):
+        for k, v in list(d.items()):
+            key = "/".join(map(str, path + (k,)))
+            if isinstance(v, Mapping):
+                recurse(v, path + (k,))
+                continue
+            if isinstance(v, torch.Tensor):
+                lay = get_global_layout(v)
+                if lay is None:
+                    src = next((b["entries"][key] for b in blobs if key in b["entries"]), None)
+                    if src is None:
+                        raise KeyError(f"{key} not in checkpoint")
+                    if src["kind"] == "replicated":
+                        v.detach().copy_(src["tensor"])
+                    elif src["kind"] == "sharded":
+                        lay = GlobalLayout(tuple(v.shape), (tuple(0 for _ in v.shape),),
+                                           (tuple(0 for _ in v.shape),), (tuple(v.shape),))
+                        _fill_boxes(v, lay, key, blobs)
+                    continue
+                _fill_boxes(v, lay, key, blobs)
+            else:
+                src = next((b["entries"][key] for b in blobs if key in b["entries"]), None)
+                if src is not None and src["kind"] == "object":
+                    d[k] = src["value"]
+
+    recurse(state_dict, ())
+    if dist.is_initialized():
+        dist.barrier(group)
+
+
+@torch.no_grad()
+def _fill_boxes(v: torch.Tensor, lay: GlobalLayout, key: str, blobs) -> None:
+    covered = 0
+    want = 0
+    for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
+        n = 1
+        for s in size:
+            n *= s
+        want += n
+        for b in blobs:
+            e = b["entries"].get(key)
+            if e is None:
+                continue
+            if e["kind"] == "replicated":
+                src = e["tensor"]
+                for d, (g, s) in enumerate(zip(goff, size)):
+                    src = src.narrow(d, g, s)
+                dst = v.detach()
+                for d, (l, s) in enumerate(zip(loff, size)):
+                    dst = dst.narrow(d, l, s)
+                dst.copy_(src)
+                covered += n
+                break
+            for cgoff, csize, ct in e["chunks"]:
+                lo = tuple(max(a, b_) for a, b_ in zip(goff, cgoff))
+                hi = tuple(min(a + sa, b_ + sb) for a, sa, b_, sb in zip(goff, size, cgoff, csize))
+                if any(h <= l for l, h in zip(lo, hi)):
+                    continue
+                src, dst = ct, v.detach()
+                m = 1
+                for d, (l, h) in enumerate(zip(lo, hi)):
+                    src = src.narrow(d, l - cgoff[d], h - l)
+                    dst = dst.narrow(d, loff[d] + l - goff[d], h - l)
+                    m *= h - l
+                dst.copy_(src)
+                covered += m
+    if covered < want:
+        raise RuntimeError(f"checkpoint does not cover all of {key}: {covered} of {want} elements")

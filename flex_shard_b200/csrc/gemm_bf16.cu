@@ -15,6 +15,7 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
 // issuer, warps 2..5 = epilogue (one TMEM lane quarter each).
 #include "common.cuh"
+#include <stdio.h>
 
 namespace {
 
@@ -300,7 +301,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-int g_num_sms = 0;
+int g_num_sms[64] = {0};
 
 }  // namespace
 
@@ -323,6 +324,14 @@ int fsb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
                      uint32_t box_cols) {
   FsbEncodeTiledFn enc = fsb_get_encode_tiled();
   if (enc == nullptr) return FSB_ERR_TMA_ENCODE;
+  // The driver entry point needs a current context on the calling thread; threads that
+  // only ever launched kernels through the runtime (e.g. autograd workers) may not have
+  // one bound yet.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_size) % 16 != 0)
     return FSB_ERR_BAD_ARG;
   cuuint64_t dims[2] = {cols, rows};
@@ -332,7 +341,16 @@ int fsb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
   CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FSB_OK : FSB_ERR_TMA_ENCODE;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "[fsb200] cuTensorMapEncodeTiled failed (CUresult %d): base=%p rows=%llu cols=%llu ld=%llu "
+            "box=[%u,%u] elem=%d\n",
+            static_cast<int>(r), base, static_cast<unsigned long long>(rows),
+            static_cast<unsigned long long>(cols), static_cast<unsigned long long>(ld), box_rows,
+            box_cols, elem_size);
+    return FSB_ERR_TMA_ENCODE;
+  }
+  return FSB_OK;
 }
 
 // D = alpha * A.B^T + beta * C (+ D). Shapes in elements; see the header comment
@@ -358,20 +376,17 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   }
   if (rc != FSB_OK) return rc;
 
-  static bool attr_set = false;
-  if (!attr_set) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
+  if (g_num_sms[dev] == 0) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM_BYTES) != cudaSuccess)
       return FSB_ERR_LAUNCH;
-    attr_set = true;
-  }
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate, status};
   gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args);

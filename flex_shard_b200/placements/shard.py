@@ -1,0 +1,246 @@
+"""``Shard(dim)``: equal chunks along one dim, the FSDP2-compatible placement.
+
+Layout facts (parity: ``custom_placements/shard.py:118-244`` of the reference):
+chunk = ceil(n/W); rank r holds ``[min(n, r*c), min(n, (r+1)*c))``; only dim 0 may be
+uneven and then every rank reserves a rank-0-sized slot whose tail is zero, so the
+bucket's byte buffer *is* the all-gather send buffer when no cast is needed. The
+gathered ``[W, row]`` buffer is copied out into per-parameter padded buffers; gradients
+are packed into ``[W, row]`` rows (cast to the reduce dtype on the way) and
+reduce-scattered.
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+import torch
+
+from ..placement_contract import (
+    GlobalLayout,
+    GradientReduction,
+    LocalStorageLayout,
+    Placement,
+    PlacementPreparedReduceGrad,
+    PlacementPreparedUnshard,
+    PlacementReduceGradResult,
+    PlacementUnshardResult,
+)
+from ..parallel.comm import plan_reduction
+from ..utils.profiling import record
+
+
+def _contig(shape):
+    stride, acc = [], 1
+    for s in reversed(shape):
+        stride.append(acc)
+        acc *= max(int(s), 1)
+    return tuple(reversed(stride))
+
+
+class Shard(Placement):
+    refills_persistent_buffers_in_finish = True
+
+    def __init__(self, dim: int = 0):
+        self.dim = int(dim)
+
+    def __eq__(self, other):
+        return isinstance(other, Shard) and other.dim == self.dim
+
+    def __hash__(self):
+        return hash(("Shard", self.dim))
+
+    def __repr__(self):
+        return f"Shard({self.dim})"
+
+    def bucket_compatibility_key(self):
+        return Shard  # one bucket may mix shard dims
+
+    # ------------------------------------------------------------------ geometry
+    def _chunk(self, n: int, W: int) -> int:
+        return -(-n // W)
+
+    def _range(self, n: int, r: int, W: int) -> tuple[int, int]:
+        c = self._chunk(n, W)
+        return min(n, r * c), min(n, (r + 1) * c)
+
+    def _check(self, shape: Sequence[int], W: int) -> None:
+        if self.dim >= len(shape) or self.dim < 0:
+            raise ValueError(f"Shard({self.dim}) does not apply to a tensor of shape {tuple(shape)}")
+        if self.dim > 0 and shape[self.dim] % W != 0:
+            raise ValueError(
+                f"Shard({self.dim}) needs dim {self.dim} (size {shape[self.dim]}) to divide evenly by the "
+                f"mesh size {W}; only Shard(0) may be uneven.")
+
+    def compute_local_shape(self, global_shape, rank, world_size):
+        self._check(global_shape, world_size)
+        lo, hi = self._range(global_shape[self.dim], rank, world_size)
+        s = list(global_shape)
+        s[self.dim] = hi - lo
+        return tuple(s)
+
+    def padded_shape(self, global_shape, world_size):
+        s = list(global_shape)
+        s[self.dim] = self._chunk(global_shape[self.dim], world_size)
+        return tuple(s)
+
+    def padded_numel(self, global_shape, world_size) -> int:
+        return math.prod(self.padded_shape(global_shape, world_size))
+
+    def extract_local_shard(self, full, rank, world_size):
+        lo, hi = self._range(full.shape[self.dim], rank, world_size)
+        return full.narrow(self.dim, lo, hi - lo)
+
+    def local_storage_layout(self, global_shape, rank, world_size):
+        ls = self.compute_local_shape(global_shape, rank, world_size)
+        return LocalStorageLayout(ls, _contig(ls), self.padded_numel(global_shape, world_size))
+
+    def global_layout(self, global_shape, rank, world_size):
+        lo, hi = self._range(global_shape[self.dim], rank, world_size)
+        gshape = tuple(global_shape)
+        if hi <= lo:
+            return GlobalLayout(gshape, (), (), ())
+        goff = tuple(lo if d == self.dim else 0 for d in range(len(gshape)))
+        size = tuple((hi - lo) if d == self.dim else gshape[d] for d in range(len(gshape)))
+        return GlobalLayout(gshape, (goff,), (tuple(0 for _ in gshape),), (size,))
+
+    def unsharded_buffer_numel(self, info, world_size):
+        return self.padded_numel(info.global_shape, world_size) * world_size
+
+    # ------------------------------------------------------------------ gather
+    @staticmethod
+    def _send_layout(infos, W):
+        """Byte offsets of each parameter's padded slot in one rank's gather row."""
+        offs, off = [], 0
+        for info in infos:
+            n = info.placement.padded_numel(info.global_shape, W) * info.param_dtype.itemsize
+            offs.append((off, n))
+            off += n
+        return offs, off
+
+    def prepare_unshard_bucket(self, infos, byte_storage, comm, persistent):
+        W = comm.world_size
+        offs, row_bytes = self._send_layout(infos, W)
+        same = all(i.param_dtype == i.storage_dtype for i in infos) and all(
+            i.byte_offset == o for i, (o, _) in zip(infos, offs)) and row_bytes == byte_storage.numel()
+        prep = PlacementPreparedUnshard(infos=infos, persistent=persistent)
+        prep.extra["offs"] = offs
+        prep.extra["row_bytes"] = row_bytes
+        if W == 1:
+            prep.local_copy_out = True
+            prep.extra["storage"] = byte_storage
+            return prep
+        with record("FlexShard::copy_in"):
+            if same:
+                prep.send = byte_storage  # zero-copy: the padded byte storage is the send buffer
+                prep.recv = torch.empty(W * row_bytes, dtype=torch.uint8, device=byte_storage.device)
+            else:
+                prep.recv = torch.empty(W * row_bytes, dtype=torch.uint8, device=byte_storage.device)
+                row = prep.recv[comm.rank * row_bytes:(comm.rank + 1) * row_bytes]
+                row.zero_()
+                for info, (o, n) in zip(infos, offs):
+                    src = info.placement.make_local_storage_view(info, byte_storage)
+                    dst = row[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype)
+                    dst.copy_(src.reshape(-1))
+                prep.send = row  # in-place all-gather: the send row aliases the gather buffer
+        return prep
+
+    def run_prepared_unshard(self, prepared, comm, async_op=False):
+        if comm.world_size == 1:
+            return
+        with record("FlexShard::all_gather"):
+            prepared.work = comm.all_gather_into_tensor(prepared.recv, prepared.send, async_op=async_op)
+
+    def finish_prepared_unshard(self, prepared, comm, persistent):
+        W = comm.world_size
+        infos = prepared.infos
+        if prepared.work is not None:
+            prepared.work.wait()
+            prepared.work = None
+        outs = []
+        with record("FlexShard::copy_out"):
+            if W == 1:
+                storage = prepared.extra["storage"]
+                for info, buf in zip(infos, persistent):
+                    src = info.placement.make_local_storage_view(info, storage)
+                    buf[: info.global_numel].view(info.global_shape).copy_(src)
+                    outs.append(buf[: info.global_numel].view(info.global_shape))
+                return PlacementUnshardResult(outs)
+            row_bytes = prepared.extra["row_bytes"]
+            recv = prepared.recv.view(W, row_bytes)
+            for info, (o, n), buf in zip(infos, prepared.extra["offs"], persistent):
+                pl: Shard = info.placement
+                padded = pl.padded_numel(info.global_shape, W)
+                src = recv[:, o:o + n].view(info.param_dtype)  # [W, padded] (row-strided)
+                if pl.dim == 0:
+                    buf.view(W, padded).copy_(src)
+                    outs.append(buf[: info.global_numel].view(info.global_shape))
+                else:
+                    full = buf[: info.global_numel].view(info.global_shape)
+                    ps = pl.padded_shape(info.global_shape, W)
+                    c = ps[pl.dim]
+                    for r in range(W):
+                        full.narrow(pl.dim, r * c, c).copy_(src[r].view(ps))
+                    outs.append(full)
+        return PlacementUnshardResult(outs, keepalive=[prepared.recv])
+
+    # ------------------------------------------------------------------ gradient reduction
+    def prepare_reduce_grad(self, infos, grads, comm, reduce_dtype):
+        W = comm.world_size
+        offs, off = [], 0
+        for info in infos:
+            n = info.placement.padded_numel(info.global_shape, W)
+            offs.append((off, n))
+            off += n
+        row = off
+        needs_zero = any(info.global_shape[info.placement.dim] % W != 0 for info in infos)
+        with record("FlexShard::reduce_scatter_copy_in"):
+            alloc = torch.zeros if needs_zero else torch.empty
+            send = alloc(W, row, dtype=reduce_dtype, device=grads[0].device)
+            for info, g, (o, n) in zip(infos, grads, offs):
+                pl: Shard = info.placement
+                dst = send[:, o:o + n]
+                if pl.dim == 0:
+                    flat = g.reshape(-1)
+                    full_ranks = flat.numel() // n if n > 0 else 0
+                    full_ranks = min(full_ranks, W)
+                    if full_ranks:
+                        dst[:full_ranks].copy_(flat[: full_ranks * n].view(full_ranks, n))
+                    rem = flat.numel() - full_ranks * n
+                    if rem > 0:
+                        dst[full_ranks, :rem].copy_(flat[full_ranks * n:])
+                else:
+                    ps = pl.padded_shape(info.global_shape, W)
+                    c = ps[pl.dim]
+                    for r in range(W):
+                        dst[r].view(ps).copy_(g.narrow(pl.dim, r * c, c))
+        prep = PlacementPreparedReduceGrad(infos=infos, send=send, reduce_dtype=reduce_dtype)
+        prep.extra["offs"] = offs
+        prep.extra["row"] = row
+        return prep
+
+    def reduce_prepared_grad(self, prepared, comm, reduction: GradientReduction):
+        W = comm.world_size
+        plan = plan_reduction(reduction, W, prepared.reduce_dtype)
+        row = prepared.extra["row"]
+        with record("FlexShard::reduce_scatter"):
+            if W == 1:
+                out = prepared.send.view(-1)
+                if plan.post_divide is not None:
+                    out.div_(plan.post_divide)
+            else:
+                out = torch.empty(row, dtype=prepared.reduce_dtype, device=prepared.send.device)
+                comm.reduce_scatter_tensor(out, prepared.send.view(-1), plan)
+        grads = []
+        for info, (o, n) in zip(prepared.infos, prepared.extra["offs"]):
+            ln = info.local_numel
+            grads.append(out[o:o + ln].view(info.local_shape) if ln > 0 else out[o:o].view(info.local_shape))
+        return PlacementReduceGradResult(grads=grads, output=out)
+
+
+def shard_placement_fn(dim: int = 0):
+    """``placement_fn`` that stores every parameter as ``Shard(dim)``."""
+
+    def fn(named_params, mesh):
+        return {fqn: Shard(dim) for fqn, _ in named_params}
+
+    return fn
