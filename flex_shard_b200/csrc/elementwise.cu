@@ -355,6 +355,22 @@ __global__ void cast_scale_kernel(const ST* __restrict__ s, DT* __restrict__ d, 
   }
 }
 
+// fp32 [T, C] (row stride lds) -> bf16 [T, C] (row stride ldd); C % 4 == 0.
+__global__ void cast2d_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d,
+                                       long long T, int C, long long lds, long long ldd) {
+  const long long total = T * (C / 4);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / (C / 4);
+    const int c = (idx % (C / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(s + t * lds + c);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(d + t * ldd + c) = o;
+  }
+}
+
 // ------------------------------------------------------------------ segment gather / cast / zero
 // One descriptor per segment chunk. mode: 0 copy bytes, 1 fp32->bf16,
 // 2 bf16->fp32, 3 zero-fill dst bytes. `n` counts bytes for modes 0/3 and
@@ -503,6 +519,14 @@ FSB_API int fsb_cast_scale(const void* src, void* dst, long long n, int mode, fl
     case 5: cast_scale_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), n, scale, accumulate); break;
     default: return FSB_ERR_BAD_ARG;
   }
+  return launch_ok();
+}
+
+FSB_API int fsb_cast2d_f32_bf16(const float* src, void* dst, long long T, int C, long long lds,
+                                long long ldd, cudaStream_t stream) {
+  if (C % 4 != 0 || lds % 4 != 0 || ldd % 4 != 0) return FSB_ERR_BAD_ARG;
+  cast2d_f32_bf16_kernel<<<grid_for(T * (C / 4), 256), 256, 0, stream>>>(
+      src, static_cast<__nv_bfloat16*>(dst), T, C, lds, ldd);
   return launch_ok();
 }
 

@@ -1,0 +1,57 @@
+"""tcgen05 flash attention forward/backward against an fp32 PyTorch reference."""
+import math
+
+import pytest
+import torch
+
+from flex_shard_b200 import ops
+from flex_shard_b200.ops import attention as att
+from flex_shard_b200.ops import elementwise as ew
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (1, 256, 2, 1), (2, 512, 4, 2), (1, 1024, 8, 2)])
+def test_attention_fwd_bwd(B, S, Hq, Hkv):
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    C = (Hq + 2 * Hkv) * 128
+    qkv = (0.5 * torch.randn(B, S, C, device=dev)).bfloat16()
+    qkv_ref = qkv.clone().float().requires_grad_()
+    x = qkv.clone().requires_grad_()
+    o = att.qkv_attention(x * 1.0, None, Hq, Hkv)
+    ops.check_status()
+    q = qkv_ref[..., : Hq * 128].reshape(B, S, Hq, 128)
+    k = qkv_ref[..., Hq * 128:(Hq + Hkv) * 128].reshape(B, S, Hkv, 128)
+    v = qkv_ref[..., (Hq + Hkv) * 128:].reshape(B, S, Hkv, 128)
+    oref = att.attention_ref(q, k, v).reshape(B, S, Hq * 128)
+    torch.testing.assert_close(o.float(), oref, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(o)
+    o.backward(g)
+    ops.check_status()
+    oref.backward(g.float())
+    gq = x.grad.float()
+    gr = qkv_ref.grad
+    err = (gq - gr).abs().max().item()
+    scale = gr.abs().max().item()
+    assert err < 3e-2 * max(scale, 1.0), (err, scale)
+    torch.testing.assert_close(gq, gr, rtol=5e-2, atol=3e-2 * max(scale, 1e-3))
+
+
+def test_attention_with_rope_matches_cpu_path():
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    B, S, Hq, Hkv = 1, 256, 4, 2
+    C = (Hq + 2 * Hkv) * 128
+    table = ew.rope_table(S, 128, 5e5, dev)
+    qkv = (0.5 * torch.randn(B, S, C, device=dev)).bfloat16()
+    x = qkv.clone().requires_grad_()
+    o = att.qkv_attention(x * 1.0, table, Hq, Hkv)
+    g = torch.randn_like(o)
+    o.backward(g)
+    xc = qkv.cpu().clone().requires_grad_()
+    oc = att.qkv_attention(xc * 1.0, table.cpu(), Hq, Hkv)
+    oc.backward(g.cpu())
+    torch.testing.assert_close(o.cpu().float(), oc.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(x.grad.cpu().float(), xc.grad.float(), rtol=5e-2, atol=5e-2)
+    ops.check_status()
