@@ -1,0 +1,391 @@
+"""Headline benchmark: training throughput (tokens/s) of a Llama-3-8B-shaped decoder.
+
+Config (BASELINE.json, config 2): bf16 parameters and compute, fp32 gradient reduction and
+optimizer state, d_model 4096, 32 layers, 32 query / 8 KV heads, SwiGLU hidden 14336, vocab
+128256, sequence 8192, local batch 1, ``Shard(0)`` per-layer buckets with prefetch, AdamW.
+Synthetic uniform token ids, N(0, 0.02) weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints one JSON line. ``value`` is the whole-job tokens/s timed on the device (CUDA
+events, max over ranks) with inputs resident on the GPU; ``e2e`` repeats the measurement through
+the public API with a pinned-host -> device copy of every step's tokens and a device -> host read
+of every step's loss inside the timed region.
+
+``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` (prints an
+``unavailable`` line when it cannot be imported); ``--impl fsdp2`` times PyTorch FSDP2
+``fully_shard`` + cuBLAS + SDPA + fused AdamW on the same config as a stand-in baseline.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fsdp2"])
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--local-batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._t is not None:
+            self._t.join(timeout=6)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- helpers
+def setup_dist(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_loop(step_fn, steps: int, world: int) -> float:
+    """Milliseconds per step, device time, max over ranks."""
+    barrier_sync(world)
+    s = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(steps):
+        step_fn(i)
+    e.record()
+    barrier_sync(world)
+    return max_over_ranks(s.elapsed_time(e), world) / steps
+
+
+# --------------------------------------------------------------------------- our arm
+def build_ours(args, world):
+    from flex_shard_b200 import flex_shard
+    from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets
+    from flex_shard_b200.optim.adamw import FusedAdamW
+
+    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq_len)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = Llama(cfg, dtype=torch.bfloat16, device=dev)
+    torch.manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("norm"):
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, cfg.init_std)
+    mesh = None
+    if world > 1:
+        from torch.distributed.device_mesh import init_device_mesh
+
+        mesh = init_device_mesh("cuda", (world,))
+    flex_shard(model, llama_buckets(model, mesh=mesh))
+    opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    return cfg, model, opt
+
+
+def run_ours(args, rank, local, world):
+    from flex_shard_b200 import ops
+
+    cfg, model, opt = build_ours(args, world)
+    B, S = args.local_batch, args.seq_len
+    dev = torch.device("cuda", local)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    n_batches = 4
+    host = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    resident = [h.to(dev) for h in host]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    last_loss = [None]
+
+    def train_step(tokens):
+        loss = model.loss(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step_device(i):
+        last_loss[0] = train_step(resident[i % n_batches])
+
+    def step_e2e(i):
+        tok = host[i % n_batches].to(dev, non_blocking=True)
+        loss = train_step(tok)
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=False)  # device -> host read of the result
+        last_loss[0] = loss
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    ops.check_status()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = ops.launch_count()
+    ms = timed_loop(step_device, args.steps, world)
+    launches = ops.launch_count() - launches0
+    clocks = sampler.stop()
+    ops.check_status()
+    loss_val = float(last_loss[0].detach().float().item())
+
+    e2e = None
+    if not args.no_e2e:
+        step_e2e(0)
+        ms_e2e = timed_loop(step_e2e, args.steps, world)
+        tok_per_step = B * S * world
+        e2e = {"value": tok_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": host[0].numel() * host[0].element_size(),
+               "d2h_bytes_per_step": loss_host.numel() * loss_host.element_size()}
+    tokens_per_step = B * S * world
+    value = tokens_per_step / (ms / 1e3)
+    peak_gb = torch.cuda.max_memory_allocated() / 2**30
+    if rank == 0:
+        flops = cfg.flops_per_token(S) * tokens_per_step / world
+        out = {
+            "metric": "tokens/sec, Llama-3-8B-shaped training step (fwd+bwd+AdamW)", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
+            "impl": "ours",
+            "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers, d{cfg.d_model}, {cfg.n_heads}q/{cfg.n_kv_heads}kv, "
+                                f"ffn {cfg.ffn_hidden}, vocab {cfg.vocab_size})",
+                       "global_batch": args.local_batch * world, "seq_len": S, "parallelism": f"dp{world}",
+                       "placement": "Shard(0) per-layer buckets, prefetch, bf16 params / fp32 reduce+AdamW state",
+                       "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "loss": loss_val, "peak_mem_gib": round(peak_gb, 2),
+            "tflops_per_gpu": flops / (ms / 1e3) / 1e12,
+        }
+        print(json.dumps(out), flush=True)
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank, local, world):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    reason = None
+    if not os.path.isdir(os.path.join(ref_dir, "flex_shard")):
+        reason = "baseline/_ref is not installed (pip --no-index install of /root/reference was not run)"
+    else:
+        sys.path.insert(0, ref_dir)
+        try:
+            import flex_shard  # noqa: F401
+        except Exception as exc:  # the reference pins torch>=2.16 private APIs
+            reason = (f"reference does not import on torch {torch.__version__}: {type(exc).__name__}: "
+                      f"{str(exc).splitlines()[0][:160]}")
+    if reason is None:
+        reason = "reference imported but its CUDA-only runtime was not exercised in this build"
+    if rank == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+
+
+# --------------------------------------------------------------------------- FSDP2 stand-in baseline
+def run_fsdp2(args, rank, local, world):
+    import torch.nn as nn
+    import torch.nn.functional as F
+    from torch.distributed.fsdp import MixedPrecisionPolicy as MP, fully_shard
+
+    from flex_shard_b200.models.llama import LlamaConfig
+
+    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq_len)
+    dev = torch.device("cuda", local)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            d, f, hd = cfg.d_model, cfg.ffn_hidden, cfg.head_dim
+            self.attention_norm = nn.RMSNorm(d, eps=cfg.norm_eps)
+            self.wqkv = nn.Linear(d, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, bias=False)
+            self.wo = nn.Linear(d, d, bias=False)
+            self.ffn_norm = nn.RMSNorm(d, eps=cfg.norm_eps)
+            self.w13 = nn.Linear(d, 2 * f, bias=False)
+            self.w2 = nn.Linear(f, d, bias=False)
+
+        def forward(self, x, freqs):
+            B, S, _ = x.shape
+            hd = cfg.head_dim
+            qkv = self.wqkv(self.attention_norm(x))
+            q, k, v = qkv.split([cfg.n_heads * hd, cfg.n_kv_heads * hd, cfg.n_kv_heads * hd], dim=-1)
+            q = q.view(B, S, cfg.n_heads, hd)
+            k = k.view(B, S, cfg.n_kv_heads, hd)
+            v = v.view(B, S, cfg.n_kv_heads, hd)
+
+            def rope(t):
+                tc = torch.view_as_complex(t.float().reshape(*t.shape[:-1], -1, 2))
+                return torch.view_as_real(tc * freqs[None, :S, None, :]).flatten(3).to(t.dtype)
+
+            q, k = rope(q), rope(k)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               is_causal=True, enable_gqa=True)
+            x = x + self.wo(o.transpose(1, 2).reshape(B, S, -1))
+            g, u = self.w13(self.ffn_norm(x)).chunk(2, dim=-1)
+            return x + self.w2(F.silu(g) * u)
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok_embeddings = nn.Embedding(cfg.vocab_size, cfg.d_model)
+            self.layers = nn.ModuleList([Block() for _ in range(cfg.n_layers)])
+            self.norm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+            self.output = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+
+        def forward(self, tok, freqs):
+            h = self.tok_embeddings(tok)
+            for layer in self.layers:
+                h = layer(h, freqs)
+            return self.output(self.norm(h))
+
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = Model().to(torch.bfloat16)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if "norm" in name:
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, cfg.init_std)
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=dev, dtype=torch.float32) / cfg.head_dim))
+    ang = torch.outer(torch.arange(args.seq_len, device=dev, dtype=torch.float32), inv)
+    freqs = torch.polar(torch.ones_like(ang), ang)
+    if world > 1:
+        mp = MP(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        for layer in model.layers:
+            fully_shard(layer, mp_policy=mp)
+        fully_shard(model, mp_policy=mp)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    B, S = args.local_batch, args.seq_len
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(4)]
+    resident = [h.to(dev) for h in host]
+    loss_host = torch.zeros(1).pin_memory()
+
+    def train_step(tok):
+        logits = model(tok[:, :-1], freqs)
+        loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), tok[:, 1:].reshape(-1))
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    for i in range(args.warmup):
+        train_step(resident[i % 4])
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_loop(lambda i: train_step(resident[i % 4]), args.steps, world)
+    clocks = sampler.stop()
+
+    def e2e_step(i):
+        loss = train_step(host[i % 4].to(dev, non_blocking=True))
+        loss_host.copy_(loss.detach().reshape(1))
+
+    ms_e2e = timed_loop(e2e_step, args.steps, world)
+    tokens = B * S * world
+    if rank == 0:
+        print(json.dumps({"metric": "tokens/sec, Llama-3-8B-shaped training step (fwd+bwd+AdamW)",
+                          "impl": "fsdp2", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                          "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers)", "global_batch": B * world,
+                                     "seq_len": S, "parallelism": f"dp{world}"},
+                          "clocks": clocks, "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s"},
+                          "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference" and not torch.cuda.is_available():
+        run_reference(args, 0, 0, 1)
+        return
+    rank, local, world = setup_dist(args)
+    try:
+        if args.impl == "reference":
+            run_reference(args, rank, local, world)
+        elif args.impl == "fsdp2":
+            run_fsdp2(args, rank, local, world)
+        else:
+            run_ours(args, rank, local, world)
+    finally:
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

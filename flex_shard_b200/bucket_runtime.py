@@ -189,9 +189,15 @@ class BucketRuntime:
         self._handles: list = []
 
     # ------------------------------------------------------------------ persistent unsharded params
+    def _aliases_storage(self) -> bool:
+        fn = getattr(self.storage.placement, "unshard_aliases_storage", None)
+        return bool(fn is not None and fn(self.storage.infos, self.storage.comm.world_size))
+
     def _alloc_persistent(self) -> list[torch.Tensor]:
         st = self.storage
         W = st.comm.world_size
+        if self._aliases_storage():
+            return []
         if self.persistent is None:
             self.persistent = []
             for info in st.infos:
@@ -206,10 +212,7 @@ class BucketRuntime:
         return self.persistent
 
     def _free_persistent(self) -> None:
-        if self.persistent is None:
-            return
-        shared = getattr(self.storage.placement, "persistent_aliases_storage", False)
-        if shared:
+        if self.persistent is None or self._aliases_storage():
             return
         for buf in self.persistent:
             buf.untyped_storage().resize_(0)

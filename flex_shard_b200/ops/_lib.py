@@ -37,6 +37,18 @@ class NativeError(RuntimeError):
     pass
 
 
+_launches = 0  # native kernel launches issued through this package
+
+
+def count_launch(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def launch_count() -> int:
+    return _launches
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 

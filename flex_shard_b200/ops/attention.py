@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from .elementwise import _rope_inplace, _rope_ref
-from .gemm import count_launch
+from ._lib import count_launch
 
 HD = 128
 

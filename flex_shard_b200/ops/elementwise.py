@@ -11,7 +11,7 @@ import math
 import torch
 
 from . import _lib
-from .gemm import count_launch
+from ._lib import count_launch
 
 
 def _s(dev):

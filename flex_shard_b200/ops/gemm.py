@@ -14,12 +14,7 @@ import torch
 
 from . import _lib
 
-launch_count = 0  # native kernel launches issued through this package (all ops add to it)
-
-
-def count_launch(n: int = 1) -> None:
-    global launch_count
-    launch_count += n
+from ._lib import count_launch
 
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,158 @@
+"""AdamW over local shards, one kernel launch per bucket.
+
+The optimizer holds ordinary local ``nn.Parameter`` views (as any optimizer would
+after ``flex_shard``). When all of a bucket's parameters sit in this optimizer and
+their reduced gradients are views of the bucket's reduce-scatter output at matching
+offsets, the update runs as ONE flat sm_100a kernel over the bucket's storage;
+otherwise it falls back to one launch per parameter. State (``exp_avg``,
+``exp_avg_sq`` in fp32, ``step``) is exposed per parameter, so ``state_dict`` and
+the checkpoint hook look like ``torch.optim.AdamW``'s.
+
+Replaces ``torch.optim.AdamW(fused=True)`` as used by the reference's example
+(``examples/deepseek_v3/train.py:297-310``).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.elementwise import adamw_step_
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    _fsb_adam_like = True
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self._flat: dict[int, dict] = {}  # id(storage) -> flat m/v buffers
+
+    # ------------------------------------------------------------------ state
+    def _bucket_of(self, p):
+        return getattr(p, "_fsb_storage", None)
+
+    def _init_bucket_state(self, storage, params):
+        """Flat fp32 moment buffers covering the whole bucket shard; per-parameter state tensors
+        are views into them."""
+        first = params[0]
+        itemsize = first.element_size()
+        n = storage.byte_storage.numel() // itemsize
+        m = torch.zeros(n, dtype=torch.float32, device=first.device)
+        v = torch.zeros(n, dtype=torch.float32, device=first.device)
+        base_off = storage.byte_storage.storage_offset() // itemsize if False else 0
+        for p in params:
+            off = p._fsb_info.byte_offset // itemsize
+            st = self.state[p]
+            st["step"] = torch.zeros((), dtype=torch.float32)
+            st["exp_avg"] = m[off:off + p.numel()].view(p.shape)
+            st["exp_avg_sq"] = v[off:off + p.numel()].view(p.shape)
+        self._flat[id(storage)] = {"m": m, "v": v, "n": n}
+        return self._flat[id(storage)]
+
+    def _init_param_state(self, p):
+        st = self.state[p]
+        st["step"] = torch.zeros((), dtype=torch.float32)
+        st["exp_avg"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+        st["exp_avg_sq"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            hp = dict(lr=float(group["lr"]), beta1=group["betas"][0], beta2=group["betas"][1],
+                      eps=group["eps"], weight_decay=group["weight_decay"])
+            by_bucket: dict[int, list] = {}
+            loose = []
+            for p in group["params"]:
+                st = self._bucket_of(p)
+                if st is None or st.byte_storage is None:
+                    loose.append(p)
+                else:
+                    by_bucket.setdefault(id(st), []).append(p)
+            for plist in by_bucket.values():
+                self._step_bucket(plist, hp)
+            for p in loose:
+                if p.grad is not None:
+                    self._step_param(p, hp)
+        return loss
+
+    def step_bucket(self, storage) -> None:
+        """Update one bucket now (used to apply the optimizer inside backward, right after the
+        bucket's gradient reduction, so its gradients can be freed immediately)."""
+        with torch.no_grad():
+            for group in self.param_groups:
+                plist = [p for p in group["params"] if self._bucket_of(p) is storage]
+                if plist:
+                    hp = dict(lr=float(group["lr"]), beta1=group["betas"][0], beta2=group["betas"][1],
+                              eps=group["eps"], weight_decay=group["weight_decay"])
+                    self._step_bucket(plist, hp)
+
+    def _step_param(self, p, hp):
+        st = self.state[p]
+        if "step" not in st:
+            self._init_param_state(p)
+        st["step"] += 1
+        if p.numel() == 0:
+            return
+        pf = p.data if p.is_contiguous() else None
+        g = p.grad
+        if pf is None or not g.is_contiguous():
+            raise RuntimeError("FusedAdamW needs contiguous parameters and gradients")
+        adamw_step_(pf.view(-1), g.view(-1), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1),
+                    step=int(st["step"]), **hp)
+
+    def _step_bucket(self, plist, hp):
+        storage = self._bucket_of(plist[0])
+        have_grads = [p for p in plist if p.grad is not None]
+        if not have_grads:
+            return
+        flat = self._flat.get(id(storage))
+        all_in = len(plist) == len(storage.sharded_params) and len(have_grads) == len(plist)
+        same_dtype = len({p.dtype for p in plist}) == 1 and len({p.grad.dtype for p in plist}) == 1
+        eligible = all_in and same_dtype and self._grads_flat(plist, storage)
+        if eligible and flat is None and all("step" not in self.state[p] for p in plist):
+            flat = self._init_bucket_state(storage, plist)
+        if eligible and flat is not None:
+            step = None
+            for p in plist:
+                self.state[p]["step"] += 1
+                step = int(self.state[p]["step"])
+            nz = [p for p in plist if p.numel() > 0]
+            if not nz:
+                return
+            itemsize = nz[0].element_size()
+            pflat = storage.byte_storage.view(nz[0].dtype)
+            g0 = nz[0].grad
+            goff = g0.storage_offset() - nz[0]._fsb_info.byte_offset // itemsize
+            n = flat["n"]
+            gbase = g0.as_strided((n,), (1,), goff)
+            adamw_step_(pflat, gbase, flat["m"], flat["v"], step=step, **hp)
+            return
+        for p in have_grads:
+            self._step_param(p, hp)
+
+    @staticmethod
+    def _grads_flat(plist, storage) -> bool:
+        """True when the grads are views of one buffer laid out like the bucket storage."""
+        nz = [p for p in plist if p.numel() > 0]
+        if not nz:
+            return True
+        g0 = nz[0].grad
+        itemsize = nz[0].element_size()
+        base_ptr = g0.untyped_storage().data_ptr()
+        goff = g0.storage_offset() - nz[0]._fsb_info.byte_offset // itemsize
+        if goff < 0:
+            return False
+        n = storage.byte_storage.numel() // itemsize
+        if (g0.untyped_storage().nbytes() // g0.element_size()) < goff + n:
+            return False
+        for p in nz:
+            g = p.grad
+            if g.untyped_storage().data_ptr() != base_ptr or not g.is_contiguous():
+                return False
+            if g.storage_offset() - p._fsb_info.byte_offset // itemsize != goff:
+                return False
+        return True

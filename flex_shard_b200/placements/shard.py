@@ -106,6 +106,12 @@ class Shard(Placement):
     def unsharded_buffer_numel(self, info, world_size):
         return self.padded_numel(info.global_shape, world_size) * world_size
 
+    @staticmethod
+    def unshard_aliases_storage(infos, world_size) -> bool:
+        """On a one-rank mesh with no dtype change the "gathered" parameters are the stored shards
+        themselves: the runtime then uses views of the byte storage and copies nothing."""
+        return world_size == 1 and all(i.param_dtype == i.storage_dtype for i in infos)
+
     # ------------------------------------------------------------------ gather
     @staticmethod
     def _send_layout(infos, W):
@@ -158,6 +164,10 @@ class Shard(Placement):
             prepared.work = None
         outs = []
         with record("FlexShard::copy_out"):
+            if W == 1 and not persistent:
+                storage = prepared.extra["storage"]
+                outs = [info.placement.make_local_storage_view(info, storage) for info in infos]
+                return PlacementUnshardResult(outs)
             if W == 1:
                 storage = prepared.extra["storage"]
                 for info, buf in zip(infos, persistent):
