@@ -153,6 +153,8 @@ def build_ours(args, world):
                 p.fill_(1.0)
             else:
                 p.normal_(0.0, cfg.init_std)
+    for p in model.parameters():
+        p.grad_dtype = torch.float32  # keep the fp32-reduced gradients (no cast back to bf16)
     mesh = None
     if world > 1:
         from torch.distributed.device_mesh import init_device_mesh

@@ -411,6 +411,8 @@ class BucketRuntime:
                 from .utils.validation import alloc_grads_in_param_layout
 
                 alloc_grads_in_param_layout(self.storage)
+            elif getattr(self.storage.placement, "wants_grad_bucket", lambda infos: False)(self.storage.infos):
+                self.storage.placement.alloc_grad_bucket(self.storage, self.unsharded_params)
             self._prefetch(forward=False)
 
     def on_input_grads(self) -> None:
@@ -434,8 +436,22 @@ class BucketRuntime:
                 continue
             g = up.grad
             mg = getattr(up, "main_grad", None)
-            if g is None and mg is not None and getattr(up, "main_grad_written", False):
-                g = mg
+            if mg is not None:
+                if getattr(up, "main_grad_written", False):
+                    if g is not None:  # autograd also produced a gradient (e.g. a second use): fold it in
+                        from .ops.elementwise import cast_scale_
+
+                        dense = g.contiguous()
+                        if mg.is_contiguous():
+                            cast_scale_(mg.view(-1), dense.view(-1), 1.0, accumulate=True)
+                        else:
+                            br = mg.shape[1]
+                            for i in range(mg.shape[0]):
+                                lo, hi = i * br, min((i + 1) * br, dense.shape[0])
+                                if hi > lo:
+                                    mg[i, : hi - lo].add_(dense[lo:hi])
+                    g = mg
+                up.main_grad = None
                 up.main_grad_written = False
             if g is not None:
                 any_grad = True
@@ -474,6 +490,7 @@ class BucketRuntime:
         if not self.is_unsharded and self.unsharded_params is None:
             return
         grads = self._take_grads()
+        st._grad_bucket = None
         hook = st.spec.post_reduce_hook
         if st.reshard_after_backward:
             self.reshard()

@@ -187,6 +187,7 @@ class ShardedBucketStorage:
         self.forward_prefetch: list["ShardedBucketStorage"] | None = None
         self.backward_prefetch: list["ShardedBucketStorage"] | None = None
         self.reduce_comm = comm  # replaced by set_separate_reduce_scatter_group
+        self._grad_bucket: torch.Tensor | None = None
         self.modules: list[nn.Module] = []
         self.module_names: list[str] = []
 
@@ -331,7 +332,9 @@ def create_param_infos(spec: BucketSpec, named_params: list[tuple[str, nn.Parame
         storage_dtype = p.dtype
         param_dtype = mp.compute_dtype_for(fqn, storage_dtype)
         reduce_dtype = mp.reduce_dtype if mp.reduce_dtype is not None else param_dtype
-        grad_dtype = getattr(p, "grad_dtype", None) if getattr(p, "_has_grad_dtype_override", False) else None
+        grad_dtype = getattr(p, "grad_dtype", None)
+        if grad_dtype == storage_dtype:
+            grad_dtype = None  # only an explicit override (e.g. fp32 grads on bf16 shards) is recorded
         if bucket_layout is not None:
             bl: BucketParamStorageLayout = bucket_layout.param_layouts[fqn]
             local_shape, local_stride = bl.local_shape, bl.local_stride

@@ -323,22 +323,54 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias1, bias2_sqrt, grad_scale;
 };
+__device__ __forceinline__ void ld8(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) { load8(p, f); }
+__device__ __forceinline__ void st8(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) { store8(p, f); }
+
+__device__ __forceinline__ void adamw_update(float& pv, float gv, float& mv, float& vv, const AdamArgs& a) {
+  gv *= a.grad_scale;
+  pv *= (1.f - a.lr * a.weight_decay);
+  mv = mv + (1.f - a.beta1) * (gv - mv);  // lerp, as torch does
+  vv = a.beta2 * vv + (1.f - a.beta2) * gv * gv;
+  const float denom = sqrtf(vv) / a.bias2_sqrt + a.eps;
+  pv -= (a.lr / a.bias1) * (mv / denom);
+}
+
+// 8 elements per thread per iteration with 16-byte accesses; `n8` full groups, then a scalar tail.
 template <typename PT, typename GT>
-__global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, float* __restrict__ m,
-                             float* __restrict__ v, __nv_bfloat16* __restrict__ p_lowp, long long n,
-                             AdamArgs a) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float pv = static_cast<float>(p[i]);
-    const float gv = static_cast<float>(g[i]) * a.grad_scale;
-    pv *= (1.f - a.lr * a.weight_decay);
-    const float mv = m[i] + (1.f - a.beta1) * (gv - m[i]);           // lerp, as torch does
-    const float vv = a.beta2 * v[i] + (1.f - a.beta2) * gv * gv;
+__global__ void __launch_bounds__(256)
+adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, float* __restrict__ m,
+             float* __restrict__ v, __nv_bfloat16* __restrict__ p_lowp, long long n, int vec_ok,
+             AdamArgs a) {
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long n8 = vec_ok ? n / 8 : 0;
+  for (long long i = tid; i < n8; i += stride) {
+    float pf[8], gf[8], mf[8], vf[8];
+    ld8(p + i * 8, pf);
+    ld8(g + i * 8, gf);
+    ld8(m + i * 8, mf);
+    ld8(v + i * 8, vf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) adamw_update(pf[j], gf[j], mf[j], vf[j], a);
+    st8(p + i * 8, pf);
+    st8(m + i * 8, mf);
+    st8(v + i * 8, vf);
+    if (p_lowp) store8(p_lowp + i * 8, pf);
+  }
+  for (long long i = n8 * 8 + tid; i < n; i += stride) {
+    float pv = static_cast<float>(p[i]), mv = m[i], vv = v[i];
+    adamw_update(pv, static_cast<float>(g[i]), mv, vv, a);
+    p[i] = static_cast<PT>(pv);
     m[i] = mv;
     v[i] = vv;
-    const float denom = sqrtf(vv) / a.bias2_sqrt + a.eps;
-    pv -= (a.lr / a.bias1) * (mv / denom);
-    p[i] = static_cast<PT>(pv);
     if (p_lowp) p_lowp[i] = __float2bfloat16(pv);
   }
 }
@@ -494,16 +526,20 @@ FSB_API int fsb_adamw(void* p, const void* g, float* m, float* v, void* p_lowp, 
   a.bias1 = 1.f - powf(beta1, static_cast<float>(step));
   a.bias2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
   a.grad_scale = grad_scale;
-  const int grid = grid_for(n, 256, 4);
+  const int grid = grid_for(n, 256, 8);
   __nv_bfloat16* lp = static_cast<__nv_bfloat16*>(p_lowp);
+  const uintptr_t al = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                       reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                       reinterpret_cast<uintptr_t>(p_lowp);
+  const int vec = (al & 15) == 0;
   if (p_fp32 && g_fp32)
-    adamw_kernel<float, float><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const float*>(g), m, v, lp, n, a);
+    adamw_kernel<float, float><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const float*>(g), m, v, lp, n, vec, a);
   else if (p_fp32)
-    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, a);
+    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<float*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, vec, a);
   else if (g_fp32)
-    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const float*>(g), m, v, lp, n, a);
+    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const float*>(g), m, v, lp, n, vec, a);
   else
-    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, a);
+    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(g), m, v, lp, n, vec, a);
   return launch_ok();
 }
 

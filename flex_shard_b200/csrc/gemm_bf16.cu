@@ -45,6 +45,10 @@ struct GemmArgs {
   int c_fp32;
   float alpha, beta;
   int accumulate;
+  // When d_block_rows > 0, D is cut into blocks of that many rows and block i starts at
+  // element offset i * d_block_stride (the [world, rows/world, N] rows of a reduce-scatter
+  // send buffer), so a weight gradient can be written straight into its reduction layout.
+  long long d_block_rows, d_block_stride;
   int* status;
 };
 
@@ -204,6 +208,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
       const bool row_ok = row < args.M;
+      const long long d_off = args.d_block_rows > 0
+                                  ? (row / args.d_block_rows) * args.d_block_stride +
+                                        (row % args.d_block_rows) * args.ldd
+                                  : row * args.ldd;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -232,8 +240,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
           if (args.d_fp32) {
-            float* dp = static_cast<float*>(args.d) + row * args.ldd + col;
-            if (full && (args.ldd % 4 == 0)) {
+            float* dp = static_cast<float*>(args.d) + d_off + col;
+            if (full && (args.ldd % 4 == 0) && (args.d_block_stride % 4 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
                 float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
@@ -248,8 +256,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (col + i < args.N) dp[i] = args.accumulate ? dp[i] + v[i] : v[i];
             }
           } else {
-            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(args.d) + row * args.ldd + col;
-            if (full && (args.ldd % 8 == 0)) {
+            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(args.d) + d_off + col;
+            if (full && (args.ldd % 8 == 0) && (args.d_block_stride % 8 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 if (args.accumulate) {
@@ -359,7 +367,8 @@ int fsb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
 FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
                           long long lda, long long ldb, long long ldd, long long ldc, int a_mn,
                           int b_mn, int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
-                          int* status, int max_ctas, cudaStream_t stream) {
+                          long long d_block_rows, long long d_block_stride, int* status,
+                          int max_ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
   CUtensorMap map_a, map_b;
   int rc;
@@ -388,7 +397,8 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate, status};
+  GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate,
+                d_block_rows, d_block_stride, status};
   gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }

@@ -136,17 +136,22 @@ class Llama(nn.Module):
         logits = self.head(x, delta)
         return logits.view(B * S, -1)
 
-    def loss(self, tokens, targets):
-        """Mean next-token cross-entropy over all positions of ``targets`` (ignore_index -100)."""
+    def loss(self, tokens, targets, loss_is_root: bool = True):
+        """Mean next-token cross-entropy over all positions of ``targets`` (ignore_index -100).
+        With ``loss_is_root`` the returned loss must be what ``backward()`` is called on (its
+        incoming gradient is taken to be 1, which saves a pass over the logits)."""
         logits = self.forward(tokens)
-        return ew.cross_entropy(logits, targets.reshape(-1))
+        return ew.cross_entropy(logits, targets.reshape(-1), unit_grad=loss_is_root)
 
 
 def llama_buckets(model: Llama, mesh=None, mp_policy=None, placement_fn=None, fsdp2_compatible=True):
     """One bucket per block plus embedding and head buckets, FSDP2-style."""
     from ..bucket_storage import BucketSpec, MixedPrecisionPolicy
 
+    from ..placements.shard import shard_placement_fn
+
     mp = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    placement_fn = placement_fn or shard_placement_fn(0, grad_bucket=True)
     kw = dict(mesh=mesh, mp_policy=mp, placement_fn=placement_fn, fsdp2_compatible=fsdp2_compatible)
     specs = [BucketSpec(["tok_embeddings"], **kw)]
     for i in range(len(model.layers)):

@@ -75,8 +75,9 @@ class _RMSNorm(torch.autograd.Function):
             partial = torch.empty(nblk, D, dtype=torch.float32, device=xin.device)
             w = weight if weight.dtype == torch.bfloat16 else weight.to(torch.bfloat16)
             main = getattr(weight, "main_grad", None)
-            if main is not None and main.dtype == torch.float32:
-                dw_buf, dw_fp32, acc = main, 1, 1
+            use_main = main is not None and main.dtype == torch.float32 and main.dim() == 1 and main.is_contiguous()
+            if use_main:
+                dw_buf, dw_fp32, acc = main, 1, int(bool(getattr(weight, "main_grad_written", False)))
             else:
                 dw_buf = torch.empty(D, dtype=torch.float32, device=xin.device)
                 dw_fp32, acc = 1, 0
@@ -86,7 +87,7 @@ class _RMSNorm(torch.autograd.Function):
                                              _s(xin.device))
             _lib.check(rc, "fsb_rmsnorm_bwd")
             count_launch(2)
-            if main is not None and main.dtype == torch.float32:
+            if use_main:
                 weight.main_grad_written = True
                 dw = None
             else:
@@ -223,7 +224,8 @@ class _CrossEntropy(torch.autograd.Function):
     kernel in place of the logits, so the fp32 softmax never exists in memory."""
 
     @staticmethod
-    def forward(ctx, logits, target, scale, ignore_index):
+    def forward(ctx, logits, target, scale, ignore_index, unit_grad):
+        ctx.unit_grad = unit_grad
         T, V = logits.shape
         if logits.is_cuda:
             assert logits.dtype == torch.bfloat16 and logits.stride(1) == 1
@@ -248,14 +250,19 @@ class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         (dlogits,) = ctx.saved_tensors
-        return dlogits * dloss.to(dlogits.dtype), None, None, None
+        if ctx.unit_grad:
+            return dlogits, None, None, None, None
+        return dlogits * dloss.to(dlogits.dtype), None, None, None, None
 
 
-def cross_entropy(logits, target, scale: float | None = None, ignore_index: int = -100):
-    """``sum(token losses) * scale`` (default scale ``1/T``). Overwrites ``logits`` on CUDA."""
+def cross_entropy(logits, target, scale: float | None = None, ignore_index: int = -100,
+                  unit_grad: bool = False):
+    """``sum(token losses) * scale`` (default scale ``1/T``). Overwrites ``logits`` on CUDA.
+    ``unit_grad=True`` promises that the gradient flowing into the loss is exactly 1 (the loss
+    is the root of ``backward()``), which skips one multiply pass over the logits."""
     if scale is None:
         scale = 1.0 / logits.shape[0]
-    return _CrossEntropy.apply(logits, target, float(scale), ignore_index)
+    return _CrossEntropy.apply(logits, target, float(scale), ignore_index, bool(unit_grad))
 
 
 # --------------------------------------------------------------------------- AdamW / casts

@@ -35,16 +35,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     if out is None:
         assert not accumulate
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
-    assert out.shape == (M, N) and out.stride(1) == 1
+    block_rows = block_stride = 0
+    if out.dim() == 3:
+        # [blocks, rows_per_block, N] view of a reduce-scatter send buffer: rows of block i
+        # start at out[i]; rows past M (padding of the last block) are never written.
+        assert out.shape[2] == N and out.stride(2) == 1 and out.shape[0] * out.shape[1] >= M
+        block_rows, block_stride = out.shape[1], out.stride(0)
+        ldd = out.stride(1)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+        ldd = out.stride(0)
     if not a.is_cuda:
         af = (a.t() if a_t else a).float()
         bf = (b.t() if b_t else b).float()
         r = alpha * (af @ bf.t())
         if c is not None:
             r = r + beta * c.float()
+        dst = out if out.dim() == 2 else out.reshape(-1, N)[:M] if out.is_contiguous() else None
+        if dst is None:  # strided block view: write block by block
+            br = out.shape[1]
+            for i in range(out.shape[0]):
+                lo, hi = i * br, min((i + 1) * br, M)
+                if hi > lo:
+                    blk = out[i, : hi - lo]
+                    blk.copy_(r[lo:hi] + (blk.float() if accumulate else 0))
+            return out
         if accumulate:
-            r = r + out.float()
-        out.copy_(r)
+            r = r + dst.float()
+        dst.copy_(r)
         return out
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert out.dtype in (torch.bfloat16, torch.float32)
@@ -58,10 +76,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     status = _lib.status_word(a.device)
     rc = lib.fsb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), c.data_ptr() if c is not None else None,
-        M, N, K, a.stride(0), b.stride(0), out.stride(0), c.stride(0) if c is not None else 0,
+        M, N, K, a.stride(0), b.stride(0), ldd, c.stride(0) if c is not None else 0,
         int(a_t), int(b_t), int(out.dtype == torch.float32),
         int(c is not None and c.dtype == torch.float32), alpha, beta, int(accumulate),
-        status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
+        block_rows, block_stride, status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(rc, "fsb_gemm_bf16")
     count_launch()
     return out
@@ -87,10 +105,12 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, weight, b_t=True).view(x.shape)
         if ctx.needs_input_grad[1]:
             main = getattr(weight, "main_grad", None)
-            if main is not None and main.dtype == torch.float32:
-                # Megatron-style: accumulate the weight gradient into the fp32 bucket view in
-                # the GEMM epilogue and hand autograd nothing to cast or add.
-                gemm(dy2, x2, a_t=True, b_t=True, out=main, accumulate=True)
+            if main is not None and main.dtype in (torch.float32, torch.bfloat16):
+                # The weight gradient goes straight into this parameter's rows of the bucket's
+                # reduce-scatter send buffer (cast to the reduce dtype in the GEMM epilogue);
+                # autograd gets nothing to cast, pack or add.
+                gemm(dy2, x2, a_t=True, b_t=True, out=main,
+                     accumulate=bool(getattr(weight, "main_grad_written", False)))
                 weight.main_grad_written = True
                 dw = None
             else:

@@ -40,8 +40,12 @@ def _contig(shape):
 class Shard(Placement):
     refills_persistent_buffers_in_finish = True
 
-    def __init__(self, dim: int = 0):
+    def __init__(self, dim: int = 0, grad_bucket: bool = False):
         self.dim = int(dim)
+        # With grad_bucket=True the runtime allocates the reduce-scatter send buffer before the
+        # bucket's backward and gives every unsharded parameter a ``main_grad`` view of its rows,
+        # so weight-gradient kernels write the reduction layout directly (no pack/cast pass).
+        self.grad_bucket = bool(grad_bucket)
 
     def __eq__(self, other):
         return isinstance(other, Shard) and other.dim == self.dim
@@ -194,19 +198,67 @@ class Shard(Placement):
         return PlacementUnshardResult(outs, keepalive=[prepared.recv])
 
     # ------------------------------------------------------------------ gradient reduction
-    def prepare_reduce_grad(self, infos, grads, comm, reduce_dtype):
-        W = comm.world_size
+    @staticmethod
+    def _reduce_layout(infos, W):
         offs, off = [], 0
         for info in infos:
             n = info.placement.padded_numel(info.global_shape, W)
             offs.append((off, n))
             off += n
-        row = off
+        return offs, off
+
+    def wants_grad_bucket(self, infos) -> bool:
+        return all(getattr(i.placement, "grad_bucket", False) for i in infos)
+
+    def alloc_grad_bucket(self, storage, unsharded_params) -> None:
+        """Allocate the ``[W, row]`` reduce-scatter send buffer now and hand each trainable
+        dim-0 parameter a ``main_grad`` view of its rows (``[W, chunk, ...]`` strided, or the
+        plain parameter shape on one rank)."""
+        if getattr(storage, "_grad_bucket", None) is not None:
+            return
+        W = storage.comm.world_size
+        pairs = [(i, u) for i, u in zip(storage.infos, unsharded_params) if i.requires_grad and u.requires_grad]
+        infos = [i for i, _ in pairs]
+        if not infos:
+            return
+        reduce_dtype = storage.bucket_reduce_dtype
+        if reduce_dtype not in (torch.float32, torch.bfloat16):
+            return
+        offs, row = self._reduce_layout(infos, W)
+        needs_zero = any(i.global_shape[i.placement.dim] % W != 0 for i in infos)
+        buf = (torch.zeros if needs_zero else torch.empty)(W, row, dtype=reduce_dtype, device=storage.device)
+        for (info, up), (o, n) in zip(pairs, offs):
+            pl: Shard = info.placement
+            if pl.dim != 0:
+                continue
+            if W == 1:
+                view = buf[0, o:o + n].view(info.global_shape)
+            else:
+                ps = pl.padded_shape(info.global_shape, W)
+                view = buf.as_strided((W, *ps), (row, *_contig(ps)), o)
+            view._fsb_bucket = buf
+            up.main_grad = view
+            up.main_grad_written = False
+        storage._grad_bucket = buf
+
+    def prepare_reduce_grad(self, infos, grads, comm, reduce_dtype):
+        W = comm.world_size
+        offs, row = self._reduce_layout(infos, W)
         needs_zero = any(info.global_shape[info.placement.dim] % W != 0 for info in infos)
+        bucket = next((getattr(g, "_fsb_bucket", None) for g in grads if getattr(g, "_fsb_bucket", None) is not None), None)
+        if bucket is not None and (bucket.dtype != reduce_dtype or tuple(bucket.shape) != (W, row)):
+            bucket = None
         with record("FlexShard::reduce_scatter_copy_in"):
-            alloc = torch.zeros if needs_zero else torch.empty
-            send = alloc(W, row, dtype=reduce_dtype, device=grads[0].device)
+            if bucket is not None:
+                send = bucket
+            else:
+                alloc = torch.zeros if needs_zero else torch.empty
+                send = alloc(W, row, dtype=reduce_dtype, device=grads[0].device)
             for info, g, (o, n) in zip(infos, grads, offs):
+                if bucket is not None and getattr(g, "_fsb_bucket", None) is bucket:
+                    continue  # already written in place by the weight-gradient kernel
+                if getattr(g, "_fsb_bucket", None) is not None:
+                    g = self._dense_from_main(info, g, W)
                 pl: Shard = info.placement
                 dst = send[:, o:o + n]
                 if pl.dim == 0:
@@ -228,6 +280,13 @@ class Shard(Placement):
         prep.extra["row"] = row
         return prep
 
+    @staticmethod
+    def _dense_from_main(info, g, W):
+        """A ``main_grad`` view of a foreign bucket back in the parameter's own shape."""
+        if g.dim() == len(info.global_shape):
+            return g
+        return g.reshape(-1, *g.shape[2:])[: info.global_shape[0]]
+
     def reduce_prepared_grad(self, prepared, comm, reduction: GradientReduction):
         W = comm.world_size
         plan = plan_reduction(reduction, W, prepared.reduce_dtype)
@@ -247,10 +306,10 @@ class Shard(Placement):
         return PlacementReduceGradResult(grads=grads, output=out)
 
 
-def shard_placement_fn(dim: int = 0):
+def shard_placement_fn(dim: int = 0, grad_bucket: bool = False):
     """``placement_fn`` that stores every parameter as ``Shard(dim)``."""
 
     def fn(named_params, mesh):
-        return {fqn: Shard(dim) for fqn, _ in named_params}
+        return {fqn: Shard(dim, grad_bucket=grad_bucket) for fqn, _ in named_params}
 
     return fn
