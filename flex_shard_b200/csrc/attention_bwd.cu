@@ -10,7 +10,8 @@
 //   dV  += P^T  dO        A = P^T  (K-major)    B = dO (same tile, MN-major)
 //   dK  += dS^T Q         A = dS^T (K-major)    B = Q  (same tile, MN-major)
 //   dQ^T = K^T dS         A = K (MN-major)      B = dS^T (same tile, MN-major) -> TMEM buf[b][0:64)
-// dQ^T is drained with coalesced fp32 atomics into a [B*S, Hq*128] accumulator.
+// dQ^T is transposed through shared memory and added into a fp32 [B*S, Hq*128] accumulator
+// by one bulk tensor reduce-add per query tile (the copy engine does the read-modify-write at L2).
 // TMEM: two (S^T|dP^T) buffers (256 columns) + dV (128) + dK (128) = 512 columns.
 #include "common.cuh"
 
@@ -23,7 +24,8 @@ constexpr int BQ = 64;
 constexpr int KV_TILE_BYTES = BKV * HD * 2;  // 32 KB, two chunks of 16 KB
 constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KB, two chunks of 8 KB
 constexpr int PT_BYTES = BKV * BQ * 2;       // 16 KB
-constexpr int SMEM_BWD = 2 * KV_TILE_BYTES + 2 * 2 * Q_TILE_BYTES + 2 * PT_BYTES + 1024 + 4096 + 256;
+constexpr int DQ_BYTES = BQ * HD * 4;           // 32 KB fp32 staging tile [64 q][128 d]
+constexpr int SMEM_BWD = 2 * KV_TILE_BYTES + 2 * 2 * Q_TILE_BYTES + 2 * PT_BYTES + DQ_BYTES + 1024 + 4096 + 256;
 constexpr int THREADS = 192;
 
 struct BwdArgs {
@@ -55,7 +57,7 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&o
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                const BwdArgs args) {
+                const __grid_constant__ CUtensorMap map_dq, const BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -67,8 +69,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint8_t* sDST = sPT + PT_BYTES;            // dS^T
   // per softmax warp: [2 stages][64 lse | 64 delta] (each warp stages its own copy, so the
   // warps never have to meet at a CTA-wide barrier inside the loop)
-  float* s_stats = reinterpret_cast<float*>(sDST + PT_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDST + PT_BYTES + 4096);
+  float* sDQ = reinterpret_cast<float*>(sDST + PT_BYTES);   // [64 q][128 d] fp32
+  float* s_stats = reinterpret_cast<float*>(sDST + PT_BYTES + DQ_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDST + PT_BYTES + DQ_BYTES + 4096);
   uint64_t* kv_full = bars;          // 1
   uint64_t* qdo_full = bars + 1;     // [2]
   uint64_t* qdo_empty = bars + 3;    // [2]
@@ -78,12 +81,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* pds_empty = bars + 10;   // MMAs finished reading P^T / dS^T
   uint64_t* dq_full = bars + 11;     // [2]
   uint64_t* all_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* sdq_free = bars + 14;     // the previous reduce-add has finished reading sDQ
+  uint64_t* sdq_written = bars + 15;  // all four warps have written their part of sDQ
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_tile = blockIdx.x;
-  const int hk = blockIdx.y, b = blockIdx.z;
+  // x = (kv head, batch) so that CTAs are handed out tile by tile: kv tile 0 has the most
+  // query tiles below the diagonal, so ascending y is longest-job-first.
+  const int kv_tile = blockIdx.y;
+  const int hk = blockIdx.x % args.Hkv, b = blockIdx.x / args.Hkv;
   const int G = args.Hq / args.Hkv;
   const int kv0 = kv_tile * BKV;
   const int row_base = b * args.S;
@@ -103,6 +110,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(pds_full, 4);
     mbar_init(pds_empty, 1);
     mbar_init(all_done, 1);
+    mbar_init(sdq_free, 1);
+    mbar_init(sdq_written, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -239,6 +248,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
 
+    // dQ^T (lane = d, column = q) -> sDQ[q][d] -> one bulk reduce-add into dq_acc.
     auto drain_dq = [&](int it) -> bool {
       const int s = it & 1;
       const uint32_t ph = (it >> 1) & 1;
@@ -246,19 +256,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after();
       const int g = it / n_qt, qt = qt_first + it % n_qt;
       const int h = hk * G + g;
-      float* base = args.dq_acc + static_cast<long long>(row_base + qt * BQ) * (args.Hq * HD) + h * HD + r;
+      // the previous tile's reduce must have finished reading sDQ before it is overwritten
+      // (mbarriers with bounded waits rather than a CTA barrier: a warp that gave up must not
+      // leave the others waiting for it)
+      const uint32_t dph = static_cast<uint32_t>(it) & 1;
+      if (threadIdx.x == 64) {
+        tma_store_wait_read0();
+        mbar_arrive(sdq_free);
+      }
+      if (!mbar_wait(sdq_free, dph, abort_flag)) return false;
 #pragma unroll 1
       for (int c0 = 0; c0 < BQ; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + lane_off + s * 128 + c0, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          atomicAdd(base + static_cast<long long>(c0 + i) * (args.Hq * HD), __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) sDQ[(c0 + i) * HD + r] = __uint_as_float(v[i]);
       }
       tc_fence_before();
+      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&buf_empty[s]);
+      if (lane == 0) {
+        mbar_arrive(&buf_empty[s]);
+        mbar_arrive(sdq_written);
+      }
+      if (threadIdx.x == 64) {
+        if (!mbar_wait(sdq_written, dph, abort_flag)) return false;
+        tma_reduce_add_2d(&map_dq, sDQ, h * HD, row_base + qt * BQ);
+        tma_store_commit();
+      }
       return true;
     };
 
@@ -329,6 +355,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
     if (ok && n_it > 0) ok = drain_dq(n_it - 1);
+    if (threadIdx.x == 64) tma_store_wait_all();
     if (ok && mbar_wait(all_done, 0, abort_flag)) {
       tc_fence_after();
       __nv_bfloat16* dkrow = args.dk + static_cast<long long>(row_base + kv_row) * args.lddk + hk * HD;
@@ -408,8 +435,11 @@ FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void
                          long long lddo, long long lddk, long long lddv, float softmax_scale,
                          int* status, cudaStream_t stream) {
   if (S % BKV != 0 || Hq % Hkv != 0 || B <= 0 || (lddk % 8) || (lddv % 8)) return FSB_ERR_BAD_ARG;
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
+  int rc0 = fsb_make_tmap_2d_plain(&mdq, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rows,
+                                   static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD, BQ, HD);
+  if (rc0 != FSB_OK) return rc0;
   int rc = fsb_make_tmap_2d(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, static_cast<uint64_t>(Hq) * HD, ldq, BQ, 64);
   if (rc != FSB_OK) return rc;
   rc = fsb_make_tmap_2d(&mdo, d_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, static_cast<uint64_t>(Hq) * HD, lddo, BQ, 64);
@@ -435,7 +465,7 @@ FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void
   a.dk = static_cast<__nv_bfloat16*>(dk); a.lddk = lddk;
   a.dv = static_cast<__nv_bfloat16*>(dv); a.lddv = lddv;
   a.status = status;
-  dim3 grid(S / BKV, Hkv, B);
-  attn_bwd_kernel<<<grid, THREADS, SMEM_BWD, stream>>>(mq, mk, mv, mdo, a);
+  dim3 grid(Hkv * B, S / BKV, 1);
+  attn_bwd_kernel<<<grid, THREADS, SMEM_BWD, stream>>>(mq, mk, mv, mdo, mdq, a);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }

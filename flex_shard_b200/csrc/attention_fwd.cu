@@ -60,8 +60,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // x = (head, batch), y = query tile from the bottom of the causal triangle up, so CTAs are
+  // handed out longest-job-first.
+  const int q_tile = gridDim.y - 1 - blockIdx.y;
+  const int h = blockIdx.x % args.Hq, b = blockIdx.x / args.Hq;
   const int hk = h / (args.Hq / args.Hkv);
   const int q0 = q_tile * BQ;
   const int n_kv = (q0 + BQ) / BKV;
@@ -223,6 +225,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float m_new = fmaxf(m_used, mx);
       const bool need = (j == 0) || ((m_new - m_used) * args.scale_log2 > 8.f);
       const bool warp_need = __any_sync(0xffffffffu, need);
+      float alpha = 1.f;
+      if (warp_need) {
+        if (j > 0) alpha = exp2f((m_used - m_new) * args.scale_log2);
+        m_used = m_new;
+      }
+      // Exponentials first (registers only), so they overlap the previous tile's P V product.
+      const float mb = m_used * args.scale_log2;
+      float sum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = exp2f(__uint_as_float(r0[2 * i]) * args.scale_log2 - mb);
+        const float p1 = exp2f(__uint_as_float(r0[2 * i + 1]) * args.scale_log2 - mb);
+        const float p2 = exp2f(__uint_as_float(r1[2 * i]) * args.scale_log2 - mb);
+        const float p3 = exp2f(__uint_as_float(r1[2 * i + 1]) * args.scale_log2 - mb);
+        sum += (p0 + p1) + (p2 + p3);
+        pk[i] = pack_bf16x2(p0, p1);
+        pk[16 + i] = pack_bf16x2(p2, p3);
+      }
       if (j > 0) {
         // P buffer free and O settled: PV of the previous tile has retired.
         if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag)) {
@@ -234,54 +255,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           break;
         }
       }
-      if (warp_need) {
-        if (j > 0) {
-          const float alpha = exp2f((m_used - m_new) * args.scale_log2);
-          l *= alpha;
-          tc_fence_after();
+      if (warp_need && j > 0) {
+        l *= alpha;
+        tc_fence_after();
 #pragma unroll 1
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld_32x32(tmem_o + lane_off + c0, o);
-            tmem_ld_wait();
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + lane_off + c0, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            asm volatile(
-                "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-                ::"r"(tmem_o + lane_off + c0),
-                "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
-                "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]),
-                "r"(o[15]), "r"(o[16]), "r"(o[17]), "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]),
-                "r"(o[22]), "r"(o[23]), "r"(o[24]), "r"(o[25]), "r"(o[26]), "r"(o[27]), "r"(o[28]),
-                "r"(o[29]), "r"(o[30]), "r"(o[31])
-                : "memory");
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+              "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+              "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+              ::"r"(tmem_o + lane_off + c0),
+              "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+              "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]),
+              "r"(o[15]), "r"(o[16]), "r"(o[17]), "r"(o[18]), "r"(o[19]), "r"(o[20]), "r"(o[21]),
+              "r"(o[22]), "r"(o[23]), "r"(o[24]), "r"(o[25]), "r"(o[26]), "r"(o[27]), "r"(o[28]),
+              "r"(o[29]), "r"(o[30]), "r"(o[31])
+              : "memory");
         }
-        m_used = m_new;
+        tmem_st_wait();
       }
-      const float mb = m_used * args.scale_log2;
-      float sum = 0.f;
       // P row -> shared memory, 16-byte units XOR-swizzled by (row & 7) as the 128B-swizzle MMA expects.
       uint8_t* prow = sP + r * 128;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = u * 8 + i;
-          const float sv = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
-          p[i] = exp2f(sv * args.scale_log2 - mb);
-          sum += p[i];
-        }
-        uint4 pk;
-        pk.x = pack_bf16x2(p[0], p[1]);
-        pk.y = pack_bf16x2(p[2], p[3]);
-        pk.z = pack_bf16x2(p[4], p[5]);
-        pk.w = pack_bf16x2(p[6], p[7]);
-        *reinterpret_cast<uint4*>(prow + ((u ^ (r & 7)) << 4)) = pk;
+        uint4 q4 = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        *reinterpret_cast<uint4*>(prow + ((u ^ (r & 7)) << 4)) = q4;
       }
       l += sum;
       fence_proxy_async_smem();
@@ -358,7 +361,7 @@ FSB_API int fsb_attn_fwd(const void* q, const void* k, const void* v, void* o, f
   a.ldo = ldo;
   a.lse = lse;
   a.status = status;
-  dim3 grid(S / BQ, Hq, B);
+  dim3 grid(Hq * B, S / BQ, 1);
   attn_fwd_kernel<<<grid, THREADS, SMEM_FWD, stream>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }

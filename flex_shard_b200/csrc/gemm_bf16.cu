@@ -361,6 +361,32 @@ int fsb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
   return FSB_OK;
 }
 
+int fsb_make_tmap_2d_plain(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
+                           int elem_size, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint32_t box_rows, uint32_t box_cols) {
+  FsbEncodeTiledFn enc = fsb_get_encode_tiled();
+  if (enc == nullptr) return FSB_ERR_TMA_ENCODE;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_size) % 16 != 0)
+    return FSB_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_size)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[fsb200] cuTensorMapEncodeTiled (plain) failed (CUresult %d)\n", static_cast<int>(r));
+    return FSB_ERR_TMA_ENCODE;
+  }
+  return FSB_OK;
+}
+
 // D = alpha * A.B^T + beta * C (+ D). Shapes in elements; see the header comment
 // for the meaning of a_mn / b_mn. `status` is a device int the kernel writes an
 // error code to when a bounded wait runs out (left untouched otherwise).
