@@ -26,7 +26,7 @@ constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KB, two chunks of 8 KB
 constexpr int PT_BYTES = BKV * BQ * 2;       // 16 KB
 constexpr int DQ_BYTES = BQ * HD * 4;           // 32 KB fp32 staging tile [64 q][128 d]
 constexpr int SMEM_BWD = 2 * KV_TILE_BYTES + 2 * 2 * Q_TILE_BYTES + 2 * PT_BYTES + DQ_BYTES + 1024 + 4096 + 256;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 compute (two per TMEM lane quarter)
 
 struct BwdArgs {
   int S, Hq, Hkv;
@@ -104,14 +104,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&buf_empty[i], 4);
+      mbar_init(&buf_empty[i], 8);
       mbar_init(&dq_full[i], 1);
     }
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(all_done, 1);
     mbar_init(sdq_free, 1);
-    mbar_init(sdq_written, 4);
+    mbar_init(sdq_written, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -241,7 +241,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------ softmax / drain warps
+    // Two warps share each TMEM lane quarter and split the columns between them: every element of
+    // the backward pass is independent (no row reductions), so the split needs no exchange.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;    // 0: columns [0,32) of a 64-wide tile, 1: columns [32,64)
     const int r = quarter * 32 + lane;   // kv row inside the tile (S^T, dP^T, dK, dV) or d (dQ^T)
     const int kv_row = kv0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -265,8 +268,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(sdq_free);
       }
       if (!mbar_wait(sdq_free, dph, abort_flag)) return false;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BQ; c0 += 32) {
+      {
+        const int c0 = half * 32;
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + lane_off + s * 128 + c0, v);
         tmem_ld_wait();
@@ -295,14 +298,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int h = hk * G + g;
       const int q0 = qt * BQ;
       // stage this tile's lse / delta rows (64 each) in this warp's private slot
-      float* s_lse = s_stats + (quarter * 2 + s) * 128;
-      float* s_delta = s_lse + 64;
+      float* s_lse = s_stats + ((warp - 2) * 2 + s) * 64;   // this warp's 32 queries: lse | delta
+      float* s_delta = s_lse + 32;
       {
-        const long long off = (static_cast<long long>(b) * args.Hq + h) * args.S + q0;
+        const long long off = (static_cast<long long>(b) * args.Hq + h) * args.S + q0 + half * 32;
         s_lse[lane] = args.lse[off + lane] * LOG2E;
-        s_lse[lane + 32] = args.lse[off + lane + 32] * LOG2E;
         s_delta[lane] = args.delta[off + lane];
-        s_delta[lane + 32] = args.delta[off + lane + 32];
         __syncwarp();
       }
       if (!mbar_wait(&sdp_full[s], ph, abort_flag)) {
@@ -317,8 +318,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const bool diag = q0 < kv0 + BKV;  // some (kv, q) pairs of this tile are above the diagonal
       uint8_t* prow = sPT + r * 128;
       uint8_t* drow = sDST + r * 128;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BQ; c0 += 32) {
+      {
+        const int c0 = half * 32;
         uint32_t sv[32], dp[32];
         tmem_ld_32x32(tmem_base + lane_off + s * 128 + c0, sv);
         tmem_ld_32x32(tmem_base + lane_off + s * 128 + 64 + c0, dp);
@@ -330,10 +331,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int i = 0; i < 8; ++i) {
             const int c = u * 8 + i;
             const int qi = c0 + c;
-            float pv = exp2f(__uint_as_float(sv[c]) * args.scale_log2 - s_lse[qi]);
+            float pv = exp2f(__uint_as_float(sv[c]) * args.scale_log2 - s_lse[c]);
             if (diag && kv_row > q0 + qi) pv = 0.f;
             p[i] = pv;
-            d[i] = pv * (__uint_as_float(dp[c]) - s_delta[qi]) * args.scale;
+            d[i] = pv * (__uint_as_float(dp[c]) - s_delta[c]) * args.scale;
           }
           uint4 pk, dk;
           pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
@@ -361,7 +362,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       __nv_bfloat16* dkrow = args.dk + static_cast<long long>(row_base + kv_row) * args.lddk + hk * HD;
       __nv_bfloat16* dvrow = args.dv + static_cast<long long>(row_base + kv_row) * args.lddv + hk * HD;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
         uint32_t a[32], c[32];
         tmem_ld_32x32(tmem_dk + lane_off + c0, a);
         tmem_ld_32x32(tmem_dv + lane_off + c0, c);

@@ -22,7 +22,9 @@ constexpr int BKV = 64;
 constexpr int Q_BYTES = BQ * HD * 2;        // 32 KB (two 64-wide chunks)
 constexpr int KV_BYTES = BKV * HD * 2;      // 16 KB (two 64-wide chunks of 8 KB)
 constexpr int P_BYTES = BQ * BKV * 2;       // 16 KB
-constexpr int SMEM_FWD = Q_BYTES + 2 * KV_BYTES + 2 * KV_BYTES + P_BYTES + 1024 + 256;
+// No alignment slack: two CTAs must fit in the SM's 228 KB (each also pays 1 KB of reserved
+// shared memory), so the dynamic buffer is declared 1024-byte aligned and checked at run time.
+constexpr int SMEM_FWD = Q_BYTES + 2 * KV_BYTES + 2 * KV_BYTES + P_BYTES + 128;
 constexpr int TMEM_COLS_FWD = 256;          // S0 [0,64) S1 [64,128) O [128,256)
 constexpr int THREADS = 192;
 
@@ -39,9 +41,12 @@ struct FwdArgs {
 __global__ void __launch_bounds__(THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const FwdArgs args) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(args.status, FSB_ERR_BAD_ARG);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Q_BYTES;            // [2][KV_BYTES]
   uint8_t* sV = sK + 2 * KV_BYTES;       // [2][KV_BYTES]
