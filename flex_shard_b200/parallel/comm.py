@@ -91,7 +91,16 @@ class Comm:
             if outs[0].data_ptr() != inp.data_ptr():
                 outs[0].copy_(inp)
             return None
-        return dist.all_gather(list(outs), inp, group=self.group, async_op=async_op)
+        if self.is_nccl:
+            return dist.all_gather(list(outs), inp, group=self.group, async_op=async_op)
+        # gloo has no uneven all-gather: one broadcast per row
+        ranks = self.ranks()
+        if outs[self.rank].data_ptr() != inp.data_ptr():
+            outs[self.rank].copy_(inp)
+        for r, t in enumerate(outs):
+            if t.numel():
+                dist.broadcast(t, src=ranks[r], group=self.group)
+        return None
 
     # ------------------------------------------------------------------ reduce-scatter
     def _apply_plan_pre(self, inp: torch.Tensor, plan: ReducePlan) -> torch.Tensor:

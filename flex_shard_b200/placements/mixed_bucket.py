@@ -1,0 +1,72 @@
+"""``MixedBucketPlacement``: one all-gather and one reduce-scatter for a bucket that mixes
+``Shard(0)``-style, ``BlockShard`` and ``BucketedOwned`` members (and dtypes).
+
+Every member is a slice placement, so the shared row engine (``placements/sliced.py``) plans one
+row per rank ``[owner-exclusive region | regular slots]``, gathers rows as bytes and reduces rows in
+the bucket's reduce dtype. This class only adapts a member placement to that engine.
+
+Parity: ``custom_placements/mixed_bucket.py:173-365`` (member wrappers) and ``:663-684``
+(one collective per bucket) of the reference.
+"""
+from __future__ import annotations
+
+from .shard import Shard
+from .sliced import Piece, SlicedPlacement
+
+
+class ShardSlice(SlicedPlacement):
+    """``Shard(dim)`` geometry expressed as a slice placement (member of a mixed bucket)."""
+
+    def __init__(self, dim: int = 0):
+        self.dim = int(dim)
+        self._shard = Shard(dim)
+
+    def __eq__(self, other):
+        return isinstance(other, ShardSlice) and other.dim == self.dim
+
+    def __hash__(self):
+        return hash(("ShardSlice", self.dim))
+
+    def __repr__(self):
+        return f"ShardSlice({self.dim})"
+
+    def pieces(self, global_shape, rank, world_size):
+        self._shard._check(global_shape, world_size)
+        lo, hi = self._shard._range(global_shape[self.dim], rank, world_size)
+        return [Piece(self.dim, lo, hi - lo)] if hi > lo else []
+
+
+class MixedBucketPlacement(SlicedPlacement):
+    """Wraps one member placement of a mixed bucket."""
+
+    def __init__(self, member):
+        if isinstance(member, Shard):
+            member = ShardSlice(member.dim)
+        if not isinstance(member, SlicedPlacement):
+            raise TypeError(f"{member!r} cannot be a member of a mixed bucket")
+        self.member = member
+        self.owner_style = getattr(member, "owner_style", False)
+
+    def __eq__(self, other):
+        return isinstance(other, MixedBucketPlacement) and other.member == self.member
+
+    def __hash__(self):
+        return hash(("Mixed", self.member))
+
+    def __repr__(self):
+        return f"MixedBucketPlacement({self.member!r})"
+
+    def pieces(self, global_shape, rank, world_size):
+        return self.member.pieces(global_shape, rank, world_size)
+
+    def reduces_grads_in_param_layout(self, infos) -> bool:
+        return False
+
+
+def make_mixed_placement_fn(member_fn):
+    """Wrap the placements returned by ``member_fn`` so that they may share one bucket."""
+
+    def fn(named_params, mesh):
+        return {f: MixedBucketPlacement(pl) for f, pl in member_fn(named_params, mesh).items()}
+
+    return fn

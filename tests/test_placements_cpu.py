@@ -1,0 +1,141 @@
+"""Sliced placements (BlockShard, BucketedOwned, mixed buckets) on 2 gloo ranks: training parity
+with an unsharded model, storage goldens, relayout and checkpoint resharding."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.nn as nn
+
+from tests.common import FakeMesh, run_ranks
+
+
+class MLP(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(16, 16)
+        self.b = nn.Linear(16, 8)
+        self.norm = nn.LayerNorm(8)
+
+    def forward(self, x):
+        return self.norm(self.b(torch.relu(self.a(x))))
+
+
+def _placement_fn(kind):
+    from flex_shard_b200.placements import (BlockShard, BucketedOwned, MixedBucketPlacement, Shard,
+                                            make_bucketed_owned_full_param_placement_fn)
+
+    if kind == "block":
+        return lambda named, mesh: {f: BlockShard((1, 1) if p.shape[0] % 2 == 0 else (1, 0), 0) for f, p in named}
+    if kind == "owned":
+        return make_bucketed_owned_full_param_placement_fn()
+    if kind == "mixed":
+        def fn(named, mesh):
+            out = {}
+            for i, (f, p) in enumerate(named):
+                if p.dim() == 2 and i % 2 == 0:
+                    out[f] = MixedBucketPlacement(BucketedOwned(((i % 2, 0, p.shape[0]),)))
+                elif p.dim() == 2:
+                    out[f] = MixedBucketPlacement(BlockShard((1, 1), 1))
+                else:
+                    out[f] = MixedBucketPlacement(Shard(0))
+            return out
+        return fn
+    raise ValueError(kind)
+
+
+def _train(rank, world, kind, steps):
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    torch.manual_seed(0)
+    model = MLP()
+    ref = MLP()
+    ref.load_state_dict(model.state_dict())
+    flex_shard(model, [BucketSpec(["*"], placement_fn=_placement_fn(kind))])
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    for s in range(steps):
+        xs = [torch.randn(4, 16, generator=torch.Generator().manual_seed(10 * s + r)) for r in range(world)]
+        model(xs[rank]).square().mean().backward()
+        opt.step()
+        opt.zero_grad()
+        sum(ref(x).square().mean() for x in xs).div(world).backward()
+        ropt.step()
+        ropt.zero_grad()
+    # compare full parameters
+    model.unshard()
+    err = 0.0
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        err = max(err, float((p.detach() - q.detach()).abs().max()))
+    model.reshard()
+    sizes = [sp.numel() for sp in model.sharded_bucket_storages[0].sharded_params]
+    return err, sizes, model.sharded_bucket_storages[0].total_bytes
+
+
+@pytest.mark.parametrize("kind", ["block", "owned", "mixed"])
+def test_sliced_placements_train_like_unsharded(kind):
+    res = run_ranks(_train, 2, kind, 3)
+    for err, sizes, nbytes in res:
+        assert err < 1e-5, (kind, err)
+    if kind == "owned":
+        # owners hold whole parameters and no padding; the other rank holds nothing of them
+        total = sum(p.numel() for p in MLP().parameters())
+        assert sum(res[0][1]) + sum(res[1][1]) == total
+        assert all(a == 0 or b == 0 for a, b in zip(res[0][1], res[1][1]))
+
+
+def test_owner_rows_hold_no_padding_golden():
+    """Linear(16,16)+Linear(16,8) on 2 ranks: weights and biases are whole on their owners."""
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+    from flex_shard_b200.placements.sliced import plan_rows
+    from flex_shard_b200.bucket_storage import BucketSpec, create_param_infos
+
+    m = nn.Sequential(nn.Linear(16, 16), nn.Linear(16, 8))
+    named = list(m.named_parameters())
+    fn = make_bucketed_owned_full_param_placement_fn()
+    pls = fn(named, FakeMesh(2))
+    infos, total0 = create_param_infos(BucketSpec(["*"]), named, pls, 0, 2, {})
+    _, total1 = create_param_infos(BucketSpec(["*"]), named, pls, 1, 2, {})
+    assert total0 // 4 + total1 // 4 >= 408  # 256 + 16 + 128 + 8 elements in all
+    plan = plan_rows(infos, 2, lambda i: 1)
+    assert plan.owner_only and sum(plan.row_by_rank) >= 408
+
+
+def _relayout_and_checkpoint(rank, world, tmp):
+    from flex_shard_b200 import BucketSpec, checkpoint, flex_shard, relayout_bucket, set_state_dict_global_layouts
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+
+    torch.manual_seed(0)
+    model = MLP()
+    full = {k: v.clone() for k, v in model.state_dict().items()}
+    flex_shard(model, [BucketSpec(["a", "b"]), BucketSpec(["norm"])])
+    st = model.sharded_bucket_storages[0]
+    relayout_bucket(model, st, make_bucketed_owned_full_param_placement_fn())
+    sd = model.state_dict()
+    set_state_dict_global_layouts(model, sd)
+    checkpoint.save({"model": sd}, tmp)
+    # reload into a Shard(0) model and compare against the original full tensors
+    other = MLP()
+    for p in other.parameters():
+        p.data.zero_()
+    flex_shard(other, [BucketSpec(["*"])])
+    sd2 = other.state_dict()
+    set_state_dict_global_layouts(other, sd2)
+    checkpoint.load({"model": sd2}, tmp)
+    other.load_state_dict(sd2)
+    other.unshard()
+    err = max(float((p.detach() - full[n]).abs().max()) for n, p in other.named_parameters())
+    other.reshard()
+    x = torch.randn(3, 16, generator=torch.Generator().manual_seed(5))
+    ref = MLP()
+    ref.load_state_dict(full)
+    out_err = float((model(x) - ref(x)).abs().max())
+    return err, out_err
+
+
+def test_relayout_then_checkpoint_reshards_bitwise():
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks(_relayout_and_checkpoint, 2, os.path.join(d, "ckpt"))
+    for err, out_err in res:
+        assert err == 0.0
+        assert out_err < 1e-6
