@@ -1,0 +1,111 @@
+"""Owner assignment for Muon matrices and the bucket recipe built on it.
+
+``assign_matrices`` balances Newton-Schulz cost over ranks with longest-processing-time first,
+hosts before ranks, group by group; ``materialize_dist_muon_buckets`` turns a model description
+(initial / per-block / final parameter groups) into the ``BucketSpec`` list.
+
+Parity: ``dist_muon/bucket_planner.py:147-517`` of the reference. Note the reference's own
+remark (``:159-171``): balancing each group separately leaves the most loaded rank at about
+1.39x the mean on a 4-layer/8-rank example where a global LPT reaches 1.06x; ``carry_loads``
+carries the loads from group to group to approach the latter.
+"""
+from __future__ import annotations
+
+import fnmatch
+from dataclasses import dataclass
+from typing import Mapping, Sequence
+
+import torch.distributed as dist
+
+from ..bucket_storage import BucketSpec, MixedPrecisionPolicy
+from ..placements.block_shard import BlockShard
+from ..placements.mixed_bucket import MixedBucketPlacement
+from ..placements.owned import BucketedOwned, newton_schulz_cost
+from ..placements.shard import Shard, shard_placement_fn
+from ..utils.validation import assign_to_hosts_then_ranks, mesh_rank_hosts
+
+
+@dataclass(frozen=True)
+class MatrixSpec:
+    fqn: str
+    shape: tuple[int, ...]
+    num_blocks: int = 1   # > 1: a block group (e.g. heads) spread over ranks block by block
+
+
+def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, ranks_per_host: int | None = None,
+                    ns_steps: int = 5, carry_loads: bool = False,
+                    fixed_owners: Mapping[str, int] | None = None) -> dict[str, int | tuple[int, ...]]:
+    """Owner rank per matrix (or per block, as a tuple of blocks-per-rank, for block groups)."""
+    hosts = mesh_rank_hosts(num_ranks, ranks_per_host)
+    loads = [0.0] * num_ranks
+    out: dict[str, int | tuple[int, ...]] = {}
+    for group in groups:
+        if not carry_loads:
+            loads = [0.0] * num_ranks
+        whole = [m for m in group if m.num_blocks <= 1]
+        for m in whole:
+            if fixed_owners and m.fqn in fixed_owners:
+                out[m.fqn] = fixed_owners[m.fqn]
+                loads[out[m.fqn]] += newton_schulz_cost(m.shape, ns_steps)
+        free = [m for m in whole if m.fqn not in out]
+        owners = assign_to_hosts_then_ranks([newton_schulz_cost(m.shape, ns_steps) for m in free], hosts, loads)
+        for m, r in zip(free, owners):
+            out[m.fqn] = r
+        for m in group:
+            if m.num_blocks <= 1:
+                continue
+            rows = m.shape[0] // m.num_blocks
+            cost = newton_schulz_cost((rows, *m.shape[1:]), ns_steps)
+            per_block = assign_to_hosts_then_ranks([cost] * m.num_blocks, hosts, loads)
+            counts = [0] * num_ranks
+            for r in per_block:
+                counts[r] += 1
+            out[m.fqn] = tuple(counts)
+    return out
+
+
+def materialize_dist_muon_buckets(named_params, mesh, *, initial: Sequence[str], blocks: Sequence[Sequence[str]],
+                                  final: Sequence[str], is_matrix=None, num_blocks_of=None,
+                                  mp_policy: MixedPrecisionPolicy | None = None, carry_loads: bool = True,
+                                  ranks_per_host: int | None = None) -> list[BucketSpec]:
+    """BucketSpecs for a Muon-trained model: ``initial`` / ``final`` pattern groups stay ``Shard(0)``
+    (AdamW parameters); each entry of ``blocks`` becomes one mixed bucket whose matrices are owned
+    whole (or block-sharded when ``num_blocks_of`` says so) and whose vectors are ``Shard(0)``.
+    All buckets sum gradients (``ReduceOp.SUM``), as the reference's recipe does."""
+    from ..parallel.comm import mesh_group
+
+    _, _, W, _ = mesh_group(mesh)
+    named = list(named_params)
+    is_matrix = is_matrix or (lambda n, p: p.dim() >= 2)
+    mp = mp_policy or MixedPrecisionPolicy()
+    groups = []
+    for pats in blocks:
+        g = []
+        for n, p in named:
+            if any(fnmatch.fnmatchcase(n, pat) or n.startswith(pat + ".") for pat in pats) and is_matrix(n, p):
+                nb = num_blocks_of(n, p) if num_blocks_of else 1
+                g.append(MatrixSpec(n, tuple(p.shape), nb))
+        groups.append(g)
+    owners = assign_matrices(groups, W, ranks_per_host=ranks_per_host, carry_loads=carry_loads)
+
+    def block_fn(named_in, mesh_in):
+        res = {}
+        for n, p in named_in:
+            o = owners.get(n)
+            if o is None:
+                res[n] = MixedBucketPlacement(Shard(0))
+            elif isinstance(o, tuple):
+                res[n] = MixedBucketPlacement(BlockShard(o, 0))
+            else:
+                res[n] = MixedBucketPlacement(BucketedOwned(((o, 0, p.shape[0]),)))
+        return res
+
+    kw = dict(mesh=mesh, mp_policy=mp, gradient_reduce_op=dist.ReduceOp.SUM)
+    specs = []
+    if initial:
+        specs.append(BucketSpec(tuple(initial), placement_fn=shard_placement_fn(0), **kw))
+    for pats in blocks:
+        specs.append(BucketSpec(tuple(pats), placement_fn=block_fn, **kw))
+    if final:
+        specs.append(BucketSpec(tuple(final), placement_fn=shard_placement_fn(0), reshard_after_forward=False, **kw))
+    return specs

@@ -1,0 +1,118 @@
+"""Newton-Schulz orthogonalisation on the tcgen05 GEMM, with the polynomial fused in epilogues.
+
+Per step (coefficients a, b, c), for ``X`` of shape ``[s, l]`` with ``s <= l``::
+
+    A = X X^T                      one GEMM
+    B = b*A + c*A@A                one GEMM, epilogue  c*acc + b*A
+    X = a*X + B@X                  one GEMM, epilogue  acc + a*X
+
+Tall matrices use ``A = X^T X`` and ``X = a*X + X@B`` instead, through the GEMM's transposed
+operand modes, so no transpose copy is ever made. Math parity with the reference's
+``_zeropower_via_newtonschulz`` (``dist_muon/optimizer.py:2120-2151``): bf16 operands, fp32
+accumulation, Frobenius normalisation first.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import count_launch
+from .gemm import gemm
+
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+_declared = False
+
+
+def _ensure():
+    global _declared
+    if not _declared:
+        c = ctypes
+        vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+        _lib.declare("fsb_muon_prepare", [vp, vp, i32, vp, vp, i64, f32, i32, vp])
+        _lib.declare("fsb_muon_scale", [vp, vp, i64, f32, vp])
+        _lib.declare("fsb_muon_update", [vp, i32, vp, i64, f32, f32, vp])
+        _declared = True
+
+
+def ns_iterations(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> torch.Tensor:
+    """Run the iteration on an already normalised bf16 matrix ``x`` (any aspect ratio)."""
+    a, b, c = coeffs
+    rows, cols = x.shape
+    wide = rows <= cols
+    s = min(rows, cols)
+    A = torch.empty(s, s, dtype=x.dtype, device=x.device)
+    B = torch.empty(s, s, dtype=x.dtype, device=x.device)
+    nxt = torch.empty_like(x)
+    for _ in range(steps):
+        if wide:
+            gemm(x, x, out=A)                                   # A = X X^T
+            gemm(A, A, out=B, c=A, alpha=c, beta=b)             # B = b A + c A A   (A symmetric)
+            gemm(B, x, b_t=True, out=nxt, c=x, alpha=1.0, beta=a)  # X = a X + B X
+        else:
+            gemm(x, x, a_t=True, b_t=True, out=A)               # A = X^T X
+            gemm(A, A, out=B, c=A, alpha=c, beta=b)
+            gemm(x, B, out=nxt, c=x, alpha=1.0, beta=a)         # X = a X + X B     (B symmetric)
+        x, nxt = nxt, x
+    return x
+
+
+def newton_schulz(g: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
+    """Approximate polar factor of ``g`` ([rows, cols] or batched [n, rows, cols]); returns bf16."""
+    if g.dim() == 3:
+        return torch.stack([newton_schulz(m, steps, coeffs, eps) for m in g])
+    x = g.to(torch.bfloat16)
+    x = x / x.float().norm().clamp_min(eps).to(torch.bfloat16) if not x.is_cuda else _normalise_cuda(x, eps)
+    return ns_iterations(x.contiguous(), steps, coeffs)
+
+
+def _normalise_cuda(x: torch.Tensor, eps: float) -> torch.Tensor:
+    _ensure()
+    x = x.contiguous().clone()
+    ss = (x.float() ** 2).sum().reshape(1)
+    rc = _lib.load().fsb_muon_scale(x.data_ptr(), ss.data_ptr(), x.numel(), eps, _lib.stream_ptr(x.device))
+    _lib.check(rc, "fsb_muon_scale")
+    count_launch()
+    return x
+
+
+def muon_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: float, nesterov: bool, steps: int,
+                    coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
+    """Momentum update (in place, fp32) + Nesterov + normalise + Newton-Schulz; returns the bf16
+    direction with the shape of ``grad`` (2-D)."""
+    assert grad.dim() == 2 and momentum.shape == grad.shape
+    if not grad.is_cuda:
+        momentum.lerp_(grad.float(), 1 - mu)
+        u = grad.float().lerp(momentum, mu) if nesterov else momentum
+        x = u.to(torch.bfloat16)
+        x = x / x.float().norm().clamp_min(eps).to(torch.bfloat16)
+        return ns_iterations(x.contiguous(), steps, coeffs)
+    _ensure()
+    lib = _lib.load()
+    g = grad.contiguous()
+    assert momentum.is_contiguous() and momentum.dtype == torch.float32
+    u = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
+    ss = torch.zeros(1, dtype=torch.float32, device=g.device)
+    s = _lib.stream_ptr(g.device)
+    rc = lib.fsb_muon_prepare(momentum.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), u.data_ptr(),
+                              ss.data_ptr(), g.numel(), mu, int(nesterov), s)
+    _lib.check(rc, "fsb_muon_prepare")
+    rc = lib.fsb_muon_scale(u.data_ptr(), ss.data_ptr(), u.numel(), eps, s)
+    _lib.check(rc, "fsb_muon_scale")
+    count_launch(2)
+    return ns_iterations(u, steps, coeffs)
+
+
+def muon_apply_(param: torch.Tensor, direction: torch.Tensor, lr: float, weight_decay: float, ratio: float):
+    """``p <- p (1 - lr*wd) - lr*ratio*direction`` in place."""
+    if not param.is_cuda:
+        param.mul_(1 - lr * weight_decay).add_(direction.to(param.dtype), alpha=-lr * ratio)
+        return
+    _ensure()
+    assert param.is_contiguous() and direction.is_contiguous() and direction.dtype == torch.bfloat16
+    rc = _lib.load().fsb_muon_update(param.data_ptr(), int(param.dtype == torch.float32), direction.data_ptr(),
+                                     param.numel(), 1.0 - lr * weight_decay, lr * ratio,
+                                     _lib.stream_ptr(param.device))
+    _lib.check(rc, "fsb_muon_update")
+    count_launch()
