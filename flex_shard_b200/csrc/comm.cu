@@ -1,0 +1,242 @@
+// Collectives over NVLink peer memory for one process per GPU.
+//
+// Every rank maps the same symmetric buffer of all peers (the Python side exchanges the
+// mappings), so a kernel can read or write any rank's shard with plain loads and stores.
+// Ordering between ranks uses 32-bit epoch flags inside the symmetric buffer:
+//   flag[slot][src_rank] on rank r  =  "src_rank has reached epoch e for this slot"
+// A producer publishes with a system-scope release after its data is written; a consumer
+// spins with system-scope acquires, for a bounded number of polls, and records
+// FSB_ERR_WAIT_TIMEOUT_PEER in the status word when the flag never arrives (the kernel then
+// skips its work and returns, so the context stays usable).
+//
+// Kernels:
+//   signal        publish an epoch to every peer's flag row
+//   gather_pull   wait for the peers' epoch, then copy a list of (peer source -> local
+//                 destination) segments: all-gather and copy-out into per-parameter buffers
+//                 in one pass (replaces NCCL all-gather + the strided copy-out)
+//   reduce_adamw  wait for the peers' epoch, then for every element of this rank's shard sum
+//                 the W peers' gradient rows in rank order (deterministic), scale, apply AdamW
+//                 to the bf16/fp32 master shard and fp32 moments: reduce-scatter, cast/scale
+//                 and the sharded optimizer in one pass over the data
+//   reduce_pull   the same reduction without the optimizer
+#include "common.cuh"
+
+namespace {
+using namespace fsb;
+
+constexpr int MAX_RANKS = 16;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Returns false on timeout. Epochs only grow, so ">= epoch" also accepts a peer that is ahead.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, uint32_t max_polls) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
+    if (static_cast<int32_t>(ld_acquire_sys(p) - epoch) >= 0) return true;
+    if (i > 64) __nanosleep(200);
+  }
+  return false;
+}
+
+// All threads of the CTA return the same verdict.
+__device__ __forceinline__ bool cta_wait_peers(const uint32_t* my_flags, int world, uint32_t epoch,
+                                               uint32_t max_polls, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag(my_flags + threadIdx.x, epoch, max_polls)) {
+      s_ok = 0;
+      atomicExch(status, FSB_ERR_WAIT_TIMEOUT_PEER);
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__global__ void signal_kernel(PeerPtrs flags, int rank, int world, uint32_t epoch) {
+  // flags.p[r] = address of this slot's flag row on rank r
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(flags.p[threadIdx.x]) + rank, epoch);
+  }
+}
+
+__global__ void wait_kernel(const uint32_t* my_flags, int world, uint32_t epoch, uint32_t max_polls,
+                            int* status) {
+  cta_wait_peers(my_flags, world, epoch, max_polls, status);
+}
+
+struct SegDesc {
+  const void* src;
+  void* dst;
+  long long n;  // bytes
+  int mode;
+  int pad;
+};
+
+__global__ void gather_pull_kernel(const SegDesc* __restrict__ descs, const uint32_t* my_flags, int world,
+                                   uint32_t epoch, uint32_t max_polls, int* status) {
+  if (my_flags != nullptr && !cta_wait_peers(my_flags, world, epoch, max_polls, status)) return;
+  const SegDesc d = descs[blockIdx.y];
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(d.src) | reinterpret_cast<uintptr_t>(d.dst);
+  if ((al & 15) == 0) {
+    const long long nv = d.n / 16;
+    const uint4* s = static_cast<const uint4*>(d.src);
+    uint4* t = static_cast<uint4*>(d.dst);
+    // four independent 16-byte loads in flight per thread: NVLink latency is long
+    long long i = tid;
+    for (; i + 3 * stride < nv; i += 4 * stride) {
+      const uint4 a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
+      t[i] = a; t[i + stride] = b; t[i + 2 * stride] = c; t[i + 3 * stride] = e;
+    }
+    for (; i < nv; i += stride) t[i] = s[i];
+    for (long long j = nv * 16 + tid; j < d.n; j += stride)
+      static_cast<uint8_t*>(d.dst)[j] = static_cast<const uint8_t*>(d.src)[j];
+  } else {
+    for (long long j = tid; j < d.n; j += stride)
+      static_cast<uint8_t*>(d.dst)[j] = static_cast<const uint8_t*>(d.src)[j];
+  }
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2_sqrt;
+};
+
+// rows.p[r] = address of rank r's gradient row that belongs to THIS rank (fp32, n elements).
+template <typename PT, bool WITH_ADAM>
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel(PeerPtrs rows, int world, long long n, float scale, float* __restrict__ g_out,
+                   PT* __restrict__ p, float* __restrict__ m, float* __restrict__ v, AdamArgs a,
+                   const uint32_t* my_flags, uint32_t epoch, uint32_t max_polls, int* status) {
+  if (my_flags != nullptr && !cta_wait_peers(my_flags, world, epoch, max_polls, status)) return;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long n4 = n / 4;
+  for (long long i = tid; i < n4; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {  // fixed rank order: the sum is deterministic
+      const float4 t = static_cast<const float4*>(rows.p[r])[i];
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    float g[4] = {acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale};
+    if (g_out) *reinterpret_cast<float4*>(g_out + i * 4) = make_float4(g[0], g[1], g[2], g[3]);
+    if (WITH_ADAM) {
+      const float4 mv = *reinterpret_cast<const float4*>(m + i * 4);
+      const float4 vv = *reinterpret_cast<const float4*>(v + i * 4);
+      float mm[4] = {mv.x, mv.y, mv.z, mv.w}, vq[4] = {vv.x, vv.y, vv.z, vv.w};
+      float pv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pv[j] = static_cast<float>(p[i * 4 + j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        pv[j] *= (1.f - a.lr * a.weight_decay);
+        mm[j] = mm[j] + (1.f - a.beta1) * (g[j] - mm[j]);
+        vq[j] = a.beta2 * vq[j] + (1.f - a.beta2) * g[j] * g[j];
+        pv[j] -= (a.lr / a.bias1) * (mm[j] / (sqrtf(vq[j]) / a.bias2_sqrt + a.eps));
+        p[i * 4 + j] = static_cast<PT>(pv[j]);
+      }
+      *reinterpret_cast<float4*>(m + i * 4) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(v + i * 4) = make_float4(vq[0], vq[1], vq[2], vq[3]);
+    }
+  }
+  for (long long i = n4 * 4 + tid; i < n; i += stride) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) acc += static_cast<const float*>(rows.p[r])[i];
+    const float g = acc * scale;
+    if (g_out) g_out[i] = g;
+    if (WITH_ADAM) {
+      float pv = static_cast<float>(p[i]) * (1.f - a.lr * a.weight_decay);
+      const float mm = m[i] + (1.f - a.beta1) * (g - m[i]);
+      const float vq = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
+      pv -= (a.lr / a.bias1) * (mm / (sqrtf(vq) / a.bias2_sqrt + a.eps));
+      p[i] = static_cast<PT>(pv);
+      m[i] = mm;
+      v[i] = vq;
+    }
+  }
+}
+
+inline int grid_for(long long n, int per_thread) {
+  long long b = (n + 256LL * per_thread - 1) / (256LL * per_thread);
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  return static_cast<int>(b);
+}
+inline int ok() { return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH; }
+
+}  // namespace
+
+// flag_rows[r]: address (in this process's address space) of the slot's flag row on rank r.
+FSB_API int fsb_comm_signal(const unsigned long long* flag_rows, int rank, int world, unsigned epoch,
+                            cudaStream_t stream) {
+  if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
+  PeerPtrs f;
+  for (int r = 0; r < world; ++r) f.p[r] = reinterpret_cast<void*>(flag_rows[r]);
+  signal_kernel<<<1, 32, 0, stream>>>(f, rank, world, epoch);
+  return ok();
+}
+
+FSB_API int fsb_comm_wait(const void* my_flags, int world, unsigned epoch, unsigned max_polls, int* status,
+                          cudaStream_t stream) {
+  if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
+  wait_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t*>(my_flags), world, epoch, max_polls, status);
+  return ok();
+}
+
+// descs: device array of nseg {src, dst, bytes, mode, pad} records; sources may be peer addresses.
+// my_flags may be null (no wait).
+FSB_API int fsb_comm_gather_pull(const void* descs, int nseg, int blocks_per_seg, const void* my_flags,
+                                 int world, unsigned epoch, unsigned max_polls, int* status,
+                                 cudaStream_t stream) {
+  if (nseg <= 0) return FSB_OK;
+  if (nseg > 65535 || world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
+  dim3 grid(blocks_per_seg < 1 ? 1 : blocks_per_seg, nseg);
+  gather_pull_kernel<<<grid, 256, 0, stream>>>(static_cast<const SegDesc*>(descs),
+                                               static_cast<const uint32_t*>(my_flags), world, epoch,
+                                               max_polls, status);
+  return ok();
+}
+
+// rows[r]: address of rank r's fp32 gradient row for this rank (n elements, 16-byte aligned).
+// g_out may be null. With p != null the AdamW update is applied in the same pass.
+FSB_API int fsb_comm_reduce_rows(const unsigned long long* rows, int world, long long n, float scale,
+                                 float* g_out, void* p, int p_fp32, float* m, float* v, float lr,
+                                 float beta1, float beta2, float eps, float weight_decay, int step,
+                                 const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
+                                 cudaStream_t stream) {
+  if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
+  if (n <= 0) return FSB_OK;
+  PeerPtrs rp;
+  for (int r = 0; r < world; ++r) {
+    if (rows[r] & 15) return FSB_ERR_BAD_ARG;
+    rp.p[r] = reinterpret_cast<void*>(rows[r]);
+  }
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, static_cast<float>(step)),
+             sqrtf(1.f - powf(beta2, static_cast<float>(step)))};
+  const int grid = grid_for(n, 8);
+  const uint32_t* fl = static_cast<const uint32_t*>(my_flags);
+  if (p == nullptr) {
+    reduce_rows_kernel<float, false><<<grid, 256, 0, stream>>>(rp, world, n, scale, g_out, nullptr, nullptr,
+                                                               nullptr, a, fl, epoch, max_polls, status);
+  } else if (p_fp32) {
+    reduce_rows_kernel<float, true><<<grid, 256, 0, stream>>>(rp, world, n, scale, g_out, static_cast<float*>(p),
+                                                              m, v, a, fl, epoch, max_polls, status);
+  } else {
+    reduce_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(
+        rp, world, n, scale, g_out, static_cast<__nv_bfloat16*>(p), m, v, a, fl, epoch, max_polls, status);
+  }
+  return ok();
+}

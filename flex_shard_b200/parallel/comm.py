@@ -181,6 +181,24 @@ class Comm:
 
 
 _comm_cache: dict[Any, Comm] = {}
+_default_backend = None  # "symm" routes GPU meshes to the peer-memory collectives
+
+
+def set_default_backend(name: str | None) -> None:
+    """``"symm"``: all-gather / reduce-scatter of GPU meshes run on this library's NVLink
+    peer-memory kernels; ``None`` / ``"nccl"``: on torch.distributed. Also settable with the
+    environment variable ``FSB200_COMM``."""
+    global _default_backend
+    if name not in (None, "nccl", "symm"):
+        raise ValueError(f"unknown comm backend {name!r}")
+    _default_backend = None if name == "nccl" else name
+    _comm_cache.clear()
+
+
+def _backend() -> str | None:
+    import os
+
+    return _default_backend or (os.environ.get("FSB200_COMM") or None)
 
 
 def mesh_group(mesh) -> tuple[dist.ProcessGroup | None, int, int, torch.device]:
@@ -216,6 +234,11 @@ def comm_for(mesh) -> Comm:
     key = (id(g), rank, ws, str(dev))
     c = _comm_cache.get(key)
     if c is None:
-        c = Comm(g, rank, ws, dev)
+        if _backend() == "symm" and dev.type == "cuda" and ws > 1:
+            from .symm import SymmComm
+
+            c = SymmComm(g, rank, ws, dev)
+        else:
+            c = Comm(g, rank, ws, dev)
         _comm_cache[key] = c
     return c

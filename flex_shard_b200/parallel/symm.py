@@ -1,0 +1,223 @@
+"""Symmetric memory over NVLink and the collectives built on it.
+
+``SymmRegion`` is one symmetric allocation (same size on every rank of a group, every rank
+maps every peer's copy) carved into a flag area and a payload area. ``SymmComm`` is a drop-in
+``Comm`` whose all-gather and reduce-scatter are this library's own peer-memory kernels
+(``csrc/comm.cu``): ranks publish epoch flags, consumers pull remote rows with plain loads.
+The reduce-scatter sums the W rows in rank order, so its result is deterministic and equal
+on every run (NCCL's order depends on the algorithm it picks).
+
+The allocation and the exchange of mappings use ``torch.distributed._symmetric_memory``
+(CUDA VMM handles over the process group's store); nothing else of it is used.
+
+Parity: this is the native counterpart of the reference's symmetric-memory transport
+(``custom_placements/owner_rows_transport.py:182-244``); on one NVSwitch domain every peer is
+one hop away, so its host/relay planning reduces to direct peer access.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops._lib import count_launch
+from .comm import Comm, ReducePlan
+
+FLAG_BYTES = 64 * 1024          # 1024 slots x 16 ranks x 4 bytes
+MAX_RANKS = 16
+DEFAULT_MAX_POLLS = 20_000_000  # x >=200 ns back-off: several seconds before a wait gives up
+_declared = False
+
+
+def _ensure():
+    global _declared
+    if _declared:
+        return
+    c = ctypes
+    vp, i32, i64, u32, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_uint, c.c_float
+    _lib.declare("fsb_comm_signal", [vp, i32, i32, u32, vp])
+    _lib.declare("fsb_comm_wait", [vp, i32, u32, u32, vp, vp])
+    _lib.declare("fsb_comm_gather_pull", [vp, i32, i32, vp, i32, u32, u32, vp, vp])
+    _lib.declare("fsb_comm_reduce_rows", [vp, i32, i64, f32, vp, vp, i32, vp, vp, f32, f32, f32, f32, f32, i32,
+                                          vp, u32, u32, vp, vp])
+    _declared = True
+
+
+class SymmRegion:
+    """A symmetric buffer: ``[flags (64 KB) | payload]`` on every rank, peers mapped."""
+
+    def __init__(self, group: dist.ProcessGroup, payload_bytes: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        _ensure()
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > MAX_RANKS:
+            raise ValueError(f"symmetric regions support up to {MAX_RANKS} ranks")
+        self.device = device
+        self.payload_bytes = (payload_bytes + 255) // 256 * 256
+        total = FLAG_BYTES + self.payload_bytes
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.buf[:FLAG_BYTES].zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone signals
+        self.max_polls = DEFAULT_MAX_POLLS
+
+    # ---- addressing
+    @property
+    def payload(self) -> torch.Tensor:
+        return self.buf[FLAG_BYTES:]
+
+    def peer_payload_addr(self, r: int, offset: int = 0) -> int:
+        return self.peer_base[r] + FLAG_BYTES + offset
+
+    def flag_row_addr(self, r: int, slot: int) -> int:
+        return self.peer_base[r] + slot * MAX_RANKS * 4
+
+    # ---- flags
+    def signal(self, slot: int, epoch: int) -> None:
+        rows = (ctypes.c_ulonglong * self.world)(*[self.flag_row_addr(r, slot) for r in range(self.world)])
+        rc = _lib.load().fsb_comm_signal(rows, self.rank, self.world, epoch & 0xFFFFFFFF,
+                                         _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_signal")
+        count_launch()
+
+    def wait(self, slot: int, epoch: int) -> None:
+        rc = _lib.load().fsb_comm_wait(self.flag_row_addr(self.rank, slot), self.world, epoch & 0xFFFFFFFF,
+                                       self.max_polls, _lib.status_word(self.device).data_ptr(),
+                                       _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_wait")
+        count_launch()
+
+
+_SEG = 32  # bytes per descriptor
+
+
+def _pack_descs(segments, device) -> torch.Tensor:
+    """(src_addr, dst_addr, nbytes) triples -> device tensor of SegDesc records."""
+    import struct
+
+    raw = bytearray()
+    for src, dst, n in segments:
+        raw += struct.pack("<QQqii", src, dst, n, 0, 0)
+    host = torch.frombuffer(raw, dtype=torch.uint8).clone().pin_memory()
+    return host.to(device, non_blocking=True)
+
+
+class SymmComm(Comm):
+    """``Comm`` whose all-gather / reduce-scatter run on peer memory instead of NCCL.
+
+    Send data is staged into the symmetric payload (one local copy), published with an epoch
+    flag, and pulled by every consumer. Separate staging areas and flag slots serve gathers and
+    reductions, which run on different streams.
+    """
+
+    SLOT_AG_READY, SLOT_AG_DONE, SLOT_RS_READY, SLOT_RS_DONE = 0, 1, 2, 3
+
+    def __init__(self, group, rank, world_size, device, ag_bytes: int = 0, rs_bytes: int = 0):
+        super().__init__(group, rank, world_size, device)
+        self._ag: SymmRegion | None = None
+        self._rs: SymmRegion | None = None
+        self._ag_epoch = 0
+        self._rs_epoch = 0
+        self._ag_hint, self._rs_hint = ag_bytes, rs_bytes
+        self._desc_cache: dict = {}
+
+    @classmethod
+    def from_mesh(cls, mesh, **kw) -> "SymmComm":
+        from .comm import mesh_group
+
+        g, rank, ws, dev = mesh_group(mesh)
+        return cls(g, rank, ws, dev, **kw)
+
+    def new_like(self) -> "SymmComm":
+        return SymmComm(self.group, self.rank, self.world_size, self.device, self._ag_hint, self._rs_hint)
+
+    def _region(self, which: str, nbytes: int) -> SymmRegion:
+        cur = self._ag if which == "ag" else self._rs
+        if cur is None or cur.payload_bytes < nbytes:
+            hint = self._ag_hint if which == "ag" else self._rs_hint
+            size = max(nbytes, hint)
+            if cur is not None:
+                torch.cuda.synchronize(self.device)
+                size = max(size, 2 * cur.payload_bytes)
+            cur = SymmRegion(self.group, size, self.device)
+            if which == "ag":
+                self._ag, self._ag_epoch = cur, 0
+            else:
+                self._rs, self._rs_epoch = cur, 0
+            self._desc_cache.clear()
+        return cur
+
+    # ------------------------------------------------------------------ all-gather
+    def all_gather_into_tensor(self, out: torch.Tensor, inp: torch.Tensor, async_op: bool = False):
+        if self.world_size == 1:
+            return super().all_gather_into_tensor(out, inp)
+        W = self.world_size
+        nbytes = inp.numel() * inp.element_size()
+        assert out.numel() * out.element_size() == W * nbytes and out.is_contiguous() and inp.is_contiguous()
+        reg = self._region("ag", nbytes)
+        self._ag_epoch += 1
+        e = self._ag_epoch
+        if e > 1:
+            reg.wait(self.SLOT_AG_DONE, e - 1)          # peers finished reading the previous payload
+        reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
+        reg.signal(self.SLOT_AG_READY, e)
+        key = ("ag", out.data_ptr(), nbytes)
+        descs = self._desc_cache.get(key)
+        if descs is None:
+            segs = [(reg.peer_payload_addr(r), out.data_ptr() + r * nbytes, nbytes) for r in range(W)]
+            descs = _pack_descs(segs, self.device)
+            if len(self._desc_cache) < 4096:
+                self._desc_cache[key] = descs
+        blocks = max(1, min(64, nbytes // (64 * 1024)))
+        rc = _lib.load().fsb_comm_gather_pull(descs.data_ptr(), W, blocks, reg.flag_row_addr(self.rank, self.SLOT_AG_READY),
+                                              W, e, reg.max_polls, _lib.status_word(self.device).data_ptr(),
+                                              _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_gather_pull")
+        count_launch()
+        reg.signal(self.SLOT_AG_DONE, e)
+        return None
+
+    # ------------------------------------------------------------------ reduce-scatter
+    def reduce_scatter_tensor(self, out: torch.Tensor, inp: torch.Tensor, plan: ReducePlan, async_op: bool = False):
+        if self.world_size == 1 or inp.dtype != torch.float32 or out.numel() % 4 != 0:
+            return super().reduce_scatter_tensor(out, inp, plan, async_op)
+        W = self.world_size
+        self._apply_plan_pre(inp, plan)
+        n = out.numel()
+        nbytes = inp.numel() * 4
+        assert inp.numel() == W * n and out.dtype == torch.float32 and out.is_contiguous()
+        reg = self._region("rs", nbytes)
+        self._rs_epoch += 1
+        e = self._rs_epoch
+        if e > 1:
+            reg.wait(self.SLOT_RS_DONE, e - 1)
+        reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
+        reg.signal(self.SLOT_RS_READY, e)
+        if plan.op == "avg":
+            scale = 1.0 / W
+        elif plan.op == "premul_sum":
+            scale = float(plan.premul)
+        else:
+            scale = 1.0
+        if plan.post_divide is not None:
+            scale /= plan.post_divide
+        rows = (ctypes.c_ulonglong * W)(*[reg.peer_payload_addr(r, self.rank * n * 4) for r in range(W)])
+        rc = _lib.load().fsb_comm_reduce_rows(rows, W, n, scale, out.data_ptr(), None, 0, None, None,
+                                              0.0, 0.0, 0.0, 0.0, 0.0, 1,
+                                              reg.flag_row_addr(self.rank, self.SLOT_RS_READY), e, reg.max_polls,
+                                              _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_reduce_rows")
+        count_launch()
+        reg.signal(self.SLOT_RS_DONE, e)
+        return None
+
+
+def symm_comm_for(mesh, **kw) -> SymmComm:
+    return SymmComm.from_mesh(mesh, **kw)
