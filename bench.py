@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--local-batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm", default=os.environ.get("FSB200_COMM", "symm"), choices=["symm", "nccl"],
+                    help="collectives of the sharded arm: this library's NVLink peer-memory kernels or NCCL")
     return ap.parse_args()
 
 
@@ -189,6 +191,9 @@ def build_ours(args, world):
     if world > 1:
         from torch.distributed.device_mesh import init_device_mesh
 
+        from flex_shard_b200.parallel.comm import set_default_backend
+
+        set_default_backend(args.comm)
         mesh = init_device_mesh("cuda", (world,))
     flex_shard(model, llama_buckets(model, mesh=mesh))
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
@@ -261,6 +266,7 @@ def run_ours(args, rank, local, world):
                                 f"ffn {cfg.ffn_hidden}, vocab {cfg.vocab_size})",
                        "global_batch": args.local_batch * world, "seq_len": S, "parallelism": f"dp{world}",
                        "placement": "Shard(0) per-layer buckets, prefetch, bf16 params / fp32 reduce+AdamW state",
+                       "collectives": (args.comm if world > 1 else "none (1 rank)"),
                        "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "loss": loss_val, "peak_mem_gib": round(peak_gb, 2),

@@ -52,6 +52,50 @@ struct GemmArgs {
   int* status;
 };
 
+// All-gather fused into the GEMM: `n_stagers` CTAs of the grid pull the weight's row shards from
+// the peers' memory (NVLink) into the local gathered buffer, 16 KB pieces through a shared-memory
+// ring of bulk copies, in the order the GEMM consumes them; the GEMM CTAs wait per 256-row chunk.
+constexpr int AG_PIECE = 16384;
+constexpr int AG_RING = 11;          // 176 KB of the CTA's shared memory
+constexpr int AG_LAG = 3;            // store groups allowed in flight before completion is published
+constexpr int AG_MAX_RANKS = 16;
+struct AgArgs {
+  const uint8_t* peer[AG_MAX_RANKS];  // peer[r]: rank r's shard of the weight (shard_bytes each)
+  uint8_t* local;                     // gathered weight [N, K] bf16, row-major, ld == K
+  long long shard_bytes, total_bytes, chunk_bytes;  // chunk = BN rows
+  int* counters;                      // [tiles_n] pieces landed per chunk (monotonic across calls)
+  int call_index;                     // 1-based number of this call for these counters
+  int n_stagers;
+  const uint32_t* peer_flags;         // this rank's flag row: peers' shards are valid from `epoch` on
+  int world;
+  uint32_t epoch, max_polls;
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void tile_coords_nmajor(int tile, int tiles_m, int& tm, int& tn) {
+  tn = tile / tiles_m;
+  tm = tile % tiles_m;
+}
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = GROUP_M * tiles_n;
   const int group = tile / per_group;
@@ -62,9 +106,10 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / rows;
 }
 
+template <bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const GemmArgs args) {
+                 const GemmArgs args, const AgArgs ag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -82,6 +127,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int tiles_n = (args.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (args.K + BK - 1) / BK;
+  const bool stager = AG && static_cast<int>(blockIdx.x) < ag.n_stagers;
+  const int tile0 = AG ? static_cast<int>(blockIdx.x) - ag.n_stagers : static_cast<int>(blockIdx.x);
+  const int tile_step = AG ? static_cast<int>(gridDim.x) - ag.n_stagers : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -95,26 +143,147 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 1 && !stager) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = stager ? 0u : *tmem_slot;
 
-  if (warp == 0) {
+  if (stager) {
+    // ------------------------------------------------------------ all-gather stager CTA
+    if constexpr (AG) {
+      if (threadIdx.x == 0) {
+        uint64_t* ring_bar = bars + 2 * STAGES + 8;  // [AG_RING], past the GEMM's barriers
+        for (int i = 0; i < AG_RING; ++i) mbar_init(&ring_bar[i], 1);
+        mbar_fence_init();
+        bool ok = true;
+        // peers' shards must be valid (their optimizer step of this epoch has been published)
+        for (int r = 0; r < ag.world && ok; ++r) {
+          uint32_t polls = 0;
+          while (static_cast<int32_t>(ld_acquire_sys_u32(ag.peer_flags + r) - ag.epoch) < 0) {
+            if (++polls > ag.max_polls) {
+              ok = false;
+              break;
+            }
+            if (polls > 64) __nanosleep(200);
+          }
+        }
+        if (!ok) {
+          atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_PEER);
+        } else {
+          // Work list of this stager: inside every 256-row chunk a contiguous run of pieces, chunks in
+          // the order the GEMM consumes them. Completion is published once per (stager, chunk).
+          const int S = ag.n_stagers, me = blockIdx.x;
+          const long long n_chunks = (ag.total_bytes + ag.chunk_bytes - 1) / ag.chunk_bytes;
+          auto chunk_pieces = [&](long long c) {
+            long long hi = (c + 1) * ag.chunk_bytes;
+            if (hi > ag.total_bytes) hi = ag.total_bytes;
+            return (hi - c * ag.chunk_bytes + AG_PIECE - 1) / AG_PIECE;
+          };
+          auto my_lo = [&](long long c) { return chunk_pieces(c) * me / S; };
+          auto my_hi = [&](long long c) { return chunk_pieces(c) * (me + 1) / S; };
+          // iterator over (chunk, piece) pairs of this stager, used twice: for loads (ahead) and stores
+          struct It { long long c, p; };
+          auto advance = [&](It& it) {
+            ++it.p;
+            while (it.c < n_chunks && it.p >= my_hi(it.c)) {
+              ++it.c;
+              if (it.c < n_chunks) it.p = my_lo(it.c);
+            }
+          };
+          auto first = [&]() {
+            It it{0, my_lo(0)};
+            while (it.c < n_chunks && it.p >= my_hi(it.c)) {
+              ++it.c;
+              if (it.c < n_chunks) it.p = my_lo(it.c);
+            }
+            return it;
+          };
+          auto off_of = [&](const It& it) { return it.c * ag.chunk_bytes + it.p * static_cast<long long>(AG_PIECE); };
+          auto len_of = [&](const It& it) {
+            const long long rem = ag.total_bytes - off_of(it);
+            return static_cast<uint32_t>(rem < AG_PIECE ? rem : AG_PIECE);
+          };
+          long long n_loaded = 0, n_stored = 0;
+          It ld = first(), st = first();
+          auto issue_load = [&]() {
+            const long long off = off_of(ld);
+            const int owner = static_cast<int>(off / ag.shard_bytes);
+            const int slot = static_cast<int>(n_loaded % AG_RING);
+            mbar_expect_tx(&ring_bar[slot], len_of(ld));
+            bulk_load(smem + slot * AG_PIECE, ag.peer[owner] + (off - owner * ag.shard_bytes), len_of(ld),
+                      &ring_bar[slot]);
+            ++n_loaded;
+            advance(ld);
+          };
+          const long long ahead = AG_RING - AG_LAG - 1;
+          while (ld.c < n_chunks && n_loaded < ahead) issue_load();
+          while (st.c < n_chunks && ok) {
+            const int slot = static_cast<int>(n_stored % AG_RING);
+            if (!mbar_wait(&ring_bar[slot], static_cast<uint32_t>(n_stored / AG_RING) & 1, abort_flag)) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              ok = false;
+              break;
+            }
+            bulk_store(ag.local + off_of(st), smem + slot * AG_PIECE, len_of(st));
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            ++n_stored;
+            const long long c_done = st.c;
+            const long long pieces_in_chunk = my_hi(c_done) - my_lo(c_done);
+            advance(st);
+            if (st.c != c_done) {
+              // last piece of this chunk: wait for the stores to land, then publish them
+              asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+              asm volatile("fence.proxy.async;" ::: "memory");
+              __threadfence();
+              atomicAdd(ag.counters + static_cast<int>(c_done), static_cast<int>(pieces_in_chunk));
+            } else {
+              // the slot that the next load will reuse must have been read by its store
+              asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(AG_LAG) : "memory");
+            }
+            if (ld.c < n_chunks) issue_load();
+          }
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&map_a);
       tma_prefetch_desc(&map_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int ready_tn = -1;
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        if (AG) tile_coords_nmajor(tile, tiles_m, tm, tn);
+        else tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if (AG && tn != ready_tn) {
+          // wait until every piece of this 256-row chunk of the weight has landed locally
+          const long long lo = static_cast<long long>(tn) * ag.chunk_bytes;
+          long long hi = lo + ag.chunk_bytes;
+          if (hi > ag.total_bytes) hi = ag.total_bytes;
+          const int pieces = static_cast<int>((hi - lo + AG_PIECE - 1) / AG_PIECE);
+          const int target = pieces * ag.call_index;
+          uint32_t polls = 0;
+          while (ld_acquire_gpu(ag.counters + tn) < target) {
+            if (++polls > ag.max_polls || *abort_flag) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_PEER);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            if (polls > 32) __nanosleep(100);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy flag -> async-proxy (TMA) reads
+          ready_tn = tn;
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -156,7 +325,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t a_kstep = args.a_mn ? 2048u : 32u, b_kstep = args.b_mn ? 2048u : 32u;
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
@@ -193,9 +362,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t local_tile = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+    for (int tile = tile0; tile < num_tiles; tile += tile_step, ++local_tile) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (AG) tile_coords_nmajor(tile, tiles_m, tm, tn);
+      else tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
@@ -296,7 +466,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   // Common exit: every loop above is bounded, so all warps arrive here.
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 1 && !stager) {
     if (*abort_flag) {
       // Give copies that were already issued time to land before the CTA's
       // shared memory and TMEM go away.
@@ -414,17 +584,75 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
-  if (g_num_sms[dev] == 0) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static bool plain_attr_set[64] = {false};
+  if (!plain_attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM_BYTES) != cudaSuccess)
       return FSB_ERR_LAUNCH;
-    cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    plain_attr_set[dev] = true;
   }
+  if (g_num_sms[dev] == 0) cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate,
                 d_block_rows, d_block_stride, status};
-  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args);
+  AgArgs none{};
+  gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args, none);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}
+
+// All-gather -> GEMM in one kernel: D[M,N] = A[M,K] . W[N,K]^T where W is row-sharded over
+// `world` ranks (peer_shards[r] = address of rank r's rows, shard_rows each; the last rank may
+// hold padding). `gathered` receives the full weight (it is the GEMM's B operand and stays valid
+// afterwards, e.g. for the backward pass). `counters` is a zero-initialised int array of
+// ceil(N/256) entries that belongs to this weight; `call_index` counts calls using it (1, 2, ...).
+// `peer_flags` / `epoch`: this rank's flag row saying from which epoch on the peers' shards are
+// valid (null: no wait). Launched cooperatively so that stager and GEMM CTAs are co-resident.
+FSB_API int fsb_gemm_bf16_allgather(const void* a, const unsigned long long* peer_shards, void* gathered,
+                                    void* d, int M, int N, int K, long long lda, long long ldd,
+                                    int d_fp32, int world, int shard_rows, int* counters, int call_index,
+                                    int n_stagers, const void* peer_flags, unsigned epoch,
+                                    unsigned max_polls, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > AG_MAX_RANKS) return FSB_ERR_BAD_ARG;
+  const long long shard_bytes = static_cast<long long>(shard_rows) * K * 2;
+  if (shard_bytes % AG_PIECE != 0 || (static_cast<long long>(BN) * K * 2) % AG_PIECE != 0)
+    return FSB_ERR_BAD_ARG;
+  CUtensorMap map_a, map_b;
+  int rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  if (rc != FSB_OK) return rc;
+  rc = fsb_make_tmap_2d(&map_b, gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, BN, BK);
+  if (rc != FSB_OK) return rc;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess)
+      return FSB_ERR_LAUNCH;
+    attr_set[dev] = true;
+  }
+  if (g_num_sms[dev] == 0) cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  if (n_stagers < 1) n_stagers = 1;
+  if (n_stagers > g_num_sms[dev] / 2) n_stagers = g_num_sms[dev] / 2;
+  GemmArgs args{M, N, K, 0, 0, d, ldd, d_fp32, nullptr, 0, 0, 1.f, 0.f, 0, 0, 0, status};
+  AgArgs ag{};
+  for (int r = 0; r < world; ++r) ag.peer[r] = reinterpret_cast<const uint8_t*>(peer_shards[r]);
+  ag.local = static_cast<uint8_t*>(gathered);
+  ag.shard_bytes = shard_bytes;
+  ag.total_bytes = static_cast<long long>(N) * K * 2;
+  ag.chunk_bytes = static_cast<long long>(BN) * K * 2;
+  ag.counters = counters;
+  ag.call_index = call_index;
+  ag.n_stagers = n_stagers;
+  ag.peer_flags = static_cast<const uint32_t*>(peer_flags);
+  ag.world = peer_flags ? world : 0;
+  ag.epoch = epoch;
+  ag.max_polls = max_polls;
+  const int grid = g_num_sms[dev];
+  void* params[] = {&map_a, &map_b, &args, &ag};
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(gemm_bf16_kernel<true>), dim3(grid),
+                                              dim3(NUM_THREADS), params, SMEM_BYTES, stream);
+  return e == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }

@@ -3,7 +3,7 @@
     python -m flex_shard_b200.utils.kernel_cases <case> [--iters N]
 
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, adamw, rmsnorm, swiglu, cross_entropy,
-newton_schulz, fp8_quant, fp8_gemm. Each prints one JSON line with the CUDA-event time (median of
+newton_schulz, fp8_quant, fp8_gemm, allgather_gemm. Each prints one JSON line with the CUDA-event time (median of
 ``iters`` launches after 3 warm-up launches, L2 flushed between launches by writing a 256 MB buffer)
 and the achieved FLOP/s or bytes/s. Inputs are a few hundred MB, larger than the 126 MB L2, so DRAM
 counters of a profiler capture of the same command stay meaningful.
@@ -136,6 +136,20 @@ def main():
         ms = _time(lambda: fp8_linear_forward(x, wq, ws), args.iters)
         out.update(M=M, N=N, K=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9,
                    note="includes the 1x128 activation quantisation")
+    elif args.case == "allgather_gemm":
+        # 8 emulated peers on one GPU (the stager CTAs run the same bulk-copy ring; on a multi-GPU
+        # job the sources are NVLink peer addresses instead of local ones)
+        from flex_shard_b200.ops.fused import AllGatherLinear
+
+        M, N, K, W = 8192, 14336, 4096, 8
+        w = torch.randn(N, K, device=dev).bfloat16()
+        c = N // W
+        shards = [w[r * c:(r + 1) * c].clone() for r in range(W)]
+        lin = AllGatherLinear([t.data_ptr() for t in shards], N, K, c, dev, n_stagers=12)
+        x = torch.randn(M, K, device=dev).bfloat16()
+        ms = _time(lambda: lin(x), args.iters)
+        out.update(M=M, N=N, K=K, world=W, ms=ms, tflops=2.0 * M * N * K / ms / 1e9,
+                   gathered_gbs=N * K * 2 / ms / 1e6)
     else:
         raise SystemExit(f"unknown case {args.case}")
     ops.check_status()
