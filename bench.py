@@ -197,6 +197,8 @@ def build_ours(args, world):
         mesh = init_device_mesh("cuda", (world,))
     flex_shard(model, llama_buckets(model, mesh=mesh))
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    if world > 1 and args.comm == "symm":
+        opt.fuse_into_backward(model)  # AdamW runs inside the fused reduce kernel of each bucket
     return cfg, model, opt
 
 

@@ -87,6 +87,11 @@ def begin_reduce_grad(runtime, grads, reduce_dtype, reduction: GradientReduction
     placement = storage.placement
     comm = storage.reduce_comm
     prep = placement.prepare_reduce_grad(storage.infos_for_reduce, grads, comm, reduce_dtype)
+    fused_opt = getattr(storage, "_fused_opt", None)
+    if fused_opt is not None and prep.extra.get("peer_bucket") is not None:
+        adam = fused_opt.fused_bucket_args(storage)
+        if adam is not None:
+            prep.extra["adam"] = adam
     if stream is None or comm.world_size == 1:
         res = placement.reduce_prepared_grad(prep, comm, reduction)
         runtime.accumulate_sharded_grads(res)

@@ -187,6 +187,8 @@ class BucketRuntime:
         self.needs_sync = False        # holds unreduced unsharded grads (no-sync accumulation)
         self.deferred_params: set[int] = set()
         self._handles: list = []
+        self._bucket_base = None
+        self._bucket_nbytes = 0
 
     # ------------------------------------------------------------------ persistent unsharded params
     def _aliases_storage(self) -> bool:
@@ -198,6 +200,15 @@ class BucketRuntime:
         W = st.comm.world_size
         if self._aliases_storage():
             return []
+        bucket_alloc = getattr(st.placement, "alloc_unsharded_bucket", None)
+        if bucket_alloc is not None:
+            # one buffer for the whole bucket; the parameters are views of it
+            if self.persistent is None:
+                self._bucket_base, self.persistent = bucket_alloc(st)
+                self._bucket_nbytes = self._bucket_base.untyped_storage().size()
+            elif self._bucket_base.untyped_storage().size() != self._bucket_nbytes:
+                self._bucket_base.untyped_storage().resize_(self._bucket_nbytes)
+            return self.persistent
         if self.persistent is None:
             self.persistent = []
             for info in st.infos:
@@ -213,6 +224,9 @@ class BucketRuntime:
 
     def _free_persistent(self) -> None:
         if self.persistent is None or self._aliases_storage():
+            return
+        if getattr(self, "_bucket_base", None) is not None:
+            self._bucket_base.untyped_storage().resize_(0)
             return
         for buf in self.persistent:
             buf.untyped_storage().resize_(0)
@@ -239,7 +253,13 @@ class BucketRuntime:
         if not st.placement.refills_persistent_buffers_in_finish:
             persistent = self._alloc_persistent()
         stream = self.context.unshard_stream
-        self.pending = begin_bucket_unshard(st, persistent, stream)
+        # a gather that lands straight in the persistent buffers refills tensors autograd may have
+        # saved: same values, so the version counters must not move
+        guard = tuple(persistent or ())
+        if self._bucket_base is not None:
+            guard = guard + (self._bucket_base,)
+        with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(guard):
+            self.pending = begin_bucket_unshard(st, persistent, stream)
         self.context.stats["unshards"] += 1
 
     def finish_unshard(self) -> None:
@@ -287,7 +307,11 @@ class BucketRuntime:
             persistent = None
             if not st.placement.refills_persistent_buffers_in_finish:
                 persistent = self._alloc_persistent()
-            self.pending = begin_explicit_bucket_unshard(st, persistent, async_op)
+            guard = tuple(persistent or ())
+            if self._bucket_base is not None:
+                guard = guard + (self._bucket_base,)
+            with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(guard):
+                self.pending = begin_explicit_bucket_unshard(st, persistent, async_op)
             self.context.stats["unshards"] += 1
         handle = _UnshardHandle([self])
         if not async_op:
@@ -438,6 +462,10 @@ class BucketRuntime:
             mg = getattr(up, "main_grad", None)
             if mg is not None:
                 if getattr(up, "main_grad_written", False):
+                    if g is not None and not hasattr(mg, "is_contiguous"):
+                        raise RuntimeError(
+                            "a parameter received both an in-place peer-memory gradient and an autograd "
+                            "gradient in one backward; use grad_bucket=False for this bucket")
                     if g is not None:  # autograd also produced a gradient (e.g. a second use): fold it in
                         from .ops.elementwise import cast_scale_
 

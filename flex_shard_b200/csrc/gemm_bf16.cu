@@ -49,6 +49,10 @@ struct GemmArgs {
   // element offset i * d_block_stride (the [world, rows/world, N] rows of a reduce-scatter
   // send buffer), so a weight gradient can be written straight into its reduction layout.
   long long d_block_rows, d_block_stride;
+  // With d_peer_n > 0 block i of D starts at d_peer[i] instead (another GPU's memory mapped over
+  // NVLink): the epilogue's stores ARE the all-to-all leg of a reduce-scatter.
+  void* d_peer[16];
+  int d_peer_n;
   int* status;
 };
 
@@ -378,10 +382,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
       const bool row_ok = row < args.M;
-      const long long d_off = args.d_block_rows > 0
-                                  ? (row / args.d_block_rows) * args.d_block_stride +
-                                        (row % args.d_block_rows) * args.ldd
-                                  : row * args.ldd;
+      long long d_off = args.d_block_rows > 0
+                            ? (row / args.d_block_rows) * args.d_block_stride +
+                                  (row % args.d_block_rows) * args.ldd
+                            : row * args.ldd;
+      void* d_base = args.d;
+      if (args.d_peer_n > 0 && row_ok) {
+        d_base = args.d_peer[row / args.d_block_rows];
+        d_off = (row % args.d_block_rows) * args.ldd;
+      }
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -410,7 +419,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
           if (args.d_fp32) {
-            float* dp = static_cast<float*>(args.d) + d_off + col;
+            float* dp = static_cast<float*>(d_base) + d_off + col;
             if (full && (args.ldd % 4 == 0) && (args.d_block_stride % 4 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
@@ -426,7 +435,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (col + i < args.N) dp[i] = args.accumulate ? dp[i] + v[i] : v[i];
             }
           } else {
-            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(args.d) + d_off + col;
+            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(d_base) + d_off + col;
             if (full && (args.ldd % 8 == 0) && (args.d_block_stride % 8 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -563,8 +572,9 @@ int fsb_make_tmap_2d_plain(CUtensorMap* map, const void* base, CUtensorMapDataTy
 FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
                           long long lda, long long ldb, long long ldd, long long ldc, int a_mn,
                           int b_mn, int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
-                          long long d_block_rows, long long d_block_stride, int* status,
-                          int max_ctas, cudaStream_t stream) {
+                          long long d_block_rows, long long d_block_stride,
+                          const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
+                          cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
   CUtensorMap map_a, map_b;
   int rc;
@@ -595,8 +605,10 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (d_peer_n < 0 || d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
   GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate,
-                d_block_rows, d_block_stride, status};
+                d_block_rows, d_block_stride, {}, d_peer_n, status};
+  for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
   AgArgs none{};
   gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args, none);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
@@ -636,7 +648,7 @@ FSB_API int fsb_gemm_bf16_allgather(const void* a, const unsigned long long* pee
   if (g_num_sms[dev] == 0) cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
   if (n_stagers < 1) n_stagers = 1;
   if (n_stagers > g_num_sms[dev] / 2) n_stagers = g_num_sms[dev] / 2;
-  GemmArgs args{M, N, K, 0, 0, d, ldd, d_fp32, nullptr, 0, 0, 1.f, 0.f, 0, 0, 0, status};
+  GemmArgs args{M, N, K, 0, 0, d, ldd, d_fp32, nullptr, 0, 0, 1.f, 0.f, 0, 0, 0, {}, 0, status};
   AgArgs ag{};
   for (int r = 0; r < world; ++r) ag.peer[r] = reinterpret_cast<const uint8_t*>(peer_shards[r]);
   ag.local = static_cast<uint8_t*>(gathered);

@@ -80,6 +80,7 @@ class FlexShardModule:
             if st.runtime is not None:
                 st.runtime.unsharded_params = None
                 st.runtime.persistent = None
+                st.runtime._bucket_base = None
                 st.runtime.is_unsharded = False
         # buffers and any unmanaged tensors
         for mod in self.modules():

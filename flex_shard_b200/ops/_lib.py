@@ -89,7 +89,7 @@ def _declare(lib) -> None:
     vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_float
     sigs = {
         "fsb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, i32, i32,
-                          f32, f32, i32, i64, i64, vp, i32, vp],
+                          f32, f32, i32, i64, i64, vp, i32, vp, i32, vp],
         "fsb_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
         "fsb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, vp],
         "fsb_rope": [vp, vp, i64, i32, i32, i32, i64, i32, vp],

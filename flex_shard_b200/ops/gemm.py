@@ -17,6 +17,25 @@ from . import _lib
 from ._lib import count_launch
 
 
+class PeerBlocked:
+    """A ``[rows, cols]`` gradient destination cut into ``len(addrs)`` row blocks of ``block_rows``
+    rows, block ``i`` living at address ``addrs[i]`` (peer GPU ``i``'s incoming slot, row stride
+    ``cols``). Handing it to ``gemm(out=...)`` makes the epilogue store each block straight into the
+    owner's memory over NVLink."""
+
+    def __init__(self, addrs, block_rows: int, rows: int, cols: int, dtype: torch.dtype, device):
+        import ctypes
+
+        self.addrs = (ctypes.c_ulonglong * len(addrs))(*addrs)
+        self.n = len(addrs)
+        self.block_rows, self.rows, self.cols = block_rows, rows, cols
+        self.dtype, self.device = dtype, device
+        self.shape = (rows, cols)
+
+    def dim(self):
+        return 2
+
+
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     if t.stride(-1) != 1 or (t.dim() == 2 and t.stride(0) % 8 != 0) or t.data_ptr() % 16 != 0:
         t = t.contiguous()
@@ -36,7 +55,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         assert not accumulate
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     block_rows = block_stride = 0
-    if out.dim() == 3:
+    peer = None
+    if isinstance(out, PeerBlocked):
+        assert a.is_cuda and out.shape == (M, N) and c is None
+        peer, block_rows, ldd = out, out.block_rows, out.cols
+    elif out.dim() == 3:
         # [blocks, rows_per_block, N] view of a reduce-scatter send buffer: rows of block i
         # start at out[i]; rows past M (padding of the last block) are never written.
         assert out.shape[2] == N and out.stride(2) == 1 and out.shape[0] * out.shape[1] >= M
@@ -66,6 +89,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         return out
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert out.dtype in (torch.bfloat16, torch.float32)
+    if peer is None:
+        out_ptr, peer_ptrs, peer_n = out.data_ptr(), None, 0
+    else:
+        out_ptr, peer_ptrs, peer_n = None, peer.addrs, peer.n
     a = _rowmajor(a)
     b = _rowmajor(b)
     if c is not None:
@@ -75,11 +102,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     lib = _lib.load()
     status = _lib.status_word(a.device)
     rc = lib.fsb_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), c.data_ptr() if c is not None else None,
+        a.data_ptr(), b.data_ptr(), out_ptr, c.data_ptr() if c is not None else None,
         M, N, K, a.stride(0), b.stride(0), ldd, c.stride(0) if c is not None else 0,
         int(a_t), int(b_t), int(out.dtype == torch.float32),
         int(c is not None and c.dtype == torch.float32), alpha, beta, int(accumulate),
-        block_rows, block_stride, status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
+        block_rows, block_stride, peer_ptrs, peer_n, status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(rc, "fsb_gemm_bf16")
     count_launch()
     return out
@@ -105,7 +132,7 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, weight, b_t=True).view(x.shape)
         if ctx.needs_input_grad[1]:
             main = getattr(weight, "main_grad", None)
-            if main is not None and main.dtype in (torch.float32, torch.bfloat16):
+            if main is not None and (isinstance(main, PeerBlocked) or main.dtype in (torch.float32, torch.bfloat16)):
                 # The weight gradient goes straight into this parameter's rows of the bucket's
                 # reduce-scatter send buffer (cast to the reduce dtype in the GEMM epilogue);
                 # autograd gets nothing to cast, pack or add.

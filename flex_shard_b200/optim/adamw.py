@@ -54,6 +54,39 @@ class FusedAdamW(torch.optim.Optimizer):
         st["exp_avg"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
         st["exp_avg_sq"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
 
+    # ------------------------------------------------------------------ optimizer inside backward
+    def fuse_into_backward(self, module) -> None:
+        """Let the fused reduce-scatter kernel apply this optimizer's update to a bucket the moment its
+        gradients are reduced (no gradient is materialised for those buckets; ``step()`` then only
+        covers what is left). Only for buckets reduced through peer memory; others are unaffected.
+        Not compatible with gradient clipping, which needs every gradient before any update."""
+        for st in module.sharded_bucket_storages:
+            plist = [p for p in st.sharded_params]
+            mine = {id(p) for g in self.param_groups for p in g["params"]}
+            if all(id(p) in mine for p in plist) and len({p.dtype for p in plist}) == 1:
+                st._fused_opt = self
+        self._stepped_in_backward: set[int] = set()
+
+    def fused_bucket_args(self, storage):
+        """Hyper-parameters and flat state for one bucket, or ``None`` when it cannot be fused."""
+        plist = list(storage.sharded_params)
+        group = next((g for g in self.param_groups if any(p is plist[0] for p in g["params"])), None)
+        if group is None or not all(p.requires_grad for p in plist):
+            return None
+        flat = self._flat.get(id(storage))
+        if flat is None:
+            if any("step" in self.state[p] for p in plist):
+                return None
+            flat = self._init_bucket_state(storage, plist)
+        step = None
+        for p in plist:
+            self.state[p]["step"] += 1
+            step = int(self.state[p]["step"])
+        self._stepped_in_backward.add(id(storage))
+        return dict(p=storage.byte_storage.view(plist[0].dtype), m=flat["m"], v=flat["v"], lr=float(group["lr"]),
+                    beta1=group["betas"][0], beta2=group["betas"][1], eps=group["eps"],
+                    weight_decay=group["weight_decay"], step=step)
+
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, closure=None):
@@ -61,6 +94,7 @@ class FusedAdamW(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        done = getattr(self, "_stepped_in_backward", None)
         for group in self.param_groups:
             hp = dict(lr=float(group["lr"]), beta1=group["betas"][0], beta2=group["betas"][1],
                       eps=group["eps"], weight_decay=group["weight_decay"])
@@ -72,11 +106,15 @@ class FusedAdamW(torch.optim.Optimizer):
                     loose.append(p)
                 else:
                     by_bucket.setdefault(id(st), []).append(p)
-            for plist in by_bucket.values():
+            for key, plist in by_bucket.items():
+                if done and key in done:
+                    continue  # already updated by the fused reduce kernel during backward
                 self._step_bucket(plist, hp)
             for p in loose:
                 if p.grad is not None:
                     self._step_param(p, hp)
+        if done:
+            done.clear()
         return loss
 
     def step_bucket(self, storage) -> None:

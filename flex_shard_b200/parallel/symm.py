@@ -127,6 +127,8 @@ class SymmComm(Comm):
         self._rs_epoch = 0
         self._ag_hint, self._rs_hint = ag_bytes, rs_bytes
         self._desc_cache: dict = {}
+        self.fused_reduce = True      # weight gradients go straight into the owners' memory
+        self._grad_ring: SymmGradRing | None = None
 
     @classmethod
     def from_mesh(cls, mesh, **kw) -> "SymmComm":
@@ -153,6 +155,47 @@ class SymmComm(Comm):
                 self._rs, self._rs_epoch = cur, 0
             self._desc_cache.clear()
         return cur
+
+    def grad_ring(self, entry_bytes: int) -> SymmGradRing:
+        if self._grad_ring is None or self._grad_ring.entry_bytes < entry_bytes:
+            if self._grad_ring is not None:
+                torch.cuda.synchronize(self.device)
+            self._grad_ring = SymmGradRing(self.group, self.device, entry_bytes)
+        return self._grad_ring
+
+    def scatter_to_peers(self, segments) -> None:
+        """Copy (local src addr, peer dst addr, nbytes) segments with one kernel launch."""
+        if not segments:
+            return
+        descs = _pack_descs(segments, self.device)
+        n = max(s[2] for s in segments)
+        rc = _lib.load().fsb_comm_gather_pull(descs.data_ptr(), len(segments), max(1, min(32, n // (64 * 1024))),
+                                              None, self.world_size, 0, 0,
+                                              _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_gather_pull")
+        count_launch()
+
+    def reduce_incoming(self, bucket: "PeerBucket", scale: float, out: torch.Tensor | None, adam: dict | None):
+        """Owner side of the fused reduce-scatter: wait for every source's ``written`` flag, sum the W
+        incoming rows in rank order (+ AdamW on the shard when ``adam`` is given), then release the entry."""
+        ring, k, u, row = bucket.ring, bucket.k, bucket.use, bucket.row
+        reg = ring.region
+        W = self.world_size
+        reg.signal(ring.SLOT_WRITTEN0 + k, u)
+        rows = (ctypes.c_ulonglong * W)(*[ring.incoming_addr(self.rank, k, s, row) for s in range(W)])
+        a = adam or {}
+        p = a.get("p")
+        rc = _lib.load().fsb_comm_reduce_rows(
+            rows, W, row, scale, out.data_ptr() if out is not None else None,
+            p.data_ptr() if p is not None else None, int(p is not None and p.dtype == torch.float32),
+            a["m"].data_ptr() if adam else None, a["v"].data_ptr() if adam else None,
+            a.get("lr", 0.0), a.get("beta1", 0.0), a.get("beta2", 0.0), a.get("eps", 0.0),
+            a.get("weight_decay", 0.0), a.get("step", 1),
+            reg.flag_row_addr(self.rank, ring.SLOT_WRITTEN0 + k), u, reg.max_polls,
+            _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_reduce_rows")
+        count_launch()
+        reg.signal(ring.SLOT_CONSUMED0 + k, u)
 
     # ------------------------------------------------------------------ all-gather
     def all_gather_into_tensor(self, out: torch.Tensor, inp: torch.Tensor, async_op: bool = False):
@@ -217,6 +260,48 @@ class SymmComm(Comm):
         count_launch()
         reg.signal(self.SLOT_RS_DONE, e)
         return None
+
+
+class SymmGradRing:
+    """Symmetric *incoming gradient* regions for the fused weight-gradient -> reduce-scatter path.
+
+    Entry ``k`` on rank ``r`` holds ``[W source ranks][row]`` fp32: source ``s`` writes its
+    contribution to ``r``'s shard of the bucket into row ``s`` (the weight-gradient GEMM's epilogue
+    stores there directly over NVLink). ``written[k]`` flags say a source has finished a bucket,
+    ``consumed[k]`` flags say the owner has reduced it and the entry may be overwritten.
+    """
+
+    SLOT_WRITTEN0, SLOT_CONSUMED0 = 16, 32
+
+    def __init__(self, group, device, entry_bytes: int, entries: int = 2):
+        self.entry_bytes = (entry_bytes + 255) // 256 * 256
+        self.entries = entries
+        self.region = SymmRegion(group, entries * self.entry_bytes, device)
+        self.uses = [0] * entries
+        self.count = 0
+
+    def acquire(self) -> tuple[int, int]:
+        """Next entry and its use index; enqueues (on the current stream) the wait for every peer to
+        have consumed the entry's previous use."""
+        k = self.count % self.entries
+        self.count += 1
+        self.uses[k] += 1
+        u = self.uses[k]
+        if u > 1:
+            self.region.wait(self.SLOT_CONSUMED0 + k, u - 1)
+        return k, u
+
+    def incoming_addr(self, owner: int, k: int, src: int, row_elems: int, elem_off: int = 0) -> int:
+        return self.region.peer_payload_addr(owner, k * self.entry_bytes + (src * row_elems + elem_off) * 4)
+
+
+class PeerBucket:
+    """Bookkeeping of one bucket's gradients living in the peers' incoming regions."""
+
+    kind = "peer"
+
+    def __init__(self, ring: SymmGradRing, k: int, use: int, row: int):
+        self.ring, self.k, self.use, self.row = ring, k, use, row
 
 
 def symm_comm_for(mesh, **kw) -> SymmComm:

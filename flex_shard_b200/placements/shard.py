@@ -226,6 +226,11 @@ class Shard(Placement):
             return
         offs, row = self._reduce_layout(infos, W)
         needs_zero = any(i.global_shape[i.placement.dim] % W != 0 for i in infos)
+        comm = storage.reduce_comm
+        if (W > 1 and getattr(comm, "fused_reduce", False) and reduce_dtype == torch.float32 and not needs_zero
+                and all(i.placement.dim == 0 and i.partial_grad_group is None for i in infos) and row % 4 == 0):
+            self._alloc_peer_bucket(storage, pairs, offs, row, comm)
+            return
         buf = (torch.zeros if needs_zero else torch.empty)(W, row, dtype=reduce_dtype, device=storage.device)
         for (info, up), (o, n) in zip(pairs, offs):
             pl: Shard = info.placement
@@ -241,9 +246,61 @@ class Shard(Placement):
             up.main_grad_written = False
         storage._grad_bucket = buf
 
+    def _alloc_peer_bucket(self, storage, pairs, offs, row, comm) -> None:
+        """Fused path: every 2-D+ parameter's ``main_grad`` is a ``PeerBlocked`` destination whose
+        block i is rank i's incoming row for this rank, so the weight-gradient GEMM's epilogue is the
+        all-to-all leg of the reduce-scatter. Vectors are scattered at reduce time."""
+        from ..ops.gemm import PeerBlocked
+        from ..parallel.symm import PeerBucket
+
+        W, me = comm.world_size, comm.rank
+        ctx = storage.runtime.context
+        biggest = 0
+        for rt in ctx.runtimes:
+            st = rt.storage
+            if st.reduce_comm is comm:
+                tr = [i for i in st.infos if i.requires_grad]
+                if tr and all(isinstance(i.placement, Shard) for i in tr):
+                    biggest = max(biggest, W * self._reduce_layout(tr, W)[1] * 4)
+        ring = comm.grad_ring(biggest)
+        k, use = ring.acquire()
+        bucket = PeerBucket(ring, k, use, row)
+        for (info, up), (o, n) in zip(pairs, offs):
+            if len(info.global_shape) < 2:
+                continue
+            cols = math.prod(info.global_shape[1:])
+            c = info.global_shape[0] // W
+            addrs = [ring.incoming_addr(i, k, me, row, o) for i in range(W)]
+            view = PeerBlocked(addrs, c, info.global_shape[0], cols, torch.float32, storage.device)
+            view._fsb_bucket = bucket
+            up.main_grad = view
+            up.main_grad_written = False
+        storage._grad_bucket = bucket
+
+    def _prepare_peer_reduce(self, infos, grads, comm, bucket, offs):
+        """Scatter the gradients that were not written in place (vectors, autograd-produced ones)."""
+        W, me = comm.world_size, comm.rank
+        ring, k, row = bucket.ring, bucket.k, bucket.row
+        segs, keep = [], []
+        for info, g, (o, n) in zip(infos, grads, offs):
+            if getattr(g, "_fsb_bucket", None) is bucket:
+                continue
+            gf = g.reshape(-1).float().contiguous() if g.dtype != torch.float32 else g.reshape(-1).contiguous()
+            keep.append(gf)
+            for i in range(W):
+                segs.append((gf.data_ptr() + i * n * 4, ring.incoming_addr(i, k, me, row, o), n * 4))
+        comm.scatter_to_peers(segs)
+        prep = PlacementPreparedReduceGrad(infos=infos, send=None, reduce_dtype=torch.float32)
+        prep.extra.update(offs=offs, row=row, peer_bucket=bucket, keep=keep)
+        return prep
+
     def prepare_reduce_grad(self, infos, grads, comm, reduce_dtype):
         W = comm.world_size
         offs, row = self._reduce_layout(infos, W)
+        pb = next((getattr(g, "_fsb_bucket", None) for g in grads
+                   if getattr(getattr(g, "_fsb_bucket", None), "kind", None) == "peer"), None)
+        if pb is not None:
+            return self._prepare_peer_reduce(infos, grads, comm, pb, offs)
         needs_zero = any(info.global_shape[info.placement.dim] % W != 0 for info in infos)
         bucket = next((getattr(g, "_fsb_bucket", None) for g in grads if getattr(g, "_fsb_bucket", None) is not None), None)
         if bucket is not None and (bucket.dtype != reduce_dtype or tuple(bucket.shape) != (W, row)):
@@ -291,6 +348,19 @@ class Shard(Placement):
         W = comm.world_size
         plan = plan_reduction(reduction, W, prepared.reduce_dtype)
         row = prepared.extra["row"]
+        pb = prepared.extra.get("peer_bucket")
+        if pb is not None:
+            scale = {"avg": 1.0 / W, "premul_sum": plan.premul or 1.0}.get(plan.op, 1.0)
+            if plan.post_divide is not None:
+                scale /= plan.post_divide
+            adam = prepared.extra.get("adam")
+            with record("FlexShard::fused_reduce_scatter"):
+                out = None if adam is not None else torch.empty(row, dtype=torch.float32, device=comm.device)
+                comm.reduce_incoming(pb, scale, out, adam)
+            if out is None:
+                return PlacementReduceGradResult(grads=[None] * len(prepared.infos), output=None)
+            grads = [out[o:o + i.local_numel].view(i.local_shape) for i, (o, n) in zip(prepared.infos, prepared.extra["offs"])]
+            return PlacementReduceGradResult(grads=grads, output=out)
         with record("FlexShard::reduce_scatter"):
             if W == 1:
                 out = prepared.send.view(-1)

@@ -29,6 +29,14 @@ def _placement_fn(kind):
         return lambda named, mesh: {f: BlockShard((1, 1) if p.shape[0] % 2 == 0 else (1, 0), 0) for f, p in named}
     if kind == "owned":
         return make_bucketed_owned_full_param_placement_fn()
+    if kind == "flat":
+        from flex_shard_b200.placements import make_bucketed_block_shard_placement_fn
+
+        return make_bucketed_block_shard_placement_fn()
+    if kind == "flat_uneven":
+        from flex_shard_b200.placements import make_bucketed_block_shard_placement_fn
+
+        return make_bucketed_block_shard_placement_fn((1, 3))
     if kind == "mixed":
         def fn(named, mesh):
             out = {}
@@ -72,7 +80,7 @@ def _train(rank, world, kind, steps):
     return err, sizes, model.sharded_bucket_storages[0].total_bytes
 
 
-@pytest.mark.parametrize("kind", ["block", "owned", "mixed"])
+@pytest.mark.parametrize("kind", ["block", "owned", "mixed", "flat", "flat_uneven"])
 def test_sliced_placements_train_like_unsharded(kind):
     res = run_ranks(_train, 2, kind, 3)
     for err, sizes, nbytes in res:
@@ -139,3 +147,19 @@ def test_relayout_then_checkpoint_reshards_bitwise():
     for err, out_err in res:
         assert err == 0.0
         assert out_err < 1e-6
+
+
+def test_flat_bucket_plan_formulas():
+    """align = lcm(row sizes); offsets aligned; padded_total multiple of align * sum(blocks)."""
+    from flex_shard_b200.placements import FlatBucketPlan
+
+    plan = FlatBucketPlan([(16, 8), (8, 12), (5,)], (1, 1))
+    assert plan.align == 24
+    assert plan.param_off == [0, 144, 240]
+    assert plan.padded_total % (24 * 2) == 0 and plan.padded_total >= 245
+    lo, hi = plan.rank_range(1)
+    assert hi - lo == plan.padded_total // 2
+    # every rank holds whole rows of every parameter
+    for i in range(3):
+        rows = sum(plan.local_rows(i, r)[1] - plan.local_rows(i, r)[0] for r in range(2))
+        assert rows == plan.shapes[i][0]

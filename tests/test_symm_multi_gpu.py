@@ -78,3 +78,68 @@ def test_symm_collectives_match_nccl(tmp_path):
                 assert v is True, (k, v)
             elif k.endswith("_close"):
                 assert v < 1e-5, (k, v)
+
+
+def _train_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from torch.distributed.device_mesh import init_device_mesh
+
+        from flex_shard_b200 import flex_shard, ops
+        from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets
+        from flex_shard_b200.optim.adamw import FusedAdamW
+        from flex_shard_b200.parallel.comm import set_default_backend
+
+        dev = torch.device("cuda", rank)
+        mesh = init_device_mesh("cuda", (world,))
+        cfg = LlamaConfig(vocab_size=4096, d_model=512, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=1024,
+                          max_seq_len=256)
+        results = {}
+        for mode in ("nccl", "symm", "symm_fused_adam"):
+            set_default_backend("symm" if mode.startswith("symm") else "nccl")
+            torch.manual_seed(0)
+            model = Llama(cfg, dtype=torch.bfloat16, device=dev)
+            model.init_weights(0)
+            for p in model.parameters():
+                p.grad_dtype = torch.float32
+            flex_shard(model, llama_buckets(model, mesh=mesh))
+            opt = FusedAdamW(model.parameters(), lr=1e-3, weight_decay=0.1)
+            if mode == "symm_fused_adam":
+                opt.fuse_into_backward(model)
+            losses = []
+            for step in range(4):
+                g = torch.Generator().manual_seed(100 * step + rank)
+                tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=g).to(dev)
+                loss = model.loss(tok[:, :-1], tok[:, 1:])
+                loss.backward()
+                opt.step()
+                opt.zero_grad()
+                losses.append(float(loss.detach()))
+            torch.cuda.synchronize()
+            ops.check_status()
+            results[mode] = losses
+            del model, opt
+        dist.barrier()
+        torch.save(results, os.path.join(out, f"t{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_training_symm_paths_match_nccl(tmp_path):
+    """Peer-memory collectives, with weight gradients stored straight into the owners' memory and
+    (third arm) AdamW applied inside the reduce kernel, train like the NCCL path."""
+    import torch.multiprocessing as mp
+
+    from tests.common import free_port
+
+    mp.spawn(_train_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"t{r}.pt")
+        for mode in ("symm", "symm_fused_adam"):
+            for a, b in zip(res[mode], res["nccl"]):
+                assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (mode, res)
