@@ -496,6 +496,13 @@ class BucketRuntime:
             if info.partial_grad_group is not None:
                 torch.distributed.all_reduce(g, group=info.partial_grad_group)
             out.append(g)
+        bucket = getattr(self.storage, "_grad_bucket", None)
+        if getattr(bucket, "kind", None) == "peer":
+            # the bucket's ring entry is already reserved on every rank: gradients that were not
+            # written in place must still travel through it
+            for g in out:
+                if isinstance(g, torch.Tensor):
+                    g._fsb_peer_target = bucket
         return out
 
     def post_backward(self) -> None:

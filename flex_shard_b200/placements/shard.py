@@ -262,6 +262,8 @@ class Shard(Placement):
                 tr = [i for i in st.infos if i.requires_grad]
                 if tr and all(isinstance(i.placement, Shard) for i in tr):
                     biggest = max(biggest, W * self._reduce_layout(tr, W)[1] * 4)
+        if not any(len(i.global_shape) >= 2 for i, _ in pairs):
+            return  # nothing a GEMM would write in place: use the ordinary reduction
         ring = comm.grad_ring(biggest)
         k, use = ring.acquire()
         bucket = PeerBucket(ring, k, use, row)
@@ -297,12 +299,20 @@ class Shard(Placement):
     def prepare_reduce_grad(self, infos, grads, comm, reduce_dtype):
         W = comm.world_size
         offs, row = self._reduce_layout(infos, W)
-        pb = next((getattr(g, "_fsb_bucket", None) for g in grads
-                   if getattr(getattr(g, "_fsb_bucket", None), "kind", None) == "peer"), None)
+        pb = None
+        for g in grads:
+            for attr in ("_fsb_bucket", "_fsb_peer_target"):
+                cand = getattr(g, attr, None)
+                if cand is not None and not isinstance(cand, torch.Tensor) and getattr(cand, "kind", None) == "peer":
+                    pb = cand
+                    break
+            if pb is not None:
+                break
         if pb is not None:
             return self._prepare_peer_reduce(infos, grads, comm, pb, offs)
         needs_zero = any(info.global_shape[info.placement.dim] % W != 0 for info in infos)
-        bucket = next((getattr(g, "_fsb_bucket", None) for g in grads if getattr(g, "_fsb_bucket", None) is not None), None)
+        bucket = next((getattr(g, "_fsb_bucket", None) for g in grads
+                       if isinstance(getattr(g, "_fsb_bucket", None), torch.Tensor)), None)
         if bucket is not None and (bucket.dtype != reduce_dtype or tuple(bucket.shape) != (W, row)):
             bucket = None
         with record("FlexShard::reduce_scatter_copy_in"):
