@@ -32,7 +32,8 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;              // two 256-column accumulators
 constexpr int GROUP_M = 8;                  // tile rasterisation group
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 33 * 4;  // per epilogue warp: a padded 32x32 fp32 transpose tile
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
 
 struct GemmArgs {
   int M, N, K;
@@ -399,6 +400,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
+        if (args.d_peer_n > 0 && args.d_fp32 && !args.accumulate && args.c == nullptr && col + 32 <= args.N) {
+          // Rows of this tile live in other GPUs' memory: transpose the warp's 32x32 block through
+          // shared memory so that every store instruction writes one full 128-byte row segment
+          // (NVLink moves whole lines efficiently, scattered 16-byte pieces poorly).
+          float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 32 * 33;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r[i]) * args.alpha;
+          __syncwarp();
+          const long long row0 = static_cast<long long>(tm) * BM + quarter * 32;
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const long long gr = row0 + rr;
+            if (gr < args.M) {
+              float* base = static_cast<float*>(args.d_peer[gr / args.d_block_rows]) +
+                            (gr % args.d_block_rows) * args.ldd + col;
+              base[lane] = stg[rr * 33 + lane];
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         if (row_ok) {
           float v[32];
 #pragma unroll
