@@ -83,6 +83,8 @@ class Comm:
             if out.data_ptr() != inp.data_ptr():
                 out.view(-1)[: inp.numel()].copy_(inp.view(-1))
             return None
+        if not self.is_nccl and inp.untyped_storage().data_ptr() == out.untyped_storage().data_ptr():
+            inp = inp.clone()  # gloo does not accept a send buffer inside the gather buffer
         return dist.all_gather_into_tensor(out, inp, group=self.group, async_op=async_op)
 
     def all_gather_list(self, outs: Sequence[torch.Tensor], inp: torch.Tensor, async_op: bool = False):

@@ -1,0 +1,63 @@
+"""Linear layers that consume prequantised (FP8 blockwise) weights.
+
+``FlexShardFloat8BlockwiseLinear`` keeps a bf16 master ``weight``. Under ``flex_shard`` with
+``Fp8BucketedBlockShard`` the runtime swaps in a ``BlockwiseFp8Weight`` whose payload was
+quantised on the owning ranks and gathered as FP8; the forward and dgrad GEMMs run block-scaled
+FP8 on tcgen05, the weight gradient is a bf16 GEMM in the parameter's gradient dtype. Without
+sharding the master is quantised on the fly (same kernels, same numerics).
+
+Parity: ``blockwise_quant/linear.py:20-184`` and ``blockwise_fp8/fp8_blockwise_linear.py:42-211``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops.fp8 import fp8_linear, quantize_blockwise
+from .weight import BlockwiseFp8Weight, BlockwiseQuantWeight
+
+
+class FlexShardPrequantizedLinear(nn.Module):
+    """Base: ``weight`` is ``[out, in]`` (stacked weights multiply as the flattened matrix)."""
+
+    def __init__(self, in_features: int, out_features: int, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+
+    def payload(self, w):
+        raise NotImplementedError
+
+    def forward(self, x):
+        raise NotImplementedError
+
+
+class FlexShardFloat8BlockwiseLinear(FlexShardPrequantizedLinear):
+    def payload(self, w):
+        if isinstance(w, BlockwiseFp8Weight):
+            return w.qdata, w.scale
+        wq, ws = quantize_blockwise(w.detach().to(torch.bfloat16))
+        return wq, ws
+
+    def forward(self, x):
+        w = self.weight
+        wq, ws = self.payload(w)
+        return fp8_linear(x, w, wq, ws)
+
+
+def convert_to_flex_shard_float8_blockwise_linear(module: nn.Module, filter_fn=None) -> nn.Module:
+    """Replace ``nn.Linear`` layers (without bias, dims multiples of 128) by the FP8 blockwise linear,
+    keeping the weights. ``filter_fn(name, linear) -> bool`` selects layers."""
+    for name, child in list(module.named_children()):
+        if isinstance(child, nn.Linear) and child.bias is None and child.in_features % 128 == 0 \
+                and child.out_features % 128 == 0 and (filter_fn is None or filter_fn(name, child)):
+            new = FlexShardFloat8BlockwiseLinear(child.in_features, child.out_features, child.weight.dtype,
+                                                 child.weight.device)
+            new.weight = child.weight
+            setattr(module, name, new)
+        else:
+            convert_to_flex_shard_float8_blockwise_linear(child, filter_fn)
+    return module
+
+
+convert_to_flex_shard_prequantized_linear = convert_to_flex_shard_float8_blockwise_linear
