@@ -191,6 +191,14 @@ class BucketRuntime:
         self._bucket_nbytes = 0
 
     # ------------------------------------------------------------------ persistent unsharded params
+    def _refills_in_finish(self) -> bool:
+        """False when the gather itself writes the persistent buffers (they must exist beforehand)."""
+        pl = self.storage.placement
+        direct = getattr(pl, "gathers_into_persistent", None)
+        if direct is not None and direct(self.storage.infos, self.storage.comm):
+            return False
+        return pl.refills_persistent_buffers_in_finish
+
     def _aliases_storage(self) -> bool:
         fn = getattr(self.storage.placement, "unshard_aliases_storage", None)
         return bool(fn is not None and fn(self.storage.infos, self.storage.comm.world_size))
@@ -250,7 +258,7 @@ class BucketRuntime:
             return
         st = self.storage
         persistent = None
-        if not st.placement.refills_persistent_buffers_in_finish:
+        if not self._refills_in_finish():
             persistent = self._alloc_persistent()
         stream = self.context.unshard_stream
         # a gather that lands straight in the persistent buffers refills tensors autograd may have
@@ -305,7 +313,7 @@ class BucketRuntime:
         if self.pending is None:
             st = self.storage
             persistent = None
-            if not st.placement.refills_persistent_buffers_in_finish:
+            if not self._refills_in_finish():
                 persistent = self._alloc_persistent()
             guard = tuple(persistent or ())
             if self._bucket_base is not None:

@@ -54,7 +54,28 @@ struct GemmArgs {
   // NVLink): the epilogue's stores ARE the all-to-all leg of a reduce-scatter.
   void* d_peer[16];
   int d_peer_n;
+  // Grouped (mixture-of-experts) modes; rows of every group start on a multiple of 128 and are
+  // padded with zero rows to a multiple of 128.
+  //   1: grouped rows  - A [R, K]; m-tile t belongs to expert tile_expert[t] and multiplies that
+  //      expert's B slice (b_group_rows rows of B per expert); *num_mtiles m-tiles are valid
+  //   2: grouped K     - D [E, M, N] = A_e^T-style products over each expert's row range
+  //      [group_offs[e], group_offs[e+1]) of the MN-major operands A [R, M] and B [R, N]
+  int group_mode;
+  int num_groups;
+  const int* tile_expert;
+  const int* num_mtiles;
+  const int* group_offs;
+  long long b_group_rows;
   int* status;
+};
+
+struct TileInfo {
+  int tm, tn;
+  int num_kb;
+  int k_off;          // added to the K coordinate of both operands (mode 2)
+  int b_row_off;      // added to B's N coordinate (K-major B) or K coordinate (MN-major B) (mode 1)
+  long long d_row_off;
+  bool valid;
 };
 
 // All-gather fused into the GEMM: `n_stagers` CTAs of the grid pull the weight's row shards from
@@ -112,6 +133,35 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 }
 
 template <bool AG>
+__device__ __forceinline__ TileInfo get_tile(const GemmArgs& args, int tile, int tiles_m, int tiles_n,
+                                             int num_kb_full) {
+  TileInfo t;
+  t.num_kb = num_kb_full;
+  t.k_off = 0;
+  t.b_row_off = 0;
+  t.d_row_off = 0;
+  t.valid = true;
+  if (AG) {
+    tile_coords_nmajor(tile, tiles_m, t.tm, t.tn);
+  } else if (args.group_mode == 2) {
+    const int per = tiles_m * tiles_n;
+    const int e = tile / per;
+    tile_coords(tile - e * per, tiles_m, tiles_n, t.tm, t.tn);
+    const int r0 = args.group_offs[e], r1 = args.group_offs[e + 1];
+    t.k_off = r0;
+    t.num_kb = (r1 - r0 + BK - 1) / BK;
+    t.d_row_off = static_cast<long long>(e) * args.M;
+  } else {
+    tile_coords(tile, tiles_m, tiles_n, t.tm, t.tn);
+    if (args.group_mode == 1) {
+      t.valid = t.tm < *args.num_mtiles;
+      if (t.valid) t.b_row_off = args.tile_expert[t.tm] * static_cast<int>(args.b_group_rows);
+    }
+  }
+  return t;
+}
+
+template <bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const GemmArgs args, const AgArgs ag) {
@@ -130,7 +180,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int tiles_m = (args.M + BM - 1) / BM;
   const int tiles_n = (args.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * (args.group_mode == 2 ? args.num_groups : 1);
   const int num_kb = (args.K + BK - 1) / BK;
   const bool stager = AG && static_cast<int>(blockIdx.x) < ag.n_stagers;
   const int tile0 = AG ? static_cast<int>(blockIdx.x) - ag.n_stagers : static_cast<int>(blockIdx.x);
@@ -264,9 +314,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       int ready_tn = -1;
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
-        int tm, tn;
-        if (AG) tile_coords_nmajor(tile, tiles_m, tm, tn);
-        else tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const TileInfo ti = get_tile<AG>(args, tile, tiles_m, tiles_n, num_kb);
+        if (!ti.valid || ti.num_kb == 0) continue;
+        const int tm = ti.tm, tn = ti.tn;
         const int m0 = tm * BM, n0 = tn * BN;
         if (AG && tn != ready_tn) {
           // wait until every piece of this 256-row chunk of the weight has landed locally
@@ -289,7 +339,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy flag -> async-proxy (TMA) reads
           ready_tn = tn;
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < ti.num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
@@ -301,7 +351,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BK + ti.k_off;
           if (!args.a_mn) {
             tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
           } else {
@@ -310,11 +360,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tma_load_2d(sa + j * 8192, &map_a, &full_bar[s], m0 + 64 * j, k0);
           }
           if (!args.b_mn) {
-            tma_load_2d(sb, &map_b, &full_bar[s], k0, n0);
+            tma_load_2d(sb, &map_b, &full_bar[s], k0, n0 + ti.b_row_off);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * 8192, &map_b, &full_bar[s], n0 + 64 * j, k0);
+              tma_load_2d(sb + j * 8192, &map_b, &full_bar[s], n0 + 64 * j, k0 + ti.b_row_off);
           }
         }
       }
@@ -330,9 +380,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t a_kstep = args.a_mn ? 2048u : 32u, b_kstep = args.b_mn ? 2048u : 32u;
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
-      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
+        const TileInfo ti = get_tile<AG>(args, tile, tiles_m, tiles_n, num_kb);
+        if (!ti.valid || ti.num_kb == 0) continue;
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
+        ++local_tile;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
           atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
@@ -340,7 +393,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < ti.num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
@@ -367,12 +420,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t local_tile = 0;
-    for (int tile = tile0; tile < num_tiles; tile += tile_step, ++local_tile) {
-      int tm, tn;
-      if (AG) tile_coords_nmajor(tile, tiles_m, tm, tn);
-      else tile_coords(tile, tiles_m, tiles_n, tm, tn);
+    for (int tile = tile0; tile < num_tiles; tile += tile_step) {
+      const TileInfo ti = get_tile<AG>(args, tile, tiles_m, tiles_n, num_kb);
+      if (!ti.valid) continue;
+      const int tm = ti.tm, tn = ti.tn;
+      const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      if (ti.num_kb == 0) {
+        // an empty group contributes nothing: its output tile is zero (or left alone when accumulating)
+        if (row_ok && !args.accumulate) {
+          for (int c = tn * BN; c < min(args.N, tn * BN + BN); ++c) {
+            const long long o = (ti.d_row_off + row) * args.ldd + c;
+            if (args.d_fp32) static_cast<float*>(args.d)[o] = 0.f;
+            else static_cast<__nv_bfloat16*>(args.d)[o] = __float2bfloat16(0.f);
+          }
+        }
+        continue;
+      }
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
+      ++local_tile;
       if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
         if (lane == 0) {
           atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_FULL);
@@ -381,12 +448,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         break;
       }
       tc_fence_after();
-      const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
-      const bool row_ok = row < args.M;
       long long d_off = args.d_block_rows > 0
                             ? (row / args.d_block_rows) * args.d_block_stride +
                                   (row % args.d_block_rows) * args.ldd
-                            : row * args.ldd;
+                            : (ti.d_row_off + row) * args.ldd;
       void* d_base = args.d;
       if (args.d_peer_n > 0 && row_ok) {
         d_base = args.d_peer[row / args.d_block_rows];
@@ -596,6 +661,71 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
                           int b_mn, int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
                           long long d_block_rows, long long d_block_stride,
                           const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
+                          cudaStream_t stream);
+
+// Grouped GEMMs for mixture-of-experts layers (see GemmArgs::group_mode). Row groups start on
+// multiples of 128 and are zero-padded to multiples of 128.
+//   mode 1: D[R, N] = A[R, K] . B_e[N, K]^T (b_mn = 0, B is [E*N, K]) or A[R, K] . B_e[K, N]
+//           (b_mn = 1, B is [E*K, N]); tile_expert[t] names the expert of m-tile t, *num_mtiles the
+//           number of valid m-tiles (device memory: no host synchronisation), max_mtiles bounds it.
+//   mode 2: D[E, M, N] = sum over each expert's rows of A[r, :M]^T B[r, :N] (A, B row-major
+//           [R, M] / [R, N]); group_offs is the int[E+1] array of padded row offsets.
+FSB_API int fsb_gemm_bf16_grouped(const void* a, const void* b, void* d, int mode, int num_groups, int M,
+                                  int N, int K, long long lda, long long ldb, long long ldd, int b_mn,
+                                  int d_fp32, int accumulate, const int* tile_expert,
+                                  const int* num_mtiles, const int* group_offs, int max_rows,
+                                  int* status, cudaStream_t stream) {
+  if (mode != 1 && mode != 2) return FSB_ERR_BAD_ARG;
+  CUtensorMap map_a, map_b;
+  int rc;
+  GemmArgs args{};
+  if (mode == 1) {
+    // A [max_rows, K] K-major; B stacked over experts
+    rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, K, lda, BM, BK);
+    if (rc != FSB_OK) return rc;
+    if (!b_mn) rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                     static_cast<uint64_t>(num_groups) * N, K, ldb, BN, BK);
+    else rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                               static_cast<uint64_t>(num_groups) * K, N, ldb, BK, 64);
+    if (rc != FSB_OK) return rc;
+    args.M = max_rows; args.N = N; args.K = K; args.a_mn = 0; args.b_mn = b_mn;
+    args.b_group_rows = b_mn ? K : N;
+  } else {
+    // A [max_rows, M], B [max_rows, N] both MN-major; contraction over the rows of each group
+    rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, M, lda, BK, 64);
+    if (rc != FSB_OK) return rc;
+    rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, N, ldb, BK, 64);
+    if (rc != FSB_OK) return rc;
+    args.M = M; args.N = N; args.K = max_rows; args.a_mn = 1; args.b_mn = 1;
+  }
+  args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.alpha = 1.f; args.beta = 0.f;
+  args.accumulate = accumulate; args.group_mode = mode; args.num_groups = num_groups;
+  args.tile_expert = tile_expert; args.num_mtiles = num_mtiles; args.group_offs = group_offs;
+  args.status = status;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess)
+      return FSB_ERR_LAUNCH;
+    attr_set[dev] = true;
+  }
+  if (g_num_sms[dev] == 0) cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = static_cast<long long>((args.M + BM - 1) / BM) * ((N + BN - 1) / BN) *
+                          (mode == 2 ? num_groups : 1);
+  const int grid = tiles < g_num_sms[dev] ? static_cast<int>(tiles) : g_num_sms[dev];
+  AgArgs none{};
+  gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args, none);
+  return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}
+
+FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
+                          long long lda, long long ldb, long long ldd, long long ldc, int a_mn,
+                          int b_mn, int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
+                          long long d_block_rows, long long d_block_stride,
+                          const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
   CUtensorMap map_a, map_b;
@@ -628,8 +758,12 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (d_peer_n < 0 || d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
-  GemmArgs args{M, N, K, a_mn, b_mn, d, ldd, d_fp32, c, ldc, c_fp32, alpha, beta, accumulate,
-                d_block_rows, d_block_stride, {}, d_peer_n, status};
+  GemmArgs args{};
+  args.M = M; args.N = N; args.K = K; args.a_mn = a_mn; args.b_mn = b_mn;
+  args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
+  args.alpha = alpha; args.beta = beta; args.accumulate = accumulate;
+  args.d_block_rows = d_block_rows; args.d_block_stride = d_block_stride; args.d_peer_n = d_peer_n;
+  args.status = status;
   for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
   AgArgs none{};
   gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args, none);
@@ -670,7 +804,9 @@ FSB_API int fsb_gemm_bf16_allgather(const void* a, const unsigned long long* pee
   if (g_num_sms[dev] == 0) cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
   if (n_stagers < 1) n_stagers = 1;
   if (n_stagers > g_num_sms[dev] / 2) n_stagers = g_num_sms[dev] / 2;
-  GemmArgs args{M, N, K, 0, 0, d, ldd, d_fp32, nullptr, 0, 0, 1.f, 0.f, 0, 0, 0, {}, 0, status};
+  GemmArgs args{};
+  args.M = M; args.N = N; args.K = K; args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32;
+  args.alpha = 1.f; args.status = status;
   AgArgs ag{};
   for (int r = 0; r < world; ++r) ag.peer[r] = reinterpret_cast<const uint8_t*>(peer_shards[r]);
   ag.local = static_cast<uint8_t*>(gathered);

@@ -1,0 +1,123 @@
+// Row movement for mixture-of-experts layers: token rows are gathered into an expert-major,
+// 128-row-aligned layout for the grouped tcgen05 GEMMs and combined back with the routing weights.
+// One warp per row, 16-byte accesses; indices and weights stay on the device (no host sync).
+#include "common.cuh"
+
+namespace {
+using namespace fsb;
+
+struct alignas(16) bf16x8 { __nv_bfloat162 v[4]; };
+
+// dst[i, :] = scale[i] * src[index[i], :]   (index < 0 -> zero row; scale may be null)
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ index,
+                                   const float* __restrict__ scale, __nv_bfloat16* __restrict__ dst,
+                                   long long n, int D, long long lds, long long ldd) {
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= n) return;
+  const int s = index[w];
+  const float sc = (scale != nullptr && s >= 0) ? scale[w] : 1.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    bf16x8 v;
+    if (s >= 0) {
+      v = *reinterpret_cast<const bf16x8*>(src + static_cast<long long>(s) * lds + c);
+      if (scale != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(v.v[j]);
+          v.v[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v.v[j] = __floats2bfloat162_rn(0.f, 0.f);
+    }
+    *reinterpret_cast<bf16x8*>(dst + w * ldd + c) = v;
+  }
+}
+
+// out[t, :] = sum_k w[t, k] * rows[pos[t, k], :]   (w may be null: plain sum)
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ pos,
+                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                    long long T, int k, int D, long long ldr, long long ldo) {
+  const long long t = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int c = lane * 8; c < D; c += 256) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const int p = pos[t * k + j];
+      if (p < 0) continue;
+      const float wj = w ? w[t * k + j] : 1.f;
+      const bf16x8 v = *reinterpret_cast<const bf16x8*>(rows + static_cast<long long>(p) * ldr + c);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(v.v[q]);
+        acc[2 * q] += wj * f.x;
+        acc[2 * q + 1] += wj * f.y;
+      }
+    }
+    bf16x8 o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o.v[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    *reinterpret_cast<bf16x8*>(out + t * ldo + c) = o;
+  }
+}
+
+// dw[t, k] = <dy[t, :], rows[pos[t, k], :]>
+__global__ void combine_bwd_w_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ rows,
+                                     const int* __restrict__ pos, float* __restrict__ dw, long long TK, int k,
+                                     int D, long long lddy, long long ldr) {
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= TK) return;
+  const long long t = i / k;
+  const int p = pos[i];
+  float acc = 0.f;
+  if (p >= 0) {
+    for (int c = lane * 8; c < D; c += 256) {
+      const bf16x8 a = *reinterpret_cast<const bf16x8*>(dy + t * lddy + c);
+      const bf16x8 b = *reinterpret_cast<const bf16x8*>(rows + static_cast<long long>(p) * ldr + c);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 x = __bfloat1622float2(a.v[q]), y = __bfloat1622float2(b.v[q]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dw[i] = acc;
+}
+
+inline unsigned blocks_for_warps(long long warps) {
+  return static_cast<unsigned>((warps * 32 + 255) / 256);
+}
+inline int ok() { return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH; }
+}  // namespace
+
+FSB_API int fsb_moe_gather_rows(const void* src, const int* index, const float* scale, void* dst, long long n,
+                                int D, long long lds, long long ldd, cudaStream_t stream) {
+  if (D % 8 != 0 || lds % 8 != 0 || ldd % 8 != 0) return FSB_ERR_BAD_ARG;
+  if (n <= 0) return FSB_OK;
+  gather_rows_kernel<<<blocks_for_warps(n), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), index, scale,
+                                                             static_cast<__nv_bfloat16*>(dst), n, D, lds, ldd);
+  return ok();
+}
+
+FSB_API int fsb_moe_combine_rows(const void* rows, const int* pos, const float* w, void* out, long long T, int k,
+                                 int D, long long ldr, long long ldo, cudaStream_t stream) {
+  if (D % 8 != 0 || ldr % 8 != 0 || ldo % 8 != 0) return FSB_ERR_BAD_ARG;
+  if (T <= 0) return FSB_OK;
+  combine_rows_kernel<<<blocks_for_warps(T), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(rows), pos, w,
+                                                              static_cast<__nv_bfloat16*>(out), T, k, D, ldr, ldo);
+  return ok();
+}
+
+FSB_API int fsb_moe_combine_bwd_w(const void* dy, const void* rows, const int* pos, float* dw, long long T, int k,
+                                  int D, long long lddy, long long ldr, cudaStream_t stream) {
+  if (D % 8 != 0) return FSB_ERR_BAD_ARG;
+  if (T <= 0) return FSB_OK;
+  combine_bwd_w_kernel<<<blocks_for_warps(T * k), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(rows), pos, dw, T * k, k, D, lddy, ldr);
+  return ok();
+}

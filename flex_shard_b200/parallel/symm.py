@@ -227,6 +227,35 @@ class SymmComm(Comm):
         reg.signal(self.SLOT_AG_DONE, e)
         return None
 
+    def all_gather_segments(self, inp: torch.Tensor, segments) -> None:
+        """All-gather whose destination is a list of segments: ``segments`` = (rank, source byte offset
+        inside that rank's ``inp``, destination address, nbytes). One pull kernel moves every piece to
+        its final place (e.g. straight into per-parameter buffers), so no gather buffer and no
+        copy-out pass exist."""
+        W = self.world_size
+        nbytes = inp.numel() * inp.element_size()
+        reg = self._region("ag", nbytes)
+        self._ag_epoch += 1
+        e = self._ag_epoch
+        if e > 1:
+            reg.wait(self.SLOT_AG_DONE, e - 1)
+        reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
+        reg.signal(self.SLOT_AG_READY, e)
+        key = ("seg", tuple((r, o, d, n) for r, o, d, n in segments))
+        descs = self._desc_cache.get(key)
+        if descs is None:
+            descs = _pack_descs([(reg.peer_payload_addr(r, o), d, n) for r, o, d, n in segments], self.device)
+            if len(self._desc_cache) < 4096:
+                self._desc_cache[key] = descs
+        biggest = max(n for _, _, _, n in segments)
+        blocks = max(1, min(48, biggest // (128 * 1024)))
+        rc = _lib.load().fsb_comm_gather_pull(descs.data_ptr(), len(segments), blocks,
+                                              reg.flag_row_addr(self.rank, self.SLOT_AG_READY), W, e, reg.max_polls,
+                                              _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_gather_pull")
+        count_launch()
+        reg.signal(self.SLOT_AG_DONE, e)
+
     # ------------------------------------------------------------------ reduce-scatter
     def reduce_scatter_tensor(self, out: torch.Tensor, inp: torch.Tensor, plan: ReducePlan, async_op: bool = False):
         if self.world_size == 1 or inp.dtype != torch.float32 or out.numel() % 4 != 0:

@@ -127,9 +127,43 @@ class Shard(Placement):
             off += n
         return offs, off
 
+    @staticmethod
+    def gathers_into_persistent(infos, comm) -> bool:
+        """With a peer-memory communicator each rank's chunk is pulled straight into its place in the
+        per-parameter unsharded buffers: no gather buffer, no copy-out pass."""
+        return (comm.world_size > 1 and hasattr(comm, "all_gather_segments")
+                and all(i.placement.dim == 0 for i in infos))
+
+    def _prepare_direct(self, infos, byte_storage, comm, persistent, offs, row_bytes, same):
+        W = comm.world_size
+        prep = PlacementPreparedUnshard(infos=infos, persistent=persistent)
+        prep.extra.update(offs=offs, row_bytes=row_bytes, direct=True)
+        with record("FlexShard::copy_in"):
+            if same:
+                send = byte_storage
+            else:
+                send = torch.zeros(row_bytes, dtype=torch.uint8, device=byte_storage.device)
+                for info, (o, n) in zip(infos, offs):
+                    src = info.placement.make_local_storage_view(info, byte_storage)
+                    send[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype).copy_(src.reshape(-1))
+        prep.send = send
+        segs = []
+        for info, (o, n), buf in zip(infos, offs, persistent):
+            if n == 0:
+                continue
+            base = buf.data_ptr()
+            for r in range(W):
+                segs.append((r, o, base + r * n, n))
+        prep.extra["segments"] = segs
+        return prep
+
     def prepare_unshard_bucket(self, infos, byte_storage, comm, persistent):
         W = comm.world_size
         offs, row_bytes = self._send_layout(infos, W)
+        if persistent and self.gathers_into_persistent(infos, comm):
+            same = all(i.param_dtype == i.storage_dtype for i in infos) and all(
+                i.byte_offset == o for i, (o, _) in zip(infos, offs)) and row_bytes == byte_storage.numel()
+            return self._prepare_direct(infos, byte_storage, comm, persistent, offs, row_bytes, same)
         same = all(i.param_dtype == i.storage_dtype for i in infos) and all(
             i.byte_offset == o for i, (o, _) in zip(infos, offs)) and row_bytes == byte_storage.numel()
         prep = PlacementPreparedUnshard(infos=infos, persistent=persistent)
@@ -157,6 +191,10 @@ class Shard(Placement):
     def run_prepared_unshard(self, prepared, comm, async_op=False):
         if comm.world_size == 1:
             return
+        if prepared.extra.get("direct"):
+            with record("FlexShard::all_gather"):
+                comm.all_gather_segments(prepared.send, prepared.extra["segments"])
+            return
         with record("FlexShard::all_gather"):
             prepared.work = comm.all_gather_into_tensor(prepared.recv, prepared.send, async_op=async_op)
 
@@ -167,6 +205,10 @@ class Shard(Placement):
             prepared.work.wait()
             prepared.work = None
         outs = []
+        if prepared.extra.get("direct"):
+            for info, buf in zip(infos, persistent):
+                outs.append(buf[: info.global_numel].view(info.global_shape))
+            return PlacementUnshardResult(outs, keepalive=[prepared.send])
         with record("FlexShard::copy_out"):
             if W == 1 and not persistent:
                 storage = prepared.extra["storage"]
