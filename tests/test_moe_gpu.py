@@ -17,9 +17,9 @@ def test_moe_layer_matches_cpu_reference(T, k, E, D, F):
     gw = torch.rand(T, k)
     res = {}
     for dev in ("cpu", "cuda"):
-        xi = x.to(dev).requires_grad_()
-        wi = w1.to(dev).requires_grad_()
-        gi = gw.to(dev).requires_grad_()
+        xi = x.clone().to(dev).requires_grad_()
+        wi = w1.clone().to(dev).requires_grad_()
+        gi = gw.clone().to(dev).requires_grad_()
         plan = moe.plan_routes(idx.to(dev), E)
         y = moe.moe_combine(moe.grouped_linear(moe.moe_dispatch(xi, plan), wi, plan), gi, plan)
         y.float().square().sum().backward()
