@@ -140,7 +140,7 @@ class Llama(nn.Module):
         """Mean next-token cross-entropy over all positions of ``targets`` (ignore_index -100).
         With ``loss_is_root`` the returned loss must be what ``backward()`` is called on (its
         incoming gradient is taken to be 1, which saves a pass over the logits)."""
-        logits = self.forward(tokens)
+        logits = self(tokens)  # through __call__, so that root-level bucket hooks run
         return ew.cross_entropy(logits, targets.reshape(-1), unit_grad=loss_is_root)
 
 

@@ -1,0 +1,75 @@
+"""DeepSeek-V3-style MoE model on CPU: sharded vs unsharded on one rank group, and expert
+parallelism (2 gloo ranks, experts split, all-to-all dispatch) against the non-EP model."""
+import torch
+
+from tests.common import run_ranks
+
+CFG = dict(vocab_size=512, d_model=128, n_layers=2, n_dense_layers=1, n_heads=2, q_lora_rank=64, kv_lora_rank=32,
+           qk_nope_dim=32, qk_rope_dim=16, v_dim=32, dense_hidden=256, n_experts=4, expert_hidden=64, top_k=2,
+           n_shared_experts=1, max_seq_len=64)
+
+
+def _tok(step, rank):
+    return torch.randint(0, CFG["vocab_size"], (2, 33), generator=torch.Generator().manual_seed(17 * step + rank))
+
+
+def _make():
+    from flex_shard_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config
+
+    torch.manual_seed(0)
+    m = DeepSeekV3(DeepSeekV3Config(**CFG), dtype=torch.float32)
+    m.init_weights(0)
+    return m
+
+
+def _ep_worker(rank, world, steps):
+    import torch.distributed as dist
+
+    from flex_shard_b200 import flex_shard
+    from flex_shard_b200.models.deepseek_v3 import deepseek_buckets
+    from flex_shard_b200.parallel.expert_parallel import apply_expert_parallel
+    from flex_shard_b200.bucket_storage import MixedPrecisionPolicy
+
+    model = _make()
+    apply_expert_parallel(model, dist.group.WORLD)
+    # experts are already split over the EP group: shard them over a 1-rank mesh (this rank alone)
+    solo = dist.new_group([rank]) if False else None
+    groups = [dist.new_group([r]) for r in range(world)]
+    specs = deepseek_buckets(model, mesh=None, expert_mesh=groups[rank], mp_policy=MixedPrecisionPolicy())
+    flex_shard(model, specs)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    losses = []
+    for s in range(steps):
+        t = _tok(s, rank)
+        loss = model.loss(t[:, :-1], t[:, 1:], loss_is_root=False) / world
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(float(loss.detach()) * world)
+    return losses
+
+
+def _reference(world, steps):
+    model = _make()
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    out = []
+    for s in range(steps):
+        tot = 0.0
+        for r in range(world):
+            t = _tok(s, r)
+            loss = model.loss(t[:, :-1], t[:, 1:], loss_is_root=False) / world
+            loss.backward()
+            tot += float(loss.detach())
+        opt.step()
+        opt.zero_grad()
+        out.append(tot)
+    return out
+
+
+def test_expert_parallel_matches_single_process():
+    steps, world = 3, 2
+    ref = _reference(world, steps)
+    res = run_ranks(_ep_worker, world, steps)
+    mean = [sum(r[i] for r in res) / world for i in range(steps)]
+    for a, b in zip(mean, ref):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (mean, ref)
