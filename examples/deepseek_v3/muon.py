@@ -1,0 +1,42 @@
+"""Muon for the DeepSeek-V3 example: Kimi-K2-style matrix split and a communication-free optimizer.
+
+Attention projections are orthogonalised per head (and per role), routed experts per expert, every
+other matrix whole, with the update scale ``0.2 * sqrt(max(rows, cols))``; embeddings, norms, router
+gates and the output projection train with AdamW. Role parity: ``examples/deepseek_v3/muon.py:29-104``.
+"""
+from __future__ import annotations
+
+import torch
+
+from flex_shard_b200 import relayout_bucket
+from flex_shard_b200.dist_muon import build_local_dist_muon
+from flex_shard_b200.optim.adamw import FusedAdamW
+from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+
+
+def is_muon_param(name: str, p) -> bool:
+    shape = getattr(p, "_fsb_global_shape", None) or tuple(p.shape)
+    if len(shape) < 2:
+        return False
+    return not (name.startswith("tok_embeddings") or name == "output" or name.endswith(".gate"))
+
+
+def kimi_block_rows(cfg) -> dict:
+    """Rows of one orthogonalisation block for the per-head attention matrices."""
+    return {"wq_b": cfg.qk_dim, "wkv_b": cfg.qk_nope_dim + cfg.v_dim}
+
+
+def store_on_owners(model) -> None:
+    """Move every block's non-expert bucket to whole-parameter owners (LPT with carried loads)."""
+    fn = make_bucketed_owned_full_param_placement_fn(carry_loads=True)
+    for st in list(model.sharded_bucket_storages):
+        if st.name.startswith("layers.") and ".moe" not in st.name:
+            relayout_bucket(model, st, fn)
+
+
+def build_muon(model, lr: float, weight_decay: float, adamw_lr: float | None = None):
+    muon = build_local_dist_muon(model, is_muon_param=is_muon_param, lr=lr, weight_decay=weight_decay,
+                                 adjust_lr_fn="match_rms_adamw")
+    rest = [p for n, p in model.named_parameters() if not is_muon_param(n, p)]
+    adam = FusedAdamW(rest, lr=adamw_lr or lr, betas=(0.9, 0.95), weight_decay=weight_decay)
+    return muon, adam

@@ -1,0 +1,173 @@
+"""Train the DeepSeek-V3-style MoE model with flex_shard_b200 on one host.
+
+    python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc-per-node 8 \
+        examples/deepseek_v3/train.py --steps 100 --ep 8 --optimizer muon
+
+Flags follow the reference's example (``examples/deepseek_v3/train.py:61-111``): ``--ep`` sets the
+expert-parallel degree, ``--optimizer {adamw,muon}``, ``--checkpoint-dir`` saves and resumes,
+``--deterministic`` fixes seeds, ``--profile-dir`` writes a Chrome trace of step 5 per rank.
+``--small`` shrinks the model for smoke runs (also on CPU with the gloo backend).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from data import SyntheticBatches  # noqa: E402
+from muon import build_muon, store_on_owners  # noqa: E402
+
+from flex_shard_b200 import (checkpoint, flex_shard, register_optimizer_checkpoint_hook,  # noqa: E402
+                             set_state_dict_global_layouts)
+from flex_shard_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config, deepseek_buckets  # noqa: E402
+from flex_shard_b200.optim.adamw import FusedAdamW  # noqa: E402
+from flex_shard_b200.parallel.expert_parallel import apply_expert_parallel  # noqa: E402
+from flex_shard_b200.utils.training import JsonMetrics, clip_grad_norm_, lr_lambda  # noqa: E402
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--local-batch-size", type=int, default=2)
+    ap.add_argument("--ep", type=int, default=0, help="expert-parallel degree (0: all ranks, 1: off)")
+    ap.add_argument("--optimizer", choices=["adamw", "muon"], default="adamw")
+    ap.add_argument("--data", choices=["synthetic"], default="synthetic")
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--weight-decay", type=float, default=0.1)
+    ap.add_argument("--warmup-steps", type=int, default=2)
+    ap.add_argument("--decay-ratio", type=float, default=0.1)
+    ap.add_argument("--min-lr-factor", type=float, default=0.1)
+    ap.add_argument("--max-norm", type=float, default=1.0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--deterministic", action="store_true")
+    ap.add_argument("--checkpoint-dir", default=None)
+    ap.add_argument("--checkpoint-interval", type=int, default=0)
+    ap.add_argument("--profile-dir", default=None)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--comm", choices=["nccl", "symm"], default="nccl")
+    return ap.parse_args()
+
+
+def main():
+    args = parse()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if args.deterministic:
+        torch.use_deterministic_algorithms(True, warn_only=True)
+    torch.manual_seed(args.seed)
+    if args.comm == "symm" and cuda:
+        from flex_shard_b200.parallel.comm import set_default_backend
+
+        set_default_backend("symm")
+
+    cfg = DeepSeekV3Config(max_seq_len=args.seq_len)
+    if args.small:
+        cfg = DeepSeekV3Config(vocab_size=2048, d_model=256, n_layers=3, n_heads=2, q_lora_rank=128, kv_lora_rank=64,
+                               qk_nope_dim=64, qk_rope_dim=32, v_dim=64, dense_hidden=512, n_experts=8,
+                               expert_hidden=128, top_k=2, max_seq_len=args.seq_len)
+    ep = world if args.ep == 0 else args.ep
+    model = DeepSeekV3(cfg, dtype=torch.bfloat16 if cuda else torch.float32, device=dev)
+    model.init_weights(args.seed)
+
+    dp_group = dist.group.WORLD
+    expert_mesh = None
+    if ep > 1:
+        # EP groups of `ep` consecutive ranks; experts are then sharded over ranks holding the same ones
+        ep_groups = [dist.new_group(list(range(s, s + ep))) for s in range(0, world, ep)]
+        efsdp_groups = [dist.new_group(list(range(o, world, ep))) for o in range(ep)]
+        apply_expert_parallel(model, ep_groups[rank // ep])
+        expert_mesh = efsdp_groups[rank % ep]
+    flex_shard(model, deepseek_buckets(model, mesh=dp_group, expert_mesh=expert_mesh))
+
+    if args.optimizer == "muon":
+        store_on_owners(model)
+        muon, adam = build_muon(model, args.lr, args.weight_decay)
+        opts = [muon, adam]
+    else:
+        adam = FusedAdamW(model.parameters(), lr=args.lr, betas=(0.9, 0.95), weight_decay=args.weight_decay)
+        opts = [adam]
+    register_optimizer_checkpoint_hook(adam, model)
+    scheds = [torch.optim.lr_scheduler.LambdaLR(o, lambda s: lr_lambda(s, args.warmup_steps, args.steps,
+                                                                       args.decay_ratio, args.min_lr_factor))
+              for o in opts]
+    data = SyntheticBatches(cfg.vocab_size, args.local_batch_size, args.seq_len, args.seed, rank, pin_memory=cuda)
+
+    def state():
+        sd = model.state_dict()
+        set_state_dict_global_layouts(model, sd)
+        return {"model": sd, "adam": adam.state_dict(), "data": data.state_dict(),
+                "sched": [s.state_dict() for s in scheds]}
+
+    start = 0
+    if args.checkpoint_dir and os.path.isdir(args.checkpoint_dir) and os.listdir(args.checkpoint_dir):
+        last = sorted(os.listdir(args.checkpoint_dir))[-1]
+        # optimizer state must exist before it can be filled: one step with zero gradients and zero lr
+        for p in model.parameters():
+            p.grad = torch.zeros_like(p, dtype=getattr(p, "grad_dtype", None) or p.dtype)
+        saved_lr = [g["lr"] for g in adam.param_groups]
+        for g in adam.param_groups:
+            g["lr"] = 0.0
+        adam.step()
+        adam.zero_grad(set_to_none=True)
+        for g, lr in zip(adam.param_groups, saved_lr):
+            g["lr"] = lr
+        sd = state()
+        checkpoint.load(sd, os.path.join(args.checkpoint_dir, last))
+        model.load_state_dict(sd["model"])
+        adam.load_state_dict(sd["adam"])
+        data.load_state_dict(sd["data"])
+        for s_, ssd in zip(scheds, sd["sched"]):
+            s_.load_state_dict(ssd)
+        start = data.step
+
+    metrics = JsonMetrics(rank=rank)
+    for step in range(start, args.steps):
+        prof = None
+        if args.profile_dir and step == 5:
+            prof = torch.profiler.profile()
+            prof.__enter__()
+        metrics.start_step()
+        tok = next(data).to(dev, non_blocking=True)
+        ntok = torch.tensor([tok[:, 1:].numel()], dtype=torch.float32, device=dev)
+        dist.all_reduce(ntok)
+        # sum of token losses divided by the global token count (buckets sum gradients)
+        loss = model.loss(tok[:, :-1], tok[:, 1:], loss_is_root=False) * (tok[:, 1:].numel() / ntok.squeeze())
+        loss.backward()
+        gnorm = clip_grad_norm_(model, args.max_norm)
+        for m in model.moe_layers():
+            m.update_expert_bias()
+        for o in opts:
+            o.step()
+        for s in scheds:
+            s.step()
+        for o in opts:
+            o.zero_grad(set_to_none=True)
+        red = loss.detach().clone()
+        dist.all_reduce(red)
+        metrics.end_step(step, tok[:, 1:].numel(), loss=red, grad_norm=gnorm, lr=scheds[0].get_last_lr()[0])
+        if prof is not None:
+            prof.__exit__(None, None, None)
+            os.makedirs(args.profile_dir, exist_ok=True)
+            prof.export_chrome_trace(os.path.join(args.profile_dir, f"rank{rank}.json"))
+        if args.checkpoint_dir and args.checkpoint_interval and (step + 1) % args.checkpoint_interval == 0:
+            checkpoint.save(state(), os.path.join(args.checkpoint_dir, f"step{step + 1:08d}"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -40,7 +40,11 @@ def get_flex_shard_muon_compute_layouts(module: nn.Module,
         for info in st.infos:
             pl = _unwrap(info.placement)
             gshape = tuple(info.global_shape)
-            if isinstance(pl, BucketedOwned):
+            if W == 1:
+                # a one-rank mesh stores every parameter whole, whatever the placement
+                out[info.fqn] = LocalMuonComputeLayout("matrix_batch" if len(gshape) == 3 else "owned",
+                                                       global_shape=gshape)
+            elif isinstance(pl, BucketedOwned):
                 if pl.view_kind == "expert_block" and len(gshape) == 3:
                     out[info.fqn] = LocalMuonComputeLayout("matrix_batch", global_shape=gshape)
                 else:

@@ -1,0 +1,91 @@
+"""Training-loop helpers over sharded parameters: gradient-norm clipping, LR schedule, JSON metrics.
+
+Parity: the helper functions of the reference's example (``examples/deepseek_v3/train.py:230-291``:
+warm-up / stable / decay LR schedule, sharded grad-norm clip with one all-reduce per mesh).
+"""
+from __future__ import annotations
+
+import json
+import math
+import sys
+import time
+from typing import Iterable
+
+import torch
+import torch.distributed as dist
+
+
+def lr_lambda(step: int, warmup_steps: int, total_steps: int, decay_ratio: float = 0.0, min_lr_factor: float = 0.0):
+    """Linear warm-up, constant plateau, linear decay over the last ``decay_ratio`` of training."""
+    if warmup_steps > 0 and step < warmup_steps:
+        return (step + 1) / (warmup_steps + 1)
+    decay_steps = int(total_steps * decay_ratio)
+    stable_end = total_steps - decay_steps
+    if decay_steps <= 0 or step < stable_end:
+        return 1.0
+    progress = min(1.0, (step - stable_end + 1) / decay_steps)
+    return 1.0 - progress * (1.0 - min_lr_factor)
+
+
+@torch.no_grad()
+def clip_grad_norm_(module, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+    """Global gradient norm over every bucket's local shards (one all-reduce per distinct mesh), then
+    scale the local gradients in place. Returns the total norm."""
+    by_group: dict = {}
+    for st in module.sharded_bucket_storages:
+        key = id(st.comm.group)
+        acc = by_group.setdefault(key, [st.comm, None])
+        for p in st.sharded_params:
+            if p.grad is None or p.grad.numel() == 0:
+                continue
+            v = p.grad.float().norm(norm_type) ** norm_type
+            acc[1] = v if acc[1] is None else acc[1] + v
+    total = None
+    for comm, v in by_group.values():
+        if v is None:
+            continue
+        if comm.world_size > 1:
+            dist.all_reduce(v, group=comm.group)
+        total = v if total is None else total + v
+    if total is None:
+        return torch.zeros(())
+    total_norm = total ** (1.0 / norm_type)
+    coef = (max_norm / (total_norm + 1e-6)).clamp(max=1.0)
+    for st in module.sharded_bucket_storages:
+        for p in st.sharded_params:
+            if p.grad is not None:
+                p.grad.mul_(coef.to(p.grad.dtype))
+    return total_norm
+
+
+class JsonMetrics:
+    """One JSON line per step: loss, grad-norm, lr, tokens/s (device-timed), peak memory."""
+
+    def __init__(self, stream=None, rank: int = 0):
+        self.stream = stream or sys.stdout
+        self.rank = rank
+        self._ev = None
+        self._t = None
+
+    def start_step(self):
+        if torch.cuda.is_available():
+            self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._ev[0].record()
+        self._t = time.perf_counter()
+
+    def end_step(self, step: int, tokens: int, **fields):
+        if self._ev is not None:
+            self._ev[1].record()
+            self._ev[1].synchronize()
+            ms = self._ev[0].elapsed_time(self._ev[1])
+        else:
+            ms = (time.perf_counter() - self._t) * 1e3
+        rec = {"step": step, "ms": round(ms, 3), "tokens_per_s_per_gpu": round(tokens / (ms / 1e3), 1)}
+        if torch.cuda.is_available():
+            rec["peak_mem_gib"] = round(torch.cuda.max_memory_allocated() / 2**30, 2)
+        for k, v in fields.items():
+            rec[k] = float(v) if isinstance(v, torch.Tensor) else v
+        if self.rank == 0:
+            self.stream.write(json.dumps(rec) + "\n")
+            self.stream.flush()
+        return rec
