@@ -227,19 +227,20 @@ class SymmComm(Comm):
         reg.signal(self.SLOT_AG_DONE, e)
         return None
 
-    def all_gather_segments(self, inp: torch.Tensor, segments) -> None:
+    def all_gather_segments(self, inp: torch.Tensor, segments, alloc_bytes: int = 0) -> None:
         """All-gather whose destination is a list of segments: ``segments`` = (rank, source byte offset
         inside that rank's ``inp``, destination address, nbytes). One pull kernel moves every piece to
         its final place (e.g. straight into per-parameter buffers), so no gather buffer and no
         copy-out pass exist."""
         W = self.world_size
         nbytes = inp.numel() * inp.element_size()
-        reg = self._region("ag", nbytes)
+        reg = self._region("ag", max(nbytes, alloc_bytes))  # same size on every rank
         self._ag_epoch += 1
         e = self._ag_epoch
         if e > 1:
             reg.wait(self.SLOT_AG_DONE, e - 1)
-        reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
+        if nbytes:
+            reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
         reg.signal(self.SLOT_AG_READY, e)
         key = ("seg", tuple((r, o, d, n) for r, o, d, n in segments))
         descs = self._desc_cache.get(key)

@@ -236,7 +236,9 @@ def run_unshard(prepared, comm, async_op=False) -> None:
     rows = prepared.extra.get("rows")
     if rows is not None:
         with record("FlexShard::owner_rows_gather"):
-            prepared.work = comm.all_gather_list(rows, prepared.send, async_op=async_op)
+            from .owner_rows_transport import gather_owner_rows
+
+            gather_owner_rows(comm, prepared.send, [r.numel() for r in rows], rows)
     else:
         with record("FlexShard::mixed_all_gather"):
             prepared.work = comm.all_gather_into_tensor(prepared.recv, prepared.send, async_op=async_op)

@@ -1,0 +1,150 @@
+"""Host-side planners and contracts that need no process group: owner-rows transport plan, layout
+composition, adapters, reduce-op mapping, API validation errors, LPT balancing."""
+import pytest
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from tests.common import FakeMesh
+
+
+def test_transport_plan_writes_every_position_once_and_counts_crossing():
+    from flex_shard_b200.placements.owner_rows_transport import choose_transport, plan_chunks
+
+    lens = [1000, 300, 0, 2500]
+    plan = plan_chunks(lens, hosts=[0, 0, 1, 1])
+    assert plan.chunk % 128 == 0 and plan.chunk * 4 >= sum(lens)
+    cover = [0] * (plan.chunk * 4)
+    for m in plan.moves:
+        for i in range(m.length):
+            cover[m.dst * plan.chunk + m.dst_off + i] += 1
+    assert sum(cover) == sum(lens) and max(cover) == 1
+    # cross-host elements = what host 1 owns beyond its chunk share, here host-1 rows landing on host-0 chunks
+    assert plan.cross_host_elems == sum(m.length for m in plan.moves if (m.src < 2) != (m.dst < 2))
+    assert all((m.via >= 0) == ((m.src < 2) != (m.dst < 2)) for m in plan.moves)
+    assert plan.buffer_elems >= plan.chunk
+    assert choose_transport(plan) == "chunks"
+
+
+def test_transport_threshold(monkeypatch):
+    from flex_shard_b200.placements.owner_rows_transport import ChunkPlan, choose_transport
+
+    p = ChunkPlan(chunk=128, cross_host_elems=83, total_elems=100)
+    assert choose_transport(p) == "grouped"
+    monkeypatch.setenv("FLEX_SHARD_OWNER_ROWS_TRANSPORT", "chunks")
+    assert choose_transport(p) == "chunks"
+    monkeypatch.setenv("FLEX_SHARD_OWNER_ROWS_TRANSPORT", "auto")
+    monkeypatch.setenv("FLEX_SHARD_OWNER_ROWS_MAX_CROSSING", "0.9")
+    assert choose_transport(p) == "chunks"
+
+
+def test_compose_global_layouts_multi_chunk():
+    from flex_shard_b200 import GlobalLayout, compose_global_layouts
+
+    outer = GlobalLayout((16, 4), ((8, 0),), ((0, 0),), ((8, 4),))       # EP rank 1 of 2 holds rows 8..16
+    inner = GlobalLayout((8, 4), ((2, 0), (6, 0)), ((0, 0), (2, 0)), ((2, 4), (2, 4)))
+    c = compose_global_layouts(outer, inner)
+    assert c.global_shape == (16, 4)
+    assert c.global_offsets == ((10, 0), (14, 0)) and c.local_offsets == ((0, 0), (2, 0))
+
+
+def test_shard_layout_goldens_uneven_and_empty():
+    from flex_shard_b200.placements import BlockShard, BucketedOwned, Shard
+
+    s = Shard(0)
+    assert s.compute_local_shape((10, 3), 0, 4) == (3, 3) and s.compute_local_shape((10, 3), 3, 4) == (1, 3)
+    assert s.compute_local_shape((2, 3), 3, 4) == (0, 3)
+    assert s.global_layout((2, 3), 3, 4).global_offsets == ()
+    assert s.local_storage_layout((10, 3), 3, 4).storage_numel == 9      # rank-0-sized slot on every rank
+    with pytest.raises(ValueError):
+        Shard(1).compute_local_shape((4, 10), 0, 4)
+    b = BlockShard((1, 0, 2, 1), 1)
+    assert b.compute_local_shape((3, 8), 2, 4) == (3, 4)
+    assert b.global_layout((3, 8), 2, 4).global_offsets == ((0, 2),)
+    o = BucketedOwned(((1, 0, 6),))
+    assert o.compute_local_shape((6, 5), 1, 2) == (6, 5) and o.compute_local_shape((6, 5), 0, 2) == (0, 5)
+
+
+def test_reduce_plan_mapping():
+    from flex_shard_b200 import GradientReduction
+    from flex_shard_b200.parallel.comm import plan_reduction
+
+    assert plan_reduction(GradientReduction(dist.ReduceOp.SUM), 8, torch.float32).op == "sum"
+    assert plan_reduction(GradientReduction(), 8, torch.float32).op == "avg"
+    p = plan_reduction(GradientReduction(dist.ReduceOp.AVG, 3.0), 8, torch.bfloat16)
+    assert p.op == "premul_sum" and abs(p.premul - 1 / 3) < 1e-12
+    h = plan_reduction(GradientReduction(dist.ReduceOp.AVG, 8.0), 8, torch.float16)
+    assert (h.pre_divide, h.post_divide) == (4.0, 2.0)
+    h = plan_reduction(GradientReduction(dist.ReduceOp.AVG, 6.0), 4, torch.float16)
+    assert (h.pre_divide, h.post_divide) == (4.0, 1.5)
+    one = plan_reduction(GradientReduction(), 1, torch.float32)
+    assert one.op == "sum" and one.post_divide is None
+    with pytest.raises(ValueError):
+        GradientReduction(dist.ReduceOp.SUM, 2.0)
+    with pytest.raises(ValueError):
+        GradientReduction(dist.ReduceOp.AVG, -1.0)
+
+
+def test_api_validation_errors():
+    from flex_shard_b200 import BucketSpec, OffloadPolicy, flex_shard
+
+    def net():
+        return nn.Sequential(nn.Linear(4, 4), nn.ReLU(), nn.Linear(4, 2))
+
+    with pytest.raises(ValueError, match="matches no BucketSpec"):
+        flex_shard(net(), [BucketSpec(["0.*"])])
+    with pytest.raises(ValueError, match="more than one BucketSpec"):
+        flex_shard(net(), [BucketSpec(["*"]), BucketSpec(["0.*"])])
+    with pytest.raises(ValueError, match="offload_policy"):
+        flex_shard(net(), [BucketSpec(["*"], offload_policy=OffloadPolicy())])
+    m = net()
+    flex_shard(m, [BucketSpec(["*"])])
+    with pytest.raises(ValueError, match="already applied"):
+        flex_shard(m, [BucketSpec(["*"])])
+    outer = nn.Sequential(m)
+    with pytest.raises(ValueError, match="already"):
+        flex_shard(outer, [BucketSpec(["*"])])
+    tied = net()
+    tied[2].weight = nn.Parameter(torch.zeros(2, 4))
+    shared = nn.Linear(4, 4)
+    tied2 = nn.Sequential(shared, shared)
+    flex_shard(tied2, [BucketSpec(["*"])])
+    assert tied2[0].weight is tied2[1].weight
+    mixed = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 4).to(torch.bfloat16))
+    with pytest.raises(ValueError, match="mixes parameter dtypes"):
+        flex_shard(mixed, [BucketSpec(["*"])])
+
+
+def test_fsdp2_param_order_is_post_order():
+    from flex_shard_b200.bucket_storage import fsdp2_param_order
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.own = nn.Parameter(torch.zeros(1))
+            self.child = nn.Linear(2, 2)
+
+    m = M()
+    names = [n for n, _ in fsdp2_param_order(m, list(m.named_parameters()))]
+    assert names == ["child.weight", "child.bias", "own"]
+
+
+def test_lpt_even_positions_first_and_carry():
+    from flex_shard_b200.utils.validation import assign_to_hosts_then_ranks
+
+    hosts = [r // 8 for r in range(64)]
+    assert [r // 8 for r in assign_to_hosts_then_ranks([1.0] * 4, hosts)] == [0, 2, 4, 6]
+    loads = [0.0] * 8
+    a = assign_to_hosts_then_ranks([1.0] * 4, [0] * 8, loads)
+    assert a == [0, 2, 4, 6]
+    b = assign_to_hosts_then_ranks([1.0] * 4, [0] * 8, loads)
+    assert sorted(b) == [1, 3, 5, 7]
+
+
+def test_adapters():
+    from flex_shard_b200.layout_adapters import spmd_layout
+
+    lay = spmd_layout((4, 8), {"tp": ("shard", 0), "ep": ("replicate",)}, {"tp": (1, 2), "ep": (0, 4)})
+    assert lay.global_shape == (8, 8) and lay.global_offsets == ((4, 0),)
+    lay = spmd_layout((2, 8), {"a": ("shard", 0), "b": ("shard", 0)}, {"a": (1, 2), "b": (0, 2)}, {0: ("a", "b")})
+    assert lay.global_shape == (8, 8) and lay.global_offsets == ((4, 0),)
