@@ -30,8 +30,9 @@ enum FsbStatus : int {
 
 namespace fsb {
 
-constexpr uint32_t kSpinFast = 4096;          // polls before backing off
-constexpr uint32_t kSpinLimit = 1u << 24;     // backed-off polls before giving up (~2-4 s)
+constexpr uint32_t kSpinFast = 64;            // parked tries before the abort flag is looked at too
+constexpr uint32_t kSpinLimit = 1u << 21;     // parked tries (each at most kWaitHintNs) before giving up: seconds
+constexpr uint32_t kWaitHintNs = 2000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -77,19 +78,47 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds; it is woken early
+// when the phase completes, so a long hint costs no latency and keeps a blocked waiter from
+// flooding the shared-memory pipeline with polls.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait. Returns false when the limit ran out (or another thread of the
 // CTA already gave up, which `abort_flag` in shared memory says).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag) {
+  // The common case (the phase has already completed) costs one try_wait round trip; the loops are
+  // kept rolled so that a failed try is followed by exactly one new try, not by a batch of them.
+  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
   for (uint32_t i = 0; i < kSpinFast; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
   }
+#pragma unroll 1
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
     if (*abort_flag) return false;
-    __nanosleep(64);
   }
   return false;
+}
+
+// The same wait for a whole (converged) warp: lane 0 polls, the result is broadcast. 32 lanes that
+// poll one barrier issue 32 separate shared-memory operations per try; with several waiting warps
+// that traffic slows every other shared-memory access of the SM, tensor-core operand reads included.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 
 // ---------------------------------------------------------------- proxies / fences
