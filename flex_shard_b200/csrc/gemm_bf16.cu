@@ -161,6 +161,118 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& args, int tile, int
   return t;
 }
 
+// Epilogue of one 128 x 256 accumulator tile: the calling warp owns TMEM lanes [32*quarter, +32)
+// (t_row = TMEM address of its lane quarter, column 0 of the accumulator) = rows
+// tm*128 + 32*quarter + lane of D. `stg` is the warp's padded 32x32 fp32 staging tile.
+__device__ __forceinline__ void store_tile(const GemmArgs& args, long long d_row_off, int tm, int tn,
+                                           uint32_t t_row, float* stg, int quarter, int lane) {
+  const long long row = static_cast<long long>(tm) * BM + quarter * 32 + lane;
+  const bool row_ok = row < args.M;
+  long long d_off = args.d_block_rows > 0
+                        ? (row / args.d_block_rows) * args.d_block_stride +
+                              (row % args.d_block_rows) * args.ldd
+                        : (d_row_off + row) * args.ldd;
+  void* d_base = args.d;
+  if (args.d_peer_n > 0 && row_ok) {
+    d_base = args.d_peer[row / args.d_block_rows];
+    d_off = (row % args.d_block_rows) * args.ldd;
+  }
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    const int col = tn * BN + c0;
+    if (col >= args.N) break;  // uniform across the warp
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c0, r);
+    tmem_ld_wait();
+    if (args.d_peer_n > 0 && args.d_fp32 && !args.accumulate && args.c == nullptr && col + 32 <= args.N) {
+      // Rows of this tile live in other GPUs' memory: transpose the warp's 32x32 block through
+      // shared memory so that every store instruction writes one full 128-byte row segment
+      // (NVLink moves whole lines efficiently, scattered 16-byte pieces poorly).
+#pragma unroll
+      for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r[i]) * args.alpha;
+      __syncwarp();
+      const long long row0 = static_cast<long long>(tm) * BM + quarter * 32;
+#pragma unroll 4
+      for (int rr = 0; rr < 32; ++rr) {
+        const long long gr = row0 + rr;
+        if (gr < args.M) {
+          float* base = static_cast<float*>(args.d_peer[gr / args.d_block_rows]) +
+                        (gr % args.d_block_rows) * args.ldd + col;
+          base[lane] = stg[rr * 33 + lane];
+        }
+      }
+      __syncwarp();
+      continue;
+    }
+    if (row_ok) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
+      const bool full = (col + 32 <= args.N);
+      if (args.c != nullptr) {
+        if (args.c_fp32) {
+          const float* cp = static_cast<const float*>(args.c) + row * args.ldc + col;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (full || col + i < args.N) v[i] += args.beta * cp[i];
+        } else {
+          const __nv_bfloat16* cp =
+              static_cast<const __nv_bfloat16*>(args.c) + row * args.ldc + col;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (full || col + i < args.N) v[i] += args.beta * __bfloat162float(cp[i]);
+        }
+      }
+      if (args.d_fp32) {
+        float* dp = static_cast<float*>(d_base) + d_off + col;
+        if (full && (args.ldd % 4 == 0) && (args.d_block_stride % 4 == 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            if (args.accumulate) {
+              const float4 old = *reinterpret_cast<const float4*>(dp + i);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dp + i) = o;
+          }
+        } else {
+          for (int i = 0; i < 32; ++i)
+            if (col + i < args.N) dp[i] = args.accumulate ? dp[i] + v[i] : v[i];
+        }
+      } else {
+        __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(d_base) + d_off + col;
+        if (full && (args.ldd % 8 == 0) && (args.d_block_stride % 8 == 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (args.accumulate) {
+              const uint4 old = *reinterpret_cast<const uint4*>(dp + i);
+              const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(ob[j]);
+                v[i + 2 * j] += f.x;
+                v[i + 2 * j + 1] += f.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[i], v[i + 1]);
+            o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+            o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+            o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+            *reinterpret_cast<uint4*>(dp + i) = o;
+          }
+        } else {
+          for (int i = 0; i < 32; ++i)
+            if (col + i < args.N) {
+              const float o = args.accumulate ? __bfloat162float(dp[i]) + v[i] : v[i];
+              dp[i] = __float2bfloat16(o);
+            }
+        }
+      }
+    }
+  }
+}
+
 template <bool AG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -448,111 +560,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         break;
       }
       tc_fence_after();
-      long long d_off = args.d_block_rows > 0
-                            ? (row / args.d_block_rows) * args.d_block_stride +
-                                  (row % args.d_block_rows) * args.ldd
-                            : (ti.d_row_off + row) * args.ldd;
-      void* d_base = args.d;
-      if (args.d_peer_n > 0 && row_ok) {
-        d_base = args.d_peer[row / args.d_block_rows];
-        d_off = (row % args.d_block_rows) * args.ldd;
-      }
-      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col = tn * BN + c0;
-        if (col >= args.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (args.d_peer_n > 0 && args.d_fp32 && !args.accumulate && args.c == nullptr && col + 32 <= args.N) {
-          // Rows of this tile live in other GPUs' memory: transpose the warp's 32x32 block through
-          // shared memory so that every store instruction writes one full 128-byte row segment
-          // (NVLink moves whole lines efficiently, scattered 16-byte pieces poorly).
-          float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 32 * 33;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r[i]) * args.alpha;
-          __syncwarp();
-          const long long row0 = static_cast<long long>(tm) * BM + quarter * 32;
-#pragma unroll 4
-          for (int rr = 0; rr < 32; ++rr) {
-            const long long gr = row0 + rr;
-            if (gr < args.M) {
-              float* base = static_cast<float*>(args.d_peer[gr / args.d_block_rows]) +
-                            (gr % args.d_block_rows) * args.ldd + col;
-              base[lane] = stg[rr * 33 + lane];
-            }
-          }
-          __syncwarp();
-          continue;
-        }
-        if (row_ok) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
-          const bool full = (col + 32 <= args.N);
-          if (args.c != nullptr) {
-            if (args.c_fp32) {
-              const float* cp = static_cast<const float*>(args.c) + row * args.ldc + col;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (full || col + i < args.N) v[i] += args.beta * cp[i];
-            } else {
-              const __nv_bfloat16* cp =
-                  static_cast<const __nv_bfloat16*>(args.c) + row * args.ldc + col;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (full || col + i < args.N) v[i] += args.beta * __bfloat162float(cp[i]);
-            }
-          }
-          if (args.d_fp32) {
-            float* dp = static_cast<float*>(d_base) + d_off + col;
-            if (full && (args.ldd % 4 == 0) && (args.d_block_stride % 4 == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (args.accumulate) {
-                  const float4 old = *reinterpret_cast<const float4*>(dp + i);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dp + i) = o;
-              }
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (col + i < args.N) dp[i] = args.accumulate ? dp[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(d_base) + d_off + col;
-            if (full && (args.ldd % 8 == 0) && (args.d_block_stride % 8 == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                if (args.accumulate) {
-                  const uint4 old = *reinterpret_cast<const uint4*>(dp + i);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = __bfloat1622float2(ob[j]);
-                    v[i + 2 * j] += f.x;
-                    v[i + 2 * j + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[i], v[i + 1]);
-                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
-                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(dp + i) = o;
-              }
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (col + i < args.N) {
-                  const float o = args.accumulate ? __bfloat162float(dp[i]) + v[i] : v[i];
-                  dp[i] = __float2bfloat16(o);
-                }
-            }
-          }
-        }
-      }
+      store_tile(args, ti.d_row_off, tm, tn, tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16),
+                 reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 32 * 33, quarter, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -575,7 +584,257 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-SM variant for dense GEMMs: a cluster of two CTAs (one SM pair) owns a 256 x 256 tile of D.
+// CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and rows [128 r, +128) of the B
+// tile into its own shared memory; one thread of CTA 0 issues tcgen05.mma.cta_group::2, which
+// reads both CTAs' operands and accumulates D rows [128 r, +128) x 256 columns into CTA r's TMEM.
+// Per SM and per 16-deep step the tensor core reads 4 KB of A and 4 KB of B instead of 4 KB + 8 KB,
+// which takes the operand reads off the shared-memory bandwidth limit, and each SM's ring holds
+// 6 x 64-deep stages instead of 4.
+// Signals that cross the pair: TMA completion bytes of both CTAs land on CTA 0's `full` barrier;
+// tcgen05.commit arrives on the `empty` / `tmem_full` barriers of both CTAs; the epilogue warps of
+// both CTAs arrive on CTA 0's `tmem_empty` barrier. Every wait is bounded; a CTA that gives up
+// still walks to the cluster barrier at the end, so its peer is never left alone.
+constexpr int BN_HALF = 128;                       // B rows per CTA
+constexpr int STAGES2 = 6;
+constexpr int B2_STAGE_BYTES = BN_HALF * BK * 2;   // 16 KB
+constexpr int STAGE2_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256 + EPI_STAGE_BYTES;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of the executing CTA whose completion bytes are counted on a barrier that may live in
+// the peer CTA of the pair (no fan-out of the data: each CTA fetches its own tiles).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at `cluster_addr` (own or peer CTA) once every MMA issued so far has retired.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* full_bar = bars;                      // [STAGES2]  used in CTA 0
+  uint64_t* empty_bar = bars + STAGES2;           // [STAGES2]  one per CTA
+  uint64_t* tmem_full = bars + 2 * STAGES2;       // [2]        one per CTA
+  uint64_t* tmem_empty = bars + 2 * STAGES2 + 2;  // [2]        used in CTA 0 (8 arrivals: 4 warps x 2 CTAs)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int tiles_m = (args.M + 2 * BM - 1) / (2 * BM);   // 256-row tiles
+  const int tiles_n = (args.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+  const int tile0 = static_cast<int>(blockIdx.x >> 1);
+  const int tile_step = static_cast<int>(gridDim.x >> 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
+        int tm2, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+        const int m0 = tm2 * 2 * BM + static_cast<int>(rank) * BM;
+        const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE2_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          const uint32_t full0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE2_BYTES);   // the bytes of both CTAs
+          const int k0 = kb * BK;
+          if (!args.a_mn) {
+            tma_load_2d_pair(sa, &map_a, full0, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, full0, m0 + 64 * j, k0);
+          }
+          if (!args.b_mn) {
+            tma_load_2d_pair(sb, &map_b, full0, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, full0, n0 + 64 * j, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (CTA 0 only)
+    if (rank == 0) {
+      const uint32_t idesc = make_idesc(2 * BM, BN, 1, 1, args.a_mn ? 1u : 0u, args.b_mn ? 1u : 0u);
+      const uint32_t a_lbo = args.a_mn ? 8192u : 16u, b_lbo = args.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = (args.a_mn ? 2048u : 32u) >> 4, b_kstep = (args.b_mn ? 2048u : 32u) >> 4;
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        ++local_tile;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
+          if (lane == 0) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_EMPTY);
+            *abort_flag = 1;
+          }
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+            if (lane == 0) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              *abort_flag = 1;
+            }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE2_BYTES);
+          const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t db = make_smem_desc_sw128(sa + A_STAGE_BYTES, b_lbo, 1024);
+          const uint32_t e_own = smem_u32(&empty_bar[s]);
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f16_pair(d_tmem, da + k * a_kstep, db + k * b_kstep, idesc, (kb | k) != 0 ? 1u : 0u);
+            // the stage is free in both CTAs once these MMAs have read it
+            umma_commit_pair(e_own);
+            umma_commit_pair(map_to_cta(e_own, 1));
+          }
+          __syncwarp();
+        }
+        if (ok) {
+          const uint32_t f_own = smem_u32(&tmem_full[acc]);
+          if (elect_one()) {
+            umma_commit_pair(f_own);
+            umma_commit_pair(map_to_cta(f_own, 1));
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0;
+    for (int tile = tile0; tile < num_tiles; tile += tile_step) {
+      int tm2, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+      const int tm = tm2 * 2 + static_cast<int>(rank);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      ++local_tile;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
+        if (lane == 0) {
+          atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      store_tile(args, 0, tm, tn, tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16),
+                 reinterpret_cast<float*>(smem + STAGES2 * STAGE2_BYTES + 256) + (warp - 2) * 32 * 33, quarter, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+    }
+  }
+
+  // Common exit: every loop above is bounded, so all warps of both CTAs arrive here. Neither CTA may
+  // leave (its barriers and shared memory are targets of the peer) before both are done.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    if (*abort_flag) {
+      const unsigned long long t0 = clock64();
+      while (clock64() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 int g_num_sms[64] = {0};
+int g_pair_clusters[64] = {0};   // co-resident clusters of the two-SM kernel, per device (-1: unusable)
 
 }  // namespace
 
@@ -653,6 +912,60 @@ int fsb_make_tmap_2d_plain(CUtensorMap* map, const void* base, CUtensorMapDataTy
   return FSB_OK;
 }
 
+static int g_use_pairs_value();
+static inline bool g_use_pairs_fwd() { return g_use_pairs_value() != 0; }
+
+static int gemm_pair_launch(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
+                            long long lda, long long ldb, long long ldd, long long ldc, int a_mn, int b_mn,
+                            int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
+                            long long d_block_rows, long long d_block_stride, const unsigned long long* d_peer,
+                            int d_peer_n, int* status, cudaStream_t stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
+  if (g_pair_clusters[dev] == 0) {
+    g_pair_clusters[dev] = -1;
+    if (cudaFuncSetAttribute(gemm_bf16_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES) ==
+        cudaSuccess) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = SMEM2_BYTES;
+      cudaLaunchAttribute at{};
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2;
+      at.val.clusterDim.y = 1;
+      at.val.clusterDim.z = 1;
+      cfg.attrs = &at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_2sm_kernel, &cfg) == cudaSuccess && n > 0)
+        g_pair_clusters[dev] = n;
+    }
+    cudaGetLastError();
+  }
+  if (g_pair_clusters[dev] < 0) return FSB_ERR_TOO_LARGE;
+  CUtensorMap map_a, map_b;
+  int rc;
+  if (!a_mn) rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  else rc = fsb_make_tmap_2d(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
+  if (rc != FSB_OK) return rc;
+  if (!b_mn) rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN_HALF, BK);
+  else rc = fsb_make_tmap_2d(&map_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc != FSB_OK) return rc;
+  GemmArgs args{};
+  args.M = M; args.N = N; args.K = K; args.a_mn = a_mn; args.b_mn = b_mn;
+  args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
+  args.alpha = alpha; args.beta = beta; args.accumulate = accumulate;
+  args.d_block_rows = d_block_rows; args.d_block_stride = d_block_stride; args.d_peer_n = d_peer_n;
+  args.status = status;
+  for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
+  const long long tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int clusters = tiles < g_pair_clusters[dev] ? static_cast<int>(tiles) : g_pair_clusters[dev];
+  gemm_bf16_2sm_kernel<<<2 * clusters, NUM_THREADS, SMEM2_BYTES, stream>>>(map_a, map_b, args);
+  return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}
+
 // D = alpha * A.B^T + beta * C (+ D). Shapes in elements; see the header comment
 // for the meaning of a_mn / b_mn. `status` is a device int the kernel writes an
 // error code to when a bounded wait runs out (left untouched otherwise).
@@ -728,6 +1041,13 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
                           const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
+  if (d_peer_n < 0 || d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
+  if (g_use_pairs_fwd() && M >= 2 * BM && N >= BN && max_ctas <= 0) {
+    const int rc2 = gemm_pair_launch(a, b, d, c, M, N, K, lda, ldb, ldd, ldc, a_mn, b_mn, d_fp32, c_fp32, alpha,
+                                     beta, accumulate, d_block_rows, d_block_stride, d_peer, d_peer_n, status,
+                                     stream);
+    if (rc2 != FSB_ERR_TOO_LARGE) return rc2;   // TOO_LARGE here means "pairs unusable on this device"
+  }
   CUtensorMap map_a, map_b;
   int rc;
   if (!a_mn) {
@@ -757,7 +1077,6 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms[dev] ? tiles : g_num_sms[dev];
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  if (d_peer_n < 0 || d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
   GemmArgs args{};
   args.M = M; args.N = N; args.K = K; args.a_mn = a_mn; args.b_mn = b_mn;
   args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
@@ -768,6 +1087,14 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   AgArgs none{};
   gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, args, none);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}
+
+// 0: one-SM kernel only; 1 (default): dense GEMMs with M >= 256 and N >= 256 run on SM pairs.
+static int g_use_pairs = 1;
+static int g_use_pairs_value() { return g_use_pairs; }
+FSB_API int fsb_gemm_set_pair_mode(int on) {
+  g_use_pairs = on;
+  return FSB_OK;
 }
 
 // All-gather -> GEMM in one kernel: D[M,N] = A[M,K] . W[N,K]^T where W is row-sharded over
