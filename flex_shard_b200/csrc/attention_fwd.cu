@@ -28,6 +28,12 @@ constexpr int SMEM_FWD = Q_BYTES + 2 * KV_BYTES + 2 * KV_BYTES + P_BYTES + 128;
 constexpr int TMEM_COLS_FWD = 256;          // S0 [0,64) S1 [64,128) O [128,256)
 constexpr int THREADS = 192;
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct FwdArgs {
   int S, Hq, Hkv;
   float scale_log2;   // softmax_scale * log2(e)
@@ -131,12 +137,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the loop (waits and descriptor arithmetic stay warp-uniform); one elected
+    // lane issues the tcgen05 instructions.
+    {
       const uint32_t idesc_s = make_idesc(BQ, BKV, 1, 1, 0, 0);
       const uint32_t idesc_o = make_idesc(BQ, HD, 1, 1, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dp = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      if (!ok) {
+      if (!ok && lane == 0) {
         atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
         *abort_flag = 1;
       }
@@ -145,43 +154,49 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int s = j & 1;
           const uint32_t ph = (j >> 1) & 1;
           if (!mbar_wait(&k_full[s], ph, abort_flag) || !mbar_wait(&s_empty[s], ph ^ 1, abort_flag)) {
-            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
-            *abort_flag = 1;
+            if (lane == 0) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              *abort_flag = 1;
+            }
             break;
           }
           tc_fence_after();
-          const uint32_t k_addr = smem_u32(sK + s * KV_BYTES);
+          const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + s * KV_BYTES), 16, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) {
-            const uint32_t qa = q_addr + (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32;
-            const uint32_t ka = k_addr + (k >> 2) * (KV_BYTES / 2) + (k & 3) * 32;
-            umma_f16(tmem_base + s * BKV, make_smem_desc_sw128(qa, 16, 1024),
-                     make_smem_desc_sw128(ka, 16, 1024), idesc_s, k != 0);
+            for (int k = 0; k < HD / 16; ++k) {
+              const uint32_t qo = ((k >> 2) * (Q_BYTES / 2) + (k & 3) * 32) >> 4;
+              const uint32_t ko = ((k >> 2) * (KV_BYTES / 2) + (k & 3) * 32) >> 4;
+              umma_f16(tmem_base + s * BKV, dq + qo, dk + ko, idesc_s, k != 0);
+            }
+            umma_commit(&k_empty[s]);
+            umma_commit(&s_full[s]);
           }
-          umma_commit(&k_empty[s]);
-          umma_commit(&s_full[s]);
+          __syncwarp();
         }
         if (j > 0) {
           const int jj = j - 1;
           const int s = jj & 1;
           const uint32_t ph = (jj >> 1) & 1;
           if (!mbar_wait(p_full, jj & 1, abort_flag) || !mbar_wait(&v_full[s], ph, abort_flag)) {
-            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
-            *abort_flag = 1;
+            if (lane == 0) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              *abort_flag = 1;
+            }
             break;
           }
           tc_fence_after();
-          const uint32_t v_addr = smem_u32(sV + s * KV_BYTES);
+          // A = P: K-major, 16 kv per step = 32 B inside the 128-byte row.
+          // B = V: MN-major, d chunks 8 KB apart (LBO), 8-kv groups 1 KB apart (SBO), 16 kv = 2 KB.
+          const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + s * KV_BYTES), KV_BYTES / 2, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k) {
-            // A = P: K-major, 16 kv per step = 32 B inside the 128-byte row.
-            // B = V: MN-major, d chunks 8 KB apart (LBO), 8-kv groups 1 KB apart (SBO), 16 kv = 2 KB.
-            umma_f16(tmem_o, make_smem_desc_sw128(p_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(v_addr + k * 2048, KV_BYTES / 2, 1024), idesc_o,
-                     (jj | k) != 0);
+            for (int k = 0; k < BKV / 16; ++k)
+              umma_f16(tmem_o, dp + ((k * 32) >> 4), dv + ((k * 2048) >> 4), idesc_o, (jj | k) != 0);
+            umma_commit(&v_empty[s]);
+            umma_commit(pv_done);
           }
-          umma_commit(&v_empty[s]);
-          umma_commit(pv_done);
+          __syncwarp();
         }
       }
     }
@@ -232,7 +247,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const bool warp_need = __any_sync(0xffffffffu, need);
       float alpha = 1.f;
       if (warp_need) {
-        if (j > 0) alpha = exp2f((m_used - m_new) * args.scale_log2);
+        if (j > 0) alpha = fast_exp2((m_used - m_new) * args.scale_log2);
         m_used = m_new;
       }
       // Exponentials first (registers only), so they overlap the previous tile's P V product.
@@ -241,10 +256,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t pk[32];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = exp2f(__uint_as_float(r0[2 * i]) * args.scale_log2 - mb);
-        const float p1 = exp2f(__uint_as_float(r0[2 * i + 1]) * args.scale_log2 - mb);
-        const float p2 = exp2f(__uint_as_float(r1[2 * i]) * args.scale_log2 - mb);
-        const float p3 = exp2f(__uint_as_float(r1[2 * i + 1]) * args.scale_log2 - mb);
+        const float p0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), args.scale_log2, -mb));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), args.scale_log2, -mb));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), args.scale_log2, -mb));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), args.scale_log2, -mb));
         sum += (p0 + p1) + (p2 + p3);
         pk[i] = pack_bf16x2(p0, p1);
         pk[16 + i] = pack_bf16x2(p2, p3);

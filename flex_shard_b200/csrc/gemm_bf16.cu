@@ -483,13 +483,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (waits and descriptor arithmetic stay warp-uniform); one elected
+    // lane issues the tcgen05 instructions.
+    {
       const uint32_t idesc = make_idesc(BM, BN, 1, 1, args.a_mn ? 1u : 0u, args.b_mn ? 1u : 0u);
       // K-major: 8-row groups 1024 B apart, K step of 16 elements = 32 B inside the atom.
       // MN-major: 64-wide MN groups 8192 B apart (LBO), 8-deep K groups 1024 B apart (SBO),
       //           K step of 16 = two K groups = 2048 B.
       const uint32_t a_lbo = args.a_mn ? 8192u : 16u, b_lbo = args.b_mn ? 8192u : 16u;
-      const uint32_t a_kstep = args.a_mn ? 2048u : 32u, b_kstep = args.b_mn ? 2048u : 32u;
+      const uint32_t a_kstep = (args.a_mn ? 2048u : 32u) >> 4, b_kstep = (args.b_mn ? 2048u : 32u) >> 4;
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
@@ -499,8 +501,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         ++local_tile;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
-          atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_EMPTY);
-          *abort_flag = 1;
+          if (lane == 0) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_TMEM_EMPTY);
+            *abort_flag = 1;
+          }
           break;
         }
         tc_fence_after();
@@ -509,23 +513,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
-            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
-            *abort_flag = 1;
+            if (lane == 0) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              *abort_flag = 1;
+            }
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t db = make_smem_desc_sw128(sa + A_STAGE_BYTES, b_lbo, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
-            const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f16(d_tmem, da + k * a_kstep, db + k * b_kstep, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
           }
-          umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
+          __syncwarp();
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        if (ok) {
+          if (elect_one()) umma_commit(&tmem_full[acc]);
+          __syncwarp();
+        }
       }
     }
   } else {
