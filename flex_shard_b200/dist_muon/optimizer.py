@@ -74,6 +74,7 @@ class DistMuon(torch.optim.Optimizer):
         self.compute_layouts = dict(compute_layouts or {})
         self.group = group
         self.collectives_issued = 0
+        self.p2p_exchanges = 0
         self._owner_by_fqn = dict(owner_by_fqn or {})
         self._ranks_per_host = ranks_per_host
         self._row_shard_plan = None
@@ -199,8 +200,15 @@ class DistMuon(torch.optim.Optimizer):
                 for r in range(W):
                     recv_sizes[r] += rows_of(shape, r) * math.prod(shape[1:])
         recv = torch.empty(sum(recv_sizes), dtype=torch.float32, device=dev)
+        # sizes[r][o]: elements rank r sends to owner o (every rank can compute the whole table)
+        sizes = [[0] * W for _ in range(W)]
+        for shape, owner in zip(shapes, owners):
+            cols = math.prod(shape[1:])
+            for r in range(W):
+                sizes[r][owner] += rows_of(shape, r) * cols
         if W > 1:
-            dist.all_to_all_single(recv, send, recv_sizes, send_sizes, group=pg)
+            self._exchange(recv, send, [sizes[r][rank] for r in range(W)],
+                           [[sizes[r][o] for o in range(W)] for r in range(W)], pg, rank)
             self.collectives_issued += 1
         else:
             recv.copy_(send)
@@ -230,7 +238,9 @@ class DistMuon(torch.optim.Optimizer):
         back_send = torch.cat([c for ch in back_chunks for c in ch]) if sum(back_send_sizes) else torch.empty(0, device=dev)
         back_recv = torch.empty(sum(send_sizes), dtype=torch.float32, device=dev)
         if W > 1:
-            dist.all_to_all_single(back_recv, back_send, send_sizes, back_send_sizes, group=pg)
+            # the way back: owner o returns to rank r exactly what r sent it
+            self._exchange(back_recv, back_send, [sizes[rank][o] for o in range(W)],
+                           [[sizes[r][o] for r in range(W)] for o in range(W)], pg, rank)
             self.collectives_issued += 1
         else:
             back_recv.copy_(back_send)
@@ -245,6 +255,47 @@ class DistMuon(torch.optim.Optimizer):
             rows, cols = shape[0], math.prod(shape[1:])
             muon_apply_(p.data, x.to(torch.bfloat16).contiguous(), float(group["lr"]), group["weight_decay"],
                         lr_ratio(group["adjust_lr_fn"], rows, cols))
+
+    def _exchange(self, recv, send, recv_from, send_table, pg, rank):
+        """Uneven all-to-all of fp32 elements. ``send_table[r][d]``: elements rank r sends to rank d, laid
+        out in r's ``send`` in order of d; ``recv_from[r]``: elements this rank receives from r, stored
+        in ``recv`` in order of r.
+
+        On NVLink meshes with the peer-memory backend every rank publishes its send buffer in the
+        symmetric region and *pulls* its pieces from the owners' memory with one kernel (no packing on
+        the receiving side, no NCCL all-to-all); otherwise ``all_to_all_single``. The reference moves
+        these row regions with ``all_to_all_single`` (``dist_muon/optimizer.py``)."""
+        W = len(send_table)
+        sc = self._symm_comm(pg, rank, W, send.device)
+        aligned = all(n % 4 == 0 for row in send_table for n in row)   # 16-byte pieces
+        if sc is None or not aligned:
+            dist.all_to_all_single(recv, send, list(recv_from), list(send_table[rank]), group=pg)
+            return
+        segs = []
+        dst = 0
+        for r in range(W):
+            n = send_table[r][rank]
+            if n:
+                src_off = sum(send_table[r][:rank])
+                segs.append((r, src_off * 4, recv.data_ptr() + dst * 4, n * 4))
+            dst += recv_from[r]
+        alloc = max(sum(row) for row in send_table) * 4
+        if not segs:   # nothing to receive: still publish, the peers pull from this rank
+            segs = [(rank, 0, recv.data_ptr() if recv.numel() else send.data_ptr(), 0)]
+        sc.all_gather_segments(send, segs, alloc_bytes=alloc)
+        self.p2p_exchanges += 1
+
+    def _symm_comm(self, pg, rank, W, device):
+        from ..parallel import comm as _comm
+
+        if device.type != "cuda" or W <= 1 or _comm._backend() != "symm":
+            return None
+        sc = getattr(self, "_symm", None)
+        if sc is None:
+            from ..parallel.symm import SymmComm
+
+            sc = self._symm = SymmComm(pg if pg is not None else dist.group.WORLD, rank, W, device)
+        return sc
 
     # ------------------------------------------------------------------ state dict
     def load_state_dict(self, state_dict):

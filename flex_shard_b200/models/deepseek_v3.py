@@ -128,13 +128,9 @@ class MoE(nn.Module):
 
     def route(self, xt):
         cfg = self.cfg
-        scores = torch.sigmoid(F.linear(xt.float(), self.gate.float()))
-        _, idx = (scores + self.expert_bias).topk(cfg.top_k, dim=-1)
-        w = scores.gather(1, idx)
-        w = w / (w.sum(-1, keepdim=True) + 1e-20) * cfg.route_scale
-        with torch.no_grad():
-            self.tokens_per_expert += torch.bincount(idx.reshape(-1), minlength=cfg.n_experts).float()
-        return idx, w
+        logits = F.linear(xt.float(), self.gate.float())
+        return moe_ops.route_topk(logits, cfg.top_k, bias=self.expert_bias, mode="sigmoid",
+                                  scale=cfg.route_scale, normalize=True, counts=self.tokens_per_expert)
 
     def forward(self, x):
         B, S, D = x.shape

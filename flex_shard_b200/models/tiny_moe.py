@@ -14,6 +14,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.moe import route_topk
+
 
 @dataclass
 class TinyMoEConfig:
@@ -110,9 +112,8 @@ class MoE(nn.Module):
     def forward(self, x):
         B, S, D = x.shape
         xt = x.reshape(-1, D)
-        probs = torch.softmax(self.router(xt).float(), dim=-1)
-        w, idx = probs.topk(self.top_k, dim=-1)
-        w = (w / w.sum(-1, keepdim=True)).to(x.dtype)
+        idx, w = route_topk(self.router(xt).float(), self.top_k, mode="softmax", normalize=True)
+        w = w.to(x.dtype)
         return self.experts(xt, idx, w).view(B, S, D)
 
 

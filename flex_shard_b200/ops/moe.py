@@ -30,6 +30,7 @@ def _ensure():
         _lib.declare("fsb_moe_combine_bwd_w", [vp, vp, vp, vp, i64, i32, i32, i64, i64, vp])
         _lib.declare("fsb_gemm_bf16_grouped", [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, i32, i32,
                                                vp, vp, vp, i32, vp, vp])
+        _lib.declare("fsb_route_topk", [vp, vp, i64, i32, i32, i32, i32, c.c_float, vp, vp, vp, vp])
         _declared = True
 
 
@@ -241,3 +242,71 @@ class _GroupedLinear(torch.autograd.Function):
 def grouped_linear(x_rows, weight, plan):
     """``x_rows`` in the expert-major layout of ``plan`` times the stacked ``weight [E, N, K]``."""
     return _GroupedLinear.apply(x_rows, weight, plan)
+
+
+def _route_scores(logits, mode):
+    return torch.sigmoid(logits) if mode == "sigmoid" else torch.softmax(logits, dim=-1)
+
+
+class _RouteTopK(torch.autograd.Function):
+    """Fused router: activation, biased top-k, weight normalisation, token histogram (one kernel on
+    CUDA); the backward pass is a handful of [T, k] / [T, E] elementwise ops."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, k, mode, scale, normalize, counts):
+        T, E = logits.shape
+        lg = logits.float().contiguous()
+        if lg.is_cuda:
+            _ensure()
+            idx = torch.empty(T, k, dtype=torch.int64, device=lg.device)
+            w = torch.empty(T, k, dtype=torch.float32, device=lg.device)
+            b = bias.float().contiguous() if bias is not None else None
+            if counts is not None and not (counts.dtype == torch.float32 and counts.is_contiguous()):
+                raise ValueError("counts must be a contiguous fp32 tensor")
+            rc = _lib.load().fsb_route_topk(lg.data_ptr(), b.data_ptr() if b is not None else None, T, E, k,
+                                            int(mode == "softmax"), int(normalize), float(scale), idx.data_ptr(),
+                                            w.data_ptr(), counts.data_ptr() if counts is not None else None,
+                                            _lib.stream_ptr(lg.device))
+            _lib.check(rc, "fsb_route_topk")
+            count_launch(1)
+        else:
+            s = _route_scores(lg, mode)
+            _, idx = (s + bias.float() if bias is not None else s).topk(k, dim=-1)
+            sel = s.gather(1, idx)
+            w = sel / (sel.sum(-1, keepdim=True) + 1e-20) * scale if normalize else sel * scale
+            if counts is not None:
+                counts += torch.bincount(idx.reshape(-1), minlength=E).to(counts.dtype)
+        ctx.save_for_backward(lg, idx)
+        ctx.cfg = (mode, float(scale), bool(normalize), logits.dtype)
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _didx, dw):
+        lg, idx = ctx.saved_tensors
+        mode, scale, normalize, in_dtype = ctx.cfg
+        s = _route_scores(lg, mode)
+        sel = s.gather(1, idx)
+        dw = dw.float()
+        if normalize:
+            denom = sel.sum(-1, keepdim=True) + 1e-20
+            dsel = scale * (dw / denom - (dw * sel).sum(-1, keepdim=True) / (denom * denom))
+        else:
+            dsel = scale * dw
+        ds = torch.zeros_like(s).scatter_(1, idx, dsel)
+        if mode == "sigmoid":
+            dlogits = ds * s * (1 - s)
+        else:
+            dlogits = s * (ds - (ds * s).sum(-1, keepdim=True))
+        return dlogits.to(in_dtype), None, None, None, None, None, None
+
+
+def route_topk(logits, k, bias=None, mode="sigmoid", scale=1.0, normalize=True, counts=None):
+    """Router decision for [T, E] logits: ``(idx [T, k] int64, weights [T, k] fp32)``.
+
+    ``mode``: "sigmoid" (DeepSeek-V3 style; ``bias`` steers the selection only) or "softmax".
+    ``normalize`` divides the selected scores by their sum; ``counts`` (fp32 [E]) is incremented
+    by the number of tokens sent to each expert."""
+    if mode not in ("sigmoid", "softmax"):
+        raise ValueError(f"unknown router mode {mode!r}")
+    return _RouteTopK.apply(logits, bias, k, mode, scale, normalize, counts)

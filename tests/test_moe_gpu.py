@@ -29,3 +29,24 @@ def test_moe_layer_matches_cpu_reference(T, k, E, D, F):
     for n, a, b in zip(names, res["cpu"], res["cuda"]):
         scale = max(a.abs().max().item(), 1e-3)
         assert (a - b).abs().max().item() < 4e-2 * scale, (n, (a - b).abs().max().item(), scale)
+
+
+@pytest.mark.parametrize("mode,normalize,E,k", [("sigmoid", True, 256, 8), ("softmax", True, 8, 2),
+                                                ("softmax", False, 64, 6), ("sigmoid", True, 40, 3)])
+def test_router_kernel_matches_reference(mode, normalize, E, k):
+    torch.manual_seed(3)
+    T = 1000
+    logits = torch.randn(T, E) * 2
+    bias = torch.randn(E) * 0.1 if mode == "sigmoid" else None
+    res = {}
+    for dev in ("cpu", "cuda"):
+        lg = logits.clone().to(dev).requires_grad_()
+        counts = torch.zeros(E, device=dev)
+        idx, w = moe.route_topk(lg, k, bias=None if bias is None else bias.to(dev), mode=mode, scale=2.5,
+                                normalize=normalize, counts=counts)
+        (w * torch.arange(1, k + 1, device=dev)).sum().backward()
+        res[dev] = (idx.cpu(), w.detach().cpu(), counts.cpu(), lg.grad.cpu())
+    assert torch.equal(res["cpu"][0], res["cuda"][0])
+    torch.testing.assert_close(res["cpu"][1], res["cuda"][1], rtol=1e-4, atol=1e-6)
+    assert torch.equal(res["cpu"][2], res["cuda"][2])
+    torch.testing.assert_close(res["cpu"][3], res["cuda"][3], rtol=1e-4, atol=1e-6)

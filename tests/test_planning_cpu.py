@@ -148,3 +148,28 @@ def test_adapters():
     assert lay.global_shape == (8, 8) and lay.global_offsets == ((4, 0),)
     lay = spmd_layout((2, 8), {"a": ("shard", 0), "b": ("shard", 0)}, {"a": (1, 2), "b": (0, 2)}, {0: ("a", "b")})
     assert lay.global_shape == (8, 8) and lay.global_offsets == ((4, 0),)
+
+
+def test_router_reference_gradients_match_autograd_of_the_plain_formula():
+    import torch
+    from flex_shard_b200.ops import moe
+
+    torch.manual_seed(0)
+    T, E, k = 37, 16, 4
+    for mode, normalize in (("sigmoid", True), ("softmax", True), ("softmax", False)):
+        lg = torch.randn(T, E, dtype=torch.float64).float().requires_grad_()
+        bias = torch.randn(E) * 0.1
+        counts = torch.zeros(E)
+        idx, w = moe.route_topk(lg, k, bias=bias, mode=mode, scale=1.7, normalize=normalize, counts=counts)
+        g = torch.randn(T, k)
+        (w * g).sum().backward()
+        lg2 = lg.detach().clone().requires_grad_()
+        s = torch.sigmoid(lg2) if mode == "sigmoid" else torch.softmax(lg2, -1)
+        _, idx2 = (s + bias).topk(k, dim=-1)
+        sel = s.gather(1, idx2)
+        w2 = sel / (sel.sum(-1, keepdim=True) + 1e-20) * 1.7 if normalize else sel * 1.7
+        (w2 * g).sum().backward()
+        assert torch.equal(idx, idx2)
+        torch.testing.assert_close(w, w2)
+        torch.testing.assert_close(lg.grad, lg2.grad, rtol=1e-5, atol=1e-7)
+        assert counts.sum().item() == T * k

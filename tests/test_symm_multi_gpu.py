@@ -143,3 +143,71 @@ def test_training_symm_paths_match_nccl(tmp_path):
         for mode in ("symm", "symm_fused_adam"):
             for a, b in zip(res[mode], res["nccl"]):
                 assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (mode, res)
+
+
+def _muon_worker(rank, world, port, out):
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flex_shard_b200 import BucketSpec, flex_shard, ops
+        from flex_shard_b200.dist_muon import DistMuon, get_flex_shard_muon_compute_layouts
+        from flex_shard_b200.parallel.comm import set_default_backend
+
+        dev = torch.device("cuda", rank)
+
+        class Net(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.w1 = nn.Linear(256, 512, bias=False)
+                self.w2 = nn.Linear(512, 256, bias=False)
+                self.w3 = nn.Linear(256, 384, bias=False)
+
+            def forward(self, x):
+                return self.w2(torch.relu(self.w1(x))) + self.w3(x)[:, :256]
+
+        results = {}
+        for mode in ("nccl", "symm"):
+            set_default_backend(mode)
+            torch.manual_seed(0)
+            model = Net().to(dev)
+            flex_shard(model, [BucketSpec(["*"])])
+            lays = get_flex_shard_muon_compute_layouts(model)
+            names = [n for n, _ in model.named_parameters()]
+            opt = DistMuon(list(model.parameters()), param_names=names, compute_layouts=lays, lr=0.02)
+            for s in range(3):
+                x = torch.randn(16, 256, generator=torch.Generator().manual_seed(10 * s + rank)).to(dev)
+                model(x).square().mean().backward()
+                opt.step()
+                opt.zero_grad()
+            torch.cuda.synchronize()
+            ops.check_status()
+            model.unshard()
+            results[mode] = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
+            results[mode + "_p2p"] = opt.p2p_exchanges
+            model.reshard()
+            del model, opt
+        set_default_backend(None)
+        dist.barrier()
+        torch.save(results, os.path.join(out, f"m{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_muon_row_redistribution_by_peer_pull_matches_all_to_all(tmp_path):
+    """DistMuon on Shard(0)-stored matrices: the owners pull the row regions out of the peers'
+    memory (both directions) instead of an NCCL all-to-all; parameters come out the same."""
+    import torch.multiprocessing as mp
+
+    from tests.common import free_port
+
+    mp.spawn(_muon_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"m{r}.pt")
+        assert res["symm_p2p"] == 2 * 3 and res["nccl_p2p"] == 0
+        for n in res["nccl"]:
+            torch.testing.assert_close(res["symm"][n], res["nccl"][n], rtol=0, atol=1e-6)
