@@ -91,15 +91,21 @@ def mx_quantize_weight_ref(w: torch.Tensor):
     return q.view(pr, pc)[:rows, :cols].contiguous(), e
 
 
-def mx_quantize_weight(w: torch.Tensor):
+def mx_quantize_weight(w: torch.Tensor, out_q: torch.Tensor | None = None, out_e: torch.Tensor | None = None):
     """bf16 ``[rows, cols]`` -> (e4m3 ``[rows, cols]``, uint8 tile exponents ``[ceil(r/32), ceil(c/32)]``)."""
     rows, cols = w.shape
     if not w.is_cuda:
-        return mx_quantize_weight_ref(w)
+        q, e = mx_quantize_weight_ref(w)
+        if out_q is not None:
+            out_q.view(torch.uint8).copy_(q.view(torch.uint8))
+            out_e.copy_(e)
+            return out_q, out_e
+        return q, e
     _ensure()
     w = w if (w.dtype == torch.bfloat16 and w.stride(1) == 1) else w.to(torch.bfloat16).contiguous()
-    q = torch.empty(rows, cols, dtype=FP8, device=w.device)
-    e = torch.empty(-(-rows // GROUP), -(-cols // GROUP), dtype=torch.uint8, device=w.device)
+    q = out_q if out_q is not None else torch.empty(rows, cols, dtype=FP8, device=w.device)
+    e = out_e if out_e is not None else torch.empty(-(-rows // GROUP), -(-cols // GROUP), dtype=torch.uint8,
+                                                    device=w.device)
     rc = _lib.load().fsb_mx_quant_weight(w.data_ptr(), q.data_ptr(), e.data_ptr(), rows, cols, w.stride(0),
                                          q.stride(0), _lib.stream_ptr(w.device))
     _lib.check(rc, "fsb_mx_quant_weight")

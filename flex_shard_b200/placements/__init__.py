@@ -3,6 +3,8 @@ from .block_shard import BlockShard, make_block_shard_placement_fn
 from .blockwise_quant import (
     BlockwiseQuantBucketedBlockShard,
     Fp8BucketedBlockShard,
+    Mxfp8BucketedBlockShard,
+    make_mxfp8_bucketed_block_shard_placement_fn,
     make_fp8_bucketed_block_shard_placement_fn,
     partition_min_max,
     plan_row_ranges,
@@ -19,6 +21,7 @@ from .shard import Shard, shard_placement_fn
 
 __all__ = [
     "BlockShard", "BlockwiseQuantBucketedBlockShard", "Fp8BucketedBlockShard", "make_fp8_bucketed_block_shard_placement_fn",
+    "Mxfp8BucketedBlockShard", "make_mxfp8_bucketed_block_shard_placement_fn",
     "partition_min_max", "plan_row_ranges", "BucketedBlockShard", "BucketedOwned", "FlatBucketPlan", "make_bucketed_block_shard_placement_fn", "MixedBucketPlacement", "Shard", "ShardSlice",
     "make_block_shard_placement_fn", "make_bucketed_owned_expert_block_placement_fn",
     "make_bucketed_owned_full_param_placement_fn", "make_mixed_placement_fn", "newton_schulz_cost",

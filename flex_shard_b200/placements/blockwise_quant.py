@@ -248,6 +248,44 @@ class Fp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
                                   shape, dtype)
 
 
+class Mxfp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
+    """MXFP8 payload: every rank owns whole 128-row units, quantises them to e4m3 with 32x32 tile
+    scales and sends the data plus one exponent byte per tile; after the gather each rank expands
+    the tile exponents into the two blocked scale tensors the tensor core reads (forward and
+    input-gradient orientation), so no swizzled scale bytes cross the wire.
+    Parity: ``custom_placements/mxfp8_bucketed_block_shard.py:202-350`` of the reference (which gathers
+    both pre-swizzled scale tensors)."""
+
+    block_size = 32
+
+    def __init__(self, row_ranges, scaling_mode: str = "rceil"):
+        if scaling_mode != "rceil":
+            raise ValueError(f"unsupported MXFP8 scaling mode {scaling_mode!r} (only 'rceil': round the scale up)")
+        super().__init__(row_ranges)
+        self.scaling_mode = scaling_mode
+
+    def qdata_nbytes(self, rows, cols):
+        return rows * cols
+
+    def scale_nbytes(self, rows, cols):
+        return -(-rows // 32) * -(-cols // 32)
+
+    def quantize_into(self, w, qdata_bytes, scale_bytes):
+        from ..ops.mxfp8 import FP8, mx_quantize_weight
+
+        rows, cols = w.shape
+        mx_quantize_weight(w.contiguous(), out_q=qdata_bytes.view(FP8).view(rows, cols),
+                           out_e=scale_bytes.view(-(-rows // 32), -(-cols // 32)))
+
+    def make_weight(self, qdata_bytes, scale_bytes, shape, dtype):
+        from ..ops.mxfp8 import FP8
+        from ..quant.weight import BlockwiseMxfp8Weight
+
+        rows, cols = shape[0], math.prod(shape[1:])
+        return BlockwiseMxfp8Weight.from_tile_exponents(qdata_bytes.view(FP8).view(rows, cols),
+                                                        scale_bytes.view(-(-rows // 32), -(-cols // 32)), shape, dtype)
+
+
 def plan_row_ranges(shapes: Sequence[tuple[int, ...]], world_size: int, block_rows: int,
                     cost_of: Callable[[int, int], int]) -> list[list[tuple[int, int]]]:
     """Row range of every parameter on every rank: ``result[param][rank] = (r0, r1)``."""
@@ -289,5 +327,23 @@ def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
         cost = lambda rows, cols: rows * cols + -(-rows // block_size) * -(-cols // block_size) * 4
         ranges = plan_row_ranges(shapes, W, block_size, cost)
         return {f: Fp8BucketedBlockShard(ranges[i]) for i, (f, _) in enumerate(named_params)}
+
+    return fn
+
+
+def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil"):
+    """Placement function for MXFP8 buckets: 2-D weights, rows handed out in whole 128-row units."""
+
+    def fn(named_params, mesh):
+        from ..parallel.comm import mesh_group
+
+        _, _, W, _ = mesh_group(mesh)
+        shapes = [tuple(p.shape) for _, p in named_params]
+        for (f, p) in named_params:
+            if p.dim() != 2:
+                raise ValueError(f"Mxfp8BucketedBlockShard needs 2-D weights, {f!r} has shape {tuple(p.shape)}")
+        cost = lambda rows, cols: rows * cols + -(-rows // 32) * -(-cols // 32)
+        ranges = plan_row_ranges(shapes, W, 128, cost)
+        return {f: Mxfp8BucketedBlockShard(ranges[i], scaling_mode) for i, (f, _) in enumerate(named_params)}
 
     return fn

@@ -14,7 +14,8 @@ import torch
 import torch.nn as nn
 
 from ..ops.fp8 import fp8_linear, quantize_blockwise
-from .weight import BlockwiseFp8Weight, BlockwiseQuantWeight
+from ..ops.mxfp8 import mx_expand_scales, mx_quantize_weight, mxfp8_linear
+from .weight import BlockwiseFp8Weight, BlockwiseMxfp8Weight, BlockwiseQuantWeight
 
 
 class FlexShardPrequantizedLinear(nn.Module):
@@ -43,6 +44,42 @@ class FlexShardFloat8BlockwiseLinear(FlexShardPrequantizedLinear):
         w = self.weight
         wq, ws = self.payload(w)
         return fp8_linear(x, w, wq, ws)
+
+
+class FlexShardMxfp8BlockwiseLinear(FlexShardPrequantizedLinear):
+    """Linear on MXFP8 operands: forward and input-gradient products run on the block-scaled tensor
+    core path (``kind::mxf8f6f4``), activations and output gradients are quantised 1x32 on the fly,
+    the weight gradient is a bf16 GEMM emitted in the parameter's gradient dtype.
+    Parity: ``blockwise_mxfp8/mxfp8_blockwise_linear.py:58-196`` of the reference."""
+
+    def payload(self, w):
+        if isinstance(w, BlockwiseMxfp8Weight):
+            return w.qdata, w.scale, w.dgrad_scale
+        rows, cols = w.shape
+        q, e = mx_quantize_weight(w.detach().to(torch.bfloat16))
+        return q, mx_expand_scales(e, rows, cols, False), mx_expand_scales(e, rows, cols, True)
+
+    def forward(self, x):
+        w = self.weight
+        q, fwd, dgrad = self.payload(w)
+        return mxfp8_linear(x, w, q, fwd, dgrad)
+
+
+def _convert(module: nn.Module, cls, filter_fn) -> nn.Module:
+    for name, child in list(module.named_children()):
+        if isinstance(child, nn.Linear) and child.bias is None and child.in_features % 128 == 0 \
+                and child.out_features % 128 == 0 and (filter_fn is None or filter_fn(name, child)):
+            new = cls(child.in_features, child.out_features, child.weight.dtype, child.weight.device)
+            new.weight = child.weight
+            setattr(module, name, new)
+        else:
+            _convert(child, cls, filter_fn)
+    return module
+
+
+def convert_to_flex_shard_mxfp8_blockwise_linear(module: nn.Module, filter_fn=None) -> nn.Module:
+    """Replace bias-free ``nn.Linear`` layers whose dims are multiples of 128 by the MXFP8 linear."""
+    return _convert(module, FlexShardMxfp8BlockwiseLinear, filter_fn)
 
 
 def convert_to_flex_shard_float8_blockwise_linear(module: nn.Module, filter_fn=None) -> nn.Module:

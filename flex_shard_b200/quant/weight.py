@@ -35,10 +35,12 @@ class BlockwiseQuantWeight(torch.Tensor):
         name = getattr(func, "_schema", None)
         fname = str(func)
         if "detach" in fname or "alias" in fname:
-            self = args[0]
-            return type(self)(self.qdata, self.scale, self.shape, self.dtype, **self.extra)
+            return args[0]._rebuild()
         raise NotImplementedError(
             f"{cls.__name__} only supports detach/alias; use it through a prequantised linear module ({fname})")
+
+    def _rebuild(self):
+        return type(self)(self.qdata, self.scale, self.shape, self.dtype, **self.extra)
 
     def __repr__(self):
         return f"{type(self).__name__}(shape={tuple(self.shape)}, dtype={self.dtype}, qdata={tuple(self.qdata.shape)})"
@@ -55,6 +57,56 @@ class BlockwiseFp8Weight(BlockwiseQuantWeight):
         from ..ops.fp8 import dequantize_blockwise
 
         return dequantize_blockwise(self.qdata, self.scale, dtype)
+
+
+class BlockwiseMxfp8Weight(BlockwiseQuantWeight):
+    """MXFP8 weight handed out by the all-gather: row-major e4m3 data ``[out, in]`` with 32x32 tile
+    scales, kept as the tile exponents plus the two scale tensors the tensor core reads
+    (``fwd_scale``: groups along ``in`` for y = x W^T; ``dgrad_scale``: groups along ``out`` for
+    dx = dy W), both in the blocked 128x4 layout.
+    Parity: ``blockwise_mxfp8/blockwise_mxfp8_weight.py:41-135`` of the reference."""
+
+    inner_names = ("qdata", "scale", "dgrad_scale")
+
+    @staticmethod
+    def __new__(cls, qdata, scale, shape, dtype=torch.bfloat16, dgrad_scale=None, **extra):
+        r = BlockwiseQuantWeight.__new__(cls, qdata, scale, shape, dtype, **extra)
+        r.dgrad_scale = dgrad_scale
+        return r
+
+    @classmethod
+    def from_tile_exponents(cls, qdata, tile_exp, shape, dtype=torch.bfloat16):
+        from ..ops.mxfp8 import mx_expand_scales
+
+        rows, cols = qdata.shape
+        return cls(qdata, mx_expand_scales(tile_exp, rows, cols, False), shape, dtype,
+                   dgrad_scale=mx_expand_scales(tile_exp, rows, cols, True), tile_exp=tile_exp)
+
+    @classmethod
+    def __tensor_unflatten__(cls, inner, meta, outer_size=None, outer_stride=None):
+        return cls(inner["qdata"], inner["scale"], meta["shape"], meta["dtype"], dgrad_scale=inner["dgrad_scale"],
+                   **meta.get("extra", {}))
+
+    def _rebuild(self):
+        return type(self)(self.qdata, self.scale, self.shape, self.dtype, dgrad_scale=self.dgrad_scale, **self.extra)
+
+    @property
+    def fp8_data(self):
+        return self.qdata
+
+    @property
+    def fwd_scale(self):
+        return self.scale
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        return blockwise_mxfp8_dequant_weight(self.qdata, self.scale).reshape(self.shape).to(dtype)
+
+
+def blockwise_mxfp8_dequant_weight(fp8_data: torch.Tensor, fwd_scale: torch.Tensor) -> torch.Tensor:
+    """Row-major e4m3 data with its forward-orientation blocked scales -> fp32."""
+    from ..ops.mxfp8 import mx_dequantize
+
+    return mx_dequantize(fp8_data, fwd_scale)
 
 
 def blockwise_dequant_weight(w: BlockwiseQuantWeight, dtype=torch.float32) -> torch.Tensor:

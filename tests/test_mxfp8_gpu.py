@@ -56,3 +56,26 @@ def test_block_scaled_gemm_matches_dequantised_product(M, N, K):
         wt = wq.float().t() * torch.exp2(mx.from_blocked(dgs, K, N // 32).float() - 127).repeat_interleave(32, 1)
         ref2 = mx.mx_dequantize(dq, sd) @ wt.t()
         torch.testing.assert_close(dx, ref2, rtol=1e-3, atol=1e-3 * N ** 0.5)
+
+
+def test_mxfp8_linear_gpu_matches_cpu_restatement():
+    import torch.nn as nn
+
+    from flex_shard_b200.quant import FlexShardMxfp8BlockwiseLinear
+
+    torch.manual_seed(4)
+    res = {}
+    w0 = (torch.randn(384, 256) * 0.05).bfloat16()
+    x0 = torch.randn(4, 50, 256).bfloat16()
+    g0 = torch.randn(4, 50, 384).bfloat16()
+    for dev in ("cpu", "cuda"):
+        lin = FlexShardMxfp8BlockwiseLinear(256, 384, device=dev)
+        with torch.no_grad():
+            lin.weight.copy_(w0)
+        x = x0.clone().to(dev).requires_grad_()
+        y = lin(x)
+        y.backward(g0.to(dev))
+        res[dev] = [t.detach().float().cpu() for t in (y, x.grad, lin.weight.grad)]
+    ops.check_status()
+    for a, b in zip(res["cpu"], res["cuda"]):
+        torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2 * max(1.0, a.abs().max().item()))
