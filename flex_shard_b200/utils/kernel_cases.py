@@ -3,7 +3,7 @@
     python -m flex_shard_b200.utils.kernel_cases <case> [--iters N]
 
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, adamw, rmsnorm, swiglu, cross_entropy,
-newton_schulz, fp8_quant, fp8_gemm, allgather_gemm. Each prints one JSON line with the CUDA-event time (median of
+newton_schulz, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm. Each prints one JSON line with the CUDA-event time (median of
 ``iters`` launches after 3 warm-up launches, L2 flushed between launches by writing a 256 MB buffer)
 and the achieved FLOP/s or bytes/s. Inputs are a few hundred MB, larger than the 126 MB L2, so DRAM
 counters of a profiler capture of the same command stay meaningful.
@@ -136,6 +136,30 @@ def main():
         ms = _time(lambda: fp8_linear_forward(x, wq, ws), args.iters)
         out.update(M=M, N=N, K=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9,
                    note="includes the 1x128 activation quantisation")
+    elif args.case == "mxfp8_gemm":
+        from flex_shard_b200.ops import mxfp8 as mx
+
+        M, N, K = 8192, 14336, 4096
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = torch.randn(N, K, device=dev).bfloat16()
+        wq, e = mx.mx_quantize_weight(w)
+        fwd = mx.mx_expand_scales(e, N, K, False)
+        xq, sx = mx.mx_quantize_act(x)
+        ms = _time(lambda: mx.gemm_mxfp8(xq, sx, wq, fwd), args.iters)
+        out.update(M=M, N=N, K=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9, note="GEMM only (operands pre-quantised)")
+        ms_q = _time(lambda: mx.mx_quantize_act(x), args.iters)
+        out.update(act_quant_ms=ms_q, act_quant_gbs=M * K * 3 / ms_q / 1e6)
+        try:   # the library's block-scaled product on the same operands, when this torch build has it
+            sa = sx.view(torch.float8_e8m0fnu)
+            sb = fwd.view(torch.float8_e8m0fnu)
+            f = lambda: torch._scaled_mm(xq, wq.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+            ref = f()
+            ours = mx.gemm_mxfp8(xq, sx, wq, fwd)
+            ms_l = _time(f, args.iters)
+            out.update(cublaslt_ms=ms_l, cublaslt_tflops=2.0 * M * N * K / ms_l / 1e9,
+                       max_abs_diff_vs_cublaslt=float((ref.float() - ours.float()).abs().max()))
+        except Exception as ex:  # noqa: BLE001
+            out.update(cublaslt="unavailable: " + str(ex).split("\n")[0][:120])
     elif args.case == "allgather_gemm":
         # 8 emulated peers on one GPU (the stager CTAs run the same bulk-copy ring; on a multi-GPU
         # job the sources are NVLink peer addresses instead of local ones)
