@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fsdp2"])
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--local-batch", type=int, default=1)
+    ap.add_argument("--keep-unsharded", type=int, default=1,
+                    help="1 (default): keep the gathered bf16 parameters between forward and backward (one all-gather "
+                         "per step instead of two; +2 bytes/param of HBM, affordable on 180 GB); 0: reshard after forward")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--comm", default=os.environ.get("FSB200_COMM", "symm"), choices=["symm", "nccl"],
@@ -196,6 +199,8 @@ def build_ours(args, world):
         set_default_backend(args.comm)
         mesh = init_device_mesh("cuda", (world,))
     flex_shard(model, llama_buckets(model, mesh=mesh))
+    if args.keep_unsharded:
+        model.set_reshard_after_forward(False)
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     if world > 1 and args.comm == "symm":
         opt.fuse_into_backward(model)  # AdamW runs inside the fused reduce kernel of each bucket
@@ -267,7 +272,8 @@ def run_ours(args, rank, local, world):
             "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers, d{cfg.d_model}, {cfg.n_heads}q/{cfg.n_kv_heads}kv, "
                                 f"ffn {cfg.ffn_hidden}, vocab {cfg.vocab_size})",
                        "global_batch": args.local_batch * world, "seq_len": S, "parallelism": f"dp{world}",
-                       "placement": "Shard(0) per-layer buckets, prefetch, bf16 params / fp32 reduce+AdamW state",
+                       "placement": "Shard(0) per-layer buckets, prefetch, bf16 params / fp32 reduce+AdamW state, "
+                                    + ("gathered params kept until backward" if args.keep_unsharded else "reshard after forward"),
                        "collectives": (args.comm if world > 1 else "none (1 rank)"),
                        "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
@@ -367,8 +373,8 @@ def run_fsdp2(args, rank, local, world):
     if world > 1:
         mp = MP(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
         for layer in model.layers:
-            fully_shard(layer, mp_policy=mp)
-        fully_shard(model, mp_policy=mp)
+            fully_shard(layer, mp_policy=mp, reshard_after_forward=not args.keep_unsharded)
+        fully_shard(model, mp_policy=mp, reshard_after_forward=not args.keep_unsharded)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     B, S = args.local_batch, args.seq_len
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
