@@ -267,23 +267,10 @@ class DistMuon(torch.optim.Optimizer):
         these row regions with ``all_to_all_single`` (``dist_muon/optimizer.py``)."""
         W = len(send_table)
         sc = self._symm_comm(pg, rank, W, send.device)
-        aligned = all(n % 4 == 0 for row in send_table for n in row)   # 16-byte pieces
-        if sc is None or not aligned:
-            dist.all_to_all_single(recv, send, list(recv_from), list(send_table[rank]), group=pg)
+        if sc is not None and sc.all_to_all_pull(recv, send, [[4 * n for n in row] for row in send_table]):
+            self.p2p_exchanges += 1
             return
-        segs = []
-        dst = 0
-        for r in range(W):
-            n = send_table[r][rank]
-            if n:
-                src_off = sum(send_table[r][:rank])
-                segs.append((r, src_off * 4, recv.data_ptr() + dst * 4, n * 4))
-            dst += recv_from[r]
-        alloc = max(sum(row) for row in send_table) * 4
-        if not segs:   # nothing to receive: still publish, the peers pull from this rank
-            segs = [(rank, 0, recv.data_ptr() if recv.numel() else send.data_ptr(), 0)]
-        sc.all_gather_segments(send, segs, alloc_bytes=alloc)
-        self.p2p_exchanges += 1
+        dist.all_to_all_single(recv, send, list(recv_from), list(send_table[rank]), group=pg)
 
     def _symm_comm(self, pg, rank, W, device):
         from ..parallel import comm as _comm

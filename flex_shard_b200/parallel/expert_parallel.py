@@ -6,10 +6,10 @@ the local experts, declares where they sit in the full weights (``set_global_lay
 ``init_from_full`` and checkpoints still see full tensors) and installs an ``AllToAllDispatcher``.
 
 The dispatcher sorts (token, choice) pairs by destination expert, exchanges per-(rank, expert)
-counts, moves the rows with one uneven all-to-all each way, and runs the local experts through the
-grouped tcgen05 GEMMs on an expert-major layout planned on the device. The only host
-synchronisation is the read of the all-to-all split sizes, which ``all_to_all_single`` needs as
-Python ints (as in the reference's dispatcher, ``examples/deepseek_v3/expert_parallel.py:59-165``).
+counts, moves the rows each way (with the peer-memory backend: every rank pulls its rows out of the
+senders' memory over NVLink with one kernel; otherwise one uneven NCCL all-to-all), and runs the
+local experts through the grouped tcgen05 GEMMs on an expert-major layout planned on the device.
+The only host synchronisation is the read of the row-count table, which sizes the receive buffers (as in the reference's dispatcher, ``examples/deepseek_v3/expert_parallel.py:59-165``).
 """
 from __future__ import annotations
 
@@ -20,19 +20,33 @@ from ..ops import moe as moe_ops
 from ..placement_contract import GlobalLayout, set_global_layout
 
 
+def _exchange_rows(out, x, out_splits, in_splits, table, group, symm):
+    """Rows of ``x`` grouped by destination rank -> rows grouped by source rank. ``table[src][dst]`` is
+    the full row-count table; with a peer-memory communicator every rank pulls its rows out of the
+    senders' memory over NVLink with one kernel, otherwise NCCL's all-to-all moves them."""
+    x = x.contiguous()
+    if symm is not None and x.is_cuda:
+        row_bytes = x[0].numel() * x.element_size() if x.dim() > 1 else x.element_size()
+        if symm.all_to_all_pull(out, x, [[n * row_bytes for n in row] for row in table]):
+            symm.p2p_row_exchanges = getattr(symm, "p2p_row_exchanges", 0) + 1
+            return
+    dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+
+
 class _AllToAll(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, out_splits, in_splits, group):
-        ctx.group, ctx.out_splits, ctx.in_splits = group, out_splits, in_splits
+    def forward(ctx, x, out_splits, in_splits, table, group, symm):
+        ctx.group, ctx.out_splits, ctx.in_splits, ctx.table, ctx.symm = group, out_splits, in_splits, table, symm
         out = x.new_empty(sum(out_splits), *x.shape[1:])
-        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        _exchange_rows(out, x, out_splits, in_splits, table, group, symm)
         return out
 
     @staticmethod
     def backward(ctx, dy):
         dx = dy.new_empty(sum(ctx.in_splits), *dy.shape[1:])
-        dist.all_to_all_single(dx, dy.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
-        return dx, None, None, None
+        back = [list(col) for col in zip(*ctx.table)]   # the way back: transposed table
+        _exchange_rows(dx, dy, ctx.in_splits, ctx.out_splits, back, ctx.group, ctx.symm)
+        return dx, None, None, None, None, None
 
 
 class AllToAllDispatcher:
@@ -42,6 +56,19 @@ class AllToAllDispatcher:
         self.rank = dist.get_rank(group)
         self.num_experts = num_experts
         self.local_experts = num_experts // self.ep
+        self._symm = None
+
+    def _symm_comm(self, device):
+        """Peer-memory communicator of the EP group when that backend is selected (CUDA only)."""
+        from . import comm as _comm
+
+        if device.type != "cuda" or self.ep <= 1 or _comm._backend() != "symm":
+            return None
+        if self._symm is None:
+            from .symm import SymmComm
+
+            self._symm = SymmComm(self.group, self.rank, self.ep, device)
+        return self._symm
 
     def __call__(self, xt, idx, weights, experts):
         T, k = idx.shape
@@ -49,12 +76,15 @@ class AllToAllDispatcher:
         flat = idx.reshape(-1)
         order = torch.argsort(flat, stable=True)                     # expert-major == destination-rank-major
         counts = torch.bincount(flat, minlength=E).view(ep, le)      # [dst rank, local expert]
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=self.group)  # [src rank, local expert]
-        in_splits = counts.sum(1).tolist()                            # the one host sync of this layer
-        out_splits = recv_counts.sum(1).tolist()
+        all_counts = torch.empty(ep, ep, le, dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(all_counts.view(-1), counts.reshape(-1), group=self.group)  # [src, dst, expert]
+        recv_counts = all_counts[:, self.rank, :].contiguous()       # [src rank, local expert]
+        table = all_counts.sum(-1).tolist()                           # the one host sync of this layer
+        in_splits = table[self.rank]
+        out_splits = [table[r][self.rank] for r in range(ep)]
+        symm = self._symm_comm(xt.device)
         send_rows = xt[order // k]
-        recv_rows = _AllToAll.apply(send_rows, out_splits, in_splits, self.group)
+        recv_rows = _AllToAll.apply(send_rows, out_splits, in_splits, table, self.group, symm)
         # rows arrive grouped by (src rank, local expert); name each row's local expert
         local_e = torch.repeat_interleave(
             torch.arange(le, device=xt.device).repeat(ep), recv_counts.reshape(-1),
@@ -66,7 +96,7 @@ class AllToAllDispatcher:
         y_rows = experts(rows, plan)
         ones = torch.ones(local_e.numel(), 1, dtype=torch.float32, device=xt.device)
         back = moe_ops.moe_combine(y_rows, ones, plan)               # undo the local expert-major order
-        ret = _AllToAll.apply(back, in_splits, out_splits, self.group)
+        ret = _AllToAll.apply(back, in_splits, out_splits, [list(col) for col in zip(*table)], self.group, symm)
         # ret[i] is the expert output of pair order[i]; weight and sum the k choices of every token
         inv = torch.empty_like(order)
         inv[order] = torch.arange(order.numel(), device=order.device)

@@ -257,6 +257,25 @@ class SymmComm(Comm):
         count_launch()
         reg.signal(self.SLOT_AG_DONE, e)
 
+    def all_to_all_pull(self, recv: torch.Tensor, send: torch.Tensor, table_bytes) -> bool:
+        """Uneven all-to-all as peer pulls. ``table_bytes[src][dst]``: bytes rank ``src`` sends to rank
+        ``dst``, laid out in ``src``'s ``send`` in order of ``dst``; this rank's pieces land in ``recv`` in
+        order of ``src``. Every rank passes the same table (it is what sizes the symmetric region).
+        Returns False (nothing done) when a piece is not a multiple of 16 bytes: use NCCL then."""
+        W, me = self.world_size, self.rank
+        if any(n % 16 for row in table_bytes for n in row):
+            return False
+        segs, dst = [], 0
+        for r in range(W):
+            n = table_bytes[r][me]
+            if n:
+                segs.append((r, sum(table_bytes[r][:me]), recv.data_ptr() + dst, n))
+            dst += n
+        if not segs:   # nothing to receive: still publish, the peers pull from this rank
+            segs = [(me, 0, send.data_ptr() if send.numel() else self._region("ag", 16).payload.data_ptr(), 0)]
+        self.all_gather_segments(send, segs, alloc_bytes=max(max(sum(row) for row in table_bytes), 16))
+        return True
+
     # ------------------------------------------------------------------ reduce-scatter
     def reduce_scatter_tensor(self, out: torch.Tensor, inp: torch.Tensor, plan: ReducePlan, async_op: bool = False):
         if self.world_size == 1 or inp.dtype != torch.float32 or out.numel() % 4 != 0:

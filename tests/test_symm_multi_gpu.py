@@ -211,3 +211,62 @@ def test_muon_row_redistribution_by_peer_pull_matches_all_to_all(tmp_path):
         assert res["symm_p2p"] == 2 * 3 and res["nccl_p2p"] == 0
         for n in res["nccl"]:
             torch.testing.assert_close(res["symm"][n], res["nccl"][n], rtol=0, atol=1e-6)
+
+
+def _ep_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flex_shard_b200 import ops
+        from flex_shard_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config
+        from flex_shard_b200.parallel.comm import set_default_backend
+        from flex_shard_b200.parallel.expert_parallel import apply_expert_parallel
+
+        dev = torch.device("cuda", rank)
+        cfg = DeepSeekV3Config(vocab_size=512, d_model=256, n_layers=2, n_dense_layers=1, n_heads=2, q_lora_rank=64,
+                               kv_lora_rank=32, qk_nope_dim=32, qk_rope_dim=16, v_dim=32, dense_hidden=256,
+                               n_experts=4, expert_hidden=128, top_k=2, n_shared_experts=1, max_seq_len=64)
+        results = {}
+        for mode in ("nccl", "symm"):
+            set_default_backend(mode)
+            torch.manual_seed(0)
+            model = DeepSeekV3(cfg, dtype=torch.bfloat16, device=dev)
+            model.init_weights(0)
+            apply_expert_parallel(model, dist.group.WORLD)
+            losses = []
+            for s in range(2):
+                t = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(17 * s + rank)).to(dev)
+                loss = model.loss(t[:, :-1], t[:, 1:], loss_is_root=False)
+                loss.backward()
+                losses.append(float(loss.detach()))
+                model.zero_grad()
+            torch.cuda.synchronize()
+            ops.check_status()
+            results[mode] = losses
+            results[mode + "_p2p"] = sum(getattr(m.dispatcher._symm, "p2p_row_exchanges", 0)
+                                         for m in model.moe_layers() if m.dispatcher._symm is not None)
+            del model
+        set_default_backend(None)
+        dist.barrier()
+        torch.save(results, os.path.join(out, f"e{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_rows_travel_by_peer_pull(tmp_path):
+    """Expert-parallel dispatch and combine (forward and backward) with the token rows pulled out of
+    the senders' memory over NVLink instead of an NCCL all-to-all: same losses."""
+    import torch.multiprocessing as mp
+
+    from tests.common import free_port
+
+    mp.spawn(_ep_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"e{r}.pt")
+        assert res["symm_p2p"] >= 4 and res["nccl_p2p"] == 0, res   # 2 steps x (dispatch, combine, and their backward)
+        for a, b in zip(res["symm"], res["nccl"]):
+            assert abs(a - b) < 1e-3 * max(1.0, abs(b)), res
