@@ -54,6 +54,7 @@ struct GemmArgs {
   // NVLink): the epilogue's stores ARE the all-to-all leg of a reduce-scatter.
   void* d_peer[16];
   int d_peer_n;
+  int d_peer_remote;   // the blocks are in other GPUs' memory: store whole 128-byte row segments
   // Grouped (mixture-of-experts) modes; rows of every group start on a multiple of 128 and are
   // padded with zero rows to a multiple of 128.
   //   1: grouped rows  - A [R, K]; m-tile t belongs to expert tile_expert[t] and multiplies that
@@ -184,7 +185,7 @@ __device__ __forceinline__ void store_tile(const GemmArgs& args, long long d_row
     uint32_t r[32];
     tmem_ld_32x32(t_row + c0, r);
     tmem_ld_wait();
-    if (args.d_peer_n > 0 && args.d_fp32 && !args.accumulate && args.c == nullptr && col + 32 <= args.N) {
+    if (args.d_peer_remote && args.d_peer_n > 0 && args.d_fp32 && !args.accumulate && args.c == nullptr && col + 32 <= args.N) {
       // Rows of this tile live in other GPUs' memory: transpose the warp's 32x32 block through
       // shared memory so that every store instruction writes one full 128-byte row segment
       // (NVLink moves whole lines efficiently, scattered 16-byte pieces poorly).
@@ -654,6 +655,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
                : "memory");
 }
 
+// When the rows of D live in several GPUs' memory (row block i belongs to rank i), consecutive tiles
+// are dealt round-robin over the row blocks, so the CTAs that run at the same time write to all
+// owners at once instead of bursting into one NVLink destination after the other.
+__device__ __forceinline__ int spread_over_row_blocks(int tm, int tiles_m, int nblk) {
+  const int per = tiles_m / nblk;
+  return (tm % nblk) * per + tm / nblk;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const GemmArgs args) {
@@ -677,6 +686,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int num_kb = (args.K + BK - 1) / BK;
   const int tile0 = static_cast<int>(blockIdx.x >> 1);
   const int tile_step = static_cast<int>(gridDim.x >> 1);
+  const bool spread = args.d_peer_remote && args.d_peer_n > 1 && args.d_block_rows % (2 * BM) == 0 &&
+                      static_cast<long long>(tiles_m) * (2 * BM) == args.d_block_rows * args.d_peer_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -712,6 +723,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
         int tm2, tn;
         tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+        if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
         const int m0 = tm2 * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -807,6 +819,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     for (int tile = tile0; tile < num_tiles; tile += tile_step) {
       int tm2, tn;
       tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+      if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
       const int tm = tm2 * 2 + static_cast<int>(rank);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -967,6 +980,8 @@ static int gemm_pair_launch(const void* a, const void* b, void* d, const void* c
   args.M = M; args.N = N; args.K = K; args.a_mn = a_mn; args.b_mn = b_mn;
   args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
   args.alpha = alpha; args.beta = beta; args.accumulate = accumulate;
+  args.d_peer_remote = d_peer_n > 0;
+  if (d_peer_n < 0) d_peer_n = -d_peer_n;
   args.d_block_rows = d_block_rows; args.d_block_stride = d_block_stride; args.d_peer_n = d_peer_n;
   args.status = status;
   for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
@@ -1051,11 +1066,14 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
                           const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
-  if (d_peer_n < 0 || d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
+  // a negative block count means: the blocks are in this GPU's own memory (no row-segment staging)
+  const int d_peer_remote = d_peer_n > 0;
+  if (d_peer_n < 0) d_peer_n = -d_peer_n;
+  if (d_peer_n > 16 || (d_peer_n > 0 && d_block_rows <= 0)) return FSB_ERR_BAD_ARG;
   if (g_use_pairs_fwd() && M >= 2 * BM && N >= BN && max_ctas <= 0) {
     const int rc2 = gemm_pair_launch(a, b, d, c, M, N, K, lda, ldb, ldd, ldc, a_mn, b_mn, d_fp32, c_fp32, alpha,
-                                     beta, accumulate, d_block_rows, d_block_stride, d_peer, d_peer_n, status,
-                                     stream);
+                                     beta, accumulate, d_block_rows, d_block_stride, d_peer,
+                                     d_peer_remote ? d_peer_n : -d_peer_n, status, stream);
     if (rc2 != FSB_ERR_TOO_LARGE) return rc2;   // TOO_LARGE here means "pairs unusable on this device"
   }
   CUtensorMap map_a, map_b;
@@ -1092,6 +1110,7 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
   args.alpha = alpha; args.beta = beta; args.accumulate = accumulate;
   args.d_block_rows = d_block_rows; args.d_block_stride = d_block_stride; args.d_peer_n = d_peer_n;
+  args.d_peer_remote = d_peer_remote;
   args.status = status;
   for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
   AgArgs none{};

@@ -23,8 +23,10 @@ class PeerBlocked:
     ``cols``). Handing it to ``gemm(out=...)`` makes the epilogue store each block straight into the
     owner's memory over NVLink."""
 
-    def __init__(self, addrs, block_rows: int, rows: int, cols: int, dtype: torch.dtype, device):
+    def __init__(self, addrs, block_rows: int, rows: int, cols: int, dtype: torch.dtype, device, local: bool = False):
         import ctypes
+
+        self.local = local   # every block is in this GPU's own memory: ordinary vector stores are best
 
         self.addrs = (ctypes.c_ulonglong * len(addrs))(*addrs)
         self.n = len(addrs)
@@ -92,7 +94,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     if peer is None:
         out_ptr, peer_ptrs, peer_n = out.data_ptr(), None, 0
     else:
-        out_ptr, peer_ptrs, peer_n = None, peer.addrs, peer.n
+        out_ptr, peer_ptrs, peer_n = None, peer.addrs, (-peer.n if peer.local else peer.n)
     a = _rowmajor(a)
     b = _rowmajor(b)
     if c is not None:

@@ -16,6 +16,8 @@ one hop away, so its host/relay planning reduces to direct peer access.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 
 import torch
@@ -127,7 +129,9 @@ class SymmComm(Comm):
         self._rs_epoch = 0
         self._ag_hint, self._rs_hint = ag_bytes, rs_bytes
         self._desc_cache: dict = {}
-        self.fused_reduce = True      # weight gradients go straight into the owners' memory
+        # weight gradients go straight into the owners' memory (FSB200_FUSED_REDUCE=0: gradients are
+        # written locally in reduce-scatter layout and the owners pull and sum them)
+        self.fused_reduce = os.environ.get("FSB200_FUSED_REDUCE", "1") != "0"
         self._grad_ring: SymmGradRing | None = None
 
     @classmethod
@@ -182,7 +186,7 @@ class SymmComm(Comm):
         reg = ring.region
         W = self.world_size
         reg.signal(ring.SLOT_WRITTEN0 + k, u)
-        rows = (ctypes.c_ulonglong * W)(*[ring.incoming_addr(self.rank, k, s, row) for s in range(W)])
+        rows = (ctypes.c_ulonglong * W)(*[ring.read_addr(self.rank, s, k, row) for s in range(W)])
         a = adam or {}
         p = a.get("p")
         rc = _lib.load().fsb_comm_reduce_rows(
@@ -328,6 +332,7 @@ class SymmGradRing:
         self.region = SymmRegion(group, entries * self.entry_bytes, device)
         self.uses = [0] * entries
         self.count = 0
+        self.pull = os.environ.get("FSB200_REDUCE_MODE", "pull") != "push"
 
     def acquire(self) -> tuple[int, int]:
         """Next entry and its use index; enqueues (on the current stream) the wait for every peer to
@@ -342,6 +347,21 @@ class SymmGradRing:
 
     def incoming_addr(self, owner: int, k: int, src: int, row_elems: int, elem_off: int = 0) -> int:
         return self.region.peer_payload_addr(owner, k * self.entry_bytes + (src * row_elems + elem_off) * 4)
+
+    # Two ways to use an entry. "push": rank ``me`` stores its contribution for owner ``dst`` straight
+    # into ``dst``'s entry (slot ``me``) over NVLink, the owner sums its own entry. "pull" (default): ``me``
+    # writes all W contributions into its own entry (slot ``dst``), the owner reads slot ``dst`` of every
+    # rank's entry over NVLink while it sums. Same memory, same flags; pull keeps the GEMM epilogue's
+    # stores local (remote stores from the epilogue slowed the weight-gradient GEMMs by 20-50 %).
+    def write_addr(self, me: int, dst: int, k: int, row_elems: int, elem_off: int = 0) -> int:
+        if self.pull:
+            return self.incoming_addr(me, k, dst, row_elems, elem_off)
+        return self.incoming_addr(dst, k, me, row_elems, elem_off)
+
+    def read_addr(self, me: int, src: int, k: int, row_elems: int) -> int:
+        if self.pull:
+            return self.incoming_addr(src, k, me, row_elems)
+        return self.incoming_addr(me, k, src, row_elems)
 
 
 class PeerBucket:

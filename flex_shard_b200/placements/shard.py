@@ -314,8 +314,9 @@ class Shard(Placement):
                 continue
             cols = math.prod(info.global_shape[1:])
             c = info.global_shape[0] // W
-            addrs = [ring.incoming_addr(i, k, me, row, o) for i in range(W)]
-            view = PeerBlocked(addrs, c, info.global_shape[0], cols, torch.float32, storage.device)
+            addrs = [ring.write_addr(me, i, k, row, o) for i in range(W)]
+            view = PeerBlocked(addrs, c, info.global_shape[0], cols, torch.float32, storage.device,
+                               local=ring.pull)
             view._fsb_bucket = bucket
             up.main_grad = view
             up.main_grad_written = False
@@ -332,7 +333,7 @@ class Shard(Placement):
             gf = g.reshape(-1).float().contiguous() if g.dtype != torch.float32 else g.reshape(-1).contiguous()
             keep.append(gf)
             for i in range(W):
-                segs.append((gf.data_ptr() + i * n * 4, ring.incoming_addr(i, k, me, row, o), n * 4))
+                segs.append((gf.data_ptr() + i * n * 4, ring.write_addr(me, i, k, row, o), n * 4))
         comm.scatter_to_peers(segs)
         prep = PlacementPreparedReduceGrad(infos=infos, send=None, reduce_dtype=torch.float32)
         prep.extra.update(offs=offs, row=row, peer_bucket=bucket, keep=keep)
