@@ -110,6 +110,32 @@ __global__ void mx_quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t
   *reinterpret_cast<uint32_t*>(q + row * ldq + sp * 128 + lane * 4) = *reinterpret_cast<const uint32_t*>(o);
 }
 
+// ------------------------------------------------------------------ transposed-use quantiser (32x1 groups)
+// For products that contract over the rows of x (weight gradients): one scale per (32-row group,
+// column). The data keeps its row-major layout; the scales are those of the operand x^T, i.e. blocked
+// with "rows" = columns of x and groups = 32-row groups of x. grid = (K/128, T/32), 128 threads:
+// thread t owns column 128*bx + t over the 32 rows of the group (loads and byte stores are coalesced).
+__global__ void __launch_bounds__(128)
+mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ scales,
+                     long long T, int K, long long ldx, long long ldq, int n_gb) {
+  const int col = blockIdx.x * 128 + threadIdx.x;
+  const long long r0 = static_cast<long long>(blockIdx.y) * 32;
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = (r0 + i < T) ? __bfloat162float(x[(r0 + i) * ldx + col]) : 0.f;
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  const uint32_t e = e8m0_round_up(amax);
+  const float inv = e8m0_inv(e);
+  scales[blocked_offset(col, static_cast<int>(blockIdx.y), n_gb)] = static_cast<uint8_t>(e);
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (r0 + i < T)
+      q[(r0 + i) * ldq + col] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3));
+}
+
 // ------------------------------------------------------------------ block-scaled GEMM
 constexpr int BM = 128, BN = 128, BK = 128;  // BK bytes == elements (fp8)
 constexpr int STAGES = 6;
@@ -122,7 +148,7 @@ constexpr int SF_COL0 = 256;
 
 struct MxArgs {
   int M, N, K;
-  int b_mn;
+  int a_mn, b_mn;
   const uint8_t* sfa;   // blocked scales of A: [ceil(M/128)][K/128][512]
   const uint8_t* sfb;   // blocked scales of B: [ceil(N/128)][K/128][512]
   void* d;
@@ -158,8 +184,8 @@ __device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint
 }
 // e4m3 x e4m3, e8m0 scales; sf_id selects which of a scale word's four bytes (which 32-deep group
 // of the stage) this MMA uses.
-__device__ __forceinline__ uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32_t b_mn, uint32_t sf_id) {
-  return (sf_id << 4) | (b_mn << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+__device__ __forceinline__ uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn, uint32_t sf_id) {
+  return (sf_id << 4) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -223,7 +249,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           uint8_t* sb = sa + A_STAGE;
           uint8_t* ssf = sb + B_STAGE;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(sa, &map_a, &full_bar[s], kb * BK, tm * BM);
+          if (!args.a_mn) tma_load_2d(sa, &map_a, &full_bar[s], kb * BK, tm * BM);
+          else tma_load_2d(sa, &map_a, &full_bar[s], tm * BM, kb * BK);  // [K rows][128 M bytes]
           if (!args.b_mn) tma_load_2d(sb, &map_b, &full_bar[s], kb * BK, tn * BN);
           else tma_load_2d(sb, &map_b, &full_bar[s], tn * BN, kb * BK);  // [K rows][128 N bytes]
           bulk_load_1d(ssf, args.sfa + (static_cast<long long>(tm) * num_kb + kb) * SF_BYTES, SF_BYTES, &full_bar[s]);
@@ -236,8 +263,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // The whole warp walks the loop; one elected lane issues the tcgen05 instructions.
     // K-major: 32 elements (bytes) per MMA inside the 128-byte row. MN-major B: one 128-wide
     // N group, 8-deep K groups 1 KB apart, 32 K = 4 groups = 4 KB per MMA.
-    const uint32_t b_kstep = (args.b_mn ? 4096u : 32u) >> 4;
-    const uint32_t b_mn = args.b_mn ? 1u : 0u;
+    const uint32_t a_kstep = (args.a_mn ? 4096u : 32u) >> 4, b_kstep = (args.b_mn ? 4096u : 32u) >> 4;
+    const uint32_t a_mn = args.a_mn ? 1u : 0u, b_mn = args.b_mn ? 1u : 0u;
     uint32_t it = 0, local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -274,7 +301,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tmem_cp_32x128b_x4(tsfb, make_sf_desc(ssf + SF_BYTES));
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)
-            umma_mxf8(tmem_base + acc * BN, da + k * 2, db + k * b_kstep, make_idesc_mx(BM, BN, b_mn, k), tsfa, tsfb,
+            umma_mxf8(tmem_base + acc * BN, da + k * a_kstep, db + k * b_kstep, make_idesc_mx(BM, BN, a_mn, b_mn, k), tsfa, tsfb,
                       (kb | k) != 0);
           umma_commit(&empty_bar[s]);
         }
@@ -394,17 +421,33 @@ FSB_API int fsb_mx_quant_act(const void* x, void* q, void* scales, long long T, 
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }
 
-// D[M,N] = (Aq * 2^sfa) . (Bq * 2^sfb)^T with K % 128 == 0. A: e4m3 [M, K] K-major. B: e4m3 [N, K]
-// (b_mn == 0) or [K, N] (b_mn == 1: N contiguous, N % 16 == 0). sfa / sfb: blocked scales of the
+// x: bf16 [T, K] with T % 128 == 0 and K % 128 == 0; q: e4m3 [T, K] (same layout); scales: blocked scales of
+// the operand x^T ([K rows, T/32 groups]): K * (T/32) bytes.
+FSB_API int fsb_mx_quant_rows(const void* x, void* q, void* scales, long long T, int K, long long ldx, long long ldq,
+                              cudaStream_t stream) {
+  if (K % 128 != 0 || T % 128 != 0) return FSB_ERR_BAD_ARG;
+  if (T <= 0) return FSB_OK;
+  dim3 grid(K / 128, static_cast<unsigned>(T / 32));
+  mx_quant_rows_kernel<<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q),
+                                                 static_cast<uint8_t*>(scales), T, K, ldx, ldq,
+                                                 static_cast<int>(T / 128));
+  return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+}
+
+// D[M,N] = (Aq * 2^sfa) . (Bq * 2^sfb)^T with K % 128 == 0. A: e4m3 [M, K] (a_mn == 0) or [K, M]
+// (a_mn == 1: M contiguous, M % 16 == 0). B: e4m3 [N, K] (b_mn == 0) or [K, N] (b_mn == 1: N contiguous,
+// N % 16 == 0). sfa / sfb: blocked scales of the
 // operands as the GEMM sees them ([M, K] and [N, K]).
 FSB_API int fsb_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* sfb, void* d, int M, int N,
-                           int K, long long lda, long long ldb, long long ldd, int b_mn, int d_fp32, int* status,
-                           cudaStream_t stream) {
+                           int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32,
+                           int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || K % BK != 0) return FSB_ERR_BAD_ARG;
-  if (b_mn && N % 16 != 0) return FSB_ERR_BAD_ARG;
+  if ((b_mn && N % 16 != 0) || (a_mn && M % 16 != 0)) return FSB_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb)) & 15) return FSB_ERR_BAD_ARG;
   CUtensorMap map_a, map_b;
-  int rc = fsb_make_tmap_2d(&map_a, aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, BM, BK);
+  int rc;
+  if (!a_mn) rc = fsb_make_tmap_2d(&map_a, aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, BM, BK);
+  else rc = fsb_make_tmap_2d(&map_a, aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, lda, BK, BM);
   if (rc != FSB_OK) return rc;
   if (!b_mn) rc = fsb_make_tmap_2d(&map_b, bq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, BN, BK);
   else rc = fsb_make_tmap_2d(&map_b, bq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, ldb, BK, BN);
@@ -421,7 +464,7 @@ FSB_API int fsb_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, cons
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_sms[dev] ? tiles : g_sms[dev];
   MxArgs a;
-  a.M = M; a.N = N; a.K = K; a.b_mn = b_mn;
+  a.M = M; a.N = N; a.K = K; a.a_mn = a_mn; a.b_mn = b_mn;
   a.sfa = static_cast<const uint8_t*>(sfa); a.sfb = static_cast<const uint8_t*>(sfb);
   a.d = d; a.ldd = ldd; a.d_fp32 = d_fp32; a.status = status;
   gemm_mxfp8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, a);

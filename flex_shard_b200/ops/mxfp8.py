@@ -24,6 +24,7 @@ from .gemm import gemm
 
 FP8 = torch.float8_e4m3fn
 GROUP = 32
+MX_WGRAD = True   # weight gradients of the MXFP8 linear as a third block-scaled product (when dims allow)
 _declared = False
 
 
@@ -35,7 +36,8 @@ def _ensure():
         _lib.declare("fsb_mx_quant_weight", [vp, vp, vp, i32, i32, i64, i64, vp])
         _lib.declare("fsb_mx_expand_scales", [vp, vp, i32, i32, i32, vp])
         _lib.declare("fsb_mx_quant_act", [vp, vp, vp, i64, i32, i64, i64, vp])
-        _lib.declare("fsb_gemm_mxfp8", [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, vp])
+        _lib.declare("fsb_mx_quant_rows", [vp, vp, vp, i64, i32, i64, i64, vp])
+        _lib.declare("fsb_gemm_mxfp8", [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, i32, vp, vp])
         _declared = True
 
 
@@ -159,6 +161,27 @@ def mx_quantize_act(x: torch.Tensor):
     return q, s
 
 
+def mx_quantize_rows(x: torch.Tensor):
+    """bf16 ``[T, K]`` (T and K multiples of 128) quantised in 32x1 groups (32 consecutive rows of a
+    column share a scale), for products that contract over the rows. Returns (e4m3 ``[T, K]`` in the
+    same layout, blocked scales of the operand ``x^T``: ``[K rows, T/32 groups]``)."""
+    T, K = x.shape
+    if T % 128 or K % 128:
+        raise ValueError("both dims must be multiples of 128")
+    if not x.is_cuda:
+        q, s = mx_quantize_act_ref(x.t().contiguous())
+        return q.t().contiguous(), s
+    _ensure()
+    x = x if (x.dtype == torch.bfloat16 and x.stride(1) == 1) else x.to(torch.bfloat16).contiguous()
+    q = torch.empty(T, K, dtype=FP8, device=x.device)
+    s = torch.empty(blocked_scale_numel(K, T), dtype=torch.uint8, device=x.device)
+    rc = _lib.load().fsb_mx_quant_rows(x.data_ptr(), q.data_ptr(), s.data_ptr(), T, K, x.stride(0), q.stride(0),
+                                       _lib.stream_ptr(x.device))
+    _lib.check(rc, "fsb_mx_quant_rows")
+    count_launch()
+    return q, s
+
+
 def mx_dequantize(q: torch.Tensor, blocked: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
     """Row-major e4m3 ``[rows, cols]`` with blocked scales whose groups run along the columns."""
     rows, cols = q.shape
@@ -168,14 +191,16 @@ def mx_dequantize(q: torch.Tensor, blocked: torch.Tensor, dtype=torch.float32) -
 
 
 # --------------------------------------------------------------------------- GEMM
-def gemm_mxfp8(aq, sfa, bq, sfb, *, b_t: bool = False, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """``out[M, N] = (Aq * 2^sfa) . (Bq * 2^sfb)^T``. ``aq``: e4m3 ``[M, K]``; ``bq``: e4m3 ``[N, K]``
-    or, with ``b_t``, the same operand stored ``[K, N]``. ``sfa`` / ``sfb``: blocked scales of the
-    operands as the product sees them (``[M, K]`` and ``[N, K]``, groups along K)."""
-    M, K = aq.shape
+def gemm_mxfp8(aq, sfa, bq, sfb, *, a_t: bool = False, b_t: bool = False, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``out[M, N] = (Aq * 2^sfa) . (Bq * 2^sfb)^T``. ``aq``: e4m3 ``[M, K]`` or, with ``a_t``, stored
+    ``[K, M]``; ``bq``: e4m3 ``[N, K]`` or, with ``b_t``, stored ``[K, N]``. ``sfa`` / ``sfb``: blocked
+    scales of the operands as the product sees them (``[M, K]`` and ``[N, K]``, groups along K)."""
+    M, K = (aq.shape[1], aq.shape[0]) if a_t else aq.shape
     N = bq.shape[1] if b_t else bq.shape[0]
     if not aq.is_cuda:
-        a = mx_dequantize(aq, sfa)
+        al = aq.float().t() if a_t else aq.float()
+        ea = from_blocked(sfa, M, K // GROUP)
+        a = al * torch.exp2(ea.float() - 127.0).repeat_interleave(GROUP, 1)[:, :K]
         bl = bq.float().t() if b_t else bq.float()
         e = from_blocked(sfb, N, K // GROUP)
         b = bl * torch.exp2(e.float() - 127.0).repeat_interleave(GROUP, 1)[:, :K]
@@ -184,7 +209,7 @@ def gemm_mxfp8(aq, sfa, bq, sfb, *, b_t: bool = False, out_dtype=torch.bfloat16)
     out = torch.empty(M, N, dtype=out_dtype, device=aq.device)
     status = _lib.status_word(aq.device)
     rc = _lib.load().fsb_gemm_mxfp8(aq.data_ptr(), sfa.data_ptr(), bq.data_ptr(), sfb.data_ptr(), out.data_ptr(),
-                                    M, N, K, aq.stride(0), bq.stride(0), out.stride(0), int(b_t),
+                                    M, N, K, aq.stride(0), bq.stride(0), out.stride(0), int(a_t), int(b_t),
                                     int(out_dtype == torch.float32), status.data_ptr(), _lib.stream_ptr(aq.device))
     _lib.check(rc, "fsb_gemm_mxfp8")
     count_launch()
@@ -217,14 +242,20 @@ class _Mxfp8Linear(torch.autograd.Function):
             dx = gemm_mxfp8(dyq, sdy, wq, dgrad_scale, b_t=True).view(ctx.xshape)
         if ctx.needs_input_grad[1]:
             main = getattr(weight, "main_grad", None)
+            gd = getattr(weight, "grad_dtype", None) or torch.bfloat16
+            gd = gd if gd in (torch.bfloat16, torch.float32) else torch.bfloat16
             if main is not None and main.dtype in (torch.float32, torch.bfloat16):
                 gemm(dy2, x2, a_t=True, b_t=True, out=main,
                      accumulate=bool(getattr(weight, "main_grad_written", False)))
                 weight.main_grad_written = True
+            elif MX_WGRAD and dy2.shape[0] % 128 == 0 and dy2.shape[1] % 128 == 0 and x2.shape[1] % 128 == 0:
+                # third block-scaled product: dW = dy^T x, both operands quantised in 32x1 groups along
+                # the tokens (the contraction) and read transposed by the tensor core
+                dq, sd = mx_quantize_rows(dy2)
+                xq, sx = mx_quantize_rows(x2)
+                dw = gemm_mxfp8(dq, sd, xq, sx, a_t=True, b_t=True, out_dtype=gd)
             else:
-                gd = getattr(weight, "grad_dtype", None) or torch.bfloat16
-                dw = gemm(dy2, x2, a_t=True, b_t=True,
-                          out_dtype=gd if gd in (torch.bfloat16, torch.float32) else torch.bfloat16)
+                dw = gemm(dy2, x2, a_t=True, b_t=True, out_dtype=gd)
         return dx, dw, None, None, None
 
 

@@ -79,3 +79,28 @@ def test_mxfp8_linear_gpu_matches_cpu_restatement():
     ops.check_status()
     for a, b in zip(res["cpu"], res["cuda"]):
         torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2 * max(1.0, a.abs().max().item()))
+
+
+@pytest.mark.parametrize("T,K", [(128, 128), (512, 384)])
+def test_row_group_quantiser_matches_reference_bitwise(T, K):
+    torch.manual_seed(5)
+    x = (torch.randn(T, K) * 3).bfloat16()
+    x[32:64, 7] = 0
+    q_ref, s_ref = mx.mx_quantize_rows(x)
+    q, s = mx.mx_quantize_rows(x.cuda())
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(s.cpu(), s_ref)
+
+
+@pytest.mark.parametrize("T,N,K", [(128, 128, 128), (512, 256, 384), (2048, 1024, 512)])
+def test_weight_gradient_product_reads_both_operands_transposed(T, N, K):
+    torch.manual_seed(6)
+    dev = torch.device("cuda")
+    dy = torch.randn(T, N, device=dev).bfloat16()
+    x = (torch.randn(T, K, device=dev) * 2).bfloat16()
+    dq, sd = mx.mx_quantize_rows(dy)
+    xq, sx = mx.mx_quantize_rows(x)
+    dw = mx.gemm_mxfp8(dq, sd, xq, sx, a_t=True, b_t=True, out_dtype=torch.float32)
+    ops.check_status()
+    ref = mx.gemm_mxfp8(dq.cpu(), sd.cpu(), xq.cpu(), sx.cpu(), a_t=True, b_t=True, out_dtype=torch.float32)
+    torch.testing.assert_close(dw.cpu(), ref, rtol=1e-3, atol=1e-3 * T ** 0.5)
