@@ -1,0 +1,111 @@
+"""Checkpoints across world sizes: model + AdamW state saved from 2 gloo ranks (Shard(0) with uneven
+rows) reload bitwise into a single unsharded-size process; optimizer-hook error cases."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.nn as nn
+
+from tests.common import run_ranks
+
+
+class Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(6, 7)        # 7 rows over 2 ranks: uneven
+        self.b = nn.Linear(7, 3)
+
+    def forward(self, x):
+        return self.b(torch.tanh(self.a(x)))
+
+
+def _train_and_save(rank, world, path):
+    from flex_shard_b200 import BucketSpec, checkpoint, flex_shard, set_state_dict_global_layouts
+    from flex_shard_b200.checkpoint import register_optimizer_checkpoint_hook
+
+    torch.manual_seed(0)
+    m = Net()
+    flex_shard(m, [BucketSpec(["*"])])
+    opt = torch.optim.AdamW(m.parameters(), lr=0.05)
+    register_optimizer_checkpoint_hook(opt, m)
+    try:
+        register_optimizer_checkpoint_hook(opt, m)
+        second = ""
+    except ValueError as e:
+        second = str(e)
+    for s in range(3):
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(100 + s))   # same data on both ranks
+        m(x).square().mean().backward()
+        opt.step()
+        opt.zero_grad()
+    sd = m.state_dict()
+    set_state_dict_global_layouts(m, sd)
+    checkpoint.save({"model": sd, "optim": opt.state_dict()}, path)
+    return second
+
+
+def test_save_on_two_ranks_load_on_one():
+    from flex_shard_b200 import BucketSpec, checkpoint, flex_shard, set_state_dict_global_layouts
+    from flex_shard_b200.checkpoint import register_optimizer_checkpoint_hook
+
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ckpt")
+        res = run_ranks(_train_and_save, 2, path)
+        assert all("already has" in r for r in res)
+        # the same three steps without sharding
+        torch.manual_seed(0)
+        ref = Net()
+        ropt = torch.optim.AdamW(ref.parameters(), lr=0.05)
+        for s in range(3):
+            x = torch.randn(4, 6, generator=torch.Generator().manual_seed(100 + s))
+            ref(x).square().mean().backward()
+            ropt.step()
+            ropt.zero_grad()
+        # reload into a 1-rank flex_shard model (no process group at all)
+        torch.manual_seed(1)
+        m = Net()
+        flex_shard(m, [BucketSpec(["*"])])
+        opt = torch.optim.AdamW(m.parameters(), lr=0.05)
+        register_optimizer_checkpoint_hook(opt, m)
+        x = torch.randn(4, 6)
+        m(x).square().mean().backward()   # materialise the optimizer state so there is something to load into
+        opt.step()
+        opt.zero_grad()
+        sd = m.state_dict()
+        set_state_dict_global_layouts(m, sd)
+        osd = opt.state_dict()
+        checkpoint.load({"model": sd, "optim": osd}, path)
+        m.load_state_dict(sd)
+        opt.load_state_dict(osd)
+        m.unshard()
+        for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+            torch.testing.assert_close(p.detach(), q.detach(), rtol=0, atol=1e-6), n
+        m.reshard()
+        for p, q in zip(m.parameters(), ref.parameters()):
+            for key in ("exp_avg", "exp_avg_sq"):
+                torch.testing.assert_close(opt.state[p][key].reshape(-1), ropt.state[q][key].reshape(-1)[: opt.state[p][key].numel()],
+                                           rtol=0, atol=1e-6)
+        # and the next step agrees
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(7))
+        m(x).square().mean().backward()
+        opt.step()
+        ref(x).square().mean().backward()
+        ropt.step()
+        m.unshard()
+        for p, q in zip(m.parameters(), ref.parameters()):
+            torch.testing.assert_close(p.detach(), q.detach(), rtol=0, atol=1e-5)
+        m.reshard()
+
+
+def test_optimizer_hook_rejects_foreign_optimizers():
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.checkpoint import register_optimizer_checkpoint_hook
+
+    m = Net()
+    flex_shard(m, [BucketSpec(["*"])])
+    with pytest.raises(ValueError, match="Adam"):
+        register_optimizer_checkpoint_hook(torch.optim.SGD(m.parameters(), lr=0.1), m)
+    other = Net()
+    with pytest.raises(ValueError, match="none of the module"):
+        register_optimizer_checkpoint_hook(torch.optim.AdamW(other.parameters(), lr=0.1), m)
