@@ -202,8 +202,10 @@ def build_ours(args, world):
     if args.keep_unsharded:
         model.set_reshard_after_forward(False)
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    if world > 1 and args.comm == "symm":
-        opt.fuse_into_backward(model)  # AdamW runs inside the fused reduce kernel of each bucket
+    if world == 1 or args.comm == "symm":
+        # AdamW runs as soon as a bucket's gradients are final: inside the fused reduce kernel (N > 1) or
+        # as one flat launch on a side stream (N = 1), overlapped with the rest of the backward pass
+        opt.fuse_into_backward(model)
     return cfg, model, opt
 
 

@@ -95,6 +95,11 @@ def begin_reduce_grad(runtime, grads, reduce_dtype, reduction: GradientReduction
     if stream is None or comm.world_size == 1:
         res = placement.reduce_prepared_grad(prep, comm, reduction)
         runtime.accumulate_sharded_grads(res)
+        ctx = runtime.context
+        if (fused_opt is not None and comm.world_size == 1 and ctx.cuda and not ctx.manual_finalization):
+            # one rank: the gradients are final here; let the optimizer update this bucket on the side
+            # stream while the rest of the backward pass keeps the tensor cores busy
+            fused_opt.step_bucket_in_backward(storage, ctx.reduce_stream)
         return PendingReduce(runtime, prep, res, None)
     ev = torch.cuda.current_stream().record_event()
     stream.wait_event(ev)

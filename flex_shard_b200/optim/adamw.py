@@ -56,16 +56,35 @@ class FusedAdamW(torch.optim.Optimizer):
 
     # ------------------------------------------------------------------ optimizer inside backward
     def fuse_into_backward(self, module) -> None:
-        """Let the fused reduce-scatter kernel apply this optimizer's update to a bucket the moment its
-        gradients are reduced (no gradient is materialised for those buckets; ``step()`` then only
-        covers what is left). Only for buckets reduced through peer memory; others are unaffected.
-        Not compatible with gradient clipping, which needs every gradient before any update."""
+        """Apply this optimizer's update to a bucket the moment its gradients are complete, while the
+        backward pass of the remaining layers is still running: on multi-rank peer-memory meshes inside
+        the fused reduce-scatter kernel (no gradient is materialised for those buckets), on 1-rank meshes
+        as one flat AdamW launch on a side stream. ``step()`` then only covers what is left and joins
+        the side stream. Not compatible with gradient clipping, which needs every gradient before any
+        update, nor with reusing a layer's parameters later in the same backward pass."""
         for st in module.sharded_bucket_storages:
             plist = [p for p in st.sharded_params]
             mine = {id(p) for g in self.param_groups for p in g["params"]}
             if all(id(p) in mine for p in plist) and len({p.dtype for p in plist}) == 1:
                 st._fused_opt = self
         self._stepped_in_backward: set[int] = set()
+        self._backward_events: list = []
+
+    def step_bucket_in_backward(self, storage, stream) -> bool:
+        """1-rank path: the bucket's gradients are final; update it on ``stream`` after everything queued
+        so far on the current stream. Returns False when the bucket cannot be updated as one flat launch."""
+        plist = list(storage.sharded_params)
+        if not plist or any(p.grad is None for p in plist) or not self._grads_flat(plist, storage):
+            return False
+        if len({p.grad.dtype for p in plist}) != 1:
+            return False
+        ev = torch.cuda.current_stream().record_event()
+        stream.wait_event(ev)
+        with torch.cuda.stream(stream):
+            self.step_bucket(storage)
+            self._backward_events.append(stream.record_event())
+        self._stepped_in_backward.add(id(storage))
+        return True
 
     def fused_bucket_args(self, storage):
         """Hyper-parameters and flat state for one bucket, or ``None`` when it cannot be fused."""
@@ -95,6 +114,10 @@ class FusedAdamW(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         done = getattr(self, "_stepped_in_backward", None)
+        for ev in getattr(self, "_backward_events", ()):   # updates issued on the side stream during backward
+            torch.cuda.current_stream().wait_event(ev)
+        if getattr(self, "_backward_events", None):
+            self._backward_events.clear()
         for group in self.param_groups:
             hp = dict(lr=float(group["lr"]), beta1=group["betas"][0], beta2=group["betas"][1],
                       eps=group["eps"], weight_decay=group["weight_decay"])

@@ -73,3 +73,39 @@ def test_allgather_gemm_two_gpus(tmp_path):
         res = torch.load(tmp_path / f"r{r}.pt")
         assert res["gather"] is True
         assert res["err"] < 0.5
+
+
+def test_adamw_overlapped_with_backward_on_one_rank_matches_plain_step():
+    """On a 1-rank mesh ``fuse_into_backward`` runs each bucket's AdamW on a side stream as soon as the
+    bucket's gradients are final; the losses must be bit-identical to stepping after backward."""
+    from flex_shard_b200 import flex_shard, ops
+    from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets
+    from flex_shard_b200.optim.adamw import FusedAdamW
+
+    dev = torch.device("cuda")
+    cfg = LlamaConfig(vocab_size=2048, d_model=256, n_layers=3, n_heads=2, n_kv_heads=1, ffn_hidden=512, max_seq_len=256)
+    losses = {}
+    for mode in ("plain", "in_backward"):
+        torch.manual_seed(0)
+        model = Llama(cfg, dtype=torch.bfloat16, device=dev)
+        model.init_weights(0)
+        for p in model.parameters():
+            p.grad_dtype = torch.float32
+        flex_shard(model, llama_buckets(model, mesh=None))
+        opt = FusedAdamW(model.parameters(), lr=1e-3, weight_decay=0.1)
+        if mode == "in_backward":
+            opt.fuse_into_backward(model)
+        out = []
+        for s in range(5):
+            tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=torch.Generator().manual_seed(s)).to(dev)
+            loss = model.loss(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            if mode == "in_backward" and s == 1:
+                assert len(opt._stepped_in_backward) > 0   # buckets were updated before step() was called
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            out.append(float(loss.detach()))
+        torch.cuda.synchronize()
+        ops.check_status()
+        losses[mode] = out
+    assert losses["plain"] == losses["in_backward"], losses
