@@ -66,108 +66,166 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // `sum_out` and normalised (the pre-norm residual stream update in one pass).
 constexpr int NORM_THREADS = 256;
 
+// Block-wide sum with one barrier: every thread adds the warp partials itself. `red` holds two
+// sets of partials used alternately, so consecutive calls need no second barrier.
+__device__ __forceinline__ float block_sum_once(float v, float* red, int& ph) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[ph * 8 + w] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_THREADS / 32; ++i) t += red[ph * 8 + i];
+  ph ^= 1;
+  return t;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 q = __bfloat1622float2(h[j]);
+    f[2 * j] = q.x;
+    f[2 * j + 1] = q.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return v;
+}
+
+// The row stays in registers between the two passes (D <= 8192: up to four 8-element groups per thread).
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd, int D, float eps) {
-  __shared__ float red[32];
+  __shared__ float red[16];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * D;
   const __nv_bfloat16* rr = res ? res + row * D : nullptr;
+  uint4 cache[4];
   float ss = 0.f;
-  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
-    float f[8];
-    load8(xr + i, f);
-    if (rr) {
-      float g[8];
-      load8(rr + i, g);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] += g[j];
-      // round through bf16 so the normalised value matches the stored sum
-      bf16x8 t;
+  for (int g = 0; g < 4; ++g) {
+    const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+    if (i < D) {
+      uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+      float f[8];
+      unpack8(v, f);
+      if (rr) {
+        float q[8];
+        unpack8(*reinterpret_cast<const uint4*>(rr + i), q);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) t.v[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-      *reinterpret_cast<bf16x8*>(sum_out + row * D + i) = t;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 q = __bfloat1622float2(t.v[j]);
-        f[2 * j] = q.x;
-        f[2 * j + 1] = q.y;
+        for (int j = 0; j < 8; ++j) f[j] += q[j];
+        // round through bf16 so the normalised value matches the stored sum
+        v = pack8(f);
+        *reinterpret_cast<uint4*>(sum_out + row * D + i) = v;
+        unpack8(v, f);
       }
-    }
+      cache[g] = v;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
   }
-  ss = block_sum<NORM_THREADS>(ss, red);
+  int ph = 0;
+  ss = block_sum_once(ss, red, ph);
   const float r = rsqrtf(ss / D + eps);
   if (threadIdx.x == 0) rstd[row] = r;
-  const __nv_bfloat16* src = rr ? sum_out + row * D : xr;
-  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
-    float f[8], g[8];
-    load8(src + i, f);
-    load8(w + i, g);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
-    store8(y + row * D + i, f);
+  for (int g = 0; g < 4; ++g) {
+    const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+    if (i < D) {
+      float f[8], q[8];
+      unpack8(cache[g], f);
+      unpack8(*reinterpret_cast<const uint4*>(w + i), q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] * r * q[j];
+      *reinterpret_cast<uint4*>(y + row * D + i) = pack8(f);
+    }
   }
 }
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); optional `dres` is added to dx
 // (gradient arriving on the residual branch). dw partials: each CTA handles
-// ROWS_PER_CTA rows and writes one fp32 partial row.
+// ROWS_PER_CTA rows and writes one fp32 partial row. A row's dy and x stay in registers between
+// the reduction and the output pass; the weights are loaded once per CTA.
 constexpr int NORM_BWD_ROWS = 32;
 
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, 2)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, long long T, int D) {
-  __shared__ float red[32];
+  __shared__ float red[16];
   // Per-thread dw accumulators for up to 4 column groups (D <= 8192).
   float dwacc[4][8];
+  uint4 wv[4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int g = 0; g < 4; ++g) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[a][j] = 0.f;
+    for (int j = 0; j < 8; ++j) dwacc[g][j] = 0.f;
+    const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+    wv[g] = i < D ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);
+  }
   const long long row0 = static_cast<long long>(blockIdx.x) * NORM_BWD_ROWS;
+  int ph = 0;
   for (int rr = 0; rr < NORM_BWD_ROWS; ++rr) {
     const long long row = row0 + rr;
     if (row >= T) break;
     const float r = rstd[row];
-    float dot = 0.f;
-    for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8) {
-      float a[8], b[8], c[8];
-      load8(dy + row * D + i, a);
-      load8(x + row * D + i, b);
-      load8(w + i, c);
+    uint4 av[4], bv[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dot += a[j] * c[j] * b[j];
+    for (int g = 0; g < 4; ++g) {
+      const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+      if (i < D) {
+        av[g] = *reinterpret_cast<const uint4*>(dy + row * D + i);
+        bv[g] = *reinterpret_cast<const uint4*>(x + row * D + i);
+      }
     }
-    dot = block_sum<NORM_THREADS>(dot, red);
+    float dot = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+      if (i < D) {
+        float a[8], b[8], c[8];
+        unpack8(av[g], a);
+        unpack8(bv[g], b);
+        unpack8(wv[g], c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot += a[j] * c[j] * b[j];
+      }
+    }
+    dot = block_sum_once(dot, red, ph);
     const float coef = dot * r * r * r / D;
-    int g = 0;
-    for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8, ++g) {
-      float a[8], b[8], c[8], o[8];
-      load8(dy + row * D + i, a);
-      load8(x + row * D + i, b);
-      load8(w + i, c);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[j] = a[j] * c[j] * r - b[j] * coef;
-        if (g < 4) dwacc[g][j] += a[j] * b[j] * r;
-      }
-      if (dres) {
-        float e[8];
-        load8(dres + row * D + i, e);
+    for (int g = 0; g < 4; ++g) {
+      const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+      if (i < D) {
+        float a[8], b[8], c[8], o[8];
+        unpack8(av[g], a);
+        unpack8(bv[g], b);
+        unpack8(wv[g], c);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] += e[j];
+        for (int j = 0; j < 8; ++j) {
+          o[j] = a[j] * c[j] * r - b[j] * coef;
+          dwacc[g][j] += a[j] * b[j] * r;
+        }
+        if (dres) {
+          float e[8];
+          unpack8(*reinterpret_cast<const uint4*>(dres + row * D + i), e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        *reinterpret_cast<uint4*>(dx + row * D + i) = pack8(o);
       }
-      store8(dx + row * D + i, o);
     }
   }
-  int g = 0;
-  for (int i = threadIdx.x * 8; i < D; i += NORM_THREADS * 8, ++g) {
-    if (g < 4) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
+    if (i < D) {
       float* p = dw_partial + static_cast<long long>(blockIdx.x) * D + i;
       *reinterpret_cast<float4*>(p) = make_float4(dwacc[g][0], dwacc[g][1], dwacc[g][2], dwacc[g][3]);
       *reinterpret_cast<float4*>(p + 4) =
@@ -459,7 +517,7 @@ inline int launch_ok() { return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB
 
 FSB_API int fsb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out,
                             float* rstd, long long T, int D, float eps, cudaStream_t stream) {
-  if (D % 8 != 0 || T <= 0) return FSB_ERR_BAD_ARG;
+  if (D % 8 != 0 || D > 8192 || T <= 0) return FSB_ERR_BAD_ARG;
   rmsnorm_fwd_kernel<<<static_cast<unsigned>(T), NORM_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
