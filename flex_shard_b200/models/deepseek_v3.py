@@ -43,6 +43,12 @@ class DeepSeekV3Config:
     n_shared_experts: int = 1
     route_scale: float = 1.0
     rope_theta: float = 10000.0
+    rope_factor: float = 1.0          # > 1: YaRN context stretch (with original_seq_len, beta_fast, beta_slow, mscale)
+    original_seq_len: int = 4096
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
+    mscale: float = 0.70
+    router_fp32_out_bf16: bool = False   # router logits: bf16 operands -> fp32 output, split-precision backward
     norm_eps: float = 1e-6
     max_seq_len: int = 4096
     init_std: float = 0.02
@@ -86,7 +92,7 @@ class MLA(nn.Module):
         qf = torch.cat([q_nope, q_pe], dim=-1)
         kf = torch.cat([k_nope, k_pe.expand(B, S, H, cfg.qk_rope_dim)], dim=-1)
         o = F.scaled_dot_product_attention(qf.transpose(1, 2), kf.transpose(1, 2), v.transpose(1, 2), is_causal=True,
-                                           scale=1.0 / math.sqrt(cfg.qk_dim))
+                                           scale=ew.yarn_attention_scale(cfg.qk_dim, cfg.rope_factor, cfg.mscale))
         return linear(o.transpose(1, 2).reshape(B, S, H * cfg.v_dim), self.wo)
 
 
@@ -128,7 +134,12 @@ class MoE(nn.Module):
 
     def route(self, xt):
         cfg = self.cfg
-        logits = F.linear(xt.float(), self.gate.float())
+        if cfg.router_fp32_out_bf16:
+            from ..ops.gemm import fp32_output_linear
+
+            logits = fp32_output_linear(xt, self.gate)
+        else:
+            logits = F.linear(xt.float(), self.gate.float())
         return moe_ops.route_topk(logits, cfg.top_k, bias=self.expert_bias, mode="sigmoid",
                                   scale=cfg.route_scale, normalize=True, counts=self.tokens_per_expert)
 
@@ -199,7 +210,10 @@ class DeepSeekV3(nn.Module):
     def forward(self, tokens):
         B, S = tokens.shape
         if self._rope is None or self._rope.device != tokens.device:
-            self._rope = ew.rope_table(self.cfg.max_seq_len, self.cfg.qk_rope_dim, self.cfg.rope_theta, tokens.device)
+            c = self.cfg
+            yarn = dict(factor=c.rope_factor, original_seq_len=c.original_seq_len, beta_fast=c.beta_fast,
+                        beta_slow=c.beta_slow) if c.rope_factor != 1.0 else None
+            self._rope = ew.rope_table(c.max_seq_len, c.qk_rope_dim, c.rope_theta, tokens.device, yarn=yarn)
         x = self.tok_embeddings(tokens)
         for layer in self.layers:
             x = layer(x, self._rope[:S])

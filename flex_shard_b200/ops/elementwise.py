@@ -117,11 +117,36 @@ def add_rmsnorm(x, residual, weight, eps: float = 1e-5):
 
 
 # --------------------------------------------------------------------------- RoPE
-def rope_table(seq_len: int, head_dim: int, theta: float, device) -> torch.Tensor:
-    """[S, hd/2, 2] fp32 table of (cos, sin) for interleaved-pair rotation."""
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+def rope_table(seq_len: int, head_dim: int, theta: float, device, yarn: dict | None = None) -> torch.Tensor:
+    """[S, hd/2, 2] fp32 table of (cos, sin) for interleaved-pair rotation.
+
+    ``yarn`` = ``dict(factor, original_seq_len, beta_fast=32, beta_slow=1)`` stretches the context the
+    YaRN way: pairs that complete fewer than ``beta_slow`` turns over the original context have their
+    frequency divided by ``factor`` (interpolation), pairs with more than ``beta_fast`` turns keep it,
+    and a linear ramp over the pair index blends the two in between (parity: the rotary cache of the
+    reference's DeepSeek-V3 example, ``examples/deepseek_v3/model.py:88-109``)."""
+    idx = torch.arange(0, head_dim, 2, dtype=torch.float32, device=device)
+    inv = 1.0 / (theta ** (idx / head_dim))
+    if yarn is not None and float(yarn.get("factor", 1.0)) != 1.0:
+        factor, orig = float(yarn["factor"]), float(yarn["original_seq_len"])
+
+        def pair_with_turns(turns: float) -> float:   # pair index whose wavelength gives `turns` turns over `orig`
+            return head_dim * math.log(orig / (turns * 2 * math.pi)) / (2 * math.log(theta))
+
+        lo = max(math.floor(pair_with_turns(float(yarn.get("beta_fast", 32.0)))), 0)
+        hi = min(math.ceil(pair_with_turns(float(yarn.get("beta_slow", 1.0)))), head_dim - 1)
+        span = (hi - lo) if hi != lo else 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - lo) / span).clamp(0, 1)
+        inv = inv / factor * ramp + inv * (1 - ramp)
     ang = torch.outer(torch.arange(seq_len, dtype=torch.float32, device=device), inv)
     return torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous()
+
+
+def yarn_attention_scale(head_dim: int, factor: float, mscale: float = 0.70) -> float:
+    """Softmax scale that goes with a YaRN-stretched context: ``head_dim**-0.5 * m**2`` with
+    ``m = 0.1 * mscale * ln(factor) + 1``."""
+    m = 0.1 * mscale * math.log(factor) + 1.0 if factor > 1.0 else 1.0
+    return head_dim ** -0.5 * m * m
 
 
 def _rope_ref(x, table, inverse):

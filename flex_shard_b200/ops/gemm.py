@@ -150,3 +150,50 @@ class _Linear(torch.autograd.Function):
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return _Linear.apply(x, weight)
+
+
+def split_into_bf16_pieces(t: torch.Tensor):
+    """fp32 tensor -> three bf16 tensors (high, middle, low part) whose sum reproduces it to ~24 bits."""
+    hi = t.to(torch.bfloat16)
+    rest = t - hi.float()
+    mid = rest.to(torch.bfloat16)
+    lo = (rest - mid.float()).to(torch.bfloat16)
+    return hi, mid, lo
+
+
+class _Fp32OutputLinear(torch.autograd.Function):
+    """``x @ weight.T`` from bf16 operands, accumulated and returned in fp32 (router logits). The
+    backward pass keeps close to fp32 accuracy on bf16 tensor cores: the fp32 output gradient is cut
+    into three bf16 pieces that sum to it, and each product is three tcgen05 GEMMs accumulated in an
+    fp32 output (parity: ``_Fp32OutputLinear`` of the reference's DeepSeek-V3 example,
+    ``examples/deepseek_v3/model.py:368-422``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16)
+        w = weight.to(torch.bfloat16)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape, ctx.xdtype, ctx.wdtype = x.shape, x.dtype, weight.dtype
+        return gemm(x2, w, out_dtype=torch.float32).view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, w = ctx.saved_tensors
+        g2 = g.reshape(-1, g.shape[-1]).float().contiguous()
+        pieces = split_into_bf16_pieces(g2)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            acc = torch.empty(g2.shape[0], w.shape[1], dtype=torch.float32, device=g2.device)
+            for i, p in enumerate(pieces):
+                gemm(p, w, b_t=True, out=acc, accumulate=i > 0)
+            dx = acc.to(ctx.xdtype).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            acc = torch.empty(w.shape, dtype=torch.float32, device=g2.device)
+            for i, p in enumerate(pieces):
+                gemm(p, x2, a_t=True, b_t=True, out=acc, accumulate=i > 0)
+            dw = acc.to(ctx.wdtype)
+        return dx, dw
+
+
+def fp32_output_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return _Fp32OutputLinear.apply(x, weight)

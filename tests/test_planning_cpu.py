@@ -173,3 +173,39 @@ def test_router_reference_gradients_match_autograd_of_the_plain_formula():
         torch.testing.assert_close(w, w2)
         torch.testing.assert_close(lg.grad, lg2.grad, rtol=1e-5, atol=1e-7)
         assert counts.sum().item() == T * k
+
+
+def test_yarn_table_and_fp32_output_linear():
+    import math
+
+    import torch
+
+    from flex_shard_b200.ops.elementwise import rope_table, yarn_attention_scale
+    from flex_shard_b200.ops.gemm import fp32_output_linear, split_into_bf16_pieces
+
+    # no stretch -> the plain table; stretch -> low-frequency pairs slowed by `factor`, fast pairs untouched
+    plain = rope_table(64, 64, 10000.0, "cpu")
+    assert torch.equal(plain, rope_table(64, 64, 10000.0, "cpu", yarn=dict(factor=1.0, original_seq_len=4096)))
+    st = rope_table(64, 64, 10000.0, "cpu", yarn=dict(factor=40.0, original_seq_len=4096))
+    assert torch.equal(st[:, 0], plain[:, 0])                       # fastest pair: unchanged
+    slow_plain = torch.atan2(plain[1, -1, 1], plain[1, -1, 0])
+    slow_st = torch.atan2(st[1, -1, 1], st[1, -1, 0])
+    assert abs(slow_st.item() * 40.0 - slow_plain.item()) < 1e-6     # slowest pair: angle / factor
+    assert abs(yarn_attention_scale(192, 1.0) - 192 ** -0.5) < 1e-12
+    assert yarn_attention_scale(192, 40.0) > 192 ** -0.5
+    # three bf16 pieces reproduce an fp32 tensor far below bf16 resolution
+    t = torch.randn(1000) * 3
+    hi, mid, lo = split_into_bf16_pieces(t)
+    assert (hi.float() + mid.float() + lo.float() - t).abs().max() < 1e-6 * t.abs().max()
+    # logits in fp32 from bf16 operands, gradients close to the fp32 product's
+    x = torch.randn(40, 64).bfloat16().requires_grad_()
+    w = (torch.randn(8, 64) * 0.1).bfloat16().requires_grad_()
+    y = fp32_output_linear(x, w)
+    assert y.dtype == torch.float32
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xr @ wr.t()).backward(g)
+    torch.testing.assert_close(y, xr @ wr.t(), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=1e-1)
