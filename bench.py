@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fsdp2"])
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--local-batch", type=int, default=1)
+    ap.add_argument("--placement", choices=["shard", "fp8", "mxfp8"], default="shard",
+                    help="shard (default, the headline config): Shard(0) bf16 buckets; fp8 / mxfp8: the blocks' 2-D "
+                         "weights are gathered quantised and feed block-scaled GEMMs (a different configuration)")
     ap.add_argument("--keep-unsharded", type=int, default=1,
                     help="1 (default): keep the gathered bf16 parameters between forward and backward (one all-gather "
                          "per step instead of two; +2 bytes/param of HBM, affordable on 180 GB); 0: reshard after forward")
@@ -175,7 +178,7 @@ def timed_loop(step_fn, steps: int, world: int) -> float:
 # --------------------------------------------------------------------------- our arm
 def build_ours(args, world):
     from flex_shard_b200 import flex_shard
-    from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets
+    from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets, llama_quantized_buckets
     from flex_shard_b200.optim.adamw import FusedAdamW
 
     cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq_len)
@@ -198,7 +201,9 @@ def build_ours(args, world):
 
         set_default_backend(args.comm)
         mesh = init_device_mesh("cuda", (world,))
-    flex_shard(model, llama_buckets(model, mesh=mesh))
+    placement = getattr(args, "placement", "shard")
+    flex_shard(model, llama_buckets(model, mesh=mesh) if placement == "shard"
+               else llama_quantized_buckets(model, mesh=mesh, kind=placement))
     if args.keep_unsharded:
         model.set_reshard_after_forward(False)
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
@@ -274,7 +279,9 @@ def run_ours(args, rank, local, world):
             "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers, d{cfg.d_model}, {cfg.n_heads}q/{cfg.n_kv_heads}kv, "
                                 f"ffn {cfg.ffn_hidden}, vocab {cfg.vocab_size})",
                        "global_batch": args.local_batch * world, "seq_len": S, "parallelism": f"dp{world}",
-                       "placement": "Shard(0) per-layer buckets, prefetch, bf16 params / fp32 reduce+AdamW state, "
+                       "placement": ("Shard(0) per-layer buckets" if getattr(args, "placement", "shard") == "shard" else
+                                     f"{args.placement} quantised gather of the blocks' 2-D weights + Shard(0) for the rest")
+                                    + ", prefetch, bf16 params / fp32 reduce+AdamW state, "
                                     + ("gathered params kept until backward" if args.keep_unsharded else "reshard after forward"),
                        "collectives": (args.comm if world > 1 else "none (1 rank)"),
                        "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},

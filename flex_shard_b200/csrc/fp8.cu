@@ -191,12 +191,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the loop (waits and descriptor arithmetic stay warp-uniform); one elected
+    // lane issues the tcgen05 instructions.
+    {
       // e4m3 x e4m3 -> fp32; B MN-major for the transposed-weight product
       const uint32_t idesc = make_idesc(BM, BN, 0, 0, 0, args.b_mn ? 1u : 0u);
       // K-major: 32 elements (bytes) per MMA inside the 128-byte row. MN-major B: one 128-wide
       // N group, 8-deep K groups 1 KB apart, 32 K = 4 groups = 4 KB per MMA.
-      const uint32_t b_kstep = args.b_mn ? 4096u : 32u;
+      const uint32_t b_kstep = (args.b_mn ? 4096u : 32u) >> 4;
       uint32_t it = 0, blk = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -205,20 +207,25 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t ph = (it / STAGES) & 1;
           const uint32_t buf = blk & 1, bph = (blk >> 1) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag) || !mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag)) {
-            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
-            *abort_flag = 1;
+            if (lane == 0) {
+              atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_FULL);
+              *abort_flag = 1;
+            }
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_STAGE;
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sa + A_STAGE, 16, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k) {
-            umma_f8(tmem_base + buf * BN, make_smem_desc_sw128(sa + k * 32, 16, 1024),
-                    make_smem_desc_sw128(sb + k * b_kstep, 16, 1024), idesc, k != 0);
+            for (int k = 0; k < BK / 32; ++k)
+              umma_f8(tmem_base + buf * BN, da + k * 2, db + k * b_kstep, idesc, k != 0);
+            umma_commit(&empty_bar[s]);
+            umma_commit(&tmem_full[buf]);
           }
-          umma_commit(&empty_bar[s]);
-          umma_commit(&tmem_full[buf]);
+          __syncwarp();
         }
       }
     }

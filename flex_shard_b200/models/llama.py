@@ -144,6 +144,25 @@ class Llama(nn.Module):
         return ew.cross_entropy(logits, targets.reshape(-1), unit_grad=loss_is_root)
 
 
+def llama_quantized_buckets(model: Llama, mesh=None, kind: str = "fp8", mp_policy=None):
+    """Buckets for a quantised all-gather: every block's 2-D weights travel as FP8 128x128 blocks
+    (``kind="fp8"``) or MXFP8 (``kind="mxfp8"``) and feed the block-scaled GEMMs; norms, embedding and
+    head stay ``Shard(0)`` in bf16."""
+    from ..bucket_storage import BucketSpec, MixedPrecisionPolicy
+    from ..placements import make_fp8_bucketed_block_shard_placement_fn, make_mxfp8_bucketed_block_shard_placement_fn
+    from ..placements.shard import shard_placement_fn
+
+    mp = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    qfn = make_fp8_bucketed_block_shard_placement_fn() if kind == "fp8" else make_mxfp8_bucketed_block_shard_placement_fn()
+    plain = dict(mesh=mesh, mp_policy=mp, placement_fn=shard_placement_fn(0))
+    specs = [BucketSpec(["tok_embeddings"], **plain)]
+    for i in range(len(model.layers)):
+        specs.append(BucketSpec([f"layers.{i}.w*"], mesh=mesh, mp_policy=mp, placement_fn=qfn))
+        specs.append(BucketSpec([f"layers.{i}.*norm"], **plain))
+    specs.append(BucketSpec(["head"], reshard_after_forward=False, **plain))
+    return specs
+
+
 def llama_buckets(model: Llama, mesh=None, mp_policy=None, placement_fn=None, fsdp2_compatible=True):
     """One bucket per block plus embedding and head buckets, FSDP2-style."""
     from ..bucket_storage import BucketSpec, MixedPrecisionPolicy

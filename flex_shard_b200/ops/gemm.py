@@ -149,6 +149,19 @@ class _Linear(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T``. A weight handed out by a quantised-gather placement (FP8 128x128 blocks or
+    MXFP8) runs the matching block-scaled products; its gradient still goes to the logical parameter."""
+    if type(weight) is not torch.Tensor and type(weight) is not torch.nn.Parameter:
+        from ..quant.weight import BlockwiseFp8Weight, BlockwiseMxfp8Weight
+
+        if isinstance(weight, BlockwiseMxfp8Weight):
+            from .mxfp8 import mxfp8_linear
+
+            return mxfp8_linear(x, weight, weight.qdata, weight.scale, weight.dgrad_scale)
+        if isinstance(weight, BlockwiseFp8Weight):
+            from .fp8 import fp8_linear
+
+            return fp8_linear(x, weight, weight.qdata, weight.scale)
     return _Linear.apply(x, weight)
 
 

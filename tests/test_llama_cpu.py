@@ -65,3 +65,35 @@ def test_llama_sharded_matches_unsharded_with_grad_bucket():
         mean = [sum(r[i] for r in res) / world for i in range(steps)]
         for a, b in zip(mean, ref):
             assert abs(a - b) < 5e-4 * max(1.0, abs(b)), (grad_bucket, mean, ref)
+
+
+def test_llama_trains_with_quantised_gather_buckets():
+    """The same model with its blocks' 2-D weights gathered as FP8 128x128 blocks or as MXFP8 (the
+    weights arrive as quantised wrappers and ``linear`` runs the block-scaled products) follows the
+    bf16 run closely."""
+    import torch
+
+    from flex_shard_b200 import flex_shard
+    from flex_shard_b200.models.llama import Llama, LlamaConfig, llama_buckets, llama_quantized_buckets
+
+    cfg = LlamaConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=2, n_kv_heads=1, ffn_hidden=512, max_seq_len=64)
+    runs = {}
+    for kind in ("bf16", "fp8", "mxfp8"):
+        torch.manual_seed(0)
+        m = Llama(cfg, dtype=torch.bfloat16, device="cpu")
+        m.init_weights(0)
+        flex_shard(m, llama_buckets(m) if kind == "bf16" else llama_quantized_buckets(m, kind=kind))
+        opt = torch.optim.SGD(m.parameters(), lr=0.1)
+        losses = []
+        for s in range(3):
+            tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(s))
+            loss = m.loss(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            losses.append(float(loss.detach()))
+        runs[kind] = losses
+    for kind in ("fp8", "mxfp8"):
+        for a, b in zip(runs[kind], runs["bf16"]):
+            assert abs(a - b) < 2e-2, runs
+    assert runs["bf16"][-1] < runs["bf16"][0]
