@@ -150,6 +150,11 @@ class SymmComm(Comm):
             hint = self._ag_hint if which == "ag" else self._rs_hint
             size = max(nbytes, hint)
             if cur is not None:
+                # the peers may still be reading the old region (their pull of the last epoch): wait for
+                # every rank's "done" flag of that epoch before the memory goes away
+                last = self._ag_epoch if which == "ag" else self._rs_epoch
+                if last > 0:
+                    cur.wait(self.SLOT_AG_DONE if which == "ag" else self.SLOT_RS_DONE, last)
                 torch.cuda.synchronize(self.device)
                 size = max(size, 2 * cur.payload_bytes)
             cur = SymmRegion(self.group, size, self.device)

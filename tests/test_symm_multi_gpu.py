@@ -210,7 +210,10 @@ def test_muon_row_redistribution_by_peer_pull_matches_all_to_all(tmp_path):
         res = torch.load(tmp_path / f"m{r}.pt")
         assert res["symm_p2p"] == 2 * 3 and res["nccl_p2p"] == 0
         for n in res["nccl"]:
-            torch.testing.assert_close(res["symm"][n], res["nccl"][n], rtol=0, atol=1e-6)
+            # Newton-Schulz runs in bf16: a last-bit difference upstream (the model's own fp32 library
+            # GEMMs are not bitwise reproducible across allocator states) flips bf16 roundings, which
+            # shows as ~1e-3 here; a wrong or stale row block would be off by the update size (~2e-2).
+            torch.testing.assert_close(res["symm"][n], res["nccl"][n], rtol=0, atol=3e-3)
 
 
 def _ep_worker(rank, world, port, out):
