@@ -14,9 +14,10 @@ events, max over ranks) with inputs resident on the GPU; ``e2e`` repeats the mea
 the public API with a pinned-host -> device copy of every step's tokens and a device -> host read
 of every step's loss inside the timed region.
 
-``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` (prints an
-``unavailable`` line when it cannot be imported); ``--impl fsdp2`` times PyTorch FSDP2
-``fully_shard`` + cuBLAS + SDPA + fused AdamW on the same config as a stand-in baseline.
+``--impl reference`` trains a stock-PyTorch Llama of the same shape (cuBLAS, SDPA, fused AdamW,
+NCCL) sharded by the unmodified reference package in ``baseline/_ref`` through its public
+``flex_shard(model, buckets)`` call; ``baseline/compat.py`` supplies the few torch symbols newer than
+the installed release.  ``--impl fsdp2`` shards the same model with PyTorch FSDP2 ``fully_shard``.
 """
 from __future__ import annotations
 
@@ -292,35 +293,12 @@ def run_ours(args, rank, local, world):
         print(json.dumps(out), flush=True)
 
 
-# --------------------------------------------------------------------------- reference arm
-def run_reference(args, rank, local, world):
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    reason = None
-    if not os.path.isdir(os.path.join(ref_dir, "flex_shard")):
-        reason = "baseline/_ref is not installed (pip --no-index install of /root/reference was not run)"
-    else:
-        sys.path.insert(0, ref_dir)
-        try:
-            import flex_shard  # noqa: F401
-        except Exception as exc:  # the reference pins torch>=2.16 private APIs
-            reason = (f"reference does not import on torch {torch.__version__}: {type(exc).__name__}: "
-                      f"{str(exc).splitlines()[0][:160]}")
-    if reason is None:
-        reason = "reference imported but its CUDA-only runtime was not exercised in this build"
-    if rank == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
-
-
-# --------------------------------------------------------------------------- FSDP2 stand-in baseline
-def run_fsdp2(args, rank, local, world):
+# --------------------------------------------------------------------------- plain-PyTorch Llama for the baseline arms
+def build_plain_llama(cfg, dev):
+    """The same architecture as ``flex_shard_b200.models.llama`` written with stock PyTorch modules
+    (``nn.Linear`` -> cuBLAS, SDPA, ``nn.RMSNorm``): the model both baseline arms train."""
     import torch.nn as nn
     import torch.nn.functional as F
-    from torch.distributed.fsdp import MixedPrecisionPolicy as MP, fully_shard
-
-    from flex_shard_b200.models.llama import LlamaConfig
-
-    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq_len)
-    dev = torch.device("cuda", local)
 
     class Block(nn.Module):
         def __init__(self):
@@ -377,19 +355,76 @@ def run_fsdp2(args, rank, local, world):
             else:
                 p.normal_(0.0, cfg.init_std)
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=dev, dtype=torch.float32) / cfg.head_dim))
-    ang = torch.outer(torch.arange(args.seq_len, device=dev, dtype=torch.float32), inv)
-    freqs = torch.polar(torch.ones_like(ang), ang)
+    ang = torch.outer(torch.arange(cfg.max_seq_len, device=dev, dtype=torch.float32), inv)
+    return model, torch.polar(torch.ones_like(ang), ang)
+
+
+def shard_with_fsdp2(model, args, world):
+    from torch.distributed.fsdp import MixedPrecisionPolicy as MP, fully_shard
+
     if world > 1:
         mp = MP(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
         for layer in model.layers:
             fully_shard(layer, mp_policy=mp, reshard_after_forward=not args.keep_unsharded)
         fully_shard(model, mp_policy=mp, reshard_after_forward=not args.keep_unsharded)
+    return {"sharding": "torch.distributed.fsdp.fully_shard per layer + root" if world > 1 else "none (1 rank)"}
+
+
+def shard_with_reference(model, args, world):
+    """Shards ``model`` with the unmodified reference package (``baseline/_ref``) through its public
+    ``flex_shard(model, buckets)`` call: ``Shard(0)`` buckets for the embedding, each layer and
+    norm + head, the layout its FSDP2-parity test drives
+    (``src/flex_shard/tests/test_flex_shard_fsdp2_parity.py:170-205``)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "flex_shard")):
+        raise RuntimeError("baseline/_ref holds no installed reference package")
+    sys.path.insert(0, ref_dir)
+    from baseline import compat
+
+    shims = compat.install()
+    import flex_shard as ref
+    from flex_shard.custom_placements import per_param_placements
+    from torch.distributed.device_mesh import init_device_mesh
+
+    if not dist.is_initialized():  # a 1-rank job still needs a process group for the mesh
+        import tempfile
+
+        store = dist.FileStore(os.path.join(tempfile.mkdtemp(prefix="fsb_ref_"), "store"), 1)
+        dist.init_process_group("nccl", store=store, rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    mesh = init_device_mesh("cuda", (world,))
+    mp = ref.MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+
+    def bucket(patterns, reshard):
+        return ref.BucketSpec(patterns, placement_fn=per_param_placements, mesh=mesh, mp_policy=mp,
+                              reshard_after_forward=reshard, fsdp2_compatible=True)
+
+    reshard = not args.keep_unsharded
+    ref.flex_shard(model, buckets=[bucket(["tok_embeddings"], reshard),
+                                   *(bucket([f"layers.{i}"], reshard) for i in range(len(model.layers))),
+                                   bucket(["norm", "output"], False)])
+    return {"sharding": "reference flex_shard(model, buckets), Shard(0) per-layer buckets, fsdp2_compatible",
+            "reference_version": getattr(ref, "__version__", "0.1.0.dev0"), "torch_shims": shims}
+
+
+def run_plain(args, rank, local, world, impl):
+    """Times a baseline arm: the stock-PyTorch Llama sharded by ``impl`` ("reference" or "fsdp2"),
+    cuBLAS + SDPA + ``torch.optim.AdamW(fused=True)``, same config, steps, timing and JSON keys."""
+    import torch.nn.functional as F
+
+    from flex_shard_b200.models.llama import LlamaConfig
+
+    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq_len)
+    dev = torch.device("cuda", local)
+    model, freqs = build_plain_llama(cfg, dev)
+    info = (shard_with_reference if impl == "reference" else shard_with_fsdp2)(model, args, world)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     B, S = args.local_batch, args.seq_len
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
     host = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(4)]
     resident = [h.to(dev) for h in host]
     loss_host = torch.zeros(1).pin_memory()
+    last = [None]
 
     def train_step(tok):
         logits = model(tok[:, :-1], freqs)
@@ -397,36 +432,87 @@ def run_fsdp2(args, rank, local, world):
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
+        last[0] = loss
         return loss
 
     for i in range(args.warmup):
         train_step(resident[i % 4])
+    torch.cuda.synchronize()
     sampler = ClockSampler(local)
     sampler.start()
     ms = timed_loop(lambda i: train_step(resident[i % 4]), args.steps, world)
     clocks = sampler.stop()
+    loss_val = float(last[0].detach().float().item())
 
     def e2e_step(i):
         loss = train_step(host[i % 4].to(dev, non_blocking=True))
         loss_host.copy_(loss.detach().reshape(1))
 
-    ms_e2e = timed_loop(e2e_step, args.steps, world)
+    e2e = None
+    if not args.no_e2e:
+        e2e_step(0)
+        ms_e2e = timed_loop(e2e_step, args.steps, world)
+        e2e = {"value": B * S * world / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": host[0].numel() * host[0].element_size(),
+               "d2h_bytes_per_step": loss_host.numel() * loss_host.element_size()}
     tokens = B * S * world
+    out = {"metric": "tokens/sec, Llama-3-8B-shaped training step (fwd+bwd+AdamW)",
+           "impl": impl, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
+           "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers, d{cfg.d_model}, {cfg.n_heads}q/{cfg.n_kv_heads}kv, "
+                               f"ffn {cfg.ffn_hidden}, vocab {cfg.vocab_size})",
+                      "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
+                      "placement": info["sharding"] + ", bf16 params, fp32 gradient reduce, torch.optim.AdamW(fused=True), "
+                                   + ("gathered params kept until backward" if args.keep_unsharded else "reshard after forward"),
+                      "kernels": "stock PyTorch: cuBLAS linears, SDPA attention, NCCL collectives",
+                      "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
+           "clocks": clocks, "e2e": e2e, "loss": loss_val,
+           "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2)}
+    out.update({k: v for k, v in info.items() if k != "sharding"})
+    return out
+
+
+def run_reference(args, rank, local, world):
+    """Reference arm.  Prints the same JSON line as the other arms with ``"impl": "reference"``; when the
+    reference cannot be driven on this torch, prints ``unavailable`` naming the failing symbol, with the
+    FSDP2 stand-in measured in the same process under ``stand_in``."""
+    try:
+        out = run_plain(args, rank, local, world, "reference")
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        return
+    except Exception as exc:  # a private torch>=2.16 API the shims do not cover, or an absent install
+        import traceback
+
+        tb = traceback.extract_tb(exc.__traceback__)
+        where = f"{os.path.basename(tb[-1].filename)}:{tb[-1].lineno}" if tb else "?"
+        reason = (f"reference cannot run on torch {torch.__version__}: {type(exc).__name__}: "
+                  f"{str(exc).splitlines()[0][:200] if str(exc) else ''} (at {where})")
+    stand_in = None
+    try:
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        stand_in = run_plain(args, rank, local, world, "fsdp2")
+    except Exception as exc:
+        stand_in = {"unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
     if rank == 0:
-        print(json.dumps({"metric": "tokens/sec, Llama-3-8B-shaped training step (fwd+bwd+AdamW)",
-                          "impl": "fsdp2", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
-                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
-                          "config": {"model": f"llama3-8b-shaped ({cfg.n_layers} layers)", "global_batch": B * world,
-                                     "seq_len": S, "parallelism": f"dp{world}"},
-                          "clocks": clocks, "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s"},
-                          "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+        print(json.dumps({"impl": "reference", "unavailable": reason, "stand_in": stand_in}), flush=True)
+
+
+def run_fsdp2(args, rank, local, world):
+    out = run_plain(args, rank, local, world, "fsdp2")
+    if rank == 0:
+        print(json.dumps(out), flush=True)
 
 
 def main():
     args = parse()
     if args.impl == "reference" and not torch.cuda.is_available():
-        run_reference(args, 0, 0, 1)
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}), flush=True)
         return
     rank, local, world = setup_dist(args)
     try:

@@ -296,6 +296,9 @@ def adamw_step_(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_s
     n = p.numel()
     if n == 0:
         return
+    if m.dtype != torch.float32 or v.dtype != torch.float32 or m.numel() < n or v.numel() < n or g.numel() < n:
+        raise ValueError(f"AdamW moments must be fp32 with at least {n} elements (got {m.dtype}[{m.numel()}], "
+                         f"{v.dtype}[{v.numel()}]; gradient has {g.numel()})")
     if p.is_cuda:
         assert p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous()
         rc = _lib.load().fsb_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),

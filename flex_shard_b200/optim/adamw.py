@@ -38,7 +38,6 @@ class FusedAdamW(torch.optim.Optimizer):
         n = storage.byte_storage.numel() // itemsize
         m = torch.zeros(n, dtype=torch.float32, device=first.device)
         v = torch.zeros(n, dtype=torch.float32, device=first.device)
-        base_off = storage.byte_storage.storage_offset() // itemsize if False else 0
         for p in params:
             off = p._fsb_info.byte_offset // itemsize
             st = self.state[p]
@@ -53,6 +52,50 @@ class FusedAdamW(torch.optim.Optimizer):
         st["step"] = torch.zeros((), dtype=torch.float32)
         st["exp_avg"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
         st["exp_avg_sq"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+
+    def load_state_dict(self, state_dict) -> None:
+        """Loads like ``torch.optim.Optimizer.load_state_dict`` but keeps the moments in fp32.
+
+        The base class casts floating-point state to each parameter's dtype, so after loading into
+        bf16 parameters ``exp_avg`` / ``exp_avg_sq`` would be bf16 while the kernel reads and writes
+        them as fp32.  Here the loaded values are taken in fp32 straight from ``state_dict`` and, for
+        buckets updated as one flat launch, copied into freshly built flat buffers whose views replace
+        the per-parameter tensors (stale flat buffers from before the load are dropped)."""
+        import itertools
+
+        loaded = state_dict["state"]
+        super().load_state_dict(state_dict)
+        # map the positional ids of the saved groups onto this optimizer's parameters
+        saved_ids = itertools.chain.from_iterable(g["params"] for g in state_dict["param_groups"])
+        mine = itertools.chain.from_iterable(g["params"] for g in self.param_groups)
+        self._flat = {}
+        by_bucket: dict[int, tuple] = {}
+        for pid, p in zip(saved_ids, mine):
+            src = loaded.get(pid)
+            if src is None or p not in self.state:
+                continue
+            st = self.state[p]
+            for key in ("exp_avg", "exp_avg_sq"):
+                if key in src:
+                    st[key] = src[key].detach().to(device=p.device, dtype=torch.float32).reshape(p.shape).clone()
+            if "step" in src:
+                step = src["step"]
+                st["step"] = (step.detach().to("cpu", torch.float32).reshape(()).clone() if torch.is_tensor(step)
+                              else torch.tensor(float(step), dtype=torch.float32))
+            storage = self._bucket_of(p)
+            if storage is not None and storage.byte_storage is not None:
+                by_bucket.setdefault(id(storage), (storage, []))[1].append(p)
+        for storage, plist in by_bucket.values():
+            complete = (len(plist) == len(storage.sharded_params) and len({p.dtype for p in plist}) == 1
+                        and all("exp_avg" in self.state[p] and "step" in self.state[p] for p in plist))
+            if not complete:
+                continue
+            old = [(self.state[p]["exp_avg"], self.state[p]["exp_avg_sq"], self.state[p]["step"]) for p in plist]
+            self._init_bucket_state(storage, plist)
+            for p, (m, v, step) in zip(plist, old):
+                self.state[p]["exp_avg"].copy_(m)
+                self.state[p]["exp_avg_sq"].copy_(v)
+                self.state[p]["step"] = step
 
     # ------------------------------------------------------------------ optimizer inside backward
     def fuse_into_backward(self, module) -> None:

@@ -109,3 +109,71 @@ def test_optimizer_hook_rejects_foreign_optimizers():
     other = Net()
     with pytest.raises(ValueError, match="none of the module"):
         register_optimizer_checkpoint_hook(torch.optim.AdamW(other.parameters(), lr=0.1), m)
+
+
+def _bf16_net(seed):
+    torch.manual_seed(seed)
+    return Net().to(torch.bfloat16)
+
+
+def _fused_step(m, opt, seed):
+    x = torch.randn(4, 6, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16)
+    m(x).float().square().mean().backward()
+    opt.step()
+    opt.zero_grad()
+
+
+@pytest.mark.parametrize("warm_target", [False, True])
+def test_fused_adamw_reload_keeps_fp32_moments(warm_target):
+    """bf16 parameters: after ``load_state_dict`` both moments are still fp32 (the base optimizer would
+    cast them to bf16), flat bucket buffers hold the loaded values, and the next step equals the
+    uninterrupted run's; ``warm_target`` loads into an optimizer that already built flat buffers."""
+    import copy
+
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.optim.adamw import FusedAdamW
+
+    a = _bf16_net(0)
+    flex_shard(a, [BucketSpec(["*"])])
+    oa = FusedAdamW(a.parameters(), lr=0.05)
+    for s in range(2):
+        _fused_step(a, oa, 10 + s)
+    saved_model = copy.deepcopy(a.state_dict())
+    saved_opt = copy.deepcopy(oa.state_dict())
+    _fused_step(a, oa, 99)
+
+    b = _bf16_net(5)
+    flex_shard(b, [BucketSpec(["*"])])
+    ob = FusedAdamW(b.parameters(), lr=0.05)
+    if warm_target:
+        _fused_step(b, ob, 3)
+    b.load_state_dict(saved_model)
+    ob.load_state_dict(saved_opt)
+    for p in b.parameters():
+        st = ob.state[p]
+        assert st["exp_avg"].dtype == torch.float32 and st["exp_avg_sq"].dtype == torch.float32
+        assert st["exp_avg"].shape == p.shape and int(st["step"]) == 2
+    for p, q in zip(a.parameters(), b.parameters()):   # loaded moments equal the saved fp32 values
+        pid = [id(x) for x in a.parameters()].index(id(p))
+        assert torch.equal(ob.state[q]["exp_avg"], saved_opt["state"][pid]["exp_avg"].reshape(q.shape))
+    _fused_step(b, ob, 99)
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.equal(p.detach(), q.detach())
+        assert torch.equal(oa.state[p]["exp_avg_sq"], ob.state[q]["exp_avg_sq"])
+    if ob._flat:   # flat buffers are the storage behind the per-parameter views
+        flat = next(iter(ob._flat.values()))
+        q = next(iter(b.parameters()))
+        assert ob.state[q]["exp_avg"].untyped_storage().data_ptr() == flat["m"].untyped_storage().data_ptr()
+
+
+def test_adamw_kernel_wrapper_rejects_narrow_moments():
+    from flex_shard_b200.ops.elementwise import adamw_step_
+
+    p = torch.zeros(8, dtype=torch.bfloat16)
+    g = torch.zeros(8, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="fp32"):
+        adamw_step_(p, g, torch.zeros(8, dtype=torch.bfloat16), torch.zeros(8), lr=1e-3, beta1=0.9, beta2=0.99,
+                    eps=1e-8, weight_decay=0.0, step=1)
+    with pytest.raises(ValueError, match="at least"):
+        adamw_step_(p, g, torch.zeros(4), torch.zeros(8), lr=1e-3, beta1=0.9, beta2=0.99, eps=1e-8,
+                    weight_decay=0.0, step=1)
