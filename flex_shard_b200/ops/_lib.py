@@ -139,6 +139,40 @@ def check_status(device=None) -> None:
         raise NativeError(f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})")
 
 
+_polls: dict[int, tuple] = {}
+
+
+def poll_status(device=None) -> None:
+    """Non-blocking status check for once-per-step call sites (optimizer steps).
+
+    Raises if the copy of the status word that the *previous* call enqueued has landed and shows a
+    failed wait, then enqueues a new device -> pinned-host copy behind the work queued so far on the
+    current stream.  A failure is therefore reported one call late at most, and the host never waits
+    for the GPU.  Does nothing when no kernel of this process has asked for the status word yet."""
+    if not torch.cuda.is_available():
+        return
+    idx = (torch.cuda.current_device() if device is None or device.index is None else device.index)
+    word = _status.get(idx)
+    if word is None:
+        return
+    prev = _polls.get(idx)
+    if prev is not None:
+        host, ev = prev
+        if not ev.query():
+            return          # the previous copy has not landed yet: look again at the next call
+        code = int(host[0])
+        if code != 0:
+            word.zero_()
+            _polls.pop(idx, None)
+            raise NativeError(f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})")
+    else:
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host.copy_(word, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(idx))
+    _polls[idx] = (host, ev)
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise NativeError(f"{what}: {STATUS_NAMES.get(rc, rc)} (code {rc})")

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import _lib
 from ..ops.elementwise import adamw_step_
 
 
@@ -181,6 +182,7 @@ class FusedAdamW(torch.optim.Optimizer):
                     self._step_param(p, hp)
         if done:
             done.clear()
+        _lib.poll_status()   # a bounded device wait that ran out (late or missing peer) raises here, one step late at most
         return loss
 
     def step_bucket(self, storage) -> None:

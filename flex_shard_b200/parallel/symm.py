@@ -156,6 +156,7 @@ class SymmComm(Comm):
                 if last > 0:
                     cur.wait(self.SLOT_AG_DONE if which == "ag" else self.SLOT_RS_DONE, last)
                 torch.cuda.synchronize(self.device)
+                _lib.check_status(self.device)   # a peer that never signalled "done" may still read the old region: raise
                 size = max(size, 2 * cur.payload_bytes)
             cur = SymmRegion(self.group, size, self.device)
             if which == "ag":
@@ -280,8 +281,11 @@ class SymmComm(Comm):
             if n:
                 segs.append((r, sum(table_bytes[r][:me]), recv.data_ptr() + dst, n))
             dst += n
-        if not segs:   # nothing to receive: still publish, the peers pull from this rank
-            segs = [(me, 0, send.data_ptr() if send.numel() else self._region("ag", 16).payload.data_ptr(), 0)]
+        if not segs:
+            # nothing to receive: still publish (the peers pull from this rank) with one empty descriptor.
+            # Its address is never dereferenced; it must not come from the region, whose creation is a
+            # collective step that has to happen once, inside all_gather_segments, at the agreed size.
+            segs = [(me, 0, recv.data_ptr() if recv.numel() else 0, 0)]
         self.all_gather_segments(send, segs, alloc_bytes=max(max(sum(row) for row in table_bytes), 16))
         return True
 

@@ -78,6 +78,10 @@ class JsonMetrics:
             self._ev[1].record()
             self._ev[1].synchronize()
             ms = self._ev[0].elapsed_time(self._ev[1])
+            from ..ops import _lib
+
+            if _lib._status:       # the step has synchronised: a failed device-side wait raises on every rank that saw it
+                _lib.check_status()
         else:
             ms = (time.perf_counter() - self._t) * 1e3
         rec = {"step": step, "ms": round(ms, 3), "tokens_per_s_per_gpu": round(tokens / (ms / 1e3), 1)}
