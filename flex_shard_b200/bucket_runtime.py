@@ -41,6 +41,9 @@ def _in_backward() -> bool:
     return torch._C._current_graph_task_id() != -1
 
 
+_FSDP2_POST_ACCUMULATES: bool | None = None
+
+
 class BucketCommContext:
     """State shared by the buckets of one root module."""
 
@@ -251,6 +254,82 @@ class BucketRuntime:
             up._fsb_sharded = weakref.ref(sp)
             up._fsb_storage = self.storage
             self.unsharded_params.append(up)
+        self._set_unsharded_grad_dtypes(defer_upcast=False)
+
+    # ------------------------------------------------------------------ gradient accumulation dtype
+    def _accumulates_after_backward(self) -> bool:
+        """How gradients of the gathered parameters accumulate across backward passes without
+        reduction.  ``False`` (default): through autograd, by giving each gathered parameter the wider
+        ``grad_dtype``.  ``True``: like the FSDP2 of older torch releases (those whose ``FSDPParam`` has
+        ``to_accumulated_grad_if_needed``), which ``fsdp2_compatible`` buckets must reproduce bit for
+        bit: every backward sums in the compute dtype, a kept gradient is widened to the reduce dtype
+        after the backward, and the next backward's gradient is added to it when that backward ends."""
+        if not self.storage.spec.fsdp2_compatible:
+            return False
+        global _FSDP2_POST_ACCUMULATES
+        if _FSDP2_POST_ACCUMULATES is None:
+            try:
+                from torch.distributed.fsdp._fully_shard._fsdp_param import FSDPParam
+
+                _FSDP2_POST_ACCUMULATES = hasattr(FSDPParam, "to_accumulated_grad_if_needed")
+            except Exception:
+                _FSDP2_POST_ACCUMULATES = False
+        return _FSDP2_POST_ACCUMULATES
+
+    def _wide_grad_params(self):
+        """(info, gathered parameter, wide dtype) for parameters whose gradient accumulates in a dtype
+        wider than they compute in.  A parameter with a partial-gradient group keeps autograd's cast so
+        that its all-reduce runs in the wider dtype."""
+        for info, up in zip(self.storage.infos, self.unsharded_params or []):
+            wide, cd = info.unsharded_grad_dtype, info.param_dtype
+            if (wide is None or not up.requires_grad or not wide.is_floating_point or not cd.is_floating_point
+                    or wide.itemsize <= cd.itemsize):
+                continue
+            yield info, up, wide
+
+    def _set_unsharded_grad_dtypes(self, *, defer_upcast: bool) -> None:
+        """Defer or restore the cast of gradients that accumulate in a wider dtype.
+
+        Deferred (``grad_dtype = None``, set before a backward that reduces, or that adds to a kept
+        gradient): autograd leaves new gradients in the compute dtype, the reduce-scatter copy-in
+        widens them while it packs, and additions to a kept wide gradient happen in place; one cast
+        kernel per parameter and the wide full-size gradients are saved.  A backward that does not
+        reduce and starts a gradient keeps the cast, so a parameter used twice sums its uses in the
+        wide dtype.  Restoring widens a kept gradient once and puts ``grad_dtype`` back.
+        Parity: ``flex_shard/bucket_runtime.py:1062-1108`` of the reference."""
+        if self._accumulates_after_backward():
+            return
+        syncing = self.storage.requires_gradient_sync and not self.context.manual_finalization
+        for info, up, wide in self._wide_grad_params():
+            if info.partial_grad_group is not None:
+                if up.grad_dtype != wide:
+                    up.grad_dtype = wide
+                continue
+            if defer_upcast:
+                if up.grad is not None or syncing:
+                    up.grad_dtype = None
+                continue
+            g = up.grad
+            if g is not None and g.dtype != wide:
+                up.grad = g.to(wide)
+            up.grad_dtype = wide
+
+    def _widen_kept_grads(self) -> None:
+        """Older-FSDP2 accumulation: after a backward whose gradients are kept, move each into a wide
+        accumulator (adding to the one a previous backward left)."""
+        if not self._accumulates_after_backward():
+            return
+        for info, up, wide in self._wide_grad_params():
+            if not info.explicit_reduce_dtype:
+                continue
+            acc, g = getattr(up, "_fsb_wide_grad", None), up.grad
+            if g is None:
+                continue
+            if acc is None:
+                up._fsb_wide_grad = g.to(wide)
+            else:
+                acc += g
+            up.grad = None
 
     # ------------------------------------------------------------------ unshard / reshard
     def begin_unshard(self, prefetch: bool = False) -> None:
@@ -345,6 +424,8 @@ class BucketRuntime:
         self._free_persistent()
         self.is_unsharded = False
         self._forwards_in_pass = 0
+        if self.unsharded_params is not None and not _in_backward():
+            self._set_unsharded_grad_dtypes(defer_upcast=False)   # a deferred cast does not outlive the gathered state
 
     def release_unused_prefetch(self) -> None:
         """Drop a prefetched gather that nothing consumed (its buffers return to the allocator)."""
@@ -436,6 +517,7 @@ class BucketRuntime:
         with record("FlexShard::pre_backward", self.storage.name):
             self.unshard()
             self.swap_in_unsharded()
+            self._set_unsharded_grad_dtypes(defer_upcast=True)
             hook = self.storage.spec.pre_backward_hook
             if hook is not None:
                 hook(self.storage)
@@ -467,6 +549,12 @@ class BucketRuntime:
             if not info.requires_grad or not up.requires_grad:
                 continue
             g = up.grad
+            acc = getattr(up, "_fsb_wide_grad", None)
+            if acc is not None:     # older-FSDP2 accumulation: this backward's gradient joins the kept one
+                if g is not None:
+                    acc += g
+                g = acc
+                up._fsb_wide_grad = None
             mg = getattr(up, "main_grad", None)
             if mg is not None:
                 if getattr(up, "main_grad_written", False):
@@ -493,12 +581,18 @@ class BucketRuntime:
                 any_grad = True
             grads.append(g)
             up.grad = None
-        if not any_grad and self.storage.spec.fsdp2_compatible:
-            return None
-        out = []
-        trainable = [(i, u) for i, u in zip(self.storage.infos, self.unsharded_params)
+        trainable = [(i, u, sp) for i, u, sp in zip(self.storage.infos, self.unsharded_params,
+                                                    self.storage.sharded_params)
                      if i.requires_grad and u.requires_grad]
-        for (info, up), g in zip(trainable, grads):
+        if self.storage.spec.fsdp2_compatible:
+            # like an FSDP2 group: a parameter that received no gradient in this backward takes no part
+            # in the reduce-scatter and its sharded .grad stays untouched (None if it never had one)
+            kept = [(t, g) for t, g in zip(trainable, grads) if g is not None]
+            if not kept:
+                return None
+            trainable, grads = [t for t, _ in kept], [g for _, g in kept]
+        out = []
+        for (info, up, _), g in zip(trainable, grads):
             if g is None:
                 g = torch.zeros(info.global_shape, dtype=info.param_dtype, device=self.storage.device)
             if info.partial_grad_group is not None:
@@ -511,6 +605,8 @@ class BucketRuntime:
             for g in out:
                 if isinstance(g, torch.Tensor):
                     g._fsb_peer_target = bucket
+        self.storage.infos_for_reduce = [t[0] for t in trainable]
+        self._sharded_for_reduce = [t[2] for t in trainable]
         return out
 
     def post_backward(self) -> None:
@@ -524,6 +620,8 @@ class BucketRuntime:
                 self.needs_sync = True
                 if st.reshard_after_backward:
                     self.reshard()
+                self._set_unsharded_grad_dtypes(defer_upcast=False)
+                self._widen_kept_grads()
                 return
             self._reduce_now()
 
@@ -537,6 +635,8 @@ class BucketRuntime:
         hook = st.spec.post_reduce_hook
         if st.reshard_after_backward:
             self.reshard()
+        # the gradients are taken: this only puts the gathered parameters' grad_dtype back
+        self._set_unsharded_grad_dtypes(defer_upcast=False)
         self.needs_sync = False
         if grads is None or not grads:
             if hook is not None:
@@ -547,7 +647,6 @@ class BucketRuntime:
             reduce_dtype = torch.promote_types(reduce_dtype, g.dtype) if st.spec.mp_policy.reduce_dtype is None else reduce_dtype
         ctx.drain_reduces(max(ctx.max_pending_reduce_grads - 1, 0))
         stream = ctx.reduce_stream if st.reduce_comm.world_size > 1 else None
-        st.infos_for_reduce = [i for i, u in zip(st.infos, self.unsharded_params) if i.requires_grad and u.requires_grad]
         state = begin_reduce_grad(self, grads, reduce_dtype, st.reduction, stream)
         ctx.stats["reduces"] += 1
         ctx.pending_reduces.append(state)
@@ -557,9 +656,7 @@ class BucketRuntime:
     def accumulate_sharded_grads(self, result) -> None:
         st = self.storage
         with record("FlexShard::reduce_grad_accumulate", st.name):
-            sps = [sp for sp, i, u in zip(st.sharded_params, st.infos, self.unsharded_params)
-                   if i.requires_grad and u.requires_grad]
-            for sp, g in zip(sps, result.grads):
+            for sp, g in zip(self._sharded_for_reduce, result.grads):
                 if g is None:
                     continue
                 info = sp._fsb_info
@@ -585,6 +682,8 @@ class BucketRuntime:
             self.needs_sync = True
             if self.storage.reshard_after_backward:
                 self.reshard()
+            self._set_unsharded_grad_dtypes(defer_upcast=False)
+            self._widen_kept_grads()
 
     def reset_backward_state(self) -> None:
         self._pre_backward_done = False

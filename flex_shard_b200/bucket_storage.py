@@ -130,6 +130,19 @@ class ParamInfo:
     shared_fqns: tuple[str, ...] = ()
     bucket_layout: Any | None = None
     bucket_reduce_dtype: torch.dtype | None = None
+    explicit_reduce_dtype: bool = False    # the bucket's policy names a reduce dtype
+
+    @property
+    def unsharded_grad_dtype(self) -> torch.dtype:
+        """Dtype in which the gathered parameter's gradient accumulates across backward passes: the
+        policy's reduce dtype, else an explicit ``grad_dtype`` set on the parameter before sharding,
+        else the compute dtype (parity: ``flex_shard/bucket_storage.py:325-334`` of the reference,
+        with the compute dtype as the last resort, as the installed FSDP2 reduces in it)."""
+        if self.explicit_reduce_dtype:
+            return self.reduce_dtype
+        if self.grad_dtype is not None:
+            return self.grad_dtype
+        return self.param_dtype
 
     @property
     def local_numel(self) -> int:
@@ -354,7 +367,8 @@ def create_param_infos(spec: BucketSpec, named_params: list[tuple[str, nn.Parame
             param_dtype=param_dtype, reduce_dtype=reduce_dtype, grad_dtype=grad_dtype,
             placement=pl, requires_grad=p.requires_grad, outer_layout=get_global_layout(p),
             partial_grad_group=get_partial_grad_group(p), param_attrs=_user_attrs(p),
-            shared_fqns=tuple(shared_names.get(fqn, ())), bucket_layout=extra))
+            shared_fqns=tuple(shared_names.get(fqn, ())), bucket_layout=extra,
+            explicit_reduce_dtype=mp.reduce_dtype is not None))
     total = bucket_layout.total_bytes if bucket_layout is not None else offset
     brd = None
     for info in infos:

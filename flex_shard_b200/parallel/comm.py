@@ -28,6 +28,7 @@ class ReducePlan:
     op: str                    # "sum" | "avg" | "premul_sum"
     premul: float | None       # factor of a pre-multiplied sum
     post_divide: float | None  # divide the output by this afterwards
+    factor: float | None = None  # the divide factor behind "premul_sum" (backends without that op sum, then divide by it)
 
 
 def plan_reduction(reduction: GradientReduction, world_size: int, dtype: torch.dtype) -> ReducePlan:
@@ -44,7 +45,7 @@ def plan_reduction(reduction: GradientReduction, world_size: int, dtype: torch.d
         return ReducePlan(float(pre), "sum", None, f / pre)
     if f == world_size:
         return ReducePlan(None, "avg", None, None)
-    return ReducePlan(None, "premul_sum", 1.0 / f, None)
+    return ReducePlan(None, "premul_sum", 1.0 / f, None, factor=f)
 
 
 class Comm:
@@ -126,17 +127,22 @@ class Comm:
                 op = dist.ReduceOp.SUM
             work = dist.reduce_scatter_tensor(out, inp, op=op, group=self.group, async_op=async_op)
         else:
-            # gloo: no AVG / pre-multiplied ops; fold the scaling into the data.
-            if plan.op == "premul_sum":
-                inp.mul_(plan.premul)
+            # gloo has no pre-multiplied sum: sum, then divide the (smaller) output by the factor, which is
+            # what FSDP2 does when told to use plain sums for its collectives. AVG runs natively.
+            native_avg = plan.op == "avg" and not getattr(self, "_gloo_no_avg", False)
             try:
-                dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=self.group)
+                dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.AVG if native_avg else dist.ReduceOp.SUM,
+                                           group=self.group)
             except (RuntimeError, NotImplementedError):
+                if native_avg:
+                    self._gloo_no_avg, native_avg = True, False
                 dist.all_reduce(inp, op=dist.ReduceOp.SUM, group=self.group)
                 n = out.numel()
                 out.copy_(inp.view(-1)[self.rank * n:(self.rank + 1) * n].view_as(out))
-            if plan.op == "avg":
+            if plan.op == "avg" and not native_avg:
                 out.div_(self.world_size)
+            if plan.op == "premul_sum" and plan.factor != 1.0:
+                out.div_(plan.factor)
         if plan.post_divide is not None:
             if work is not None:
                 work.wait()
@@ -161,12 +167,12 @@ class Comm:
             dist.reduce_scatter(out, list(inps), op=op, group=self.group)
         else:
             for r, t in enumerate(inps):
-                if plan.op == "premul_sum":
-                    t.mul_(plan.premul)
                 dist.reduce(t, dst=self.ranks()[r], op=dist.ReduceOp.SUM, group=self.group)
             out.copy_(inps[self.rank])
             if plan.op == "avg":
                 out.div_(self.world_size)
+            if plan.op == "premul_sum" and plan.factor != 1.0:
+                out.div_(plan.factor)
         if plan.post_divide is not None:
             out.div_(plan.post_divide)
         return None
