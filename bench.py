@@ -266,6 +266,17 @@ def run_ours(args, rank, local, world):
         e2e = {"value": tok_per_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": host[0].numel() * host[0].element_size(),
                "d2h_bytes_per_step": loss_host.numel() * loss_host.element_size()}
+    # exposed communication: a few extra steps (outside both timed regions) with every wait of the compute
+    # stream on a gather or a reduction bracketed by timing events; per step, max over ranks
+    exposed = None
+    if world > 1:
+        ctx = model._fsb_ctx()
+        ctx.measure_exposed_comm(True)
+        n_probe = 3
+        for i in range(n_probe):
+            step_device(i)
+        exposed = max_over_ranks(ctx.exposed_comm_ms() / n_probe, world)
+        ctx.measure_exposed_comm(False)
     tokens_per_step = B * S * world
     value = tokens_per_step / (ms / 1e3)
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
@@ -287,6 +298,7 @@ def run_ours(args, rank, local, world):
                        "collectives": (args.comm if world > 1 else "none (1 rank)"),
                        "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "exposed_comm_ms": exposed,
             "loss": loss_val, "peak_mem_gib": round(peak_gb, 2),
             "tflops_per_gpu": flops / (ms / 1e3) / 1e12,
         }

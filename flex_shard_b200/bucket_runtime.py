@@ -69,6 +69,34 @@ class BucketCommContext:
         self.poisoned = False
         self.pending_finalize_handle = None
         self.stats = {"unshards": 0, "prefetch_hits": 0, "reduces": 0}
+        self._exposed: list | None = None   # (before, after) event pairs around waits on communication
+
+    # ------------------------------------------------------------------ exposed communication time
+    def measure_exposed_comm(self, enabled: bool = True) -> None:
+        """Start (or stop) timing how long the compute stream sits blocked on communication: every wait
+        on a gather's or a reduction's completion event is bracketed by two timing events."""
+        self._exposed = [] if (enabled and self.cuda) else None
+
+    def exposed_comm_ms(self) -> float:
+        """Milliseconds the compute stream spent waiting on gathers and reductions since the last call
+        (device time between the bracketing events; synchronises)."""
+        if not self._exposed:
+            return 0.0
+        torch.cuda.synchronize(self.device)
+        total = sum(a.elapsed_time(b) for a, b in self._exposed)
+        self._exposed.clear()
+        return float(total)
+
+    def wait_comm_event(self, event) -> None:
+        cur = torch.cuda.current_stream()
+        if self._exposed is None:
+            cur.wait_event(event)
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(cur)
+        cur.wait_event(event)
+        b.record(cur)
+        self._exposed.append((a, b))
 
     # ------------------------------------------------------------------ learned orders
     def note_forward(self, rt: "BucketRuntime") -> None:
@@ -104,7 +132,7 @@ class BucketCommContext:
             st = self.pending_reduces.pop(0)
             if st.event is not None:
                 with record("FlexShard::post_backward_reduce_grad_wait"):
-                    torch.cuda.current_stream().wait_event(st.event)
+                    self.wait_comm_event(st.event)
             st.keep.clear()
 
     # ------------------------------------------------------------------ end of backward
@@ -127,6 +155,7 @@ class BucketCommContext:
             else:
                 for rt in self.runtimes:
                     rt.end_of_backward_without_finalize()
+            self.fence_peer_reads()
             for rt in self.runtimes:
                 rt.release_unused_prefetch()
             if self.forward_order:
@@ -136,6 +165,18 @@ class BucketCommContext:
             self.backward_running = False
             for rt in self.runtimes:
                 rt.reset_backward_state()
+
+    def fence_peer_reads(self) -> None:
+        """Buckets whose storage the peers read in place (symmetric memory): make the current stream wait
+        until every peer has finished this backward's reads, so that whatever runs next on it (an
+        optimizer step) may overwrite the shards."""
+        seen = set()
+        for rt in self.runtimes:
+            comm = rt.storage.comm
+            fence = getattr(comm, "fence_resident", None)
+            if fence is not None and id(comm) not in seen:
+                seen.add(id(comm))
+                fence()
 
     def check_not_poisoned(self) -> None:
         if self.backward_running and not _in_backward():
@@ -355,7 +396,7 @@ class BucketRuntime:
         self.pending = None
         st = self.storage
         if p.event is not None:
-            torch.cuda.current_stream().wait_event(p.event)
+            self.context.wait_comm_event(p.event)
         persistent = self._alloc_persistent()
         # Refilling the persistent buffers must not look like an in-place edit to autograd: the
         # tensors saved by the forward are these very buffers, re-gathered with the same values.

@@ -222,10 +222,15 @@ class ShardedBucketStorage:
 
     def allocate(self) -> None:
         n = max(self.total_bytes, 0)
+        buf = None
         if getattr(self, "_allocator", None) is not None:
-            self.byte_storage = self._allocator(n, self.device)
-        else:
-            self.byte_storage = torch.empty(n, dtype=torch.uint8, device=self.device)
+            buf = self._allocator(n, self.device)
+        elif self.device.type == "cuda" and getattr(self.placement, "uniform_storage", False):
+            # same size on every rank: the bucket can live in symmetric memory, where the peers' gathers
+            # read it in place (a peer-memory communicator offers alloc_storage; others do not)
+            alloc = getattr(self.comm, "alloc_storage", None)
+            buf = alloc(n) if alloc is not None else None
+        self.byte_storage = buf if buf is not None else torch.empty(n, dtype=torch.uint8, device=self.device)
         self.byte_storage.zero_()  # padding must be deterministic zeros
 
     @property

@@ -64,6 +64,18 @@ struct PeerPtrs {
   void* p[MAX_RANKS];
 };
 
+// Sum of the same 16 bytes of every rank's copy of a multicast-bound symmetric buffer, added inside
+// the NVSwitch: one load crosses this GPU's links instead of one per peer. `mc` is an address in
+// the multicast mapping. The switch's summation order is fixed for a given set of ranks.
+__device__ __forceinline__ float4 multimem_sum_f32x4(const void* mc) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc)
+               : "memory");
+  return r;
+}
+
 __global__ void signal_kernel(PeerPtrs flags, int rank, int world, uint32_t epoch) {
   // flags.p[r] = address of this slot's flag row on rank r
   if (threadIdx.x < world) {
@@ -116,20 +128,27 @@ struct AdamArgs {
 };
 
 // rows.p[r] = address of rank r's gradient row that belongs to THIS rank (fp32, n elements).
-template <typename PT, bool WITH_ADAM>
+// With MC, rows.p[0] is instead the address of that row in the multicast mapping of the symmetric
+// buffer (the row sits at the same offset on every rank) and the W-way sum happens in the switch.
+template <typename PT, bool WITH_ADAM, bool MC>
 __global__ void __launch_bounds__(256)
 reduce_rows_kernel(PeerPtrs rows, int world, long long n, float scale, float* __restrict__ g_out,
                    PT* __restrict__ p, float* __restrict__ m, float* __restrict__ v, AdamArgs a,
                    const uint32_t* my_flags, uint32_t epoch, uint32_t max_polls, int* status) {
   if (my_flags != nullptr && !cta_wait_peers(my_flags, world, epoch, max_polls, status)) return;
+  if (MC) __threadfence_system();
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long n4 = n / 4;
   for (long long i = tid; i < n4; i += stride) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {  // fixed rank order: the sum is deterministic
-      const float4 t = static_cast<const float4*>(rows.p[r])[i];
-      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    if (MC) {
+      acc = multimem_sum_f32x4(static_cast<const float4*>(rows.p[0]) + i);
+    } else {
+      for (int r = 0; r < world; ++r) {  // fixed rank order: the sum is deterministic
+        const float4 t = static_cast<const float4*>(rows.p[r])[i];
+        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+      }
     }
     float g[4] = {acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale};
     if (g_out) *reinterpret_cast<float4*>(g_out + i * 4) = make_float4(g[0], g[1], g[2], g[3]);
@@ -152,6 +171,7 @@ reduce_rows_kernel(PeerPtrs rows, int world, long long n, float scale, float* __
       *reinterpret_cast<float4*>(v + i * 4) = make_float4(vq[0], vq[1], vq[2], vq[3]);
     }
   }
+  if (MC) return;   // the launcher only takes the multicast path for n % 4 == 0
   for (long long i = n4 * 4 + tid; i < n; i += stride) {
     float acc = 0.f;
     for (int r = 0; r < world; ++r) acc += static_cast<const float*>(rows.p[r])[i];
@@ -212,31 +232,109 @@ FSB_API int fsb_comm_gather_pull(const void* descs, int nseg, int blocks_per_seg
 
 // rows[r]: address of rank r's fp32 gradient row for this rank (n elements, 16-byte aligned).
 // g_out may be null. With p != null the AdamW update is applied in the same pass.
-FSB_API int fsb_comm_reduce_rows(const unsigned long long* rows, int world, long long n, float scale,
-                                 float* g_out, void* p, int p_fp32, float* m, float* v, float lr,
-                                 float beta1, float beta2, float eps, float weight_decay, int step,
-                                 const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
-                                 cudaStream_t stream) {
+// mc_row != 0: address of the row in the multicast mapping; the sum is then one in-switch load-reduce
+// per 16 bytes (needs n % 4 == 0) and `rows` is not read.
+static int reduce_rows_launch(const unsigned long long* rows, unsigned long long mc_row, int world, long long n,
+                              float scale, float* g_out, void* p, int p_fp32, float* m, float* v, float lr,
+                              float beta1, float beta2, float eps, float weight_decay, int step,
+                              const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
+                              cudaStream_t stream) {
   if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
   if (n <= 0) return FSB_OK;
   PeerPtrs rp;
-  for (int r = 0; r < world; ++r) {
-    if (rows[r] & 15) return FSB_ERR_BAD_ARG;
-    rp.p[r] = reinterpret_cast<void*>(rows[r]);
+  const bool mc = mc_row != 0;
+  if (mc) {
+    if ((mc_row & 15) || (n & 3)) return FSB_ERR_BAD_ARG;
+    rp.p[0] = reinterpret_cast<void*>(mc_row);
+  } else {
+    for (int r = 0; r < world; ++r) {
+      if (rows[r] & 15) return FSB_ERR_BAD_ARG;
+      rp.p[r] = reinterpret_cast<void*>(rows[r]);
+    }
   }
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, static_cast<float>(step)),
              sqrtf(1.f - powf(beta2, static_cast<float>(step)))};
   const int grid = grid_for(n, 8);
   const uint32_t* fl = static_cast<const uint32_t*>(my_flags);
+#define FSB_REDUCE_LAUNCH(PT, ADAM, MCF, PP)                                                              \
+  reduce_rows_kernel<PT, ADAM, MCF><<<grid, 256, 0, stream>>>(rp, world, n, scale, g_out, PP, m, v, a, fl, \
+                                                              epoch, max_polls, status)
   if (p == nullptr) {
-    reduce_rows_kernel<float, false><<<grid, 256, 0, stream>>>(rp, world, n, scale, g_out, nullptr, nullptr,
-                                                               nullptr, a, fl, epoch, max_polls, status);
+    if (mc) FSB_REDUCE_LAUNCH(float, false, true, static_cast<float*>(nullptr));
+    else FSB_REDUCE_LAUNCH(float, false, false, static_cast<float*>(nullptr));
   } else if (p_fp32) {
-    reduce_rows_kernel<float, true><<<grid, 256, 0, stream>>>(rp, world, n, scale, g_out, static_cast<float*>(p),
-                                                              m, v, a, fl, epoch, max_polls, status);
+    if (mc) FSB_REDUCE_LAUNCH(float, true, true, static_cast<float*>(p));
+    else FSB_REDUCE_LAUNCH(float, true, false, static_cast<float*>(p));
   } else {
-    reduce_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(
-        rp, world, n, scale, g_out, static_cast<__nv_bfloat16*>(p), m, v, a, fl, epoch, max_polls, status);
+    if (mc) FSB_REDUCE_LAUNCH(__nv_bfloat16, true, true, static_cast<__nv_bfloat16*>(p));
+    else FSB_REDUCE_LAUNCH(__nv_bfloat16, true, false, static_cast<__nv_bfloat16*>(p));
   }
+#undef FSB_REDUCE_LAUNCH
   return ok();
+}
+
+FSB_API int fsb_comm_reduce_rows(const unsigned long long* rows, int world, long long n, float scale,
+                                 float* g_out, void* p, int p_fp32, float* m, float* v, float lr,
+                                 float beta1, float beta2, float eps, float weight_decay, int step,
+                                 const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
+                                 cudaStream_t stream) {
+  return reduce_rows_launch(rows, 0ull, world, n, scale, g_out, p, p_fp32, m, v, lr, beta1, beta2, eps,
+                            weight_decay, step, my_flags, epoch, max_polls, status, stream);
+}
+
+// The same reduction (+AdamW) with the W-way sum done inside the NVSwitch: `mc_row` is the address, in the
+// multicast mapping of the symmetric gradient buffer, of the row every rank wrote for this rank.
+FSB_API int fsb_comm_reduce_rows_mc(unsigned long long mc_row, int world, long long n, float scale,
+                                    float* g_out, void* p, int p_fp32, float* m, float* v, float lr,
+                                    float beta1, float beta2, float eps, float weight_decay, int step,
+                                    const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
+                                    cudaStream_t stream) {
+  if (mc_row == 0) return FSB_ERR_BAD_ARG;
+  return reduce_rows_launch(nullptr, mc_row, world, n, scale, g_out, p, p_fp32, m, v, lr, beta1, beta2, eps,
+                            weight_decay, step, my_flags, epoch, max_polls, status, stream);
+}
+
+// One launch that waits (bounded) on up to 64 flag rows, each for its own epoch: CTA i waits until every
+// rank's entry of flag row i has reached epochs[i].
+namespace {
+struct WaitList {
+  const uint32_t* flags[64];
+  uint32_t epochs[64];
+};
+__global__ void wait_many_kernel(WaitList w, int world, uint32_t max_polls, int* status) {
+  cta_wait_peers(w.flags[blockIdx.x], world, w.epochs[blockIdx.x], max_polls, status);
+}
+}  // namespace
+
+FSB_API int fsb_comm_wait_many(const unsigned long long* flag_rows, const unsigned* epochs, int count, int world,
+                               unsigned max_polls, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
+  for (int base = 0; base < count; base += 64) {
+    WaitList w;
+    const int c = count - base < 64 ? count - base : 64;
+    for (int i = 0; i < c; ++i) {
+      w.flags[i] = reinterpret_cast<const uint32_t*>(flag_rows[base + i]);
+      w.epochs[i] = epochs[base + i];
+    }
+    wait_many_kernel<<<c, 32, 0, stream>>>(w, world, max_polls, status);
+    if (cudaGetLastError() != cudaSuccess) return FSB_ERR_LAUNCH;
+  }
+  return FSB_OK;
+}
+
+// Copy a list of (source, destination, bytes) segments with the GPU's copy engines: one asynchronous
+// device-to-device copy per segment on `stream`, in order. Sources may be peer addresses of a symmetric
+// buffer; no SM takes part, so a gather issued this way does not compete with the kernels computing
+// next to it. The caller orders the copies after the peers' "ready" flags with a wait launch.
+FSB_API int fsb_comm_copy_segments_dma(const unsigned long long* src, const unsigned long long* dst,
+                                       const long long* nbytes, int count, cudaStream_t stream) {
+  for (int i = 0; i < count; ++i) {
+    if (nbytes[i] <= 0) continue;
+    if (cudaMemcpyAsync(reinterpret_cast<void*>(dst[i]), reinterpret_cast<const void*>(src[i]),
+                        static_cast<size_t>(nbytes[i]), cudaMemcpyDefault, stream) != cudaSuccess) {
+      cudaGetLastError();
+      return FSB_ERR_LAUNCH;
+    }
+  }
+  return FSB_OK;
 }

@@ -398,6 +398,9 @@ def relayout_bucket(module: nn.Module, storage: ShardedBucketStorage, placement_
             if lst:
                 setattr(other, lst_name, [new if s is storage else s for s in lst])
     state.storages[idx] = new
+    release = getattr(comm, "release_storage", None)
+    if release is not None and storage.byte_storage is not None:
+        release(storage.byte_storage)   # a symmetric region of its own: give it back (collective-safe: same order everywhere)
     storage.byte_storage = None
     storage.sharded_params = []
     return new

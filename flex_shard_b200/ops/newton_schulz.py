@@ -104,6 +104,26 @@ def muon_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: float, neste
     return ns_iterations(u, steps, coeffs)
 
 
+def muon_momentum_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: float, nesterov: bool) -> torch.Tensor:
+    """``M <- lerp(M, g, 1-mu)`` in place (fp32) and return ``u = lerp(g, M, mu)`` (Nesterov) or ``M`` as bf16,
+    in the shape of ``grad``: the elementwise half of a Muon step, for rows that are orthogonalised elsewhere."""
+    assert momentum.shape == grad.shape and momentum.dtype == torch.float32
+    if not grad.is_cuda:
+        momentum.lerp_(grad.float(), 1 - mu)
+        u = grad.float().lerp(momentum, mu) if nesterov else momentum
+        return u.to(torch.bfloat16)
+    _ensure()
+    g = grad.contiguous()
+    assert momentum.is_contiguous()
+    u = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
+    ss = torch.zeros(1, dtype=torch.float32, device=g.device)
+    rc = _lib.load().fsb_muon_prepare(momentum.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), u.data_ptr(),
+                                      ss.data_ptr(), g.numel(), mu, int(nesterov), _lib.stream_ptr(g.device))
+    _lib.check(rc, "fsb_muon_prepare")
+    count_launch()
+    return u
+
+
 def muon_apply_(param: torch.Tensor, direction: torch.Tensor, lr: float, weight_decay: float, ratio: float):
     """``p <- p (1 - lr*wd) - lr*ratio*direction`` in place."""
     if not param.is_cuda:

@@ -44,6 +44,10 @@ def _ensure():
     _lib.declare("fsb_comm_gather_pull", [vp, i32, i32, vp, i32, u32, u32, vp, vp])
     _lib.declare("fsb_comm_reduce_rows", [vp, i32, i64, f32, vp, vp, i32, vp, vp, f32, f32, f32, f32, f32, i32,
                                           vp, u32, u32, vp, vp])
+    _lib.declare("fsb_comm_reduce_rows_mc", [c.c_ulonglong, i32, i64, f32, vp, vp, i32, vp, vp, f32, f32, f32, f32,
+                                             f32, i32, vp, u32, u32, vp, vp])
+    _lib.declare("fsb_comm_wait_many", [vp, vp, i32, i32, u32, vp, vp])
+    _lib.declare("fsb_comm_copy_segments_dma", [vp, vp, vp, i32, vp])
     _declared = True
 
 
@@ -66,6 +70,15 @@ class SymmRegion:
         self.buf[:FLAG_BYTES].zero_()
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
+        # address of the same buffer in the NVSwitch multicast mapping (0: not available or switched off);
+        # multimem loads through it return the sum over all ranks' copies, added inside the switch
+        self.mc_base = 0
+        if os.environ.get("FSB200_MULTIMEM", "1") != "0":
+            try:
+                self.mc_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            except Exception:
+                self.mc_base = 0
+        self.epoch = 0   # gather epoch of a region that holds a bucket's resident storage
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone signals
         self.max_polls = DEFAULT_MAX_POLLS
@@ -77,6 +90,9 @@ class SymmRegion:
 
     def peer_payload_addr(self, r: int, offset: int = 0) -> int:
         return self.peer_base[r] + FLAG_BYTES + offset
+
+    def mc_payload_addr(self, offset: int = 0) -> int:
+        return self.mc_base + FLAG_BYTES + offset if self.mc_base else 0
 
     def flag_row_addr(self, r: int, slot: int) -> int:
         return self.peer_base[r] + slot * MAX_RANKS * 4
@@ -133,6 +149,16 @@ class SymmComm(Comm):
         # written locally in reduce-scatter layout and the owners pull and sum them)
         self.fused_reduce = os.environ.get("FSB200_FUSED_REDUCE", "1") != "0"
         self._grad_ring: SymmGradRing | None = None
+        # buckets whose byte storage lives in symmetric memory: payload address -> region. Their gathers
+        # read the peers' storage in place (no staging copy, no shared staging region to serialise on).
+        self._resident: dict[int, SymmRegion] = {}
+        self._unfenced: set[int] = set()
+        self.resident_storage = os.environ.get("FSB200_RESIDENT", "1") != "0"
+        self.stats = {"resident_gathers": 0, "staged_gathers": 0, "dma_gathers": 0, "multimem_reduces": 0,
+                      "peer_reduces": 0}
+        self.multimem_reduce = os.environ.get("FSB200_MULTIMEM_REDUCE", "1") != "0"
+        # "dma": segment gathers are issued as copy-engine copies (no SM time); "sm": the pull kernel
+        self.gather_engine = os.environ.get("FSB200_GATHER", "dma")
 
     @classmethod
     def from_mesh(cls, mesh, **kw) -> "SymmComm":
@@ -166,6 +192,47 @@ class SymmComm(Comm):
             self._desc_cache.clear()
         return cur
 
+    # ------------------------------------------------------------------ resident bucket storage
+    def alloc_storage(self, nbytes: int) -> torch.Tensor | None:
+        """Byte storage for one bucket inside a symmetric region of its own (a collective call: every rank
+        of the group allocates the same size in the same order). Returns None when switched off."""
+        if not self.resident_storage or self.world_size == 1 or nbytes <= 0:
+            return None
+        reg = SymmRegion(self.group, nbytes, self.device)
+        buf = reg.payload[:nbytes]
+        self._resident[buf.data_ptr()] = reg
+        return buf
+
+    def release_storage(self, buf: torch.Tensor) -> None:
+        """Forget a resident storage (its bucket was laid out anew). The peers may have read it last in a
+        backward that has ended on every rank before anyone re-lays out, so no wait is needed here; the
+        memory goes back once the last tensor viewing it is gone."""
+        ptr = buf.data_ptr()
+        self._resident.pop(ptr, None)
+        self._unfenced.discard(ptr)
+
+    def _resident_region(self, inp: torch.Tensor):
+        reg = self._resident.get(inp.data_ptr())
+        if reg is not None and inp.numel() * inp.element_size() <= reg.payload_bytes:
+            return reg
+        return None
+
+    def fence_resident(self) -> None:
+        """Enqueue, on the current stream, a wait until every peer has finished reading this rank's
+        resident storages (their pulls of the latest gather epoch). Work queued afterwards, such as an
+        optimizer step, may then overwrite the shards. One launch for all buckets."""
+        regs = [self._resident[k] for k in self._unfenced if k in self._resident]
+        self._unfenced.clear()
+        regs = [r for r in regs if r.epoch > 0]
+        if not regs:
+            return
+        rows = (ctypes.c_ulonglong * len(regs))(*[r.flag_row_addr(self.rank, self.SLOT_AG_DONE) for r in regs])
+        eps = (ctypes.c_uint * len(regs))(*[r.epoch & 0xFFFFFFFF for r in regs])
+        rc = _lib.load().fsb_comm_wait_many(rows, eps, len(regs), self.world_size, regs[0].max_polls,
+                                            _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_wait_many")
+        count_launch()
+
     def grad_ring(self, entry_bytes: int) -> SymmGradRing:
         if self._grad_ring is None or self._grad_ring.entry_bytes < entry_bytes:
             if self._grad_ring is not None:
@@ -192,36 +259,61 @@ class SymmComm(Comm):
         reg = ring.region
         W = self.world_size
         reg.signal(ring.SLOT_WRITTEN0 + k, u)
-        rows = (ctypes.c_ulonglong * W)(*[ring.read_addr(self.rank, s, k, row) for s in range(W)])
         a = adam or {}
         p = a.get("p")
-        rc = _lib.load().fsb_comm_reduce_rows(
-            rows, W, row, scale, out.data_ptr() if out is not None else None,
-            p.data_ptr() if p is not None else None, int(p is not None and p.dtype == torch.float32),
-            a["m"].data_ptr() if adam else None, a["v"].data_ptr() if adam else None,
-            a.get("lr", 0.0), a.get("beta1", 0.0), a.get("beta2", 0.0), a.get("eps", 0.0),
-            a.get("weight_decay", 0.0), a.get("step", 1),
-            reg.flag_row_addr(self.rank, ring.SLOT_WRITTEN0 + k), u, reg.max_polls,
-            _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        tail = (out.data_ptr() if out is not None else None,
+                p.data_ptr() if p is not None else None, int(p is not None and p.dtype == torch.float32),
+                a["m"].data_ptr() if adam else None, a["v"].data_ptr() if adam else None,
+                a.get("lr", 0.0), a.get("beta1", 0.0), a.get("beta2", 0.0), a.get("eps", 0.0),
+                a.get("weight_decay", 0.0), a.get("step", 1),
+                reg.flag_row_addr(self.rank, ring.SLOT_WRITTEN0 + k), u, reg.max_polls,
+                _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        mc_row = ring.mc_read_addr(self.rank, k, row) if (self.multimem_reduce and row % 4 == 0) else 0
+        if mc_row:
+            # pull layout: every rank wrote its contribution for this rank at the same offset of its own
+            # entry, so one multimem load per 16 bytes returns the W-way sum (added in the switch)
+            rc = _lib.load().fsb_comm_reduce_rows_mc(mc_row, W, row, scale, *tail)
+            self.stats["multimem_reduces"] += 1
+        else:
+            self.stats["peer_reduces"] += 1
+            rows = (ctypes.c_ulonglong * W)(*[ring.read_addr(self.rank, s, k, row) for s in range(W)])
+            rc = _lib.load().fsb_comm_reduce_rows(rows, W, row, scale, *tail)
         _lib.check(rc, "fsb_comm_reduce_rows")
         count_launch()
         reg.signal(ring.SLOT_CONSUMED0 + k, u)
 
     # ------------------------------------------------------------------ all-gather
+    def _publish(self, inp: torch.Tensor, nbytes: int, alloc_bytes: int):
+        """Make this rank's send data readable by the peers and announce it; returns (region, epoch).
+        Resident storage is read in place: the announcement alone orders the peers' pulls after whatever
+        this stream did to the shard. Anything else is copied into the shared staging region first, once
+        the peers are done with the region's previous payload."""
+        reg = self._resident_region(inp) if nbytes else None
+        if reg is not None:
+            reg.epoch += 1
+            e = reg.epoch
+            self._unfenced.add(inp.data_ptr())
+            self.stats["resident_gathers"] += 1
+        else:
+            self.stats["staged_gathers"] += 1
+            reg = self._region("ag", alloc_bytes)  # same size on every rank
+            self._ag_epoch += 1
+            e = self._ag_epoch
+            if e > 1:
+                reg.wait(self.SLOT_AG_DONE, e - 1)      # peers finished reading the previous payload
+            if nbytes:
+                reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
+        reg.signal(self.SLOT_AG_READY, e)
+        return reg, e
+
     def all_gather_into_tensor(self, out: torch.Tensor, inp: torch.Tensor, async_op: bool = False):
         if self.world_size == 1:
             return super().all_gather_into_tensor(out, inp)
         W = self.world_size
         nbytes = inp.numel() * inp.element_size()
         assert out.numel() * out.element_size() == W * nbytes and out.is_contiguous() and inp.is_contiguous()
-        reg = self._region("ag", nbytes)
-        self._ag_epoch += 1
-        e = self._ag_epoch
-        if e > 1:
-            reg.wait(self.SLOT_AG_DONE, e - 1)          # peers finished reading the previous payload
-        reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
-        reg.signal(self.SLOT_AG_READY, e)
-        key = ("ag", out.data_ptr(), nbytes)
+        reg, e = self._publish(inp, nbytes, nbytes)
+        key = ("ag", id(reg), out.data_ptr(), nbytes)
         descs = self._desc_cache.get(key)
         if descs is None:
             segs = [(reg.peer_payload_addr(r), out.data_ptr() + r * nbytes, nbytes) for r in range(W)]
@@ -244,15 +336,26 @@ class SymmComm(Comm):
         copy-out pass exist."""
         W = self.world_size
         nbytes = inp.numel() * inp.element_size()
-        reg = self._region("ag", max(nbytes, alloc_bytes))  # same size on every rank
-        self._ag_epoch += 1
-        e = self._ag_epoch
-        if e > 1:
-            reg.wait(self.SLOT_AG_DONE, e - 1)
-        if nbytes:
-            reg.payload[:nbytes].copy_(inp.view(torch.uint8).view(-1))
-        reg.signal(self.SLOT_AG_READY, e)
-        key = ("seg", tuple((r, o, d, n) for r, o, d, n in segments))
+        reg, e = self._publish(inp, nbytes, max(nbytes, alloc_bytes))
+        key = ("seg", id(reg), tuple((r, o, d, n) for r, o, d, n in segments))
+        if self.gather_engine == "dma":
+            arrs = self._desc_cache.get(("dma",) + key)
+            if arrs is None:
+                # rank me reads peer me+1 first, then me+2, ...: the ranks do not all pull from the same peer at
+                # once (the sort is stable, so the caller's order is kept within a peer)
+                ordered = sorted((s for s in segments if s[3] > 0), key=lambda s: (s[0] - self.rank - 1) % W)
+                live = [(reg.peer_payload_addr(r, o), d, n) for r, o, d, n in ordered]
+                k = len(live)
+                arrs = ((ctypes.c_ulonglong * k)(*[a for a, _, _ in live]), (ctypes.c_ulonglong * k)(*[d for _, d, _ in live]),
+                        (ctypes.c_longlong * k)(*[n for _, _, n in live]), k)
+                if len(self._desc_cache) < 4096:
+                    self._desc_cache[("dma",) + key] = arrs
+            reg.wait(self.SLOT_AG_READY, e)               # every peer has published this epoch
+            rc = _lib.load().fsb_comm_copy_segments_dma(arrs[0], arrs[1], arrs[2], arrs[3], _lib.stream_ptr(self.device))
+            _lib.check(rc, "fsb_comm_copy_segments_dma")
+            self.stats["dma_gathers"] += 1
+            reg.signal(self.SLOT_AG_DONE, e)
+            return
         descs = self._desc_cache.get(key)
         if descs is None:
             descs = _pack_descs([(reg.peer_payload_addr(r, o), d, n) for r, o, d, n in segments], self.device)
@@ -335,7 +438,11 @@ class SymmGradRing:
 
     SLOT_WRITTEN0, SLOT_CONSUMED0 = 16, 32
 
-    def __init__(self, group, device, entry_bytes: int, entries: int = 2):
+    def __init__(self, group, device, entry_bytes: int, entries: int | None = None):
+        # Entries in flight: a bucket's backward may not start writing entry k before every peer has
+        # reduced the bucket that used it `entries` buckets earlier. Two is the minimum for overlap; more
+        # keep the compute stream from stalling on a peer whose reduction lags (W x 4 bytes/param each).
+        entries = entries or int(os.environ.get("FSB200_RING_ENTRIES", "3"))
         self.entry_bytes = (entry_bytes + 255) // 256 * 256
         self.entries = entries
         self.region = SymmRegion(group, entries * self.entry_bytes, device)
@@ -366,6 +473,12 @@ class SymmGradRing:
         if self.pull:
             return self.incoming_addr(me, k, dst, row_elems, elem_off)
         return self.incoming_addr(dst, k, me, row_elems, elem_off)
+
+    def mc_read_addr(self, me: int, k: int, row_elems: int) -> int:
+        """Multicast address of the row every rank wrote for ``me`` (pull layout only), or 0."""
+        if not self.pull or not self.region.mc_base:
+            return 0
+        return self.region.mc_payload_addr(k * self.entry_bytes + me * row_elems * 4)
 
     def read_addr(self, me: int, src: int, k: int, row_elems: int) -> int:
         if self.pull:

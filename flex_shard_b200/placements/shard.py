@@ -39,6 +39,7 @@ def _contig(shape):
 
 class Shard(Placement):
     refills_persistent_buffers_in_finish = True
+    uniform_storage = True   # every rank reserves rank-0-sized slots: the bucket's byte size is the same everywhere
 
     def __init__(self, dim: int = 0, grad_bucket: bool = False):
         self.dim = int(dim)

@@ -45,6 +45,43 @@ def _worker(rank, world, port, out):
             res[f"rs{n}_deterministic"] = bool(torch.equal(o1, o3))
         torch.cuda.synchronize()
         ops.check_status()
+        # in-switch reduction: every rank fills row d of its own region with its contribution to rank d;
+        # one multimem load per 16 bytes must return the sum over ranks (compared with the rank-order
+        # peer-load kernel on the same data), twice with the same bits
+        import ctypes
+
+        from flex_shard_b200.ops import _lib
+        from flex_shard_b200.parallel.symm import SymmRegion
+
+        n = 1 << 18
+        mreg = SymmRegion(g, world * n * 4, dev)
+        res["multicast_mapped"] = bool(mreg.mc_base)
+        rows_local = mreg.payload[: world * n * 4].view(torch.float32).view(world, n)
+        rows_local.copy_(torch.randn(world, n, generator=torch.Generator().manual_seed(7 + rank)).to(dev))
+        mreg.signal(5, 1)
+        mreg.wait(5, 1)
+        ref = torch.empty(n, device=dev)
+        rows = (ctypes.c_ulonglong * world)(*[mreg.peer_payload_addr(r, rank * n * 4) for r in range(world)])
+        st_ptr, stream = _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)
+        _lib.check(_lib.load().fsb_comm_reduce_rows(rows, world, n, 0.5, ref.data_ptr(), None, 0, None, None,
+                                                    0.0, 0.0, 0.0, 0.0, 0.0, 1, None, 0, 1000, st_ptr, stream), "reduce")
+        if mreg.mc_base:
+            outs = []
+            for _ in range(2):
+                o = torch.empty(n, device=dev)
+                _lib.check(_lib.load().fsb_comm_reduce_rows_mc(mreg.mc_payload_addr(rank * n * 4), world, n, 0.5,
+                                                               o.data_ptr(), None, 0, None, None, 0.0, 0.0, 0.0, 0.0, 0.0,
+                                                               1, None, 0, 1000, st_ptr, stream), "reduce_mc")
+                outs.append(o)
+            res["mc_close"] = float((outs[0] - ref).abs().max())
+            res["mc_deterministic"] = bool(torch.equal(outs[0], outs[1]))
+            if world == 2:
+                res["mc_bitwise_at_two_ranks"] = bool(torch.equal(outs[0], ref))   # a two-term sum has one order
+        torch.cuda.synchronize()
+        mreg.signal(6, 1)
+        mreg.wait(6, 1)      # nobody frees its region while a peer may still read it
+        torch.cuda.synchronize()
+        ops.check_status()
         # a flag that nothing sets: the wait gives up after its (shortened) limit and reports it
         reg = sc._ag
         reg.max_polls = 2000
@@ -74,7 +111,8 @@ def test_symm_collectives_match_nccl(tmp_path):
     for r in range(world):
         res = torch.load(tmp_path / f"r{r}.pt")
         for k, v in res.items():
-            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive"):
+            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive",
+                                                                         "mc_bitwise_at_two_ranks"):
                 assert v is True, (k, v)
             elif k.endswith("_close"):
                 assert v < 1e-5, (k, v)
@@ -99,7 +137,13 @@ def _train_worker(rank, world, port, out):
         cfg = LlamaConfig(vocab_size=4096, d_model=512, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=1024,
                           max_seq_len=256)
         results = {}
-        for mode in ("nccl", "symm", "symm_fused_adam"):
+        for mode in ("nccl", "symm", "symm_fused_adam", "symm_fused_adam_peer_loads", "symm_fused_adam_staged",
+                     "symm_fused_adam_sm_gather"):
+            # default: buckets resident in symmetric memory and (where mapped) the in-switch reduction;
+            # the last two arms switch one of them off each
+            os.environ["FSB200_MULTIMEM_REDUCE"] = "0" if mode.endswith("peer_loads") else "1"
+            os.environ["FSB200_RESIDENT"] = "0" if mode.endswith("staged") else "1"
+            os.environ["FSB200_GATHER"] = "sm" if mode.endswith("sm_gather") else "dma"
             set_default_backend("symm" if mode.startswith("symm") else "nccl")
             torch.manual_seed(0)
             model = Llama(cfg, dtype=torch.bfloat16, device=dev)
@@ -108,7 +152,7 @@ def _train_worker(rank, world, port, out):
                 p.grad_dtype = torch.float32
             flex_shard(model, llama_buckets(model, mesh=mesh))
             opt = FusedAdamW(model.parameters(), lr=1e-3, weight_decay=0.1)
-            if mode == "symm_fused_adam":
+            if mode.startswith("symm_fused_adam"):
                 opt.fuse_into_backward(model)
             losses = []
             for step in range(4):
@@ -122,6 +166,10 @@ def _train_worker(rank, world, port, out):
             torch.cuda.synchronize()
             ops.check_status()
             results[mode] = losses
+            if mode.startswith("symm"):
+                results[mode + "_stats"] = dict(model.sharded_bucket_storages[1].comm.stats)
+                results[mode + "_mc"] = bool(getattr(model.sharded_bucket_storages[1].comm._grad_ring, "region", None)
+                                             and model.sharded_bucket_storages[1].comm._grad_ring.region.mc_base)
             del model, opt
         dist.barrier()
         torch.save(results, os.path.join(out, f"t{rank}.pt"))
@@ -140,9 +188,21 @@ def test_training_symm_paths_match_nccl(tmp_path):
     mp.spawn(_train_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         res = torch.load(tmp_path / f"t{r}.pt")
-        for mode in ("symm", "symm_fused_adam"):
+        for mode in ("symm", "symm_fused_adam", "symm_fused_adam_peer_loads", "symm_fused_adam_staged",
+                     "symm_fused_adam_sm_gather"):
             for a, b in zip(res[mode], res["nccl"]):
                 assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (mode, res)
+        # at two ranks every sum has one order: the in-switch reduction, the peer-load reduction and the
+        # staged gathers must train to the same bits
+        assert (res["symm_fused_adam"] == res["symm_fused_adam_peer_loads"] == res["symm_fused_adam_staged"]
+                == res["symm_fused_adam_sm_gather"]), res
+        assert res["symm_fused_adam_stats"]["dma_gathers"] > 0 and res["symm_fused_adam_sm_gather_stats"]["dma_gathers"] == 0
+        st = res["symm_fused_adam_stats"]
+        assert st["resident_gathers"] > 0 and st["staged_gathers"] == 0, st
+        assert res["symm_fused_adam_staged_stats"]["resident_gathers"] == 0
+        assert res["symm_fused_adam_peer_loads_stats"]["multimem_reduces"] == 0
+        if res["symm_fused_adam_mc"]:
+            assert st["multimem_reduces"] > 0 and st["peer_reduces"] == 0, st
 
 
 def _muon_worker(rank, world, port, out):
