@@ -35,8 +35,12 @@ def store_on_owners(model) -> None:
 
 
 def build_muon(model, lr: float, weight_decay: float, adamw_lr: float | None = None):
-    muon = build_local_dist_muon(model, is_muon_param=is_muon_param, lr=lr, weight_decay=weight_decay,
-                                 adjust_lr_fn="match_rms_adamw")
+    """Muon over every matrix (per head for the attention up-projections, per expert for routed experts,
+    whole otherwise) + AdamW for the rest. The per-head split needs the model's config (``model.cfg``)."""
+    cfg = getattr(model, "cfg", None)
+    heads = kimi_block_rows(cfg) if cfg is not None and hasattr(cfg, "qk_nope_dim") else None
+    muon = build_local_dist_muon(model, is_muon_param=is_muon_param, block_rows_by_fqn=heads, lr=lr,
+                                 weight_decay=weight_decay, adjust_lr_fn="match_rms_adamw")
     rest = [p for n, p in model.named_parameters() if not is_muon_param(n, p)]
     adam = FusedAdamW(rest, lr=adamw_lr or lr, betas=(0.9, 0.95), weight_decay=weight_decay)
     return muon, adam

@@ -25,6 +25,7 @@ from muon import build_muon, store_on_owners  # noqa: E402
 
 from flex_shard_b200 import (checkpoint, flex_shard, register_optimizer_checkpoint_hook,  # noqa: E402
                              set_state_dict_global_layouts)
+from flex_shard_b200.dist_muon import load_muon_checkpoint_state, muon_checkpoint_state  # noqa: E402
 from flex_shard_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config, deepseek_buckets  # noqa: E402
 from flex_shard_b200.optim.adamw import FusedAdamW  # noqa: E402
 from flex_shard_b200.parallel.expert_parallel import apply_expert_parallel  # noqa: E402
@@ -109,8 +110,11 @@ def main():
     def state():
         sd = model.state_dict()
         set_state_dict_global_layouts(model, sd)
-        return {"model": sd, "adam": adam.state_dict(), "data": data.state_dict(),
-                "sched": [s.state_dict() for s in scheds]}
+        out = {"model": sd, "adam": adam.state_dict(), "data": data.state_dict(),
+               "sched": [s.state_dict() for s in scheds]}
+        if args.optimizer == "muon":    # momentum buffers, tagged with their parameters' layouts
+            out["muon"] = muon_checkpoint_state(muon, model)
+        return out
 
     start = 0
     if args.checkpoint_dir and os.path.isdir(args.checkpoint_dir) and os.listdir(args.checkpoint_dir):
@@ -129,6 +133,8 @@ def main():
         checkpoint.load(sd, os.path.join(args.checkpoint_dir, last))
         model.load_state_dict(sd["model"])
         adam.load_state_dict(sd["adam"])
+        if args.optimizer == "muon":
+            load_muon_checkpoint_state(muon, sd["muon"])
         data.load_state_dict(sd["data"])
         for s_, ssd in zip(scheds, sd["sched"]):
             s_.load_state_dict(ssd)

@@ -41,9 +41,6 @@ def _in_backward() -> bool:
     return torch._C._current_graph_task_id() != -1
 
 
-_FSDP2_POST_ACCUMULATES: bool | None = None
-
-
 class BucketCommContext:
     """State shared by the buckets of one root module."""
 
@@ -305,17 +302,9 @@ class BucketRuntime:
         ``to_accumulated_grad_if_needed``), which ``fsdp2_compatible`` buckets must reproduce bit for
         bit: every backward sums in the compute dtype, a kept gradient is widened to the reduce dtype
         after the backward, and the next backward's gradient is added to it when that backward ends."""
-        if not self.storage.spec.fsdp2_compatible:
-            return False
-        global _FSDP2_POST_ACCUMULATES
-        if _FSDP2_POST_ACCUMULATES is None:
-            try:
-                from torch.distributed.fsdp._fully_shard._fsdp_param import FSDPParam
+        from .bucket_storage import installed_fsdp2_accumulates_after_backward
 
-                _FSDP2_POST_ACCUMULATES = hasattr(FSDPParam, "to_accumulated_grad_if_needed")
-            except Exception:
-                _FSDP2_POST_ACCUMULATES = False
-        return _FSDP2_POST_ACCUMULATES
+        return self.storage.spec.fsdp2_compatible and installed_fsdp2_accumulates_after_backward()
 
     def _wide_grad_params(self):
         """(info, gathered parameter, wide dtype) for parameters whose gradient accumulates in a dtype

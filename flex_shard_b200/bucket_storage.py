@@ -136,13 +136,9 @@ class ParamInfo:
     def unsharded_grad_dtype(self) -> torch.dtype:
         """Dtype in which the gathered parameter's gradient accumulates across backward passes: the
         policy's reduce dtype, else an explicit ``grad_dtype`` set on the parameter before sharding,
-        else the compute dtype (parity: ``flex_shard/bucket_storage.py:325-334`` of the reference,
-        with the compute dtype as the last resort, as the installed FSDP2 reduces in it)."""
-        if self.explicit_reduce_dtype:
-            return self.reduce_dtype
-        if self.grad_dtype is not None:
-            return self.grad_dtype
-        return self.param_dtype
+        else the storage dtype (parity: ``flex_shard/bucket_storage.py:325-334`` of the reference); it is
+        what ``reduce_dtype`` resolves to when the bucket is built."""
+        return self.reduce_dtype
 
     @property
     def local_numel(self) -> int:
@@ -173,6 +169,25 @@ _USER_ATTR_SKIP = {"grad", "data", "requires_grad", "_grad", "grad_fn", "_backwa
 def _user_attrs(p: torch.Tensor) -> dict:
     d = getattr(p, "__dict__", {})
     return {k: v for k, v in d.items() if k not in _USER_ATTR_SKIP and not k.startswith("_fsb_")}
+
+
+_OLD_FSDP2: bool | None = None
+
+
+def installed_fsdp2_accumulates_after_backward() -> bool:
+    """True for torch releases whose FSDP2 sums every backward's gradients in the compute dtype, widens a
+    kept gradient to the reduce dtype after the backward (``FSDPParam.to_accumulated_grad_if_needed``) and
+    reduces in the compute dtype when the policy names no reduce dtype.  ``fsdp2_compatible`` buckets follow
+    the installed FSDP2, whichever it is; other buckets accumulate and reduce in the storage dtype."""
+    global _OLD_FSDP2
+    if _OLD_FSDP2 is None:
+        try:
+            from torch.distributed.fsdp._fully_shard._fsdp_param import FSDPParam
+
+            _OLD_FSDP2 = hasattr(FSDPParam, "to_accumulated_grad_if_needed")
+        except Exception:
+            _OLD_FSDP2 = False
+    return _OLD_FSDP2
 
 
 # --------------------------------------------------------------------------- storage
@@ -349,10 +364,19 @@ def create_param_infos(spec: BucketSpec, named_params: list[tuple[str, nn.Parame
         gshape = tuple(p.shape)
         storage_dtype = p.dtype
         param_dtype = mp.compute_dtype_for(fqn, storage_dtype)
-        reduce_dtype = mp.reduce_dtype if mp.reduce_dtype is not None else param_dtype
         grad_dtype = getattr(p, "grad_dtype", None)
         if grad_dtype == storage_dtype:
             grad_dtype = None  # only an explicit override (e.g. fp32 grads on bf16 shards) is recorded
+        if mp.reduce_dtype is not None:
+            reduce_dtype = mp.reduce_dtype
+        elif spec.fsdp2_compatible and installed_fsdp2_accumulates_after_backward():
+            reduce_dtype = param_dtype     # what the installed FSDP2 reduces in without a reduce dtype
+        else:
+            # gradients of the gathered parameter accumulate, and are reduced, in the dtype of the sharded
+            # .grad: an explicit grad_dtype, else the storage (master) dtype
+            wide = grad_dtype or storage_dtype
+            reduce_dtype = wide if (wide.is_floating_point and param_dtype.is_floating_point
+                                    and wide.itemsize >= param_dtype.itemsize) else param_dtype
         if bucket_layout is not None:
             bl: BucketParamStorageLayout = bucket_layout.param_layouts[fqn]
             local_shape, local_stride = bl.local_shape, bl.local_stride

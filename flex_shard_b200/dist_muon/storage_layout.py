@@ -26,6 +26,17 @@ def _unwrap(pl):
     return pl.member if isinstance(pl, MixedBucketPlacement) else pl
 
 
+def _block_rows(table: Mapping[str, int] | None, fqn: str) -> int | None:
+    """Rows of one orthogonalisation block for ``fqn``: keys are full names, fnmatch patterns, or the last
+    component of the name (``"wq_b"`` matches ``"layers.3.attn.wq_b"``)."""
+    import fnmatch
+
+    for key, rows in (table or {}).items():
+        if fqn == key or fqn.endswith("." + key) or fnmatch.fnmatchcase(fqn, key):
+            return int(rows)
+    return None
+
+
 def get_flex_shard_muon_compute_layouts(module: nn.Module,
                                         block_rows_by_fqn: Mapping[str, int] | None = None
                                         ) -> dict[str, LocalMuonComputeLayout]:
@@ -40,20 +51,24 @@ def get_flex_shard_muon_compute_layouts(module: nn.Module,
         for info in st.infos:
             pl = _unwrap(info.placement)
             gshape = tuple(info.global_shape)
-            if W == 1:
-                # a one-rank mesh stores every parameter whole, whatever the placement
-                out[info.fqn] = LocalMuonComputeLayout("matrix_batch" if len(gshape) == 3 else "owned",
-                                                       global_shape=gshape)
-            elif isinstance(pl, BucketedOwned):
-                if pl.view_kind == "expert_block" and len(gshape) == 3:
+            head_rows = _block_rows(block_rows_by_fqn, info.fqn) if len(gshape) == 2 else None
+            if head_rows is not None and gshape[0] % head_rows != 0:
+                raise ValueError(f"{info.fqn!r}: {gshape[0]} rows are not whole blocks of {head_rows}")
+            if W == 1 or isinstance(pl, BucketedOwned):
+                # whole on this rank (a one-rank mesh stores every parameter whole, whatever the placement;
+                # an owner holds all rows, everyone else none)
+                if len(gshape) == 3 and (W == 1 or pl.view_kind == "expert_block"):
                     out[info.fqn] = LocalMuonComputeLayout("matrix_batch", global_shape=gshape)
+                elif head_rows is not None:      # per-head orthogonalisation of a matrix stored whole
+                    out[info.fqn] = LocalMuonComputeLayout(
+                        "row_blocks", block_rows=(head_rows,) * (info.local_shape[0] // head_rows), global_shape=gshape)
                 else:
                     out[info.fqn] = LocalMuonComputeLayout("owned", global_shape=gshape)
             elif isinstance(pl, BlockShard) and pl.dim == 0:
                 if len(gshape) == 3:
                     out[info.fqn] = LocalMuonComputeLayout("matrix_batch", global_shape=gshape)
                 else:
-                    rows = (block_rows_by_fqn or {}).get(info.fqn, pl.block_size(gshape))
+                    rows = head_rows or pl.block_size(gshape)
                     n_local = info.local_shape[0] // rows if rows else 0
                     out[info.fqn] = LocalMuonComputeLayout("row_blocks", block_rows=(rows,) * n_local,
                                                            global_shape=gshape)

@@ -1,0 +1,41 @@
+"""The DeepSeek-V3 example end to end on two gloo ranks (``--small``): a run interrupted by a checkpoint and
+resumed prints the same losses as the uninterrupted run, for AdamW and for Muon (whose momentum buffers are
+part of the checkpoint).  Behaviour restated from ``src/flex_shard/tests/test_example_deepseek_v3.py:448-503``."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import pytest
+
+from tests.common import free_port
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(ckpt_dir, extra):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "examples", "deepseek_v3", "train.py"),
+           "--small", "--steps", "4", "--seq-len", "32", "--local-batch-size", "2", "--ep", "2", "--checkpoint-dir",
+           ckpt_dir, "--checkpoint-interval", "2", *extra]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
+    recs = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{") and '"step"' in l]
+    return {r["step"]: r for r in recs}
+
+
+@pytest.mark.parametrize("optimizer", ["adamw", "muon"])
+def test_resume_equals_uninterrupted_run(tmp_path, optimizer):
+    full_dir, part_dir = str(tmp_path / "full"), str(tmp_path / "part")
+    full = _run(full_dir, ["--optimizer", optimizer])
+    assert sorted(full) == [0, 1, 2, 3]
+    os.makedirs(part_dir)
+    shutil.copytree(os.path.join(full_dir, "step00000002"), os.path.join(part_dir, "step00000002"))
+    resumed = _run(part_dir, ["--optimizer", optimizer])
+    assert sorted(resumed) == [2, 3], resumed
+    for s in (2, 3):
+        assert resumed[s]["loss"] == full[s]["loss"], (s, resumed[s], full[s])
+        assert resumed[s]["grad_norm"] == full[s]["grad_norm"]
+        assert resumed[s]["lr"] == full[s]["lr"]
