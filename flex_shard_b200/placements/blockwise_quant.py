@@ -27,6 +27,7 @@ from typing import Callable, Sequence
 import torch
 
 from ..placement_contract import PlacementPreparedUnshard, PlacementUnshardResult
+from ..ops.segments import run_segment_ops
 from ..utils.profiling import record
 from .sliced import Piece, SlicedPlacement
 
@@ -191,6 +192,7 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
         infos, W = prepared.infos, comm.world_size
         recv = prepared.recv
         outs = []
+        copies = []
         with record("FlexShard::copy_out"):
             for i, (info, buf) in enumerate(zip(infos, persistent)):
                 pl = info.placement
@@ -208,9 +210,14 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
                     _, rows, qo, qb, so, sb = item
                     q_at = pl.qdata_nbytes(a, cols)
                     s_at = pl.scale_nbytes(a, cols)  # whole blocks precede row a
-                    qdst[q_at:q_at + qb].copy_(recv[r, qo:qo + qb])
-                    sdst[s_at:s_at + sb].copy_(recv[r, so:so + sb])
-                outs.append(pl.make_weight(qdst, sdst, info.global_shape, info.param_dtype))
+                    copies.append((qdst[q_at:q_at + qb], recv[r, qo:qo + qb]))
+                    copies.append((sdst[s_at:s_at + sb], recv[r, so:so + sb]))
+                outs.append((pl, qdst, sdst, info))
+            # compaction: every rank's payload and scale bytes of every weight land in the persistent
+            # compact buffer with one segment-copy launch; the weight wrappers (which may derive further
+            # scale tensors from the gathered bytes) are built afterwards
+            run_segment_ops(copies)
+            outs = [pl.make_weight(q, sc, info.global_shape, info.param_dtype) for pl, q, sc, info in outs]
         if not prepared.extra.get("cached") and "key" in prepared.extra:
             self._payload_cache = (prepared.extra["key"], recv)
         return PlacementUnshardResult(outs, keepalive=[])

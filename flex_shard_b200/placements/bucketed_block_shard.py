@@ -32,6 +32,7 @@ from ..placement_contract import (
     PlacementReduceGradResult,
     PlacementUnshardResult,
 )
+from ..ops.segments import run_segment_ops
 from ..utils.profiling import record
 from .sliced import contig_stride
 
@@ -241,7 +242,24 @@ class BucketedBlockShard(Placement):
         with record("FlexShard::reduce_scatter_copy_in"):
             if in_place and base is not None and len(infos) == len(plan.shapes):
                 send = base
+            elif all(g.dtype == reduce_dtype or {g.dtype, reduce_dtype} == {torch.float32, torch.bfloat16} for g in grads):
+                # path (b): one pass writes every gradient (cast to the reduce dtype) and zeroes the gaps
+                # between parameters and the padded tail; copies and zero-fills touch disjoint bytes, so they
+                # share one launch
+                send = torch.empty(plan.padded_total, dtype=reduce_dtype, device=grads[0].device)
+                spans = sorted((plan.param_off[info.bucket_layout["index"]], info.global_numel, g, info)
+                               for info, g in zip(infos, grads))
+                ops, pos = [], 0
+                for off, n, g, info in spans:
+                    if off > pos:
+                        ops.append((send[pos:off], None))
+                    ops.append((send[off:off + n].view(info.global_shape), g))
+                    pos = off + n
+                if pos < plan.padded_total:
+                    ops.append((send[pos:], None))
+                run_segment_ops(ops)
             else:
+                # path (c): zero the bucket, then copy parameter by parameter
                 send = torch.zeros(plan.padded_total, dtype=reduce_dtype, device=grads[0].device)
                 for info, g in zip(infos, grads):
                     i = info.bucket_layout["index"]

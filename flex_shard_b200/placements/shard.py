@@ -27,6 +27,7 @@ from ..placement_contract import (
 )
 from ..parallel.comm import plan_reduction
 from ..utils.profiling import record
+from .sliced import _copy_or_loop
 
 
 def _contig(shape):
@@ -144,9 +145,9 @@ class Shard(Placement):
                 send = byte_storage
             else:
                 send = torch.zeros(row_bytes, dtype=torch.uint8, device=byte_storage.device)
-                for info, (o, n) in zip(infos, offs):
-                    src = info.placement.make_local_storage_view(info, byte_storage)
-                    send[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype).copy_(src.reshape(-1))
+                _copy_or_loop([(send[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype),
+                                info.placement.make_local_storage_view(info, byte_storage).reshape(-1))
+                               for info, (o, n) in zip(infos, offs)])
         prep.send = send
         segs = []
         for info, (o, n), buf in zip(infos, offs, persistent):
@@ -182,10 +183,9 @@ class Shard(Placement):
                 prep.recv = torch.empty(W * row_bytes, dtype=torch.uint8, device=byte_storage.device)
                 row = prep.recv[comm.rank * row_bytes:(comm.rank + 1) * row_bytes]
                 row.zero_()
-                for info, (o, n) in zip(infos, offs):
-                    src = info.placement.make_local_storage_view(info, byte_storage)
-                    dst = row[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype)
-                    dst.copy_(src.reshape(-1))
+                _copy_or_loop([(row[o:o + info.local_numel * info.param_dtype.itemsize].view(info.param_dtype),
+                                info.placement.make_local_storage_view(info, byte_storage).reshape(-1))
+                               for info, (o, n) in zip(infos, offs)])
                 prep.send = row  # in-place all-gather: the send row aliases the gather buffer
         return prep
 
@@ -215,12 +215,14 @@ class Shard(Placement):
                 storage = prepared.extra["storage"]
                 outs = [info.placement.make_local_storage_view(info, storage) for info in infos]
                 return PlacementUnshardResult(outs)
+            copies = []
             if W == 1:
                 storage = prepared.extra["storage"]
                 for info, buf in zip(infos, persistent):
                     src = info.placement.make_local_storage_view(info, storage)
-                    buf[: info.global_numel].view(info.global_shape).copy_(src)
+                    copies.append((buf[: info.global_numel].view(info.global_shape), src))
                     outs.append(buf[: info.global_numel].view(info.global_shape))
+                _copy_or_loop(copies)
                 return PlacementUnshardResult(outs)
             row_bytes = prepared.extra["row_bytes"]
             recv = prepared.recv.view(W, row_bytes)
@@ -229,15 +231,16 @@ class Shard(Placement):
                 padded = pl.padded_numel(info.global_shape, W)
                 src = recv[:, o:o + n].view(info.param_dtype)  # [W, padded] (row-strided)
                 if pl.dim == 0:
-                    buf.view(W, padded).copy_(src)
+                    copies.append((buf.view(W, padded), src))
                     outs.append(buf[: info.global_numel].view(info.global_shape))
                 else:
                     full = buf[: info.global_numel].view(info.global_shape)
                     ps = pl.padded_shape(info.global_shape, W)
                     c = ps[pl.dim]
                     for r in range(W):
-                        full.narrow(pl.dim, r * c, c).copy_(src[r].view(ps))
+                        copies.append((full.narrow(pl.dim, r * c, c), src[r].view(ps)))
                     outs.append(full)
+            _copy_or_loop(copies)   # the whole bucket's copy-out (every rank's chunk of every parameter): one launch
         return PlacementUnshardResult(outs, keepalive=[prepared.recv])
 
     # ------------------------------------------------------------------ gradient reduction
@@ -365,6 +368,7 @@ class Shard(Placement):
             else:
                 alloc = torch.zeros if needs_zero else torch.empty
                 send = alloc(W, row, dtype=reduce_dtype, device=grads[0].device)
+            copies = []
             for info, g, (o, n) in zip(infos, grads, offs):
                 if bucket is not None and getattr(g, "_fsb_bucket", None) is bucket:
                     continue  # already written in place by the weight-gradient kernel
@@ -377,15 +381,16 @@ class Shard(Placement):
                     full_ranks = flat.numel() // n if n > 0 else 0
                     full_ranks = min(full_ranks, W)
                     if full_ranks:
-                        dst[:full_ranks].copy_(flat[: full_ranks * n].view(full_ranks, n))
+                        copies.append((dst[:full_ranks], flat[: full_ranks * n].view(full_ranks, n)))
                     rem = flat.numel() - full_ranks * n
                     if rem > 0:
-                        dst[full_ranks, :rem].copy_(flat[full_ranks * n:])
+                        copies.append((dst[full_ranks, :rem], flat[full_ranks * n:]))
                 else:
                     ps = pl.padded_shape(info.global_shape, W)
                     c = ps[pl.dim]
                     for r in range(W):
-                        dst[r].view(ps).copy_(g.narrow(pl.dim, r * c, c))
+                        copies.append((dst[r].view(ps), g.narrow(pl.dim, r * c, c)))
+            _copy_or_loop(copies)   # pack (and cast to the reduce dtype) every gradient of the bucket in one launch
         prep = PlacementPreparedReduceGrad(infos=infos, send=send, reduce_dtype=reduce_dtype)
         prep.extra["offs"] = offs
         prep.extra["row"] = row

@@ -38,6 +38,7 @@ from ..placement_contract import (
     PlacementReduceGradResult,
     PlacementUnshardResult,
 )
+from ..ops.segments import run_segment_ops
 from ..utils.profiling import record
 
 ALIGN = 16  # bytes; every slot starts on a 16-byte boundary
@@ -193,6 +194,16 @@ def plan_rows(infos, world_size: int, itemsize_of) -> RowPlan:
 
 
 # --------------------------------------------------------------------------- gather
+def _copy_or_loop(copies) -> None:
+    """One segment launch when every pair is a supported (same dtype, fp32<->bf16) copy, else plain copies."""
+    ok = all(d.dtype == s.dtype or {d.dtype, s.dtype} == {torch.float32, torch.bfloat16} for d, s in copies)
+    if ok:
+        run_segment_ops(copies)
+    else:
+        for d, s in copies:
+            d.copy_(s)
+
+
 def _local_flat(info, byte_storage):
     return info.placement.make_local_storage_view(info, byte_storage).reshape(-1)
 
@@ -220,12 +231,14 @@ def prepare_unshard(infos, byte_storage, comm, persistent) -> PlacementPreparedU
             needs_zero = True
             if needs_zero:
                 send.zero_()
+        copies = []
         for i, info in enumerate(infos):
             n = plan.sizes[i][rank]
             if n == 0:
                 continue
             o = plan.offsets[i][rank]
-            send[o:o + n].view(info.param_dtype).copy_(_local_flat(info, byte_storage))
+            copies.append((send[o:o + n].view(info.param_dtype), _local_flat(info, byte_storage)))
+        _copy_or_loop(copies)       # one launch for the whole bucket (casting where the compute dtype differs)
         prep.send = send
     return prep
 
@@ -252,6 +265,7 @@ def finish_unshard(prepared, comm, persistent) -> PlacementUnshardResult:
         prepared.work.wait()
         prepared.work = None
     outs = []
+    copies = []
     with record("FlexShard::copy_out"):
         for i, (info, buf) in enumerate(zip(infos, persistent)):
             full = buf[: info.global_numel].view(info.global_shape)
@@ -260,7 +274,7 @@ def finish_unshard(prepared, comm, persistent) -> PlacementUnshardResult:
                 if n == 0:
                     continue
                 if W == 1:
-                    src = _local_flat(info, prepared.extra["storage"]).to(info.param_dtype)
+                    src = _local_flat(info, prepared.extra["storage"])
                 else:
                     o = plan.offsets[i][r]
                     rows = prepared.extra.get("rows")
@@ -271,9 +285,10 @@ def finish_unshard(prepared, comm, persistent) -> PlacementUnshardResult:
                     if p.length == 0:
                         continue
                     m = p.numel(info.global_shape)
-                    full.narrow(p.dim, p.start, p.length).copy_(src[pos:pos + m].view(p.shape(info.global_shape)))
+                    copies.append((full.narrow(p.dim, p.start, p.length), src[pos:pos + m].view(p.shape(info.global_shape))))
                     pos += m
             outs.append(full)
+        _copy_or_loop(copies)       # every rank's piece of every parameter in one launch
     keep = [prepared.recv] if prepared.recv is not None else list(prepared.extra.get("rows") or [])
     return PlacementUnshardResult(outs, keepalive=keep)
 
@@ -290,6 +305,7 @@ def prepare_reduce(infos, grads, comm, reduce_dtype) -> PlacementPreparedReduceG
         else:
             flat = torch.zeros(W * plan.row, dtype=reduce_dtype, device=dev)
             rows = [flat[r * plan.row:(r + 1) * plan.row] for r in range(W)]
+        copies = []
         for i, (info, g) in enumerate(zip(infos, grads)):
             for r in range(W):
                 n = plan.sizes[i][r]
@@ -301,9 +317,10 @@ def prepare_reduce(infos, grads, comm, reduce_dtype) -> PlacementPreparedReduceG
                     if p.length == 0:
                         continue
                     m = p.numel(info.global_shape)
-                    rows[r][o + pos:o + pos + m].view(p.shape(info.global_shape)).copy_(
-                        g.narrow(p.dim, p.start, p.length))
+                    copies.append((rows[r][o + pos:o + pos + m].view(p.shape(info.global_shape)),
+                                   g.narrow(p.dim, p.start, p.length)))
                     pos += m
+        _copy_or_loop(copies)
     prep = PlacementPreparedReduceGrad(infos=infos, send=None if uneven else flat, reduce_dtype=reduce_dtype)
     prep.extra["plan"] = plan
     prep.extra["rows"] = rows
