@@ -34,6 +34,7 @@ from .bucket_comm import (
     begin_reduce_grad,
 )
 from .bucket_storage import ShardedBucketStorage
+from .utils.checkpointing import outside_selective_checkpoint
 from .utils.profiling import record
 
 
@@ -486,6 +487,7 @@ class BucketRuntime:
             nxt.begin_unshard(prefetch=True)
 
     # ------------------------------------------------------------------ hooks
+    @outside_selective_checkpoint
     def pre_forward(self, module, args, kwargs):
         ctx = self.context
         ctx.check_not_poisoned()
@@ -509,6 +511,7 @@ class BucketRuntime:
                 args, kwargs = tree_unflatten(flat, spec)
         return args, kwargs
 
+    @outside_selective_checkpoint
     def post_forward(self, module, args, output):
         ctx = self.context
         in_bwd = _in_backward()
@@ -537,6 +540,7 @@ class BucketRuntime:
 
         return hook
 
+    @outside_selective_checkpoint
     def pre_backward(self) -> None:
         ctx = self.context
         ctx.queue_final_callback()
