@@ -52,9 +52,15 @@ class BucketCommContext:
             # high priority so collectives are not starved by queued compute kernels
             self.unshard_stream = torch.cuda.Stream(device=device, priority=-1)
             self.reduce_stream = torch.cuda.Stream(device=device, priority=-1)
+            # third stream: where a retired reduction's buffers are handed back (it waits for the reduction,
+            # then the buffers' allocation stream is ordered behind it), so the hand-back is not queued
+            # behind unrelated work of either other stream
+            self.release_stream = torch.cuda.Stream(device=device, priority=-1)
         else:
             self.unshard_stream = None
             self.reduce_stream = None
+            self.release_stream = None
+        self.retired_reduces: list[PendingReduce] = []
         self.runtimes: list["BucketRuntime"] = []
         self.forward_order: list["BucketRuntime"] = []
         self.post_forward_order: list["BucketRuntime"] = []
@@ -124,14 +130,36 @@ class BucketCommContext:
 
     # ------------------------------------------------------------------ reductions
     def drain_reduces(self, keep: int = 0) -> None:
-        """Wait for (all but ``keep``) pending reductions on the current stream and release
-        their send buffers."""
+        """Retire pending reductions until at most ``keep`` are left; with ``keep == 0`` (end of backward,
+        ``finalize_backward().wait()``) also make the current stream wait for every retired one, so the
+        optimizer sees the reduced gradients.
+
+        A reduction that holds a packed send buffer is retired by ordering the buffer's allocation stream
+        behind it before the buffer is dropped: with ``max_pending_reduce_grads = 1`` the next bucket's
+        send buffer reuses the block, which bounds memory like FSDP2 does.  A reduction without buffers
+        (gradients were written straight into the peers' symmetric memory) has nothing to hand back and is
+        retired without making the compute stream wait for it."""
         while len(self.pending_reduces) > keep:
             st = self.pending_reduces.pop(0)
-            if st.event is not None:
+            buffers = [t for t in st.keep if isinstance(t, torch.Tensor)]
+            if st.event is not None and (buffers or keep == 0):
+                with record("FlexShard::post_backward_reduce_grad_retire" if keep else
+                            "FlexShard::post_backward_reduce_grad_wait"):
+                    if keep and self.release_stream is not None:
+                        alloc_stream = torch.cuda.current_stream()
+                        with torch.cuda.stream(self.release_stream):
+                            self.release_stream.wait_event(st.event)
+                            StreamHandoff.release_after_current_stream(st.keep, alloc_stream)
+                    else:
+                        self.wait_comm_event(st.event)
+            elif st.event is not None:
+                self.retired_reduces.append(st)
+            st.keep.clear()
+        if keep == 0:
+            for st in self.retired_reduces:
                 with record("FlexShard::post_backward_reduce_grad_wait"):
                     self.wait_comm_event(st.event)
-            st.keep.clear()
+            self.retired_reduces.clear()
 
     # ------------------------------------------------------------------ end of backward
     def queue_final_callback(self) -> None:
@@ -185,7 +213,7 @@ class BucketCommContext:
                 "the runtime state is not recoverable.")
 
     def idle(self) -> bool:
-        return (not self.pending_reduces and not self.backward_running
+        return (not self.pending_reduces and not self.retired_reduces and not self.backward_running
                 and all(rt.pending is None for rt in self.runtimes))
 
 

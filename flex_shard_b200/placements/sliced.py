@@ -164,15 +164,18 @@ class RowPlan:
     owner_only: bool
 
 
-def plan_rows(infos, world_size: int, itemsize_of) -> RowPlan:
-    """``itemsize_of(info)`` = bytes per element (gather rows) or 1 (reduce rows counted in elements)."""
+def plan_rows(infos, world_size: int, itemsize_of, align: int | None = None) -> RowPlan:
+    """``itemsize_of(info)`` = bytes per element (gather rows) or 1 (reduce rows counted in elements).
+    Every slot starts on a multiple of ``align`` units (default: 16 bytes for gather rows, 4 elements for
+    reduce rows, so that packing and reduction kernels can use 16-byte accesses; ``align=1`` gives the
+    reference's unpadded rows, ``custom_placements/mixed_bucket.py:1603-1657``)."""
     n = len(infos)
     sizes = [[0] * world_size for _ in range(n)]
     for i, info in enumerate(infos):
         for r in range(world_size):
             numel = sum(p.numel(info.global_shape) for p in info.placement.pieces(info.global_shape, r, world_size))
             sizes[i][r] = numel * itemsize_of(info)
-    unit_align = ALIGN if any(itemsize_of(i) > 1 for i in infos) else 4
+    unit_align = align if align is not None else (ALIGN if any(itemsize_of(i) > 1 for i in infos) else 4)
     owner_idx = [i for i, info in enumerate(infos) if getattr(info.placement, "owner_style", False)]
     regular_idx = [i for i in range(n) if i not in owner_idx]
     offsets: list[list[int | None]] = [[None] * world_size for _ in range(n)]
