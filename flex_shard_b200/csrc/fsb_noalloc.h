@@ -31,8 +31,10 @@ extern "C" {
 
 // dy, x, dx: bf16 [T, D]; w: bf16 [D]; rstd: fp32 [T]; dres: optional bf16 [T, D] added to dx
 // (may be null); dw_out: [D], fp32 when dw_fp32 != 0 else bf16; dw_accumulate != 0 adds to dw_out.
-// Returns 0 on success, 1 for a bad argument, 3 for a failed launch or address lookup, 64 when the
-// problem exceeds the built-in scratch array.
+// Returns 0 on success; 1 for a bad argument (shape outside the limits above, a null required pointer, or
+// a pointer that is not aligned as the kernels read it: 16 bytes for dy / x / w / dx / dres, element size
+// for rstd and dw_out); 3 for a failed launch or address lookup; 64 when the problem exceeds the built-in
+// scratch array (checked before the pointers, so a size can be probed with null pointers).
 int fsb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
                             const void* dres, void* dx, void* dw_out, int dw_fp32, int dw_accumulate,
                             long long T, int D, cudaStream_t stream);

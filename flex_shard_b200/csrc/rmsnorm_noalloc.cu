@@ -53,8 +53,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-// Same arithmetic, in the same order, as rmsnorm_bwd_kernel of elementwise.cu: one CTA per 32 rows,
-// one fp32 partial row per CTA written to `partial` (here: the built-in array).
+// One CTA per 32 rows: per row dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) with xhat = x*rstd, and the
+// CTA's sum of dy*xhat over its rows goes to one fp32 row of `partial` (here: the built-in array). The
+// ordinary entry point computes the same quantities with a different thread layout, so the two agree to
+// rounding, not bit for bit.
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_bwd_noalloc_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                            const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -147,6 +149,14 @@ fsb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const floa
             T, D, blocks * D, kScratchFloats);
     return FSB_ERR_TOO_LARGE;
   }
+  // the kernels use 16-byte accesses on the bf16 tensors and element accesses on rstd / dw_out: a null or
+  // misaligned pointer is refused here instead of faulting on the device
+  const auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr || dw_out == nullptr)
+    return FSB_ERR_BAD_ARG;
+  if (misaligned(dy, 16) || misaligned(x, 16) || misaligned(w, 16) || misaligned(dx, 16) ||
+      (dres != nullptr && misaligned(dres, 16)) || misaligned(rstd, 4) || misaligned(dw_out, dw_fp32 ? 4 : 2))
+    return FSB_ERR_BAD_ARG;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FSB_ERR_LAUNCH;
   if (g_scratch_addr[dev] == nullptr) {
@@ -165,6 +175,7 @@ fsb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const floa
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
       static_cast<__nv_bfloat16*>(dx), scratch, T, D);
+  if (cudaGetLastError() != cudaSuccess) return FSB_ERR_LAUNCH;   // the second launch would read an unwritten array
   colsum_noalloc_kernel<<<(D + 255) / 256, 256, 0, stream>>>(scratch, dw_out, static_cast<int>(blocks), D,
                                                               dw_fp32, dw_accumulate);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;

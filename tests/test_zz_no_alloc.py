@@ -54,13 +54,27 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice():
         # allocation-free entry point: outputs provided by the caller, nothing else
         dx = torch.empty_like(x)
         dw = torch.empty(D, device="cuda", dtype=torch.float32)
+        # the plain-PyTorch fp32 formula, evaluated before the memory measurement
+        xf, dyf, wf, r = x.float(), dy.float(), w.float(), rstd.unsqueeze(-1)
+        xhat = xf * r
+        dyw = dyf * wf
+        dx_formula = r * (dyw - xhat * (dyw * xhat).mean(-1, keepdim=True))
+        dw_formula = (dyf * xhat).sum(0)
+        del xf, dyf, wf, dyw
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        before_torch = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()      # the driver's view: sees allocations the caching allocator does not
         rc = lib.fsb_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None,
                                          dx.data_ptr(), dw.data_ptr(), 1, 0, T, D, stream)
         assert rc == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        free_after, _ = torch.cuda.mem_get_info()
+        assert torch.cuda.memory_allocated() == before_torch
+        if (T, D) != (1000, 1024):       # the very first call on a device may load the kernels' module lazily
+            assert free_after == free_before, (free_before, free_after)
+        # against the fp32 formula (bf16 outputs: one rounding of values of order 1) and the ordinary entry point
+        torch.testing.assert_close(dx.float(), dx_formula, rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(dw, dw_formula, rtol=2e-3, atol=2e-3 * (T ** 0.5))
         torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(dw, dw_ref, rtol=2e-2, atol=2e-2)
 
@@ -73,3 +87,32 @@ def test_noalloc_entry_point_rejects_oversized_problem():
     rc = lib.fsb_rmsnorm_bwd_noalloc(None, None, None, None, None, None, None, 1, 0, T, D,
                                      L.stream_ptr(torch.device("cuda")))
     assert rc == 64
+
+
+def test_noalloc_entry_point_refuses_null_and_misaligned_pointers():
+    lib, L = _lib()
+    stream = L.stream_ptr(torch.device("cuda"))
+    T, D = 64, 256
+    dy, x, w, rstd = _case(T, D, 3)
+    dx = torch.empty_like(x)
+    dw = torch.empty(D, device="cuda", dtype=torch.float32)
+    good = [dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), dw.data_ptr()]
+    assert lib.fsb_rmsnorm_bwd_noalloc(*good, 1, 0, T, D, stream) == 0
+    for i in (0, 1, 2, 3, 5, 6):                      # every required pointer, null
+        args = list(good)
+        args[i] = None
+        assert lib.fsb_rmsnorm_bwd_noalloc(*args, 1, 0, T, D, stream) == 1, i
+    for i in (0, 1, 2, 5):                            # bf16 tensors two bytes off a 16-byte boundary
+        args = list(good)
+        args[i] = good[i] + 2
+        assert lib.fsb_rmsnorm_bwd_noalloc(*args, 1, 0, T, D, stream) == 1, i
+    args = list(good)
+    args[4] = dy.data_ptr() + 2                       # optional residual gradient, misaligned
+    assert lib.fsb_rmsnorm_bwd_noalloc(*args, 1, 0, T, D, stream) == 1
+    args = list(good)
+    args[6] = dw.data_ptr() + 2                       # fp32 output on a 2-byte boundary
+    assert lib.fsb_rmsnorm_bwd_noalloc(*args, 1, 0, T, D, stream) == 1
+    torch.cuda.synchronize()
+    from flex_shard_b200 import ops
+
+    ops.check_status()
