@@ -252,6 +252,13 @@ class ShardedBucketStorage:
     def placement(self) -> Placement:
         return self.infos[0].placement
 
+    @property
+    def debug_fqn(self) -> str | None:
+        """Short name of the bucket for profiler ranges (common module path of its parameters)."""
+        from .utils.profiling import bucket_debug_fqn
+
+        return bucket_debug_fqn([i.fqn for i in self.infos])
+
     def local_view(self, info: ParamInfo) -> torch.Tensor:
         return info.placement.make_local_storage_view(info, self.byte_storage)
 

@@ -209,3 +209,14 @@ def test_yarn_table_and_fp32_output_linear():
     torch.testing.assert_close(y, xr @ wr.t(), rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=1e-1)
+
+
+def test_bucket_debug_names():
+    from flex_shard_b200.utils.profiling import bucket_debug_fqn, strip_wrapper_path
+
+    assert bucket_debug_fqn(["layers.0.attn.wq.weight", "layers.0.mlp.w1.weight"]) == "layers.0"
+    assert bucket_debug_fqn(["layers.0._checkpoint_wrapped_module.attn.w", "layers.0._checkpoint_wrapped_module.mlp.w"]) == "layers.0"
+    assert bucket_debug_fqn(["norm.weight", "lm_head.weight"]) == "lm_head, norm"
+    assert bucket_debug_fqn(["layers.1.a.w", "layers.2.a.w"]) == "layers"
+    assert bucket_debug_fqn([]) is None
+    assert strip_wrapper_path("a._orig_mod.b") == "a.b"
