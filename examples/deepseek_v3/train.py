@@ -51,9 +51,41 @@ def parse():
     ap.add_argument("--checkpoint-dir", default=None)
     ap.add_argument("--checkpoint-interval", type=int, default=0)
     ap.add_argument("--profile-dir", default=None)
+    ap.add_argument("--no-activation-checkpointing", action="store_true",
+                    help="keep every block's activations instead of recomputing the block in backward")
+    ap.add_argument("--init-checkpoint", default=None,
+                    help="checkpoint directory to take the initial weights from (model only; optimizers start fresh)")
+    ap.add_argument("--document-length", type=int, default=0,
+                    help="> 0: synthetic sequences are packed documents of this many tokens; attention stays inside them")
+    ap.add_argument("--aux-loss-coeff", type=float, default=0.0, help="weight of the sequence-wise router balance loss")
+    ap.add_argument("--no-explicit-prefetch", action="store_true",
+                    help="leave prefetching to the learned order instead of block-by-block prefetch lists")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--comm", choices=["nccl", "symm"], default="nccl")
     return ap.parse_args()
+
+
+def prefetch_blocks_in_order(model) -> None:
+    """Explicit prefetch lists: the first bucket of a block (the one that runs first) prefetches every bucket
+    of the next block in forward and of the previous block in backward; expert buckets prefetch nothing.
+    With expert parallelism the learned one-bucket-ahead order would issue the next gathers only after the
+    dispatcher's host-visible step. Parity: ``examples/deepseek_v3/train.py:178-200`` of the reference."""
+    storages = list(model.sharded_bucket_storages)
+    embedding, head = storages[0], storages[-1]
+    blocks: dict[int, list] = {}
+    for st in storages[1:-1]:
+        layer = int(st.infos[0].fqn.split(".")[1])
+        blocks.setdefault(layer, []).append(st)
+    order = [blocks[i] for i in sorted(blocks)]
+    for group in order:
+        for st in group[1:]:
+            st.set_buckets_to_forward_prefetch([])
+            st.set_buckets_to_backward_prefetch([])
+    embedding.set_buckets_to_forward_prefetch(order[0] if order else [head])
+    head.set_buckets_to_backward_prefetch(order[-1] if order else [embedding])
+    for i, group in enumerate(order):
+        group[0].set_buckets_to_forward_prefetch(order[i + 1] if i + 1 < len(order) else [head])
+        group[0].set_buckets_to_backward_prefetch(order[i - 1] if i > 0 else [embedding])
 
 
 def main():
@@ -80,6 +112,8 @@ def main():
         cfg = DeepSeekV3Config(vocab_size=2048, d_model=256, n_layers=3, n_heads=2, q_lora_rank=128, kv_lora_rank=64,
                                qk_nope_dim=64, qk_rope_dim=32, v_dim=64, dense_hidden=512, n_experts=8,
                                expert_hidden=128, top_k=2, max_seq_len=args.seq_len)
+    cfg.activation_checkpointing = not args.no_activation_checkpointing
+    cfg.aux_loss_coeff = args.aux_loss_coeff
     ep = world if args.ep == 0 else args.ep
     model = DeepSeekV3(cfg, dtype=torch.bfloat16 if cuda else torch.float32, device=dev)
     model.init_weights(args.seed)
@@ -93,6 +127,13 @@ def main():
         apply_expert_parallel(model, ep_groups[rank // ep])
         expert_mesh = efsdp_groups[rank % ep]
     flex_shard(model, deepseek_buckets(model, mesh=dp_group, expert_mesh=expert_mesh))
+    if not args.no_explicit_prefetch:
+        prefetch_blocks_in_order(model)
+    if args.init_checkpoint:
+        sd = model.state_dict()
+        set_state_dict_global_layouts(model, sd)
+        checkpoint.load({"model": sd}, args.init_checkpoint)
+        model.load_state_dict(sd)
 
     if args.optimizer == "muon":
         store_on_owners(model)
@@ -106,6 +147,9 @@ def main():
                                                                        args.decay_ratio, args.min_lr_factor))
               for o in opts]
     data = SyntheticBatches(cfg.vocab_size, args.local_batch_size, args.seq_len, args.seed, rank, pin_memory=cuda)
+    positions = None
+    if args.document_length > 0:
+        positions = (torch.arange(args.seq_len, device=dev) % args.document_length).expand(args.local_batch_size, -1)
 
     def state():
         sd = model.state_dict()
@@ -151,7 +195,11 @@ def main():
         ntok = torch.tensor([tok[:, 1:].numel()], dtype=torch.float32, device=dev)
         dist.all_reduce(ntok)
         # sum of token losses divided by the global token count (buckets sum gradients)
-        loss = model.loss(tok[:, :-1], tok[:, 1:], loss_is_root=False) * (tok[:, 1:].numel() / ntok.squeeze())
+        if args.aux_loss_coeff > 0:
+            for moe in model.moe_layers():
+                moe.aux_loss_denominator = float(ntok)
+        loss = model.loss(tok[:, :-1], tok[:, 1:], loss_is_root=False, positions=positions) * (
+            tok[:, 1:].numel() / ntok.squeeze())
         loss.backward()
         gnorm = clip_grad_norm_(model, args.max_norm)
         for m in model.moe_layers():

@@ -52,6 +52,8 @@ class DeepSeekV3Config:
     norm_eps: float = 1e-6
     max_seq_len: int = 4096
     init_std: float = 0.02
+    activation_checkpointing: bool = False   # recompute every block in backward (non-reentrant checkpoint per block)
+    aux_loss_coeff: float = 0.0              # > 0: sequence-wise balance loss on the router scores
 
     @property
     def qk_dim(self) -> int:
@@ -76,7 +78,7 @@ class MLA(nn.Module):
         self.wkv_b = nn.Parameter(torch.empty(H * (cfg.qk_nope_dim + cfg.v_dim), cfg.kv_lora_rank, **kw))
         self.wo = nn.Parameter(torch.empty(cfg.d_model, H * cfg.v_dim, **kw))
 
-    def forward(self, x, rope_table):
+    def forward(self, x, rope_table, doc_mask=None):
         cfg = self.cfg
         B, S, _ = x.shape
         H = cfg.n_heads
@@ -91,9 +93,34 @@ class MLA(nn.Module):
         k_pe = ew._rope_ref(k_pe.reshape(B, S, 1, cfg.qk_rope_dim), rope_table, False)
         qf = torch.cat([q_nope, q_pe], dim=-1)
         kf = torch.cat([k_nope, k_pe.expand(B, S, H, cfg.qk_rope_dim)], dim=-1)
-        o = F.scaled_dot_product_attention(qf.transpose(1, 2), kf.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+        # doc_mask [B, 1, S, S] (True = attend): causal within documents; without it plain causal attention
+        o = F.scaled_dot_product_attention(qf.transpose(1, 2), kf.transpose(1, 2), v.transpose(1, 2),
+                                           attn_mask=doc_mask, is_causal=doc_mask is None,
                                            scale=ew.yarn_attention_scale(cfg.qk_dim, cfg.rope_factor, cfg.mscale))
         return linear(o.transpose(1, 2).reshape(B, S, H * cfg.v_dim), self.wo)
+
+
+class _InjectAuxLoss(torch.autograd.Function):
+    """Identity on ``x`` whose backward also back-propagates a gradient of 1 into ``loss``: an auxiliary loss
+    joins the backward pass without being added to (or changing the value of) the reported main loss."""
+
+    @staticmethod
+    def forward(ctx, x, loss):
+        ctx.loss_dtype = loss.dtype
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, torch.ones((), dtype=ctx.loss_dtype, device=g.device)
+
+
+def document_causal_mask(positions: torch.Tensor) -> torch.Tensor:
+    """``positions`` [B, S]: position of every token inside its document (a document starts where it is 0).
+    Returns a boolean [B, 1, S, S] mask: token q attends token k iff k <= q and both sit in one document."""
+    doc = torch.cumsum((positions == 0).int(), dim=1)
+    S = positions.shape[1]
+    causal = torch.ones(S, S, dtype=torch.bool, device=positions.device).tril()
+    return (causal[None] & (doc[:, :, None] == doc[:, None, :]))[:, None]
 
 
 class DenseFFN(nn.Module):
@@ -140,8 +167,27 @@ class MoE(nn.Module):
             logits = fp32_output_linear(xt, self.gate)
         else:
             logits = F.linear(xt.float(), self.gate.float())
-        return moe_ops.route_topk(logits, cfg.top_k, bias=self.expert_bias, mode="sigmoid",
-                                  scale=cfg.route_scale, normalize=True, counts=self.tokens_per_expert)
+        idx, w = moe_ops.route_topk(logits, cfg.top_k, bias=self.expert_bias, mode="sigmoid",
+                                    scale=cfg.route_scale, normalize=True, counts=self.tokens_per_expert)
+        if cfg.aux_loss_coeff > 0 and torch.is_grad_enabled():
+            w = _InjectAuxLoss.apply(w, self._balance_loss(logits, idx) * cfg.aux_loss_coeff)
+        return idx, w
+
+    def _balance_loss(self, logits, idx):
+        """Sequence-wise balance loss ``sum_e f_e * p_e``: ``f`` = share of the selections each expert got
+        (times the number of experts), ``p`` = the experts' normalised scores summed over tokens; summed over
+        this microbatch's tokens and divided by ``aux_loss_denominator`` (the step's token count over all
+        ranks, set by the trainer; defaults to this microbatch's). Parity: the router of the reference's
+        example (``examples/deepseek_v3/model.py:489-530``)."""
+        E = self.cfg.n_experts
+        scores = torch.sigmoid(logits.float())
+        counts = torch.zeros(E, dtype=scores.dtype, device=scores.device).index_add_(
+            0, idx.reshape(-1).long(), torch.ones(idx.numel(), dtype=scores.dtype, device=scores.device))
+        f = counts / counts.sum().clamp_min(1) * E
+        p = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).sum(0)
+        denom = getattr(self, "aux_loss_denominator", None)
+        denom = float(logits.shape[0]) if denom is None else denom
+        return (f * p).sum() / denom
 
     def forward(self, x):
         B, S, D = x.shape
@@ -179,10 +225,18 @@ class Block(nn.Module):
         else:
             self.moe = MoE(cfg, dtype, device)
 
-    def forward(self, x, rope_table):
-        x = x + self.attention(_rms(x, self.attention_norm, self.cfg.norm_eps), rope_table)
+    def _forward(self, x, rope_table, doc_mask):
+        x = x + self.attention(_rms(x, self.attention_norm, self.cfg.norm_eps), rope_table, doc_mask)
         h = _rms(x, self.ffn_norm, self.cfg.norm_eps)
         return x + (self.ffn(h) if hasattr(self, "ffn") else self.moe(h))
+
+    def forward(self, x, rope_table, doc_mask=None):
+        if self.cfg.activation_checkpointing and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint
+
+            # per-block recompute (parity: ``examples/deepseek_v3/model.py:597-611`` of the reference)
+            return checkpoint(self._forward, x, rope_table, doc_mask, use_reentrant=False)
+        return self._forward(x, rope_table, doc_mask)
 
 
 class DeepSeekV3(nn.Module):
@@ -207,7 +261,9 @@ class DeepSeekV3(nn.Module):
             else:
                 init_from_full(p, lambda t: t.normal_(0.0, self.cfg.init_std, generator=g))
 
-    def forward(self, tokens):
+    def forward(self, tokens, positions=None):
+        """``positions`` [B, S] (optional): token positions inside their documents; attention is then causal
+        within documents (the rotary phase keeps following the position in the sequence)."""
         B, S = tokens.shape
         if self._rope is None or self._rope.device != tokens.device:
             c = self.cfg
@@ -215,12 +271,13 @@ class DeepSeekV3(nn.Module):
                         beta_slow=c.beta_slow) if c.rope_factor != 1.0 else None
             self._rope = ew.rope_table(c.max_seq_len, c.qk_rope_dim, c.rope_theta, tokens.device, yarn=yarn)
         x = self.tok_embeddings(tokens)
+        doc_mask = document_causal_mask(positions) if positions is not None else None
         for layer in self.layers:
-            x = layer(x, self._rope[:S])
+            x = layer(x, self._rope[:S], doc_mask)
         return linear(_rms(x, self.norm, self.cfg.norm_eps), self.output).view(B * S, -1)
 
-    def loss(self, tokens, targets, loss_is_root: bool = True):
-        return ew.cross_entropy(self(tokens), targets.reshape(-1), unit_grad=loss_is_root)
+    def loss(self, tokens, targets, loss_is_root: bool = True, positions=None):
+        return ew.cross_entropy(self(tokens, positions), targets.reshape(-1), unit_grad=loss_is_root)
 
     def moe_layers(self):
         return [b.moe for b in self.layers if hasattr(b, "moe")]

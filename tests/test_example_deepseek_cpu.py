@@ -39,3 +39,15 @@ def test_resume_equals_uninterrupted_run(tmp_path, optimizer):
         assert resumed[s]["loss"] == full[s]["loss"], (s, resumed[s], full[s])
         assert resumed[s]["grad_norm"] == full[s]["grad_norm"]
         assert resumed[s]["lr"] == full[s]["lr"]
+
+
+def test_init_checkpoint_document_mask_and_balance_loss_flags(tmp_path):
+    """``--init-checkpoint`` starts from saved weights with fresh optimizers and data position; the document
+    mask, the balance loss and explicit prefetch lists run end to end (activation checkpointing is on by default)."""
+    first = _run(str(tmp_path / "a"), ["--optimizer", "adamw"])
+    warm = _run(str(tmp_path / "b"), ["--optimizer", "adamw", "--init-checkpoint", str(tmp_path / "a" / "step00000002"),
+                                      "--document-length", "8", "--aux-loss-coeff", "0.01"])
+    assert sorted(warm) == [0, 1, 2, 3]
+    assert warm[0]["loss"] != first[0]["loss"]          # not the random initial weights
+    plain = _run(str(tmp_path / "c"), ["--optimizer", "adamw", "--no-activation-checkpointing", "--no-explicit-prefetch"])
+    assert [plain[s]["loss"] for s in range(4)] == [first[s]["loss"] for s in range(4)]   # recompute and prefetch lists change no value
