@@ -427,6 +427,55 @@ class SymmComm(Comm):
         return None
 
 
+def _symm_reduce_scatter_list(self, out: torch.Tensor, inps, plan: ReducePlan):
+    """Reduce rows of different lengths into their owners (``inps[r]`` is this rank's contribution to rank
+    r's row, ``out`` this rank's reduced row): every rank lays its contributions back to back in the
+    symmetric staging region (same offsets everywhere, since every rank knows every row length) and each
+    owner sums its row out of all peers' regions in rank order, one kernel, no padding to a common length.
+    The reverse direction of the owner-rows gather; the reference reduces such rows with one grouped NCCL
+    reduce per rank (``custom_placements/utils.py:175-190``) or through its chunk transport
+    (``custom_placements/owner_rows_transport.py:544-585``)."""
+    W = self.world_size
+    lens = [t.numel() for t in inps]
+    if (W == 1 or out.dtype != torch.float32 or any(t.dtype != torch.float32 for t in inps)
+            or any(n % 4 for n in lens)):
+        return Comm.reduce_scatter_list(self, out, inps, plan)
+    for t in inps:
+        self._apply_plan_pre(t, plan)
+    offs = [4 * sum(lens[:r]) for r in range(W)]
+    total = 4 * sum(lens)
+    reg = self._region("rs", max(total, 16))
+    self._rs_epoch += 1
+    e = self._rs_epoch
+    if e > 1:
+        reg.wait(self.SLOT_RS_DONE, e - 1)
+    from ..ops.segments import run_segment_ops
+
+    run_segment_ops([(reg.payload[o:o + 4 * t.numel()].view(torch.float32), t.reshape(-1))
+                     for t, o in zip(inps, offs) if t.numel()])
+    reg.signal(self.SLOT_RS_READY, e)
+    scale = {"avg": 1.0 / W, "premul_sum": float(plan.premul or 1.0)}.get(plan.op, 1.0)
+    if plan.post_divide is not None:
+        scale /= plan.post_divide
+    n = lens[self.rank]
+    if n:
+        rows = (ctypes.c_ulonglong * W)(*[reg.peer_payload_addr(r, offs[self.rank]) for r in range(W)])
+        rc = _lib.load().fsb_comm_reduce_rows(rows, W, n, scale, out.data_ptr(), None, 0, None, None,
+                                              0.0, 0.0, 0.0, 0.0, 0.0, 1,
+                                              reg.flag_row_addr(self.rank, self.SLOT_RS_READY), e, reg.max_polls,
+                                              _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc, "fsb_comm_reduce_rows")
+        count_launch()
+    else:
+        reg.wait(self.SLOT_RS_READY, e)
+    reg.signal(self.SLOT_RS_DONE, e)
+    self.stats["owner_row_reduces"] = self.stats.get("owner_row_reduces", 0) + 1
+    return None
+
+
+SymmComm.reduce_scatter_list = _symm_reduce_scatter_list
+
+
 class SymmGradRing:
     """Symmetric *incoming gradient* regions for the fused weight-gradient -> reduce-scatter path.
 

@@ -331,3 +331,59 @@ def test_expert_parallel_rows_travel_by_peer_pull(tmp_path):
         assert res["symm_p2p"] >= 4 and res["nccl_p2p"] == 0, res   # 2 steps x (dispatch, combine, and their backward)
         for a, b in zip(res["symm"], res["nccl"]):
             assert abs(a - b) < 1e-3 * max(1.0, abs(b)), res
+
+
+def _owned_worker(rank, world, port, out):
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flex_shard_b200 import BucketSpec, flex_shard, ops
+        from flex_shard_b200.parallel.comm import set_default_backend
+        from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+
+        dev = torch.device("cuda", rank)
+        results = {}
+        for mode in ("nccl", "symm"):
+            set_default_backend(mode)
+            torch.manual_seed(0)
+            model = nn.Sequential(nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 8)).to(dev)   # owner rows of 272 and 136 elements
+            flex_shard(model, [BucketSpec(["*"], placement_fn=make_bucketed_owned_full_param_placement_fn())])
+            opt = torch.optim.SGD(model.parameters(), lr=0.1)
+            for s_ in range(3):
+                x = torch.randn(4, 16, generator=torch.Generator().manual_seed(10 * s_ + rank)).to(dev)
+                model(x).square().mean().backward()
+                opt.step()
+                opt.zero_grad()
+            torch.cuda.synchronize()
+            ops.check_status()
+            model.unshard()
+            results[mode] = {n: p.detach().cpu() for n, p in model.named_parameters()}
+            model.reshard()
+            results[mode + "_stats"] = dict(getattr(model.sharded_bucket_storages[0].comm, "stats", {}))
+            del model, opt
+        set_default_backend(None)
+        dist.barrier()
+        torch.save(results, os.path.join(out, f"o{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_owner_rows_travel_both_ways_through_peer_memory(tmp_path):
+    """Owner storage with rows of different lengths: the gather pulls each owner's row at its own length and
+    the gradient reduction sums each owner's row out of the peers' memory; same parameters as the grouped NCCL
+    collectives, bit for bit at two ranks."""
+    import torch.multiprocessing as mp
+
+    from tests.common import free_port
+
+    mp.spawn(_owned_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"o{r}.pt")
+        assert res["symm_stats"].get("owner_row_reduces", 0) == 3, res["symm_stats"]
+        for n in res["nccl"]:
+            assert torch.equal(res["symm"][n], res["nccl"][n]), n
