@@ -222,3 +222,134 @@ def _fill_boxes(v: torch.Tensor, lay: GlobalLayout, key: str, blobs) -> None:
                 covered += m
     if covered < want:
         raise RuntimeError(f"checkpoint does not cover all of {key}: {covered} of {want} elements")
+
+
+# --------------------------------------------------------------------------- interop with DTensor checkpoints
+def _as_dtensor(local: torch.Tensor, lay: GlobalLayout, mesh):
+    """A tagged local tensor as a ``DTensor`` when its layout is one FSDP2 could have produced: at most one
+    box, cut along a single dim into the ``torch.chunk`` pieces of a 1-D mesh.  Returns ``None`` otherwise."""
+    from torch.distributed.tensor import DTensor, Replicate, Shard as DShard
+
+    shape = tuple(lay.global_shape)
+    W, rank = mesh.size(), mesh.get_local_rank()
+    if len(lay.global_offsets) > 1:
+        return None
+    cut = [d for d in range(len(shape)) if tuple(local.shape)[d] != shape[d]] if lay.global_offsets else []
+    if lay.global_offsets and not cut:
+        placement = Replicate() if W == 1 or all(o == 0 for o in lay.global_offsets[0]) and tuple(local.shape) == shape \
+            else None
+        if placement is None:
+            return None
+        return DTensor.from_local(local, mesh, [placement], run_check=False, shape=torch.Size(shape),
+                                  stride=local.stride())
+    if len(cut) > 1:
+        return None
+    if not lay.global_offsets:         # an empty shard: find the dim from the zero-sized one
+        cut = [d for d in range(len(shape)) if local.shape[d] == 0 and shape[d] != 0][:1]
+        if not cut:
+            return None
+    dim = cut[0]
+    chunk = -(-shape[dim] // W)
+    lo, hi = min(shape[dim], rank * chunk), min(shape[dim], (rank + 1) * chunk)
+    if lay.global_offsets and (lay.global_offsets[0][dim] != lo or lay.local_sizes[0][dim] != hi - lo):
+        return None
+    full_stride = []
+    acc = 1
+    for s in reversed(shape):
+        full_stride.append(acc)
+        acc *= max(s, 1)
+    return DTensor.from_local(local, mesh, [DShard(dim)], run_check=False, shape=torch.Size(shape),
+                              stride=tuple(reversed(full_stride)))
+
+
+def _mesh_of(module, storage):
+    from torch.distributed.device_mesh import DeviceMesh, init_device_mesh
+
+    if isinstance(storage.mesh, DeviceMesh):
+        return storage.mesh
+    if storage.mesh is None and dist.is_initialized():
+        cache = getattr(module, "_fsb_world_mesh", None)
+        if cache is None:
+            cache = init_device_mesh(storage.device.type, (dist.get_world_size(),))
+            module._fsb_world_mesh = cache
+        return cache
+    return None
+
+
+def to_dtensor_state_dict(module: nn.Module, state_dict: Mapping[str, Any], optimizer=None,
+                          optim_state_dict: Mapping[str, Any] | None = None):
+    """The model's (and optionally an Adam-style optimizer's) local shards wrapped as ``DTensor``s, so that
+    ``torch.distributed.checkpoint`` saves and loads them in the very format FSDP2 state dicts use: a
+    checkpoint written by ``fully_shard`` loads into a ``flex_shard`` model and back, at any world size.
+    Only layouts FSDP2 itself could produce qualify (``Shard(dim)`` buckets on ``DeviceMesh``es or on the world
+    group); a parameter stored any other way raises ``ValueError`` (use ``checkpoint.save`` for those).
+    The DTensors alias the local shards, so a ``dcp.load`` into the returned dict fills the model in place.
+    Parity: the reference hands tagged tensors to DCP directly (``flex_shard/checkpoint.py:57-69``), which
+    needs a newer torch; the FSDP2 <-> flex round trips of its tests
+    (``tests/test_flex_shard_checkpoint.py:483-538``) are what this provides."""
+    layouts = get_flex_shard_global_layouts(module)
+    mesh_by_fqn = {}
+    for st in module.sharded_bucket_storages:
+        for info in st.infos:
+            for name in (info.fqn, *info.shared_fqns):
+                mesh_by_fqn[name] = _mesh_of(module, st)
+    out = {}
+    for k, v in state_dict.items():
+        if isinstance(v, torch.Tensor) and k in layouts:
+            mesh = mesh_by_fqn.get(k)
+            dt = _as_dtensor(v, layouts[k], mesh) if mesh is not None else None
+            if dt is None:
+                raise ValueError(f"{k!r} is not stored in a layout a DTensor checkpoint can express; "
+                                 "use flex_shard_b200.checkpoint.save / load for it")
+            out[k] = dt
+        else:
+            out[k] = v
+    if optimizer is None:
+        return out
+    osd = optim_state_dict if optim_state_dict is not None else optimizer.state_dict()
+    names = {id(p): n for n, p in module.named_parameters()}
+    index_name = {}
+    idx = 0
+    for g in optimizer.param_groups:
+        for p in g["params"]:
+            index_name[idx] = names.get(id(p))
+            idx += 1
+    ostate = {}
+    for pid, st in osd["state"].items():
+        name = index_name.get(pid)
+        entry = {}
+        for key, t in st.items():
+            if isinstance(t, torch.Tensor) and key in _ADAM_STATE_KEYS and name in layouts:
+                dt = _as_dtensor(t, layouts[name], mesh_by_fqn[name])
+                if dt is None:
+                    raise ValueError(f"optimizer state {key!r} of {name!r} has no DTensor form")
+                entry[key] = dt
+            else:
+                entry[key] = t
+        ostate[name if name is not None else pid] = entry
+    # parameter groups name their parameters by FQN, the form torch's get_optimizer_state_dict writes
+    groups, idx = [], 0
+    for g in osd["param_groups"]:
+        fqns = []
+        for _ in g["params"]:
+            fqns.append(index_name.get(idx) or idx)
+            idx += 1
+        groups.append({**{k: v for k, v in g.items() if k != "params"}, "params": fqns})
+    return out, {"state": ostate, "param_groups": groups}
+
+
+def load_dtensor_optim_state(optimizer, module: nn.Module, dcp_optim_state: Mapping[str, Any]) -> None:
+    """Install optimizer state keyed by FQN (as ``to_dtensor_state_dict`` writes it and as
+    ``get_optimizer_state_dict`` of an FSDP2 model does) into ``optimizer``."""
+    names = {n: p for n, p in module.named_parameters()}
+    for name, entry in dcp_optim_state["state"].items():
+        p = names.get(name)
+        if p is None:
+            continue
+        for key, t in entry.items():
+            val = t.to_local() if hasattr(t, "to_local") else t
+            cur = optimizer.state[p].get(key)
+            if isinstance(cur, torch.Tensor) and isinstance(val, torch.Tensor) and cur.shape == val.shape:
+                cur.copy_(val)
+            else:
+                optimizer.state[p][key] = val.clone() if isinstance(val, torch.Tensor) else val
