@@ -415,6 +415,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (ld.c < n_chunks) issue_load();
           }
           asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          if (!ok) {
+            // A ring wait ran out: tell the rest of the CTA, then give every load that was issued but not
+            // consumed a (bounded) chance to land before the CTA may exit, so that no bulk copy is still
+            // writing this CTA's shared memory afterwards. The GEMM CTAs give up on their chunk waits by
+            // their own bounds.
+            *abort_flag = 1;
+            for (long long i = n_stored; i < n_loaded; ++i) {
+              const int slot = static_cast<int>(i % AG_RING);
+              const uint32_t parity = static_cast<uint32_t>(i / AG_RING) & 1;
+              for (uint32_t t = 0; t < kSpinFast * 16u; ++t)
+                if (mbar_try_wait_hint(&ring_bar[slot], parity, kWaitHintNs)) break;
+            }
+          }
         }
       }
     }

@@ -68,3 +68,11 @@ class AllGatherLinear:
         _lib.check(rc, "fsb_gemm_bf16_allgather")
         count_launch()
         return out.view(*x.shape[:-1], self.N)
+
+    def reset(self) -> None:
+        """Forget the progress counters. The counters grow by one chunk's pieces per call and every call waits
+        for ``pieces * call_index``; after a call that reported a timeout (``ops.check_status()`` raised) some
+        chunks never reached their count, so every later call would time out as well. Call this (on every rank
+        of the group, with the stream idle) before using the object again."""
+        self.counters.zero_()
+        self.calls = 0
