@@ -51,3 +51,31 @@ def test_init_checkpoint_document_mask_and_balance_loss_flags(tmp_path):
     assert warm[0]["loss"] != first[0]["loss"]          # not the random initial weights
     plain = _run(str(tmp_path / "c"), ["--optimizer", "adamw", "--no-activation-checkpointing", "--no-explicit-prefetch"])
     assert [plain[s]["loss"] for s in range(4)] == [first[s]["loss"] for s in range(4)]   # recompute and prefetch lists change no value
+
+
+def test_packed_document_batches_pack_label_and_resume(tmp_path):
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "examples", "deepseek_v3"))
+    from data import PackedDocumentBatches
+
+    docs = [np.arange(10, 15), np.arange(20, 23), np.arange(30, 41)]
+    np.save(tmp_path / "a.npy", np.array(docs, dtype=object), allow_pickle=True)
+    torch.save([torch.arange(50, 54)], tmp_path / "b.pt")
+    ds = PackedDocumentBatches(str(tmp_path), batch_size=1, seq_len=8, bos_id=0, eos_id=1, loop=False)
+    b0 = next(ds)
+    # [BOS 10..14 EOS] [BOS 20..22 EOS]: inputs drop each document's last token, labels its first
+    assert b0["input"].tolist() == [[0, 10, 11, 12, 13, 14, 0, 20]]
+    assert b0["labels"].tolist() == [[10, 11, 12, 13, 14, 1, 20, 21]]
+    assert b0["positions"].tolist() == [[0, 1, 2, 3, 4, 5, 0, 1]]
+    state = ds.state_dict()
+    b1 = next(ds)
+    assert b1["positions"].tolist()[0][:2] == [2, 3] and b1["positions"].tolist()[0][2] == 0   # the document continues, then a new one
+    again = PackedDocumentBatches(str(tmp_path), batch_size=1, seq_len=8, bos_id=0, eos_id=1, loop=False)
+    again.load_state_dict(state)
+    resumed = next(again)
+    assert all(torch.equal(resumed[k], b1[k]) for k in b1)
+    # files are split across ranks
+    r1 = PackedDocumentBatches(str(tmp_path), batch_size=1, seq_len=4, rank=1, world_size=2, loop=True)
+    assert next(r1)["input"].tolist() == [[0, 50, 51, 52]]
