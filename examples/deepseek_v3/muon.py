@@ -34,6 +34,37 @@ def store_on_owners(model) -> None:
             relayout_bucket(model, st, fn)
 
 
+def store_heads_blockwise(model) -> None:
+    """The other communication-free layout: per-head matrices (``wq_b``, ``wkv_b``) are stored in whole head
+    blocks spread over the ranks (``BlockShard`` by attention head), every other matrix whole on an owner, vectors
+    as ``Shard(0)``, all in one mixed bucket per block.  Each rank then orthogonalises its own heads; the Newton-
+    Schulz work of the head matrices is spread over all ranks instead of sitting on one owner."""
+    from flex_shard_b200.dist_muon.placement import get_dim0_block_partitions
+    from flex_shard_b200.parallel.comm import mesh_group
+    from flex_shard_b200.placements import BlockShard, MixedBucketPlacement, Shard
+
+    H = model.cfg.n_heads
+    owners = make_bucketed_owned_full_param_placement_fn(carry_loads=True)
+
+    def fn(named, mesh):
+        _, _, W, _ = mesh_group(mesh)
+        whole = [(n, p) for n, p in named if p.dim() >= 2 and not n.endswith(("wq_b", "wkv_b"))]
+        owned = owners(whole, mesh)
+        out = {}
+        for n, p in named:
+            if n.endswith(("wq_b", "wkv_b")):
+                out[n] = MixedBucketPlacement(BlockShard(get_dim0_block_partitions(H, W), 0))
+            elif n in owned:
+                out[n] = MixedBucketPlacement(owned[n])
+            else:
+                out[n] = MixedBucketPlacement(Shard(0))
+        return out
+
+    for st in list(model.sharded_bucket_storages):
+        if st.name.startswith("layers.") and ".moe" not in st.name and any(len(i.global_shape) >= 2 for i in st.infos):
+            relayout_bucket(model, st, fn)
+
+
 def build_muon(model, lr: float, weight_decay: float, adamw_lr: float | None = None):
     """Muon over every matrix (per head for the attention up-projections, per expert for routed experts,
     whole otherwise) + AdamW for the rest. The per-head split needs the model's config (``model.cfg``)."""

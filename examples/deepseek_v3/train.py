@@ -21,11 +21,12 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from data import SyntheticBatches  # noqa: E402
-from muon import build_muon, store_on_owners  # noqa: E402
+from muon import build_muon, store_heads_blockwise, store_on_owners  # noqa: E402
 
 from flex_shard_b200 import (checkpoint, flex_shard, register_optimizer_checkpoint_hook,  # noqa: E402
                              set_state_dict_global_layouts)
 from flex_shard_b200.dist_muon import load_muon_checkpoint_state, muon_checkpoint_state  # noqa: E402
+from flex_shard_b200.dist_muon.placement import get_mesh_rank_groups, get_strided_rank_groups  # noqa: E402
 from flex_shard_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config, deepseek_buckets  # noqa: E402
 from flex_shard_b200.optim.adamw import FusedAdamW  # noqa: E402
 from flex_shard_b200.parallel.expert_parallel import apply_expert_parallel  # noqa: E402
@@ -60,6 +61,9 @@ def parse():
     ap.add_argument("--aux-loss-coeff", type=float, default=0.0, help="weight of the sequence-wise router balance loss")
     ap.add_argument("--no-explicit-prefetch", action="store_true",
                     help="leave prefetching to the learned order instead of block-by-block prefetch lists")
+    ap.add_argument("--muon-storage", choices=["owners", "heads"], default="owners",
+                    help="owners: every matrix whole on an owner rank; heads: per-head matrices in head blocks "
+                         "spread over the ranks (BlockShard by attention head), the rest on owners")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--comm", choices=["nccl", "symm"], default="nccl")
     return ap.parse_args()
@@ -122,8 +126,8 @@ def main():
     expert_mesh = None
     if ep > 1:
         # EP groups of `ep` consecutive ranks; experts are then sharded over ranks holding the same ones
-        ep_groups = [dist.new_group(list(range(s, s + ep))) for s in range(0, world, ep)]
-        efsdp_groups = [dist.new_group(list(range(o, world, ep))) for o in range(ep)]
+        ep_groups = [dist.new_group(ranks) for ranks in get_mesh_rank_groups(world, ep)]
+        efsdp_groups = [dist.new_group(ranks) for ranks in get_strided_rank_groups(world, ep)]
         apply_expert_parallel(model, ep_groups[rank // ep])
         expert_mesh = efsdp_groups[rank % ep]
     flex_shard(model, deepseek_buckets(model, mesh=dp_group, expert_mesh=expert_mesh))
@@ -136,7 +140,7 @@ def main():
         model.load_state_dict(sd)
 
     if args.optimizer == "muon":
-        store_on_owners(model)
+        (store_heads_blockwise if args.muon_storage == "heads" else store_on_owners)(model)
         muon, adam = build_muon(model, args.lr, args.weight_decay)
         opts = [muon, adam]
     else:
@@ -184,7 +188,7 @@ def main():
             s_.load_state_dict(ssd)
         start = data.step
 
-    metrics = JsonMetrics(rank=rank)
+    metrics = JsonMetrics(rank=rank, module=model)
     for step in range(start, args.steps):
         prof = None
         if args.profile_dir and step == 5:

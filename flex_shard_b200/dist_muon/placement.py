@@ -1,33 +1,38 @@
-"""Placement helpers for DistMuon recipes. Parity: ``dist_muon/placement.py:26-222`` of the reference."""
+"""Placement helpers for DistMuon recipes: rank groups of a 2-D (efsdp x ep) layout, block partitions over a
+mesh, and the ``placement_fn`` that stores a matrix in whole head blocks (so that each rank orthogonalises its
+own heads with no exchange). Parity: ``dist_muon/placement.py:26-222`` of the reference."""
 from __future__ import annotations
-
-from dataclasses import dataclass
-from typing import Sequence
 
 from ..placements.block_shard import BlockShard
 from ..placements.mixed_bucket import make_mixed_placement_fn
 from ..placements.shard import shard_placement_fn
 
 
-@dataclass(frozen=True)
-class BlockShardPlan:
-    blocks_per_rank: tuple[int, ...]
-    block_rows: int
-
-    def rows_of(self, rank: int) -> int:
-        return self.blocks_per_rank[rank] * self.block_rows
-
-
 def get_mesh_rank_groups(world_size: int, group_size: int) -> list[list[int]]:
+    """Consecutive groups of ``group_size`` ranks (e.g. the expert-parallel groups of a job)."""
+    if group_size <= 0 or world_size % group_size:
+        raise ValueError(f"group size {group_size} does not divide the world size {world_size}")
     return [list(range(i, i + group_size)) for i in range(0, world_size, group_size)]
 
 
+def get_strided_rank_groups(world_size: int, group_size: int) -> list[list[int]]:
+    """The complementary groups: ranks at the same position of every consecutive group (e.g. the ranks that
+    hold the same experts under expert parallelism and shard them among themselves)."""
+    get_mesh_rank_groups(world_size, group_size)
+    return [list(range(o, world_size, group_size)) for o in range(group_size)]
+
+
 def get_dim0_block_partitions(num_blocks: int, world_size: int) -> tuple[int, ...]:
+    """Blocks per rank when ``num_blocks`` whole blocks are dealt to ``world_size`` ranks as evenly as possible
+    (the first ``num_blocks % world_size`` ranks hold one more)."""
     base, rem = divmod(num_blocks, world_size)
     return tuple(base + (1 if r < rem else 0) for r in range(world_size))
 
 
 def make_bucketed_block_placement_fn(num_blocks_of):
+    """``placement_fn`` storing every parameter as ``BlockShard`` over dim 0 in whole blocks;
+    ``num_blocks_of(fqn, param)`` gives the number of blocks (attention heads, experts) of a parameter."""
+
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
 
@@ -38,5 +43,5 @@ def make_bucketed_block_placement_fn(num_blocks_of):
 
 
 shard0_placement_fn = shard_placement_fn(0)
-__all__ = ["BlockShardPlan", "get_mesh_rank_groups", "get_dim0_block_partitions", "make_mixed_placement_fn",
+__all__ = ["get_mesh_rank_groups", "get_strided_rank_groups", "get_dim0_block_partitions", "make_mixed_placement_fn",
            "shard0_placement_fn", "make_bucketed_block_placement_fn"]

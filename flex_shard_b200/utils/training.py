@@ -61,11 +61,17 @@ def clip_grad_norm_(module, max_norm: float, norm_type: float = 2.0) -> torch.Te
 class JsonMetrics:
     """One JSON line per step: loss, grad-norm, lr, tokens/s (device-timed), peak memory."""
 
-    def __init__(self, stream=None, rank: int = 0):
+    def __init__(self, stream=None, rank: int = 0, module=None):
+        """``module``: a ``flex_shard`` module; when given, every record also carries ``exposed_comm_ms``,
+        the device time its compute stream spent blocked on gathers and reductions during the step."""
         self.stream = stream or sys.stdout
         self.rank = rank
         self._ev = None
         self._t = None
+        self._ctx = None
+        if module is not None and torch.cuda.is_available():
+            self._ctx = module._fsb_ctx()
+            self._ctx.measure_exposed_comm(True)
 
     def start_step(self):
         if torch.cuda.is_available():
@@ -87,6 +93,8 @@ class JsonMetrics:
         rec = {"step": step, "ms": round(ms, 3), "tokens_per_s_per_gpu": round(tokens / (ms / 1e3), 1)}
         if torch.cuda.is_available():
             rec["peak_mem_gib"] = round(torch.cuda.max_memory_allocated() / 2**30, 2)
+        if self._ctx is not None:
+            rec["exposed_comm_ms"] = round(self._ctx.exposed_comm_ms(), 3)
         for k, v in fields.items():
             rec[k] = float(v) if isinstance(v, torch.Tensor) else v
         if self.rank == 0:

@@ -79,3 +79,13 @@ def test_packed_document_batches_pack_label_and_resume(tmp_path):
     # files are split across ranks
     r1 = PackedDocumentBatches(str(tmp_path), batch_size=1, seq_len=4, rank=1, world_size=2, loop=True)
     assert next(r1)["input"].tolist() == [[0, 50, 51, 52]]
+
+
+def test_muon_head_block_storage_trains_like_owner_storage(tmp_path):
+    """Per-head matrices stored in head blocks over the ranks (BlockShard by attention head) or whole on owners:
+    the same per-head Newton-Schulz either way, so the same losses."""
+    # clipping off: the global gradient norm is summed in storage order, its last bit differs between the two
+    # layouts, and Newton-Schulz rounds its input to bf16, which turns that bit into visible differences
+    owners = _run(str(tmp_path / "o"), ["--optimizer", "muon", "--max-norm", "1e9"])
+    heads = _run(str(tmp_path / "h"), ["--optimizer", "muon", "--muon-storage", "heads", "--max-norm", "1e9"])
+    assert [heads[s]["loss"] for s in range(4)] == [owners[s]["loss"] for s in range(4)]
