@@ -31,6 +31,7 @@ def _ensure():
         _lib.declare("fsb_gemm_bf16_grouped", [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, i32, i32,
                                                vp, vp, vp, i32, vp, vp])
         _lib.declare("fsb_route_topk", [vp, vp, i64, i32, i32, i32, i32, c.c_float, vp, vp, vp, vp])
+        _lib.declare("fsb_moe_plan_routes", [vp, i32, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp])
         _declared = True
 
 
@@ -52,13 +53,38 @@ class RoutePlan:
     num_experts: int
 
 
+def plan_routes_reference(expert_idx: torch.Tensor, num_experts: int) -> RoutePlan:
+    """The same plan computed with PyTorch operators (CPU path and oracle of the kernel)."""
+    if expert_idx.is_cuda:
+        cpu = plan_routes(expert_idx.cpu(), num_experts)
+        dev = expert_idx.device
+        return RoutePlan(cpu.pos.to(dev), cpu.src.to(dev), cpu.offs.to(dev), cpu.tile_expert.to(dev),
+                         cpu.num_mtiles.to(dev), cpu.max_rows, cpu.num_experts)
+    return plan_routes(expert_idx, num_experts)
+
+
 def plan_routes(expert_idx: torch.Tensor, num_experts: int) -> RoutePlan:
     """Stable expert-major ordering of the (token, choice) pairs, every expert's block padded to 128 rows."""
     T, k = expert_idx.shape
     dev = expert_idx.device
-    flat = expert_idx.reshape(-1).to(torch.int64)
-    n = flat.numel()
+    n = expert_idx.numel()
     max_rows = (n + num_experts * (ALIGN - 1) + ALIGN - 1) // ALIGN * ALIGN
+    if expert_idx.is_cuda and num_experts <= 256 and expert_idx.dtype in (torch.int64, torch.int32):
+        # one launch: histogram, padded prefix sums, tile table and the row of every pair (stable within an expert)
+        _ensure()
+        idx = expert_idx.contiguous()
+        pos = torch.empty(T, k, dtype=torch.int32, device=dev)
+        src = torch.empty(max_rows, dtype=torch.int32, device=dev)
+        offs = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(max_rows // ALIGN, dtype=torch.int32, device=dev)
+        num_mtiles = torch.empty(1, dtype=torch.int32, device=dev)
+        rc = _lib.load().fsb_moe_plan_routes(idx.data_ptr(), int(idx.dtype == torch.int64), n, k, num_experts, max_rows,
+                                             pos.data_ptr(), src.data_ptr(), offs.data_ptr(), tile_expert.data_ptr(),
+                                             num_mtiles.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc, "fsb_moe_plan_routes")
+        count_launch()
+        return RoutePlan(pos, src, offs, tile_expert, num_mtiles, max_rows, num_experts)
+    flat = expert_idx.reshape(-1).to(torch.int64)
     order = torch.argsort(flat, stable=True)
     counts = torch.bincount(flat, minlength=num_experts)
     padded = (counts + ALIGN - 1) // ALIGN * ALIGN

@@ -50,3 +50,26 @@ def test_router_kernel_matches_reference(mode, normalize, E, k):
     torch.testing.assert_close(res["cpu"][1], res["cuda"][1], rtol=1e-4, atol=1e-6)
     assert torch.equal(res["cpu"][2], res["cuda"][2])
     torch.testing.assert_close(res["cpu"][3], res["cuda"][3], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,k,E", [(300, 2, 4), (4096, 6, 64), (7, 1, 8), (50000, 1, 16), (1000, 8, 256), (33, 3, 5)])
+def test_route_plan_kernel_equals_operator_plan(T, k, E):
+    """Histogram, padded offsets, tile table and stable rows from the one-launch kernel equal the plan
+    computed with sort / bincount / cumsum operators, exactly; skewed and empty experts included."""
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.randint(0, E, (T, k), generator=g)
+    idx[idx == E - 1] = 0                      # the last expert stays empty, the first is overloaded
+    for dtype in (torch.int64, torch.int32):
+        before = ops.launch_count()
+        got = moe.plan_routes(idx.to("cuda", dtype), E)
+        assert ops.launch_count() - before == 1
+        want = moe.plan_routes(idx, E)         # CPU tensors take the operator path
+        torch.cuda.synchronize()
+        assert torch.equal(got.pos.cpu(), want.pos)
+        assert torch.equal(got.src.cpu(), want.src)
+        assert torch.equal(got.offs.cpu(), want.offs)
+        assert int(got.num_mtiles) == int(want.num_mtiles)
+        n_tiles = int(want.num_mtiles)
+        assert torch.equal(got.tile_expert.cpu()[:n_tiles], want.tile_expert[:n_tiles])
+        assert got.max_rows == want.max_rows
+    ops.check_status()
