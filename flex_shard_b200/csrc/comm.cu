@@ -25,6 +25,7 @@ namespace {
 using namespace fsb;
 
 constexpr int MAX_RANKS = 16;
+constexpr int kMaxLocalExperts = 256;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -337,4 +338,178 @@ FSB_API int fsb_comm_copy_segments_dma(const unsigned long long* src, const unsi
     }
   }
   return FSB_OK;
+}
+
+// ------------------------------------------------------------------ expert-parallel row exchange, no host in the loop
+// Token rows travel between a *sender layout* (this rank's (token, choice) pairs in expert-major order, every
+// expert's block padded to 128 rows) and a *receiver layout* (the rows of this rank's local experts from all
+// ranks, expert-major, padded to 128 rows: what the grouped GEMM reads). All sizes stay on the device: every
+// rank publishes its per-expert counts and block offsets in symmetric memory, the receiver derives where each
+// (source rank, local expert) run lands and publishes that table for the way back, and the rows are pulled out
+// of the peers' memory by a kernel whose grid is sized for the worst case and whose CTAs stop at the real counts.
+namespace {
+
+struct EpTables {     // layout of the int32 table area at the start of every rank's symmetric payload
+  int E, le, ep;
+  __host__ __device__ int counts() const { return 0; }            // [E]   pairs per global expert (sender)
+  __host__ __device__ int offs() const { return E; }              // [E+1] padded block offsets (sender layout)
+  __host__ __device__ int recv_base() const { return 2 * E + 1; } // [ep*le] first row of (source, local expert) (receiver)
+};
+
+// Receiver set-up: wait for every rank's tables, then n / srow / drow of every (source rank s, local expert j) run,
+// the receiver-side grouped-GEMM plan, the padding rows to clear, and the published recv_base table. One CTA.
+__global__ void __launch_bounds__(256)
+ep_receiver_setup_kernel(PeerPtrs tables, EpTables t, int me, long long cap_rows, int* __restrict__ n,
+                         int* __restrict__ srow, int* __restrict__ drow, int* __restrict__ pad_lo,
+                         int* __restrict__ pad_hi, int* __restrict__ plan_offs, int* __restrict__ tile_expert,
+                         int* __restrict__ num_mtiles, const uint32_t* my_flags, uint32_t epoch, uint32_t max_polls,
+                         int* status) {
+  if (!cta_wait_peers(my_flags, t.ep, epoch, max_polls, status)) return;
+  __threadfence_system();
+  __shared__ int offs_s[kMaxLocalExperts + 1];
+  __shared__ int tot_s[kMaxLocalExperts];
+  const int pairs = t.ep * t.le;
+  for (int q = threadIdx.x; q < pairs; q += blockDim.x) {
+    const int s = q / t.le, j = q % t.le;
+    const int* tb = static_cast<const int*>(tables.p[s]);
+    n[q] = tb[t.counts() + me * t.le + j];
+    srow[q] = tb[t.offs() + me * t.le + j];
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < t.le; j += blockDim.x) {
+    int run = 0;
+    for (int s = 0; s < t.ep; ++s) run += n[s * t.le + j];
+    tot_s[j] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    offs_s[0] = 0;
+    for (int j = 0; j < t.le; ++j) offs_s[j + 1] = offs_s[j] + (tot_s[j] + 127) / 128 * 128;
+    if (offs_s[t.le] > cap_rows) {
+      // more rows than the receive buffer holds: report, and clamp so that no copy leaves the buffer
+      atomicExch(status, FSB_ERR_TOO_LARGE);
+      for (int j = 0; j <= t.le; ++j) offs_s[j] = offs_s[j] < cap_rows ? offs_s[j] : static_cast<int>(cap_rows);
+    }
+    *num_mtiles = offs_s[t.le] / 128;
+  }
+  __syncthreads();
+  int* mine = static_cast<int*>(tables.p[me]);
+  for (int j = threadIdx.x; j < t.le; j += blockDim.x) {
+    int run = offs_s[j];
+    for (int s = 0; s < t.ep; ++s) {
+      const int q = s * t.le + j;
+      const int room = offs_s[j + 1] - run;
+      if (n[q] > room) n[q] = room > 0 ? room : 0;     // only after an overflow was reported
+      drow[q] = run;
+      mine[t.recv_base() + q] = run;
+      run += n[q];
+    }
+    pad_lo[j] = run;
+    pad_hi[j] = offs_s[j + 1];
+  }
+  for (int j = threadIdx.x; j <= t.le; j += blockDim.x) plan_offs[j] = offs_s[j];
+  for (long long m = threadIdx.x; m < cap_rows / 128; m += blockDim.x) {
+    const int row = static_cast<int>(m) * 128;
+    int a = 0, b = t.le;
+    while (a < b) {
+      const int mid = (a + b) / 2;
+      if (offs_s[mid + 1] > row) b = mid; else a = mid + 1;
+    }
+    tile_expert[m] = a < t.le ? a : t.le - 1;
+  }
+}
+
+// Sender set-up for the way back: wait until every receiver has published recv_base, then for every
+// (destination rank r, its local expert j): n = my count, srow = r's row of my run, drow = my block's row.
+__global__ void __launch_bounds__(256)
+ep_sender_setup_kernel(PeerPtrs tables, EpTables t, int me, int* __restrict__ n, int* __restrict__ srow,
+                       int* __restrict__ drow, const uint32_t* my_flags, uint32_t epoch, uint32_t max_polls,
+                       int* status) {
+  if (!cta_wait_peers(my_flags, t.ep, epoch, max_polls, status)) return;
+  __threadfence_system();
+  const int* mine = static_cast<const int*>(tables.p[me]);
+  for (int q = threadIdx.x; q < t.ep * t.le; q += blockDim.x) {
+    const int r = q / t.le, j = q % t.le;
+    const int* tb = static_cast<const int*>(tables.p[r]);
+    n[q] = mine[t.counts() + q];
+    srow[q] = tb[t.recv_base() + me * t.le + j];
+    drow[q] = mine[t.offs() + q];
+  }
+}
+
+// Pull runs of rows: run q copies n[q] rows from peer q / le's area (row srow[q]) to row drow[q] of `dst`.
+// blockIdx.y >= pairs clears the padding rows [pad_lo[j], pad_hi[j]) of expert block j (pad_lo may be null).
+__global__ void __launch_bounds__(256)
+ep_pull_rows_kernel(PeerPtrs area, const int* __restrict__ n, const int* __restrict__ srow,
+                    const int* __restrict__ drow, const int* __restrict__ pad_lo, const int* __restrict__ pad_hi,
+                    uint8_t* __restrict__ dst, long long row_bytes, int pairs, int le, const uint32_t* my_flags,
+                    int world, uint32_t epoch, uint32_t max_polls, int* status) {
+  if (my_flags != nullptr && !cta_wait_peers(my_flags, world, epoch, max_polls, status)) return;
+  const int q = blockIdx.y;
+  const long long vec = row_bytes / 16;
+  if (q >= pairs) {
+    if (pad_lo == nullptr) return;
+    const int j = q - pairs;
+    const long long lo = pad_lo[j], hi = pad_hi[j];
+    uint4* d = reinterpret_cast<uint4*>(dst + lo * row_bytes);
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < (hi - lo) * vec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      d[i] = z;
+    return;
+  }
+  const long long rows = n[q];
+  if (rows <= 0) return;
+  const uint4* s = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(area.p[q / le]) + srow[q] * row_bytes);
+  uint4* d = reinterpret_cast<uint4*>(dst + drow[q] * row_bytes);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < rows * vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    d[i] = s[i];
+}
+
+}  // namespace
+
+// tables[r]: address of rank r's int32 table area. Outputs are local device int32 arrays (n, srow, drow of
+// ep*le runs; pad_lo / pad_hi of le blocks; the grouped-GEMM plan of the receive layout).
+FSB_API int fsb_ep_receiver_setup(const unsigned long long* tables, int E, int le, int ep, int me,
+                                  long long cap_rows, int* n, int* srow, int* drow, int* pad_lo, int* pad_hi,
+                                  int* plan_offs, int* tile_expert, int* num_mtiles, const void* my_flags,
+                                  unsigned epoch, unsigned max_polls, int* status, cudaStream_t stream) {
+  if (ep > MAX_RANKS || le > kMaxLocalExperts || E != ep * le || cap_rows % 128 != 0) return FSB_ERR_BAD_ARG;
+  PeerPtrs tp;
+  for (int r = 0; r < ep; ++r) tp.p[r] = reinterpret_cast<void*>(tables[r]);
+  ep_receiver_setup_kernel<<<1, 256, 0, stream>>>(tp, EpTables{E, le, ep}, me, cap_rows, n, srow, drow, pad_lo,
+                                                   pad_hi, plan_offs, tile_expert, num_mtiles,
+                                                   static_cast<const uint32_t*>(my_flags), epoch, max_polls, status);
+  return ok();
+}
+
+FSB_API int fsb_ep_sender_setup(const unsigned long long* tables, int E, int le, int ep, int me, int* n, int* srow,
+                                int* drow, const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
+                                cudaStream_t stream) {
+  if (ep > MAX_RANKS || le > kMaxLocalExperts || E != ep * le) return FSB_ERR_BAD_ARG;
+  PeerPtrs tp;
+  for (int r = 0; r < ep; ++r) tp.p[r] = reinterpret_cast<void*>(tables[r]);
+  ep_sender_setup_kernel<<<1, 256, 0, stream>>>(tp, EpTables{E, le, ep}, me, n, srow, drow,
+                                                 static_cast<const uint32_t*>(my_flags), epoch, max_polls, status);
+  return ok();
+}
+
+// area[r]: address of rank r's row area (rows of row_bytes, a multiple of 16). my_flags may be null (no wait).
+FSB_API int fsb_ep_pull_rows(const unsigned long long* area, const int* n, const int* srow, const int* drow,
+                             const int* pad_lo, const int* pad_hi, void* dst, long long row_bytes, int ep, int le,
+                             int blocks_per_run, const void* my_flags, unsigned epoch, unsigned max_polls,
+                             int* status, cudaStream_t stream) {
+  if (ep > MAX_RANKS || row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return FSB_ERR_BAD_ARG;
+  PeerPtrs ap;
+  for (int r = 0; r < ep; ++r) {
+    if (area[r] & 15) return FSB_ERR_BAD_ARG;
+    ap.p[r] = reinterpret_cast<void*>(area[r]);
+  }
+  const int pairs = ep * le;
+  dim3 grid(blocks_per_run < 1 ? 1 : blocks_per_run, pairs + (pad_lo != nullptr ? le : 0));
+  ep_pull_rows_kernel<<<grid, 256, 0, stream>>>(ap, n, srow, drow, pad_lo, pad_hi, static_cast<uint8_t*>(dst),
+                                                row_bytes, pairs, le, static_cast<const uint32_t*>(my_flags), ep,
+                                                epoch, max_polls, status);
+  return ok();
 }

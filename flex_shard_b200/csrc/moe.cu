@@ -134,7 +134,7 @@ constexpr int kPlanMaxExperts = 256;
 __global__ void __launch_bounds__(kPlanWarps * 32)
 plan_routes_kernel(const long long* __restrict__ idx64, const int* __restrict__ idx32, long long n, int k, int E,
                    long long max_rows, int* __restrict__ pos, int* __restrict__ src, int* __restrict__ offs,
-                   int* __restrict__ tile_expert, int* __restrict__ num_mtiles) {
+                   int* __restrict__ tile_expert, int* __restrict__ num_mtiles, int* __restrict__ counts) {
   extern __shared__ int sm[];
   int* cnt = sm;                              // [warps][E] counts, then running offsets
   int* off = sm + kPlanWarps * E;             // [E + 1] padded offsets
@@ -166,6 +166,7 @@ plan_routes_kernel(const long long* __restrict__ idx64, const int* __restrict__ 
       cnt[w * E + e] = run;
       run += c;
     }
+    if (counts != nullptr) counts[e] = run;
     off[e + 1] = (run + 127) / 128 * 128;     // padded size of expert e, turned into an offset below
   }
   __syncthreads();
@@ -208,15 +209,15 @@ plan_routes_kernel(const long long* __restrict__ idx64, const int* __restrict__ 
 }  // namespace
 
 // idx: n expert ids (int64 when idx_is_i64 else int32). Outputs are int32 device arrays: pos[n], src[max_rows],
-// offs[E + 1], tile_expert[max_rows / 128], num_mtiles[1]. max_rows must be a multiple of 128 that covers the
-// padded layout in the worst case.
+// offs[E + 1], tile_expert[max_rows / 128], num_mtiles[1], counts[E] (pairs per expert; may be null). max_rows
+// must be a multiple of 128 that covers the padded layout in the worst case.
 FSB_API int fsb_moe_plan_routes(const void* idx, int idx_is_i64, long long n, int k, int E, long long max_rows,
-                                int* pos, int* src, int* offs, int* tile_expert, int* num_mtiles,
+                                int* pos, int* src, int* offs, int* tile_expert, int* num_mtiles, int* counts,
                                 cudaStream_t stream) {
   if (E <= 0 || E > kPlanMaxExperts || k <= 0 || n < 0 || max_rows % 128 != 0) return FSB_ERR_BAD_ARG;
   const size_t smem = (static_cast<size_t>(kPlanWarps) * E + E + 1) * sizeof(int);
   plan_routes_kernel<<<1, kPlanWarps * 32, smem, stream>>>(
       idx_is_i64 ? static_cast<const long long*>(idx) : nullptr, idx_is_i64 ? nullptr : static_cast<const int*>(idx),
-      n, k, E, max_rows, pos, src, offs, tile_expert, num_mtiles);
+      n, k, E, max_rows, pos, src, offs, tile_expert, num_mtiles, counts);
   return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
 }

@@ -31,7 +31,7 @@ def _ensure():
         _lib.declare("fsb_gemm_bf16_grouped", [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, i32, i32,
                                                vp, vp, vp, i32, vp, vp])
         _lib.declare("fsb_route_topk", [vp, vp, i64, i32, i32, i32, i32, c.c_float, vp, vp, vp, vp])
-        _lib.declare("fsb_moe_plan_routes", [vp, i32, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp])
+        _lib.declare("fsb_moe_plan_routes", [vp, i32, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp])
         _declared = True
 
 
@@ -51,6 +51,12 @@ class RoutePlan:
     num_mtiles: torch.Tensor
     max_rows: int
     num_experts: int
+    counts: torch.Tensor | None = None     # pairs per expert (int32 [E]); filled by the planning kernel
+
+
+def max_rows_for(num_pairs: int, num_experts: int) -> int:
+    """Rows of the padded expert-major layout in the worst case (every expert's block rounded up to 128)."""
+    return (num_pairs + num_experts * (ALIGN - 1) + ALIGN - 1) // ALIGN * ALIGN
 
 
 def plan_routes_reference(expert_idx: torch.Tensor, num_experts: int) -> RoutePlan:
@@ -78,12 +84,13 @@ def plan_routes(expert_idx: torch.Tensor, num_experts: int) -> RoutePlan:
         offs = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
         tile_expert = torch.empty(max_rows // ALIGN, dtype=torch.int32, device=dev)
         num_mtiles = torch.empty(1, dtype=torch.int32, device=dev)
+        counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
         rc = _lib.load().fsb_moe_plan_routes(idx.data_ptr(), int(idx.dtype == torch.int64), n, k, num_experts, max_rows,
                                              pos.data_ptr(), src.data_ptr(), offs.data_ptr(), tile_expert.data_ptr(),
-                                             num_mtiles.data_ptr(), _lib.stream_ptr(dev))
+                                             num_mtiles.data_ptr(), counts.data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc, "fsb_moe_plan_routes")
         count_launch()
-        return RoutePlan(pos, src, offs, tile_expert, num_mtiles, max_rows, num_experts)
+        return RoutePlan(pos, src, offs, tile_expert, num_mtiles, max_rows, num_experts, counts)
     flat = expert_idx.reshape(-1).to(torch.int64)
     order = torch.argsort(flat, stable=True)
     counts = torch.bincount(flat, minlength=num_experts)
@@ -101,7 +108,8 @@ def plan_routes(expert_idx: torch.Tensor, num_experts: int) -> RoutePlan:
     tiles = torch.arange(max_rows // ALIGN, device=dev)
     tile_expert = torch.searchsorted(offs[1:] // ALIGN, tiles, right=True).clamp_max(num_experts - 1).to(torch.int32)
     num_mtiles = (offs[-1:] // ALIGN).to(torch.int32)
-    return RoutePlan(pos.view(T, k), src, offs.to(torch.int32), tile_expert, num_mtiles, max_rows, num_experts)
+    return RoutePlan(pos.view(T, k), src, offs.to(torch.int32), tile_expert, num_mtiles, max_rows, num_experts,
+                     counts.to(torch.int32))
 
 
 # --------------------------------------------------------------------------- row movement

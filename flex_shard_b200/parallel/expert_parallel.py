@@ -104,6 +104,21 @@ class AllToAllDispatcher:
         return (gathered.float() * weights[..., None]).sum(1).to(xt.dtype)
 
 
+def make_dispatcher(ep_group, num_experts: int, device):
+    """The host-free peer-memory dispatcher on CUDA meshes with the peer-memory backend selected (and
+    ``FSB200_EP_DISPATCH`` not set to ``a2a``), else the all-to-all dispatcher."""
+    import os
+
+    from . import comm as _comm
+
+    if (device.type == "cuda" and dist.get_world_size(ep_group) > 1 and _comm._backend() == "symm"
+            and os.environ.get("FSB200_EP_DISPATCH", "symm") != "a2a"):
+        from .ep_exchange import SymmDispatcher
+
+        return SymmDispatcher(ep_group, num_experts)
+    return AllToAllDispatcher(ep_group, num_experts)
+
+
 def apply_expert_parallel(model, ep_group: dist.ProcessGroup) -> None:
     """Keep this rank's experts in every MoE layer and route tokens over ``ep_group``."""
     ep, rank = dist.get_world_size(ep_group), dist.get_rank(ep_group)
@@ -123,4 +138,4 @@ def apply_expert_parallel(model, ep_group: dist.ProcessGroup) -> None:
             set_global_layout(local, GlobalLayout(shape, ((rank * le,) + (0,) * (nd - 1),), ((0,) * nd,),
                                                   ((le, *shape[1:]),)))
             setattr(moe.routed_experts, name, local)
-        moe.dispatcher = AllToAllDispatcher(ep_group, E)
+        moe.dispatcher = make_dispatcher(ep_group, E, full.device)

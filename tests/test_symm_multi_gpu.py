@@ -291,8 +291,11 @@ def _ep_worker(rank, world, port, out):
                                kv_lora_rank=32, qk_nope_dim=32, qk_rope_dim=16, v_dim=32, dense_hidden=256,
                                n_experts=4, expert_hidden=128, top_k=2, n_shared_experts=1, max_seq_len=64)
         results = {}
-        for mode in ("nccl", "symm"):
-            set_default_backend(mode)
+        for mode in ("nccl", "symm", "symm_a2a"):
+            # "symm": the host-free exchange (tables and rows through symmetric memory); "symm_a2a": the
+            # all-to-all dispatcher whose rows travel as peer pulls after a host read of the counts
+            os.environ["FSB200_EP_DISPATCH"] = "a2a" if mode == "symm_a2a" else "symm"
+            set_default_backend("nccl" if mode == "nccl" else "symm")
             torch.manual_seed(0)
             model = DeepSeekV3(cfg, dtype=torch.bfloat16, device=dev)
             model.init_weights(0)
@@ -309,6 +312,8 @@ def _ep_worker(rank, world, port, out):
             results[mode] = losses
             results[mode + "_p2p"] = sum(getattr(m.dispatcher._symm, "p2p_row_exchanges", 0)
                                          for m in model.moe_layers() if m.dispatcher._symm is not None)
+            results[mode + "_hostfree"] = sum(getattr(getattr(m.dispatcher, "_ex", None), "exchanges", 0)
+                                              for m in model.moe_layers())
             del model
         set_default_backend(None)
         dist.barrier()
@@ -328,9 +333,11 @@ def test_expert_parallel_rows_travel_by_peer_pull(tmp_path):
     mp.spawn(_ep_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         res = torch.load(tmp_path / f"e{r}.pt")
-        assert res["symm_p2p"] >= 4 and res["nccl_p2p"] == 0, res   # 2 steps x (dispatch, combine, and their backward)
-        for a, b in zip(res["symm"], res["nccl"]):
-            assert abs(a - b) < 1e-3 * max(1.0, abs(b)), res
+        assert res["symm_a2a_p2p"] >= 4 and res["nccl_p2p"] == 0, res   # 2 steps x (dispatch, combine, and their backward)
+        assert res["symm_hostfree"] == 2 * 4 and res["symm_p2p"] == 0, res   # one MoE layer: 4 exchanges per step
+        for mode in ("symm", "symm_a2a"):
+            for a, b in zip(res[mode], res["nccl"]):
+                assert abs(a - b) < 1e-3 * max(1.0, abs(b)), res
 
 
 def _owned_worker(rank, world, port, out):
