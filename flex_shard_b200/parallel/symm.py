@@ -220,6 +220,14 @@ class SymmComm(Comm):
             return reg
         return None
 
+    def wait_readers_done(self, buf: torch.Tensor) -> None:
+        """Enqueue a wait until every peer has finished its latest gather out of the resident buffer ``buf``
+        (for buffers that are rewritten between gathers, such as a quantised payload row)."""
+        reg = self._resident.get(buf.data_ptr())
+        if reg is not None and reg.epoch > 0:
+            reg.wait(self.SLOT_AG_DONE, reg.epoch)
+            self._unfenced.discard(buf.data_ptr())
+
     def fence_resident(self) -> None:
         """Enqueue, on the current stream, a wait until every peer has finished reading this rank's
         resident storages (their pulls of the latest gather epoch). Work queued afterwards, such as an
@@ -315,21 +323,9 @@ class SymmComm(Comm):
         W = self.world_size
         nbytes = inp.numel() * inp.element_size()
         assert out.numel() * out.element_size() == W * nbytes and out.is_contiguous() and inp.is_contiguous()
-        reg, e = self._publish(inp, nbytes, nbytes)
-        key = ("ag", id(reg), out.data_ptr(), nbytes)
-        descs = self._desc_cache.get(key)
-        if descs is None:
-            segs = [(reg.peer_payload_addr(r), out.data_ptr() + r * nbytes, nbytes) for r in range(W)]
-            descs = _pack_descs(segs, self.device)
-            if len(self._desc_cache) < 4096:
-                self._desc_cache[key] = descs
-        blocks = max(1, min(64, nbytes // (64 * 1024)))
-        rc = _lib.load().fsb_comm_gather_pull(descs.data_ptr(), W, blocks, reg.flag_row_addr(self.rank, self.SLOT_AG_READY),
-                                              W, e, reg.max_polls, _lib.status_word(self.device).data_ptr(),
-                                              _lib.stream_ptr(self.device))
-        _lib.check(rc, "fsb_comm_gather_pull")
-        count_launch()
-        reg.signal(self.SLOT_AG_DONE, e)
+        # one segment per rank: the same path (copy engines or pull kernel, resident or staged source) as a
+        # gather into per-parameter buffers
+        self.all_gather_segments(inp, [(r, 0, out.data_ptr() + r * nbytes, nbytes) for r in range(W)], alloc_bytes=nbytes)
         return None
 
     def all_gather_segments(self, inp: torch.Tensor, segments, alloc_bytes: int = 0) -> None:

@@ -165,8 +165,11 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
             self._payload_cache = None
             return prep
         recv = torch.empty(W, row_bytes, dtype=torch.uint8, device=byte_storage.device)
+        # quantise-on-push: on a peer-memory mesh the quantiser writes this rank's payload row straight into
+        # symmetric memory, where the peers' gather reads it in place (no staging copy of the FP8 bytes)
+        push_row = self._push_row(comm, row_bytes) if W > 1 else None
         with record("FlexShard::copy_in"):
-            row = recv[rank]
+            row = push_row if push_row is not None else recv[rank]
             for i, rows, qo, qb, so, sb in per_rank[rank]:
                 info = infos[i]
                 cols = math.prod(info.global_shape[1:])
@@ -175,9 +178,24 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
                     w = w.to(info.param_dtype)  # quantise from the compute dtype, as the dense path would
                 info.placement.quantize_into(w, row[qo:qo + qb], row[so:so + sb])
         prep.recv = recv
-        prep.send = recv[rank]
+        prep.send = push_row if push_row is not None else recv[rank]
         prep.extra["key"] = key
         return prep
+
+    def _push_row(self, comm, row_bytes):
+        """This placement object's payload row inside a symmetric region (one per bucket: all parameters of a
+        bucket share the first parameter's placement for the bucket-level calls), or None on other meshes.
+        The row is rewritten by every gather, so the previous gather's readers must be done first."""
+        alloc = getattr(comm, "alloc_storage", None)
+        if alloc is None or not getattr(comm, "resident_storage", False):
+            return None
+        row = getattr(self, "_symm_row", None)
+        if row is None or row.numel() != row_bytes:
+            row = self._symm_row = alloc(row_bytes)
+            if row is None:
+                return None
+        comm.wait_readers_done(row)
+        return row
 
     def run_prepared_unshard(self, prepared, comm, async_op=False):
         if comm.world_size == 1 or prepared.extra.get("cached"):
