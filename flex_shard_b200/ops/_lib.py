@@ -149,8 +149,8 @@ def poll_status(device=None) -> None:
     failed wait, then enqueues a new device -> pinned-host copy behind the work queued so far on the
     current stream.  A failure is therefore reported one call late at most, and the host never waits
     for the GPU.  Does nothing when no kernel of this process has asked for the status word yet."""
-    if not torch.cuda.is_available():
-        return
+    if not torch.cuda.is_available() or torch.cuda.is_current_stream_capturing():
+        return      # event queries and pinned allocations are not allowed inside a stream capture
     idx = (torch.cuda.current_device() if device is None or device.index is None else device.index)
     word = _status.get(idx)
     if word is None:

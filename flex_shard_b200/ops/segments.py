@@ -105,7 +105,9 @@ def run_segment_ops(ops, cache: dict | None = None) -> int:
     ops = [(d, s) for d, s in ops if d.numel()]
     if not ops:
         return 0
-    if not ops[0][0].is_cuda:
+    if not ops[0][0].is_cuda or torch.cuda.is_current_stream_capturing():
+        # CPU tensors, or a stream capture (descriptor upload and the event bookkeeping are not capturable):
+        # plain copies, which capture fine
         for d, s in ops:
             if s is None:
                 d.zero_()
