@@ -53,6 +53,9 @@ def parse():
                          "per step instead of two; +2 bytes/param of HBM, affordable on 180 GB); 0: reshard after forward")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="ordered dQ accumulation in the attention backward: the loss is the same bits on every run "
+                         "(off by default: the unordered kernel is faster)")
     ap.add_argument("--comm", default=os.environ.get("FSB200_COMM", "symm"), choices=["symm", "nccl"],
                     help="collectives of the sharded arm: this library's NVLink peer-memory kernels or NCCL")
     return ap.parse_args()
@@ -217,7 +220,9 @@ def build_ours(args, world):
 
 def run_ours(args, rank, local, world):
     from flex_shard_b200 import ops
+    from flex_shard_b200.ops import attention as _attention
 
+    _attention.set_deterministic(True if args.deterministic else None)
     cfg, model, opt = build_ours(args, world)
     B, S = args.local_batch, args.seq_len
     dev = torch.device("cuda", local)
@@ -296,6 +301,7 @@ def run_ours(args, rank, local, world):
                                     + ", prefetch, bf16 params / fp32 reduce+AdamW state, "
                                     + ("gathered params kept until backward" if args.keep_unsharded else "reshard after forward"),
                        "collectives": (args.comm if world > 1 else "none (1 rank)"),
+                       "deterministic": bool(args.deterministic),
                        "l2": "working set per step (>=16 GB of weights) is far larger than the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "exposed_comm_ms": exposed,

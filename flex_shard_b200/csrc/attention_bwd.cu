@@ -25,6 +25,15 @@
 // executes in issue order, so "S(i), dP(i) complete" also means "every product of tile i-2 is
 // complete": that one wait also frees the P^T / dS^T buffers of tile i-2 for tile i.
 // TMEM: S (64 columns) + dP (64) + dQ[2] (128) + dV (128) + dK (128) = 512 columns.
+//
+// Ordered mode (BwdArgs::turns != nullptr): the sum that forms dQ gets a fixed order, so two runs give
+// the same bits. Every (batch, query head, query tile) has a turn counter; the CTA of kv tile t adds its
+// contribution only when the counter shows that kv tiles 0..t-1 have added theirs (4 drain warps each, so
+// it waits for 4 t), and raises it afterwards (fence, then one atomic per drain warp). CTAs take their
+// (head, kv tile) from a ticket counter instead of blockIdx, in the same longest-first order: a CTA that
+// holds ticket n knows that every ticket below n is held by a CTA that is already running, and the CTA a
+// turn waits for always has a lower ticket, so the waits cannot deadlock whatever order the hardware
+// starts blocks in. The waits are bounded like every other wait of the kernel.
 #include "common.cuh"
 
 namespace {
@@ -48,6 +57,7 @@ struct BwdArgs {
   const float* lse;    // [B, Hq, S]
   const float* delta;  // [B, Hq, S]
   float* dq_acc;       // [B*S, Hq*128] fp32, zero-initialised
+  int* turns;          // ordered mode: [B*Hq*(S/64)] turn counters followed by one ticket counter, all zero; else null
   __nv_bfloat16* dk;
   long long lddk;
   __nv_bfloat16* dv;
@@ -62,6 +72,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 __device__ __forceinline__ void red_add_f32(float* p, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+// Lane 0 of a drain warp waits until `*ctr` reaches `want` (acquire), bounded.
+constexpr uint32_t kTurnSpin = 1u << 21;
+__device__ __forceinline__ bool turn_wait(const int* ctr, int want, volatile int* abort_flag,
+                                          const volatile int* status) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < kTurnSpin; ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= want) return true;
+    if (i > 16) __nanosleep(200);
+    if ((i & 63) == 63 && *abort_flag) return false;
+    if ((i & 1023) == 1023 && *status != 0) return false;   // another CTA gave up: do not wait out the limit
+  }
+  return false;
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -88,12 +114,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* all_done = bars + 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* ticket_slot = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // x = (kv head, batch) so that CTAs are handed out tile by tile: kv tile 0 has the most
   // query tiles below the diagonal, so ascending y is longest-job-first.
-  const int kv_tile = blockIdx.y;
-  const int hk = blockIdx.x % args.Hkv, b = blockIdx.x / args.Hkv;
+  int work = blockIdx.y * gridDim.x + blockIdx.x;
+  if (args.turns != nullptr) {   // ordered mode: the same order, but taken from a ticket counter
+    if (threadIdx.x == 0)
+      *ticket_slot = atomicAdd(args.turns + static_cast<long long>(args.Hq) * (args.S / BQ) * (gridDim.x / args.Hkv), 1);
+    __syncthreads();
+    work = *ticket_slot;
+  }
+  const int kv_tile = work / static_cast<int>(gridDim.x);
+  const int bx = work % static_cast<int>(gridDim.x);
+  const int hk = bx % args.Hkv, b = bx / args.Hkv;
   const int G = args.Hq / args.Hkv;
   const int kv0 = kv_tile * BKV;
   const int row_base = b * args.S;
@@ -399,6 +434,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const float sc = args.scale;
     const long long ldq = static_cast<long long>(args.Hq) * HD;
     int qt = qt_first, g = 0;
+    int* prev_turn = nullptr;
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(&dq_full[it & 1], (it >> 1) & 1, abort_flag)) {
         if (lane == 0) {
@@ -415,6 +451,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_free[it & 1]);
+      int* turn = nullptr;
+      if (args.turns != nullptr) {
+        // Raise the previous tile's turn first: its additions were issued an iteration ago and have mostly
+        // been performed, so the fence that orders them before the counter costs little here, while a fence
+        // right behind the additions would wait for all of them.
+        if (prev_turn != nullptr) {
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence();
+            atomicAdd(prev_turn, 1);
+          }
+        }
+        turn = args.turns + (static_cast<long long>(b) * args.Hq + hk * G + g) * (args.S / BQ) + qt;
+        prev_turn = turn;
+        uint32_t ok = 1;
+        if (lane == 0) ok = turn_wait(turn, 4 * kv_tile, abort_flag, args.status) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) {
+            atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_PEER);
+            *abort_flag = 1;
+          }
+          prev_turn = nullptr;
+          break;
+        }
+      }
       float* base = args.dq_acc + static_cast<long long>(row_base + qt * BQ) * ldq + (hk * G + g) * HD + d;
 #pragma unroll
       for (int c = 0; c < 32; ++c) red_add_f32(base + c * ldq, __uint_as_float(v0[c]) * sc);
@@ -423,6 +485,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (++qt == qt_first + n_qt) {
         qt = qt_first;
         ++g;
+      }
+    }
+    if (prev_turn != nullptr) {   // the last tile's turn
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        atomicAdd(prev_turn, 1);
       }
     }
   }
@@ -468,9 +537,10 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 }  // namespace
 
 // dq_acc: fp32 [B*S, Hq*128], must be zero on entry. dk/dv: bf16 [B*S, Hkv*128] slices with row
-// strides lddk/lddv. delta: fp32 scratch [B, Hq, S] (written here).
+// strides lddk/lddv. delta: fp32 scratch [B, Hq, S] (written here). turns: null, or B*Hq*(S/64) + 1 zeroed
+// ints, which selects the ordered (bitwise reproducible) accumulation of dQ.
 FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                         const float* lse, float* delta, float* dq_acc, void* dk, void* dv, int B, int S,
+                         const float* lse, float* delta, float* dq_acc, int* turns, void* dk, void* dv, int B, int S,
                          int Hq, int Hkv, long long ldq, long long ldk, long long ldv, long long ldo,
                          long long lddo, long long lddk, long long lddv, float softmax_scale,
                          int* status, cudaStream_t stream) {
@@ -498,7 +568,7 @@ FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void
   a.S = S; a.Hq = Hq; a.Hkv = Hkv;
   a.scale = softmax_scale;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
-  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
+  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc; a.turns = turns;
   a.dk = static_cast<__nv_bfloat16*>(dk); a.lddk = lddk;
   a.dv = static_cast<__nv_bfloat16*>(dv); a.lddv = lddv;
   a.status = status;

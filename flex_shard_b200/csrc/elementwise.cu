@@ -373,6 +373,89 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   }
 }
 
+// The same result with one read and one write of the logits: the row is held on chip between the passes,
+// its first `smem_vecs` 16-byte vectors in shared memory and the rest (up to CE_RV per thread) in registers.
+// While the row streams in, every thread keeps a running maximum and a sum of exponentials relative to it
+// (rescaled when the maximum grows), so the exponentials of the first pass hide under the loads; the block
+// then combines the (max, sum) pairs, and the final pass turns the resident row into gradients while the
+// stores drain. One CTA per SM (the row takes nearly all of its shared memory).
+constexpr int CE_RV = 4;
+constexpr int CE_SMEM_VECS = 14336;   // 224 KB of the row in shared memory
+__global__ void __launch_bounds__(CE_THREADS, 1)
+cross_entropy_resident_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
+                              float* __restrict__ loss, int V, long long ld, float grad_scale,
+                              long long ignore_index, int smem_vecs) {
+  extern __shared__ __align__(16) uint4 rowv[];
+  __shared__ float red[32];
+  const float L2E = 1.4426950408889634f;
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  uint4* g = reinterpret_cast<uint4*>(lr);
+  const long long tgt = target[row];
+  const bool ignored = (tgt == ignore_index);
+  const int nvec = V / 8;
+  const int tid = threadIdx.x;
+  float tgt_logit = 0.f;
+  if (tid == 0 && !ignored) tgt_logit = __bfloat162float(lr[tgt]);
+  float m = -INFINITY, s = 0.f;
+  auto take = [&](const uint4& v) {
+    float f[8];
+    unpack8(v, f);
+    float vm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+    if (vm > m) {
+      s *= exp2f((m - vm) * L2E);
+      m = vm;
+    }
+    const float mo = -m * L2E;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += exp2f(fmaf(f[j], L2E, mo));
+  };
+  uint4 rv[CE_RV];
+#pragma unroll
+  for (int k = 0; k < CE_RV; ++k) {
+    const int idx = smem_vecs + tid + k * CE_THREADS;
+    rv[k] = idx < nvec ? g[idx] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf: adds nothing
+  }
+  int i = tid;
+  for (; i + 3 * CE_THREADS < smem_vecs; i += 4 * CE_THREADS) {
+    const uint4 a = g[i], b = g[i + CE_THREADS], c = g[i + 2 * CE_THREADS], d = g[i + 3 * CE_THREADS];
+    rowv[i] = a; rowv[i + CE_THREADS] = b; rowv[i + 2 * CE_THREADS] = c; rowv[i + 3 * CE_THREADS] = d;
+    take(a); take(b); take(c); take(d);
+  }
+  for (; i < smem_vecs; i += CE_THREADS) {
+    const uint4 a = g[i];
+    rowv[i] = a;
+    take(a);
+  }
+#pragma unroll
+  for (int k = 0; k < CE_RV; ++k)
+    if (smem_vecs + tid + k * CE_THREADS < nvec) take(rv[k]);
+  const float mx = block_max<CE_THREADS>(m, red);
+  const float se = block_sum<CE_THREADS>(m == -INFINITY ? 0.f : s * exp2f((m - mx) * L2E), red);
+  if (tid == 0) loss[row] = ignored ? 0.f : (logf(se) + mx - tgt_logit);
+  const float inv = ignored ? 0.f : grad_scale / se;
+  const float mo = -mx * L2E;
+  const int tv = ignored ? -1 : static_cast<int>(tgt >> 3), tj = static_cast<int>(tgt & 7);
+  auto grad = [&](const uint4& v, int idx) {
+    float f[8];
+    unpack8(v, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = exp2f(fmaf(f[j], L2E, mo)) * inv;
+    if (idx == tv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j == tj) f[j] -= grad_scale;
+    }
+    g[idx] = pack8(f);
+  };
+  for (i = tid; i < smem_vecs; i += CE_THREADS) grad(rowv[i], i);   // each thread reads back what it stored itself
+#pragma unroll
+  for (int k = 0; k < CE_RV; ++k) {
+    const int idx = smem_vecs + tid + k * CE_THREADS;
+    if (idx < nvec) grad(rv[k], idx);
+  }
+}
+
 // ------------------------------------------------------------------ AdamW over a flat shard
 // p: fp32 or bf16 master; g: fp32 or bf16; m, v: fp32. Optional `p_lowp`
 // receives the updated parameter as bf16 (the all-gather send buffer when the
@@ -472,21 +555,42 @@ struct SegDesc {
   int mode;
   int pad;
 };
-__global__ void segment_kernel(const SegDesc* __restrict__ descs, int chunks_per_seg) {
+// 16-byte vectors, four in flight per thread: a long segment is a streaming copy and needs the loads of
+// many iterations outstanding to fill the memory pipeline.
+template <typename LoadStore>
+__device__ __forceinline__ void seg_loop4(long long nv, long long tid, long long stride, LoadStore body) {
+  long long i = tid;
+  for (; i + 3 * stride < nv; i += 4 * stride) body(i, i + stride, i + 2 * stride, i + 3 * stride, 4);
+  for (; i < nv; i += stride) body(i, i, i, i, 1);
+}
+
+__global__ void __launch_bounds__(256) segment_kernel(const SegDesc* __restrict__ descs, int chunks_per_seg) {
   const SegDesc d = descs[blockIdx.y];
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   (void)chunks_per_seg;
+  const uintptr_t sa = reinterpret_cast<uintptr_t>(d.src), da = reinterpret_cast<uintptr_t>(d.dst);
   if (d.mode == 0 || d.mode == 3) {
-    const uintptr_t sa = reinterpret_cast<uintptr_t>(d.src), da = reinterpret_cast<uintptr_t>(d.dst);
     uint8_t* dst = static_cast<uint8_t*>(d.dst);
     const uint8_t* src = static_cast<const uint8_t*>(d.src);
     const bool zero = d.mode == 3;
     if (((da | (zero ? 0 : sa)) & 15) == 0) {
       const long long nv = d.n / 16;
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      for (long long i = tid; i < nv; i += stride)
-        reinterpret_cast<uint4*>(dst)[i] = zero ? z : reinterpret_cast<const uint4*>(src)[i];
+      uint4* dv = reinterpret_cast<uint4*>(dst);
+      const uint4* sv = reinterpret_cast<const uint4*>(src);
+      if (zero) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (long long i = tid; i < nv; i += stride) dv[i] = z;
+      } else {
+        seg_loop4(nv, tid, stride, [&](long long i0, long long i1, long long i2, long long i3, int cnt) {
+          if (cnt == 4) {
+            const uint4 a = sv[i0], b = sv[i1], c = sv[i2], e = sv[i3];
+            dv[i0] = a; dv[i1] = b; dv[i2] = c; dv[i3] = e;
+          } else {
+            dv[i0] = sv[i0];
+          }
+        });
+      }
       for (long long i = nv * 16 + tid; i < d.n; i += stride) dst[i] = zero ? 0 : src[i];
     } else if (((da | (zero ? 0 : sa)) & 3) == 0 && (d.n & 3) == 0) {
       for (long long i = tid; i < d.n / 4; i += stride)
@@ -497,11 +601,55 @@ __global__ void segment_kernel(const SegDesc* __restrict__ descs, int chunks_per
   } else if (d.mode == 1) {
     const float* src = static_cast<const float*>(d.src);
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(d.dst);
-    for (long long i = tid; i < d.n; i += stride) dst[i] = __float2bfloat16(src[i]);
+    long long done = 0;
+    if (((sa | da) & 15) == 0) {   // eight elements per vector: two float4 in, one 16-byte store out
+      const long long nv = d.n / 8;
+      const float4* sv = reinterpret_cast<const float4*>(src);
+      uint4* dv = reinterpret_cast<uint4*>(dst);
+      auto cvt = [](const float4& lo, const float4& hi) {
+        uint4 o;
+        o.x = pack_bf16x2(lo.x, lo.y); o.y = pack_bf16x2(lo.z, lo.w);
+        o.z = pack_bf16x2(hi.x, hi.y); o.w = pack_bf16x2(hi.z, hi.w);
+        return o;
+      };
+      seg_loop4(nv, tid, stride, [&](long long i0, long long i1, long long i2, long long i3, int cnt) {
+        if (cnt == 4) {
+          const float4 a0 = sv[2 * i0], a1 = sv[2 * i0 + 1], b0 = sv[2 * i1], b1 = sv[2 * i1 + 1];
+          const float4 c0 = sv[2 * i2], c1 = sv[2 * i2 + 1], e0 = sv[2 * i3], e1 = sv[2 * i3 + 1];
+          dv[i0] = cvt(a0, a1); dv[i1] = cvt(b0, b1); dv[i2] = cvt(c0, c1); dv[i3] = cvt(e0, e1);
+        } else {
+          dv[i0] = cvt(sv[2 * i0], sv[2 * i0 + 1]);
+        }
+      });
+      done = nv * 8;
+    }
+    for (long long i = done + tid; i < d.n; i += stride) dst[i] = __float2bfloat16(src[i]);
   } else {
     const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(d.src);
     float* dst = static_cast<float*>(d.dst);
-    for (long long i = tid; i < d.n; i += stride) dst[i] = __bfloat162float(src[i]);
+    long long done = 0;
+    if (((sa | da) & 15) == 0) {   // eight elements per vector: one 16-byte load in, two float4 out
+      const long long nv = d.n / 8;
+      const uint4* sv = reinterpret_cast<const uint4*>(src);
+      float4* dv = reinterpret_cast<float4*>(dst);
+      auto put = [&](long long i, const uint4& v) {
+        // a bf16 is the upper half of the fp32 with the same value
+        dv[2 * i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+        dv[2 * i + 1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                    __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+      };
+      seg_loop4(nv, tid, stride, [&](long long i0, long long i1, long long i2, long long i3, int cnt) {
+        if (cnt == 4) {
+          const uint4 a = sv[i0], b = sv[i1], c = sv[i2], e = sv[i3];
+          put(i0, a); put(i1, b); put(i2, c); put(i3, e);
+        } else {
+          put(i0, sv[i0]);
+        }
+      });
+      done = nv * 8;
+    }
+    for (long long i = done + tid; i < d.n; i += stride) dst[i] = __bfloat162float(src[i]);
   }
 }
 
@@ -569,8 +717,38 @@ FSB_API int fsb_cross_entropy(void* logits, const long long* target, float* loss
                               long long ld, float grad_scale, long long ignore_index,
                               cudaStream_t stream) {
   if (V % 8 != 0 || ld % 8 != 0) return FSB_ERR_BAD_ARG;
+  const int nvec = V / 8;
+  const int smem_vecs = nvec < CE_SMEM_VECS ? nvec : CE_SMEM_VECS;
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && nvec - smem_vecs <= CE_RV * CE_THREADS) {
+    // the row fits on chip: one read and one write
+    const size_t smem = static_cast<size_t>(smem_vecs) * 16;
+    if (cudaFuncSetAttribute(cross_entropy_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FSB_ERR_LAUNCH;
+    cross_entropy_resident_kernel<<<static_cast<unsigned>(T), CE_THREADS, smem, stream>>>(
+        static_cast<__nv_bfloat16*>(logits), target, loss, V, ld, grad_scale, ignore_index, smem_vecs);
+    return launch_ok();
+  }
   cross_entropy_kernel<<<static_cast<unsigned>(T), CE_THREADS, 0, stream>>>(
       static_cast<__nv_bfloat16*>(logits), target, loss, V, ld, grad_scale, ignore_index);
+  return launch_ok();
+}
+
+// The same with the descriptor table left in page-locked host memory: every CTA fetches its own 32-byte
+// record over the host link, which saves the table's host-to-device copy (a copy-engine operation between
+// two kernels of the same stream costs more than the fetch for the few dozen records of a bucket).
+// Returns FSB_ERR_BAD_ARG when the table is not device-accessible page-locked memory.
+FSB_API int fsb_segment_op_host(const void* host_descs, int nseg, int blocks_per_seg, cudaStream_t stream) {
+  if (nseg <= 0) return FSB_OK;
+  if (nseg > 65535) return FSB_ERR_TOO_LARGE;
+  void* dptr = nullptr;
+  if (cudaHostGetDevicePointer(&dptr, const_cast<void*>(host_descs), 0) != cudaSuccess || dptr == nullptr) {
+    (void)cudaGetLastError();
+    return FSB_ERR_BAD_ARG;
+  }
+  if (blocks_per_seg < 1) blocks_per_seg = 1;
+  dim3 grid(blocks_per_seg, nseg);
+  segment_kernel<<<grid, 256, 0, stream>>>(static_cast<const SegDesc*>(dptr), blocks_per_seg);
   return launch_ok();
 }
 

@@ -99,6 +99,7 @@ def _declare(lib) -> None:
         "fsb_adamw": [vp, vp, vp, vp, vp, i64, i32, i32, f32, f32, f32, f32, f32, i32, f32, vp],
         "fsb_cast_scale": [vp, vp, i64, i32, f32, i32, vp],
         "fsb_segment_op": [vp, i32, i32, vp],
+        "fsb_segment_op_host": [vp, i32, i32, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name, None)

@@ -26,12 +26,29 @@ def _declare():
 
     vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_float
     _lib.declare("fsb_attn_fwd", [vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, f32, vp, vp])
-    _lib.declare("fsb_attn_bwd", [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+    _lib.declare("fsb_attn_bwd", [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                   i64, i64, i64, i64, i64, i64, i64, f32, vp, vp])
     _lib.declare("fsb_cast2d_f32_bf16", [vp, vp, i64, i32, i64, i64, vp])
 
 
 _declared = False
+_deterministic: bool | None = None
+
+
+def set_deterministic(enabled: bool | None) -> None:
+    """Ordered accumulation of dQ in the backward kernel (the same bits on every run) on / off; ``None``
+    returns to the default: on when ``torch.use_deterministic_algorithms(True)`` is set or the environment
+    variable ``FSB200_DETERMINISTIC`` is ``1``."""
+    global _deterministic
+    _deterministic = enabled
+
+
+def is_deterministic() -> bool:
+    if _deterministic is not None:
+        return _deterministic
+    import os
+
+    return os.environ.get("FSB200_DETERMINISTIC", "0") == "1" or torch.are_deterministic_algorithms_enabled()
 
 
 def _ensure():
@@ -117,13 +134,18 @@ class _QKVAttention(torch.autograd.Function):
         d_o = d_o.contiguous()
         dev = qkv.device
         dqkv = torch.empty_like(qkv)
-        dq_acc = torch.zeros(B * S, Hq * HD, dtype=torch.float32, device=dev)
+        # the fp32 dQ accumulator and, in ordered mode, the turn counters behind it: one zero-fill
+        n_acc = B * S * Hq * HD
+        n_turns = B * Hq * (S // 64) + 1 if is_deterministic() else 0
+        zeroed = torch.zeros(n_acc + n_turns, dtype=torch.float32, device=dev)
+        dq_acc = zeroed[:n_acc]
+        turns = zeroed.data_ptr() + n_acc * 4 if n_turns else None
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
         base, dbase = qkv.data_ptr(), dqkv.data_ptr()
         status = _lib.status_word(dev)
         lib = _lib.load()
         rc = lib.fsb_attn_bwd(base, base + Hq * HD * 2, base + (Hq + Hkv) * HD * 2, o.data_ptr(),
-                              d_o.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
+                              d_o.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), turns,
                               dbase + Hq * HD * 2, dbase + (Hq + Hkv) * HD * 2, B, S, Hq, Hkv,
                               C, C, C, Hq * HD, Hq * HD, C, C, scale, status.data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc, "fsb_attn_bwd")

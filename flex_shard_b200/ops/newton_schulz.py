@@ -33,7 +33,14 @@ def _ensure():
         _lib.declare("fsb_muon_prepare", [vp, vp, i32, vp, vp, i64, f32, i32, vp])
         _lib.declare("fsb_muon_scale", [vp, vp, i64, f32, vp])
         _lib.declare("fsb_muon_update", [vp, i32, vp, i64, f32, f32, vp])
+        _lib.declare("fsb_muon_workspace_floats", [])
         _declared = True
+
+
+def _workspace(device) -> torch.Tensor:
+    """Zeroed scratch of the prepare kernel: [0] receives the sum of squares, the rest holds the per-block
+    partial sums, which the last block adds in index order (the same bits on every run)."""
+    return torch.zeros(_lib.load().fsb_muon_workspace_floats(), dtype=torch.float32, device=device)
 
 
 def ns_iterations(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> torch.Tensor:
@@ -93,7 +100,7 @@ def muon_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: float, neste
     g = grad.contiguous()
     assert momentum.is_contiguous() and momentum.dtype == torch.float32
     u = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
-    ss = torch.zeros(1, dtype=torch.float32, device=g.device)
+    ss = _workspace(g.device)
     s = _lib.stream_ptr(g.device)
     rc = lib.fsb_muon_prepare(momentum.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), u.data_ptr(),
                               ss.data_ptr(), g.numel(), mu, int(nesterov), s)
@@ -116,7 +123,7 @@ def muon_momentum_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: flo
     g = grad.contiguous()
     assert momentum.is_contiguous()
     u = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
-    ss = torch.zeros(1, dtype=torch.float32, device=g.device)
+    ss = _workspace(g.device)
     rc = _lib.load().fsb_muon_prepare(momentum.data_ptr(), g.data_ptr(), int(g.dtype == torch.float32), u.data_ptr(),
                                       ss.data_ptr(), g.numel(), mu, int(nesterov), _lib.stream_ptr(g.device))
     _lib.check(rc, "fsb_muon_prepare")

@@ -8,7 +8,8 @@ bf16->fp32, zero-fill; 16-byte vectors when the addresses allow).
 
 The decomposition of a given list of shapes / strides / dtypes is computed once and cached as offsets
 relative to each view's address (numpy arrays); a later call with the same geometry only adds the current
-base addresses and uploads the table through pinned memory.  CPU tensors take a plain ``copy_`` loop, which
+base addresses and writes the table to pinned memory, which the kernel reads in place (short tables) or
+which is uploaded first (long ones).  CPU tensors take a plain ``copy_`` loop, which
 is also the oracle the GPU test compares against.
 
 Parity: the role of the reference's Triton copy kernels and their launchers
@@ -88,7 +89,9 @@ class _Plan:
         cat = (lambda xs, dt: np.concatenate(xs) if xs else np.zeros(0, dt))
         self.op, self.doff, self.soff = cat(op, np.int64), cat(doff, np.int64), cat(soff, np.int64)
         self.n, self.mode = cat(n, np.int64), cat(mode, np.int32)
-        self.blocks = int(max(1, min(32, longest // (64 * 1024))))
+        # CTAs per run: enough for the longest run to stream at full bandwidth (32 KB per CTA), bounded so that
+        # the whole grid stays near sixteen CTAs per SM
+        self.blocks = int(max(1, min(longest // (32 * 1024), (148 * 16) // max(1, self.op.size))))
 
 
 def _key(ops):
@@ -132,13 +135,24 @@ def run_segment_ops(ops, cache: dict | None = None) -> int:
     table["n"], table["mode"], table["pad"] = plan.n, plan.mode, 0
     dev = ops[0][0].device
     host = torch.from_numpy(table.view(np.uint8)).pin_memory()
-    descs = host.to(dev, non_blocking=True)
     lib, stream, launches = _lib.load(), _lib.stream_ptr(dev), 0
-    for lo in range(0, nseg, _MAX_SEGS):
-        cnt = min(_MAX_SEGS, nseg - lo)
-        rc = lib.fsb_segment_op(descs.data_ptr() + lo * _DESC.itemsize, cnt, plan.blocks, stream)
-        _lib.check(rc, "fsb_segment_op")
-        launches += 1
+    descs = None
+    global _host_tables
+    if _host_tables and nseg <= _HOST_TABLE_MAX:
+        # short table: the kernel reads it where it is (page-locked host memory), no copy in the stream
+        rc = lib.fsb_segment_op_host(host.data_ptr(), nseg, plan.blocks, stream)
+        if rc == 1:
+            _host_tables = False     # not device-accessible on this system: upload tables from now on
+        else:
+            _lib.check(rc, "fsb_segment_op_host")
+            launches = 1
+    if not launches:
+        descs = host.to(dev, non_blocking=True)
+        for lo in range(0, nseg, _MAX_SEGS):
+            cnt = min(_MAX_SEGS, nseg - lo)
+            rc = lib.fsb_segment_op(descs.data_ptr() + lo * _DESC.itemsize, cnt, plan.blocks, stream)
+            _lib.check(rc, "fsb_segment_op")
+            launches += 1
     count_launch(launches)
     # the pinned table must outlive the asynchronous upload: park it until the stream has passed this point
     _park(host, descs, dev)
@@ -146,6 +160,8 @@ def run_segment_ops(ops, cache: dict | None = None) -> int:
 
 
 _parked: list = []
+_host_tables = True
+_HOST_TABLE_MAX = 512
 
 
 def _park(host, descs, dev) -> None:

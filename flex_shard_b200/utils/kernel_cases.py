@@ -2,8 +2,8 @@
 
     python -m flex_shard_b200.utils.kernel_cases <case> [--iters N]
 
-Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, adamw, rmsnorm, swiglu, cross_entropy,
-newton_schulz, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm. Each prints one JSON line with the CUDA-event time (median of
+Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_bwd_ordered, adamw, rmsnorm, swiglu, cross_entropy,
+newton_schulz, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm, segment_cast. Each prints one JSON line with the CUDA-event time (median of
 ``iters`` launches after 3 warm-up launches, L2 flushed between launches by writing a 256 MB buffer)
 and the achieved FLOP/s or bytes/s. Inputs are a few hundred MB, larger than the 126 MB L2, so DRAM
 counters of a profiler capture of the same command stay meaningful.
@@ -67,7 +67,8 @@ def main():
             fn = lambda: ops.gemm(a, b, a_t=True, b_t=True, out=d)
         ms = _time(fn, args.iters)
         out.update(M=M, N=N, K=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9)
-    elif args.case in ("attn_fwd", "attn_bwd"):
+    elif args.case in ("attn_fwd", "attn_bwd", "attn_bwd_ordered"):
+        att.set_deterministic(args.case == "attn_bwd_ordered")
         B, S, Hq, Hkv = 1, 8192, 16, 4
         qkv = (0.5 * torch.randn(B, S, (Hq + 2 * Hkv) * 128, device=dev)).bfloat16()
         flops_fwd = 4.0 * B * Hq * S * S * 128 * 0.5
@@ -93,6 +94,21 @@ def main():
         fn = lambda: ew.adamw_step_(p, g, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
         ms = _time(fn, args.iters)
         out.update(n=n, ms=ms, gbs=n * 24 / ms / 1e6)
+    elif args.case == "segment_cast":
+        # a Llama layer bucket's gradient copy-in: seven bf16 weight gradients widened into one fp32 row
+        from flex_shard_b200.ops.segments import run_segment_ops
+
+        shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (4096,), (4096,)]
+        srcs = [torch.randn(*sh, device=dev).bfloat16() for sh in shapes]
+        n = sum(t.numel() for t in srcs)
+        row = torch.empty(n, device=dev)
+        dsts, o = [], 0
+        for t in srcs:
+            dsts.append(row[o:o + t.numel()].view(t.shape))
+            o += t.numel()
+        fn = lambda: run_segment_ops(list(zip(dsts, srcs)))
+        ms = _time(fn, args.iters)
+        out.update(elements=n, ms=ms, gbs=n * 6 / ms / 1e6)
     elif args.case == "rmsnorm":
         T, D = 32768, 4096
         x = torch.randn(T, D, device=dev).bfloat16()

@@ -11,8 +11,16 @@ from flex_shard_b200.ops import elementwise as ew
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _default_mode():
+    yield
+    att.set_deterministic(None)
+
+
+@pytest.mark.parametrize("ordered", [True, False])
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (1, 256, 2, 1), (2, 512, 4, 2), (1, 1024, 8, 2)])
-def test_attention_fwd_bwd(B, S, Hq, Hkv):
+def test_attention_fwd_bwd(B, S, Hq, Hkv, ordered):
+    att.set_deterministic(ordered)
     torch.manual_seed(0)
     dev = torch.device("cuda")
     C = (Hq + 2 * Hkv) * 128
@@ -54,4 +62,27 @@ def test_attention_with_rope_matches_cpu_path():
     oc.backward(g.cpu())
     torch.testing.assert_close(o.cpu().float(), oc.float(), rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(x.grad.cpu().float(), xc.grad.float(), rtol=5e-2, atol=5e-2)
+    ops.check_status()
+
+
+def test_ordered_backward_is_bitwise_reproducible():
+    """With the ordered dQ accumulation every element is summed in kv-tile order: repeated backward passes
+    give identical bits although 16 kv tiles (x 4 drain warps) add into the last query tiles."""
+    att.set_deterministic(True)
+    torch.manual_seed(2)
+    dev = torch.device("cuda")
+    B, S, Hq, Hkv = 2, 2048, 8, 2
+    qkv = (0.5 * torch.randn(B, S, (Hq + 2 * Hkv) * 128, device=dev)).bfloat16()
+    x = qkv.clone().requires_grad_()
+    o = att.qkv_attention(x, None, Hq, Hkv)
+    g = torch.randn_like(o)
+    first = torch.autograd.grad(o, x, g, retain_graph=True)[0].clone()
+    for _ in range(4):
+        again = torch.autograd.grad(o, x, g, retain_graph=True)[0]
+        assert torch.equal(first, again)
+    ops.check_status()
+    # and it is the same function as the unordered kernel up to the order of fp32 additions
+    att.set_deterministic(False)
+    loose = torch.autograd.grad(o, x, g, retain_graph=True)[0]
+    torch.testing.assert_close(first.float(), loose.float(), rtol=2e-2, atol=2e-3 * float(loose.float().abs().max()))
     ops.check_status()

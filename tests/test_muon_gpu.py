@@ -40,3 +40,34 @@ def test_muon_direction_and_apply_match_cpu():
         ns.muon_apply_(pg, x_cpu.cuda(), 0.02, 0.1, 1.5)
         torch.testing.assert_close(pg.float().cpu(), p.float(), rtol=1e-2, atol=1e-2)
     ops.check_status()
+
+
+def test_prepare_sum_is_reproducible_and_vector_paths_match_scalar():
+    """The sum of squares is formed from per-block partials in index order: identical bits on every run.
+    An odd length and a misaligned view go through the scalar loop and must agree with the vector path."""
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    for n, off in ((4096 * 3000, 0), (1234567, 0), (4096 * 64, 1)):
+        g = torch.randn(n + off, device=dev)[off:].view(1, -1)
+        m0 = 0.1 * torch.randn(n + off, device=dev)[off:].view(1, -1)
+        outs = []
+        for _ in range(3):
+            m = torch.empty(n + off, device=dev)[off:].view(1, -1)
+            m.copy_(m0)
+            u = ns.muon_momentum_direction_(m, g, 0.95, True)
+            outs.append((m.clone(), u.clone()))
+        m_ref = torch.lerp(m0, g, 0.05)
+        u_ref = torch.lerp(g, m_ref, 0.95).bfloat16()
+        for m, u in outs:
+            torch.testing.assert_close(m, m_ref, rtol=1e-6, atol=1e-7)
+            assert (u.float() - u_ref.float()).abs().max() <= 2 ** -7 * u_ref.float().abs().max()
+            assert torch.equal(u, outs[0][1]) and torch.equal(m, outs[0][0])
+    g = torch.randn(2048, 3000, device=dev)
+    xs = []
+    for _ in range(3):
+        m = torch.zeros_like(g)
+        xs.append(ns.muon_direction_(m, g, 0.95, True, 0))      # zero iterations: the normalised matrix itself
+    assert torch.equal(xs[0], xs[1]) and torch.equal(xs[0], xs[2])
+    ref = torch.lerp(g, 0.05 * g, 0.95).bfloat16().float()
+    torch.testing.assert_close(xs[0].float(), ref / ref.norm(), rtol=2e-2, atol=1e-6)
+    ops.check_status()

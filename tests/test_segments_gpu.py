@@ -49,6 +49,28 @@ def test_one_launch_equals_copy_loop():
         assert torch.equal(out2[k], ref[k]), k
 
 
+def test_long_runs_vector_paths_and_tails():
+    """Long contiguous runs (the benchmark's gradient copy-in: bf16 -> fp32 of whole weights) go through the
+    16-byte paths with four vectors in flight; lengths that are not multiples of the vector width and a
+    misaligned run exercise the tails and the scalar fallback."""
+    from flex_shard_b200.ops.segments import run_segment_ops
+
+    dev = torch.device("cuda")
+    torch.manual_seed(1)
+    n = 8 * 1024 * 1024 + 5
+    f = torch.randn(n, device=dev)
+    h = torch.randn(n, device=dev).bfloat16()
+    outs = [torch.zeros(n, device=dev), torch.zeros(n, device=dev, dtype=torch.bfloat16),
+            torch.zeros(n, device=dev), torch.zeros(n + 1, device=dev, dtype=torch.bfloat16),
+            torch.zeros(n + 1, device=dev)]
+    ops = [(outs[0], h), (outs[1], f), (outs[2], f), (outs[3][1:], f), (outs[4][1:], h)]
+    run_segment_ops(ops)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], h.float()) and torch.equal(outs[1], f.bfloat16()) and torch.equal(outs[2], f)
+    assert torch.equal(outs[3][1:], f.bfloat16()) and torch.equal(outs[4][1:], h.float())
+    assert outs[3][0] == 0 and outs[4][0] == 0
+
+
 def _launch_worker(rank, world, port, out):
     import os
 
