@@ -57,6 +57,7 @@ struct BwdArgs {
   const float* lse;    // [B, Hq, S]
   const float* delta;  // [B, Hq, S]
   float* dq_acc;       // [B*S, Hq*128] fp32, zero-initialised
+  int heads_inner;     // walk order of the (query tile, head) pairs, see TileWalk
   int* turns;          // ordered mode: [B*Hq*(S/64)] turn counters followed by one ticket counter, all zero; else null
   __nv_bfloat16* dk;
   long long lddk;
@@ -73,6 +74,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void red_add_f32(float* p, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
+
+// The order in which a CTA visits its (query tile, head of the group) pairs.
+//   heads_inner == 0: head by head, query tiles ascending from the diagonal.
+//   heads_inner == 1: query tiles descending from the last one, the heads of the group inside. Every CTA of
+//     a kv head then starts on the same tile and a CTA with a later kv tile simply stops earlier, so in the
+//     ordered mode a CTA runs one hand-over behind its predecessor from the first tile to the last and
+//     never has to catch up with it again (head by head it would wait at every change of head).
+struct TileWalk {
+  int qt, g;
+  __device__ __forceinline__ TileWalk(int first, int n_qt, int heads_inner)
+      : qt(heads_inner ? first + n_qt - 1 : first), g(0) {}
+  __device__ __forceinline__ void next(int first, int n_qt, int G, int heads_inner) {
+    if (heads_inner) {
+      if (++g == G) {
+        g = 0;
+        --qt;
+      }
+    } else if (++qt == first + n_qt) {
+      qt = first;
+      ++g;
+    }
+  }
+};
 
 // Lane 0 of a drain warp waits until `*ctr` reaches `want` (acquire), bounded.
 constexpr uint32_t kTurnSpin = 1u << 21;
@@ -181,15 +205,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tma_load_2d(sK + KV_TILE_BYTES / 2, &map_k, kv_full, hk * HD + 64, row_base + kv0);
       tma_load_2d(sV, &map_v, kv_full, hk * HD, row_base + kv0);
       tma_load_2d(sV + KV_TILE_BYTES / 2, &map_v, kv_full, hk * HD + 64, row_base + kv0);
-      int st = 0, pqt = qt_first, pg = 0;
+      int st = 0;
       uint32_t ph = 0;
+      TileWalk walk(qt_first, n_qt, args.heads_inner);
       for (int it = 0; it < n_it; ++it) {
-        const int h = hk * G + pg;
-        const int qt = pqt;
-        if (++pqt == qt_first + n_qt) {
-          pqt = qt_first;
-          ++pg;
-        }
+        const int h = hk * G + walk.g;
+        const int qt = walk.qt;
+        walk.next(qt_first, n_qt, G, args.heads_inner);
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag)) {
           atomicExch(args.status, FSB_ERR_WAIT_TIMEOUT_EMPTY);
           *abort_flag = 1;
@@ -323,29 +345,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float* s_lse = s_stats + (warp - 2) * 64;   // [32 lse | 32 delta] of this warp's 32 queries
     float* s_delta = s_lse + 32;
     // (head, query tile) of the running tile, advanced without divisions
-    int qt = qt_first;
-    const float* lse_p = args.lse + (static_cast<long long>(b) * args.Hq + hk * G) * args.S + c0 + lane;
-    const float* delta_p = args.delta + (static_cast<long long>(b) * args.Hq + hk * G) * args.S + c0 + lane;
+    TileWalk walk(qt_first, n_qt, args.heads_inner);
+    // index of this lane's statistic in lse / delta for (head 0 of the group, query 0); B * Hq * S < 2^31 (checked by the host)
+    const int stat_base = (b * args.Hq + hk * G) * args.S + c0 + lane;
     float nl = 0.f, nd = 0.f;
     if (n_it > 0) {
-      nl = lse_p[qt * BQ];
-      nd = delta_p[qt * BQ];
+      nl = args.lse[stat_base + walk.g * args.S + walk.qt * BQ];
+      nd = args.delta[stat_base + walk.g * args.S + walk.qt * BQ];
     }
 
     for (int it = 0; it < n_it; ++it) {
-      const int q0 = qt * BQ;
+      const int q0 = walk.qt * BQ;
       __syncwarp();   // the previous tile's reads of the statistics are done
       s_lse[lane] = nl * LOG2E;
       s_delta[lane] = nd;
       __syncwarp();
-      if (++qt == qt_first + n_qt) {   // next head of the group
-        qt = qt_first;
-        lse_p += args.S;
-        delta_p += args.S;
-      }
+      walk.next(qt_first, n_qt, G, args.heads_inner);
       if (it + 1 < n_it) {   // next tile's statistics: the loads land while this tile is computed
-        nl = lse_p[qt * BQ];
-        nd = delta_p[qt * BQ];
+        nl = args.lse[stat_base + walk.g * args.S + walk.qt * BQ];
+        nd = args.delta[stat_base + walk.g * args.S + walk.qt * BQ];
       }
       // S(it), dP(it) complete also says that every product of tile it-2 is complete (one in-order
       // pipe), so P^T[it & 1] and dS^T[it & 1] may be overwritten.
@@ -433,7 +451,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int d = quarter * 32 + lane;   // dQ^T lane = head-dim index
     const float sc = args.scale;
     const long long ldq = static_cast<long long>(args.Hq) * HD;
-    int qt = qt_first, g = 0;
+    TileWalk walk(qt_first, n_qt, args.heads_inner);
     int* prev_turn = nullptr;
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(&dq_full[it & 1], (it >> 1) & 1, abort_flag)) {
@@ -463,7 +481,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             atomicAdd(prev_turn, 1);
           }
         }
-        turn = args.turns + (static_cast<long long>(b) * args.Hq + hk * G + g) * (args.S / BQ) + qt;
+        turn = args.turns + (static_cast<long long>(b) * args.Hq + hk * G + walk.g) * (args.S / BQ) + walk.qt;
         prev_turn = turn;
         uint32_t ok = 1;
         if (lane == 0) ok = turn_wait(turn, 4 * kv_tile, abort_flag, args.status) ? 1u : 0u;
@@ -477,15 +495,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           break;
         }
       }
-      float* base = args.dq_acc + static_cast<long long>(row_base + qt * BQ) * ldq + (hk * G + g) * HD + d;
+      float* base = args.dq_acc + static_cast<long long>(row_base + walk.qt * BQ) * ldq + (hk * G + walk.g) * HD + d;
 #pragma unroll
       for (int c = 0; c < 32; ++c) red_add_f32(base + c * ldq, __uint_as_float(v0[c]) * sc);
 #pragma unroll
       for (int c = 0; c < 32; ++c) red_add_f32(base + (32 + c) * ldq, __uint_as_float(v1[c]) * sc);
-      if (++qt == qt_first + n_qt) {
-        qt = qt_first;
-        ++g;
-      }
+      walk.next(qt_first, n_qt, G, args.heads_inner);
     }
     if (prev_turn != nullptr) {   // the last tile's turn
       __syncwarp();
@@ -538,13 +553,15 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 
 // dq_acc: fp32 [B*S, Hq*128], must be zero on entry. dk/dv: bf16 [B*S, Hkv*128] slices with row
 // strides lddk/lddv. delta: fp32 scratch [B, Hq, S] (written here). turns: null, or B*Hq*(S/64) + 1 zeroed
-// ints, which selects the ordered (bitwise reproducible) accumulation of dQ.
+// ints, which selects the ordered (bitwise reproducible) accumulation of dQ. heads_inner: the walk order
+// (see TileWalk); the ordered mode wants 1.
 FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                         const float* lse, float* delta, float* dq_acc, int* turns, void* dk, void* dv, int B, int S,
+                         const float* lse, float* delta, float* dq_acc, int* turns, int heads_inner, void* dk, void* dv, int B, int S,
                          int Hq, int Hkv, long long ldq, long long ldk, long long ldv, long long ldo,
                          long long lddo, long long lddk, long long lddv, float softmax_scale,
                          int* status, cudaStream_t stream) {
   if (S % BKV != 0 || Hq % Hkv != 0 || B <= 0 || (lddk % 8) || (lddv % 8)) return FSB_ERR_BAD_ARG;
+  if (static_cast<long long>(B) * Hq * S >= (1ll << 31)) return FSB_ERR_TOO_LARGE;
   CUtensorMap mq, mk, mv, mdo;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
   int rc = fsb_make_tmap_2d(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, static_cast<uint64_t>(Hq) * HD, ldq, BQ, 64);
@@ -568,7 +585,7 @@ FSB_API int fsb_attn_bwd(const void* q, const void* k, const void* v, const void
   a.S = S; a.Hq = Hq; a.Hkv = Hkv;
   a.scale = softmax_scale;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
-  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc; a.turns = turns;
+  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc; a.turns = turns; a.heads_inner = heads_inner ? 1 : 0;
   a.dk = static_cast<__nv_bfloat16*>(dk); a.lddk = lddk;
   a.dv = static_cast<__nv_bfloat16*>(dv); a.lddv = lddv;
   a.status = status;

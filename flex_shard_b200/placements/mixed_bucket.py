@@ -60,7 +60,14 @@ class MixedBucketPlacement(SlicedPlacement):
         return self.member.pieces(global_shape, rank, world_size)
 
     def reduces_grads_in_param_layout(self, infos) -> bool:
-        return False
+        """When every member of the bucket is whole on one owner and nothing casts between the gradient and the
+        reduce dtype, the gradients may be views of one buffer in parameter order that autograd accumulates
+        into (parity: ``custom_placements/mixed_bucket.py:1262-1282`` of the reference: all members one-hot
+        owned, one dtype for gathered parameters, gradient accumulation and reduction)."""
+        dtypes = {i.param_dtype for i in infos}
+        return (len(dtypes) == 1 and all(
+            getattr(getattr(i.placement, "member", None), "owner_style", False)
+            and i.param_dtype == (i.bucket_reduce_dtype or i.reduce_dtype) for i in infos))
 
 
 def make_mixed_placement_fn(member_fn):

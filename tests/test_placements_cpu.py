@@ -37,6 +37,9 @@ def _placement_fn(kind):
         from flex_shard_b200.placements import make_bucketed_block_shard_placement_fn
 
         return make_bucketed_block_shard_placement_fn((1, 3))
+    if kind == "mixed_owned":      # every member whole on one owner: gradients accumulate in one mirror buffer
+        return lambda named, mesh: {f: MixedBucketPlacement(BucketedOwned(((i % 2, 0, p.shape[0]),)))
+                                    for i, (f, p) in enumerate(named)}
     if kind == "mixed":
         def fn(named, mesh):
             out = {}
@@ -60,6 +63,8 @@ def _train(rank, world, kind, steps):
     ref = MLP()
     ref.load_state_dict(model.state_dict())
     flex_shard(model, [BucketSpec(["*"], placement_fn=_placement_fn(kind))])
+    st = model.sharded_bucket_storages[0]
+    assert st.placement.reduces_grads_in_param_layout(st.infos) == (kind in ("owned", "mixed_owned", "flat", "flat_uneven"))
     opt = torch.optim.SGD(model.parameters(), lr=0.1)
     ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
     for s in range(steps):
@@ -80,7 +85,7 @@ def _train(rank, world, kind, steps):
     return err, sizes, model.sharded_bucket_storages[0].total_bytes
 
 
-@pytest.mark.parametrize("kind", ["block", "owned", "mixed", "flat", "flat_uneven"])
+@pytest.mark.parametrize("kind", ["block", "owned", "mixed", "mixed_owned", "flat", "flat_uneven"])
 def test_sliced_placements_train_like_unsharded(kind):
     res = run_ranks(_train, 2, kind, 3)
     for err, sizes, nbytes in res:
