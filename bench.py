@@ -53,6 +53,9 @@ def parse():
                          "per step instead of two; +2 bytes/param of HBM, affordable on 180 GB); 0: reshard after forward")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds after which a run that has not finished prints every thread's Python stack and "
+                         "exits with an error (0: off)")
     ap.add_argument("--deterministic", action="store_true",
                     help="ordered dQ accumulation in the attention backward: the loss is the same bits on every run "
                          "(off by default: the unordered kernel is faster)")
@@ -532,6 +535,13 @@ def main():
     if args.impl == "reference" and not torch.cuda.is_available():
         print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}), flush=True)
         return
+    if args.impl == "ours":
+        # before CUDA initialises: kernels that wait for a peer must not meet lazy kernel loading
+        os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+    if args.watchdog > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     rank, local, world = setup_dist(args)
     try:
         if args.impl == "reference":

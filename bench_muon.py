@@ -19,6 +19,8 @@ import argparse
 import json
 import os
 
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")   # before CUDA initialises: peer waits must not meet lazy kernel loading
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn

@@ -3,6 +3,14 @@
 Public API (same names as the reference's ``flex_shard`` package,
 ``src/flex_shard/__init__.py:7-62``).
 """
+import os as _os
+
+# Kernels of this library wait for flags that peers set from their own kernels. With CUDA's lazy kernel loading
+# the first launch of any kernel may have to wait for the context to go idle, which it does not while a wait
+# kernel spins; two ranks can then hold each other up until the waits run out. Eager loading (read by CUDA when
+# it initialises, so this must run before the first CUDA call of the process) removes the window.
+_os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 from .bucket_storage import BucketSpec, MixedPrecisionPolicy, OffloadPolicy, PlacementFn, ShardedBucketStorage
 from .checkpoint import (
     get_flex_shard_global_layouts,

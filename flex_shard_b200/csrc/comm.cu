@@ -36,13 +36,33 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// Returns false on timeout. Epochs only grow, so ">= epoch" also accepts a peer that is ahead.
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, uint32_t max_polls) {
+// Returns false on timeout, or as soon as the status word shows that some wait of this process has already
+// failed (after the first failure the step's result is lost anyway; without this every later wait would sit
+// out its own limit and a protocol error would look like a hang). Epochs only grow, so ">= epoch" also
+// accepts a peer that is ahead.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, uint32_t max_polls,
+                                          const volatile int* status) {
   for (uint32_t i = 0; i < max_polls; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - epoch) >= 0) return true;
     if (i > 64) __nanosleep(200);
+    if ((i & 1023) == 1023 && *status != 0) return false;
   }
   return false;
+}
+
+// The status record: [0] error code, then (written by the first failed wait only) [1],[2] the address of the
+// flag that never arrived, [3] the epoch waited for, [4] the peer's rank in the group, [5] the value last seen.
+constexpr int kStatusInts = 8;
+__device__ __forceinline__ void report_wait_failure(int* status, const uint32_t* flag, uint32_t epoch, int peer) {
+  if (atomicCAS(status, 0, FSB_ERR_WAIT_TIMEOUT_PEER) == 0) {
+    const unsigned long long a = reinterpret_cast<unsigned long long>(flag);
+    status[1] = static_cast<int>(a & 0xffffffffu);
+    status[2] = static_cast<int>(a >> 32);
+    status[3] = static_cast<int>(epoch);
+    status[4] = peer;
+    status[5] = static_cast<int>(ld_acquire_sys(flag));
+    __threadfence_system();
+  }
 }
 
 // All threads of the CTA return the same verdict.
@@ -52,9 +72,9 @@ __device__ __forceinline__ bool cta_wait_peers(const uint32_t* my_flags, int wor
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
-    if (!wait_flag(my_flags + threadIdx.x, epoch, max_polls)) {
+    if (!wait_flag(my_flags + threadIdx.x, epoch, max_polls, status)) {
       s_ok = 0;
-      atomicExch(status, FSB_ERR_WAIT_TIMEOUT_PEER);
+      report_wait_failure(status, my_flags + threadIdx.x, epoch, threadIdx.x);
     }
   }
   __syncthreads();
@@ -307,6 +327,22 @@ __global__ void wait_many_kernel(WaitList w, int world, uint32_t max_polls, int*
 }
 }  // namespace
 
+// How this process loads kernels: 1 eager, 2 lazy, 0 unknown. Kernels that wait for a peer's flag must not
+// meet lazy loading: the first launch of a kernel may need the context idle before its code can be loaded, the
+// context is not idle while a wait kernel spins, and the flag it waits for may depend on that very launch on
+// the peer. With CUDA_MODULE_LOADING=EAGER (read when CUDA initialises) every kernel is loaded up front.
+FSB_API int fsb_module_loading_mode() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuModuleGetLoadingMode", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  CUmoduleLoadingMode mode;
+  if (reinterpret_cast<CUresult (*)(CUmoduleLoadingMode*)>(p)(&mode) != CUDA_SUCCESS) return 0;
+  return mode == CU_MODULE_EAGER_LOADING ? 1 : 2;
+}
+
 FSB_API int fsb_comm_wait_many(const unsigned long long* flag_rows, const unsigned* epochs, int count, int world,
                                unsigned max_polls, int* status, cudaStream_t stream) {
   if (world > MAX_RANKS) return FSB_ERR_TOO_LARGE;
@@ -422,17 +458,21 @@ ep_receiver_setup_kernel(PeerPtrs tables, EpTables t, int me, long long cap_rows
 // Sender set-up for the way back: wait until every receiver has published recv_base, then for every
 // (destination rank r, its local expert j): n = my count, srow = r's row of my run, drow = my block's row.
 __global__ void __launch_bounds__(256)
-ep_sender_setup_kernel(PeerPtrs tables, EpTables t, int me, int* __restrict__ n, int* __restrict__ srow,
-                       int* __restrict__ drow, const uint32_t* my_flags, uint32_t epoch, uint32_t max_polls,
-                       int* status) {
+ep_sender_setup_kernel(PeerPtrs tables, EpTables t, int me, long long cap_rows, int* __restrict__ n,
+                       int* __restrict__ srow, int* __restrict__ drow, const uint32_t* my_flags, uint32_t epoch,
+                       uint32_t max_polls, int* status) {
   if (!cta_wait_peers(my_flags, t.ep, epoch, max_polls, status)) return;
   __threadfence_system();
   const int* mine = static_cast<const int*>(tables.p[me]);
   for (int q = threadIdx.x; q < t.ep * t.le; q += blockDim.x) {
     const int r = q / t.le, j = q % t.le;
     const int* tb = static_cast<const int*>(tables.p[r]);
-    n[q] = mine[t.counts() + q];
-    srow[q] = tb[t.recv_base() + me * t.le + j];
+    const int base = tb[t.recv_base() + me * t.le + j];
+    // a receiver that overflowed (and reported it) clamped its runs: never read past the end of its row area
+    const long long room = cap_rows - base;
+    const int cnt = mine[t.counts() + q];
+    n[q] = (base < 0 || room <= 0) ? 0 : (cnt < room ? cnt : static_cast<int>(room));
+    srow[q] = base < 0 ? 0 : base;
     drow[q] = mine[t.offs() + q];
   }
 }
@@ -484,13 +524,13 @@ FSB_API int fsb_ep_receiver_setup(const unsigned long long* tables, int E, int l
   return ok();
 }
 
-FSB_API int fsb_ep_sender_setup(const unsigned long long* tables, int E, int le, int ep, int me, int* n, int* srow,
-                                int* drow, const void* my_flags, unsigned epoch, unsigned max_polls, int* status,
-                                cudaStream_t stream) {
-  if (ep > MAX_RANKS || le > kMaxLocalExperts || E != ep * le) return FSB_ERR_BAD_ARG;
+FSB_API int fsb_ep_sender_setup(const unsigned long long* tables, int E, int le, int ep, int me, long long cap_rows,
+                                int* n, int* srow, int* drow, const void* my_flags, unsigned epoch,
+                                unsigned max_polls, int* status, cudaStream_t stream) {
+  if (ep > MAX_RANKS || le > kMaxLocalExperts || E != ep * le || cap_rows <= 0) return FSB_ERR_BAD_ARG;
   PeerPtrs tp;
   for (int r = 0; r < ep; ++r) tp.p[r] = reinterpret_cast<void*>(tables[r]);
-  ep_sender_setup_kernel<<<1, 256, 0, stream>>>(tp, EpTables{E, le, ep}, me, n, srow, drow,
+  ep_sender_setup_kernel<<<1, 256, 0, stream>>>(tp, EpTables{E, le, ep}, me, cap_rows, n, srow, drow,
                                                  static_cast<const uint32_t*>(my_flags), epoch, max_polls, status);
   return ok();
 }

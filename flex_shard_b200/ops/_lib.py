@@ -120,24 +120,53 @@ def stream_ptr(device=None) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+STATUS_INTS = 8     # [0] code; a failed peer wait also leaves [1],[2] flag address, [3] epoch, [4] peer, [5] value seen
+
+
 def status_word(device: torch.device) -> torch.Tensor:
-    """Per-device int32 the kernels write an error code to when a bounded wait runs out."""
+    """Per-device int32 record the kernels write an error code to when a bounded wait runs out (element 0;
+    a failed wait on a peer's flag adds which flag, epoch and peer in the following elements)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        t = torch.zeros(STATUS_INTS, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
     return t
+
+
+# (first flag address, bytes of flags, name) of every live symmetric region: turns the address in a failure
+# record into "which wait"
+_flag_ranges: list = []
+
+
+def register_flag_range(base: int, nbytes: int, name, slot_bytes: int) -> None:
+    _flag_ranges.append((base, nbytes, name, slot_bytes))
+    del _flag_ranges[:-4096]
+
+
+def _describe(rec) -> str:
+    code = int(rec[0])
+    text = f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})"
+    addr = (int(rec[1]) & 0xFFFFFFFF) | ((int(rec[2]) & 0xFFFFFFFF) << 32)
+    if code == 32 and addr:
+        where = f"flag at {addr:#x}"
+        for base, nbytes, name, slot_bytes in reversed(_flag_ranges):
+            if base <= addr < base + nbytes:
+                where = f"{name() if callable(name) else name}, flag slot {(addr - base) // slot_bytes}"
+                break
+        text += (f": waited for epoch {int(rec[3]) & 0xFFFFFFFF} from group rank {int(rec[4])} on {where}, "
+                 f"last value seen {int(rec[5]) & 0xFFFFFFFF}")
+    return text
 
 
 def check_status(device=None) -> None:
     """Synchronise and raise if any kernel on ``device`` reported a failed wait."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     t = status_word(dev)
-    code = int(t.item())
-    if code != 0:
+    rec = t.tolist()
+    if rec[0] != 0:
         t.zero_()
-        raise NativeError(f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})")
+        raise NativeError(_describe(rec))
 
 
 _polls: dict[int, tuple] = {}
@@ -161,13 +190,13 @@ def poll_status(device=None) -> None:
         host, ev = prev
         if not ev.query():
             return          # the previous copy has not landed yet: look again at the next call
-        code = int(host[0])
-        if code != 0:
+        rec = host.tolist()
+        if rec[0] != 0:
             word.zero_()
             _polls.pop(idx, None)
-            raise NativeError(f"device-side failure: {STATUS_NAMES.get(code, code)} (code {code})")
+            raise NativeError(_describe(rec))
     else:
-        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        host = torch.zeros(STATUS_INTS, dtype=torch.int32).pin_memory()
     host.copy_(word, non_blocking=True)
     ev = torch.cuda.Event()
     ev.record(torch.cuda.current_stream(idx))

@@ -38,7 +38,7 @@ def _ensure():
     c = ctypes
     vp, i32, i64, u32 = c.c_void_p, c.c_int, c.c_longlong, c.c_uint
     _lib.declare("fsb_ep_receiver_setup", [vp, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, vp, vp])
-    _lib.declare("fsb_ep_sender_setup", [vp, i32, i32, i32, i32, vp, vp, vp, vp, u32, u32, vp, vp])
+    _lib.declare("fsb_ep_sender_setup", [vp, i32, i32, i32, i32, i64, vp, vp, vp, vp, u32, u32, vp, vp])
     _lib.declare("fsb_ep_pull_rows", [vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, u32, u32, vp, vp])
     _declared = True
 
@@ -76,6 +76,8 @@ class SymmExpertExchange:
         self.b_off = self.a_off + (self.send_rows * self.row_bytes + 255) // 256 * 256   # receiver-layout rows
         total = self.b_off + self.cap_rows * self.row_bytes
         self.region = SymmRegion(group, total, device)
+        self.region.name = ("expert exchange region (slots: 8 tables, 9 landing rows, 10/11 area A/B ready, "
+                            "12/13 area A/B done)")
         self.epochs = {k: 0 for k in ("tables", "recv_base", "a", "b")}
         self.exchanges = 0
 
@@ -138,8 +140,8 @@ class SymmExpertExchange:
     def sender_setup(self) -> _Tables:
         t = _Tables(self.ep * self.le, self.le, self.cap_rows, self.device, receiver=False)
         rc = _lib.load().fsb_ep_sender_setup(
-            self._peer(0), self.E, self.le, self.ep, self.rank, t.n.data_ptr(), t.srow.data_ptr(), t.drow.data_ptr(),
-            self._flags(self.SLOT_RECV_BASE), self.epochs["recv_base"], self.region.max_polls, self._status(),
+            self._peer(0), self.E, self.le, self.ep, self.rank, self.cap_rows, t.n.data_ptr(), t.srow.data_ptr(),
+            t.drow.data_ptr(), self._flags(self.SLOT_RECV_BASE), self.epochs["recv_base"], self.region.max_polls, self._status(),
             _lib.stream_ptr(self.device))
         _lib.check(rc, "fsb_ep_sender_setup")
         count_launch()

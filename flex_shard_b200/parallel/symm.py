@@ -51,13 +51,41 @@ def _ensure():
     _declared = True
 
 
+_warned_lazy = False
+
+
+def _warn_if_lazy_loading() -> None:
+    """Peer waits and lazy kernel loading do not mix (see ``fsb_module_loading_mode``): say so once."""
+    global _warned_lazy
+    if _warned_lazy:
+        return
+    _warned_lazy = True
+    try:
+        fn = _lib.load().fsb_module_loading_mode
+        fn.argtypes, fn.restype = [], ctypes.c_int
+        mode = fn()
+    except Exception:
+        return
+    if mode == 2:
+        import warnings
+
+        warnings.warn(
+            "CUDA loads kernels lazily in this process (CUDA was initialised before flex_shard_b200 was imported, or "
+            "CUDA_MODULE_LOADING=LAZY is set). The first launch of a kernel can then stall behind a kernel that "
+            "waits for a peer, and two ranks can block each other until the device-side waits time out. Set "
+            "CUDA_MODULE_LOADING=EAGER in the environment of every rank.", RuntimeWarning, stacklevel=3)
+
+
 class SymmRegion:
     """A symmetric buffer: ``[flags (64 KB) | payload]`` on every rank, peers mapped."""
+
+    _count = 0
 
     def __init__(self, group: dist.ProcessGroup, payload_bytes: int, device: torch.device):
         import torch.distributed._symmetric_memory as symm_mem
 
         _ensure()
+        _warn_if_lazy_loading()
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -79,9 +107,22 @@ class SymmRegion:
             except Exception:
                 self.mc_base = 0
         self.epoch = 0   # gather epoch of a region that holds a bucket's resident storage
+        # name shown when a wait on one of this region's flags runs out (users may set a better one: .name = ...)
+        self._name = [f"symmetric region #{SymmRegion._count} ({self.payload_bytes} payload bytes)"]
+        SymmRegion._count += 1
+        box = self._name
+        _lib.register_flag_range(self.peer_base[self.rank], FLAG_BYTES, lambda: box[0], MAX_RANKS * 4)
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone signals
         self.max_polls = DEFAULT_MAX_POLLS
+
+    @property
+    def name(self) -> str:
+        return self._name[0]
+
+    @name.setter
+    def name(self, value: str) -> None:
+        self._name[0] = value
 
     # ---- addressing
     @property
@@ -188,6 +229,8 @@ class SymmComm(Comm):
                 _lib.check_status(self.device)   # a peer that never signalled "done" may still read the old region: raise
                 size = max(size, 2 * cur.payload_bytes)
             cur = SymmRegion(self.group, size, self.device)
+            cur.name = ("all-gather staging region (slots: 0 ready, 1 done)" if which == "ag" else
+                        "reduce-scatter staging region (slots: 2 ready, 3 done)") + f", {size} bytes"
             if which == "ag":
                 self._ag, self._ag_epoch = cur, 0
             else:
@@ -202,6 +245,7 @@ class SymmComm(Comm):
         if not self.resident_storage or self.world_size == 1 or nbytes <= 0:
             return None
         reg = SymmRegion(self.group, nbytes, self.device)
+        reg.name = f"resident bucket storage #{len(self._resident)} ({nbytes} bytes; slots: 0 gather ready, 1 gather done)"
         buf = reg.payload[:nbytes]
         self._resident[buf.data_ptr()] = reg
         return buf
@@ -494,6 +538,8 @@ class SymmGradRing:
         self.entry_bytes = (entry_bytes + 255) // 256 * 256
         self.entries = entries
         self.region = SymmRegion(group, entries * self.entry_bytes, device)
+        self.region.name = (f"gradient ring ({entries} entries of {self.entry_bytes} bytes; slots: "
+                            f"{self.SLOT_WRITTEN0}+k written, {self.SLOT_CONSUMED0}+k consumed)")
         self.uses = [0] * entries
         self.count = 0
         self.pull = os.environ.get("FSB200_REDUCE_MODE", "pull") != "push"

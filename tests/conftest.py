@@ -3,6 +3,10 @@ import sys
 
 import pytest
 
+# inherited by the worker processes of the multi-GPU tests, which select their device (and so initialise CUDA)
+# before they import the package: kernels that wait for a peer must not meet lazy kernel loading
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
