@@ -197,10 +197,11 @@ class SymmComm(Comm):
         self.resident_storage = os.environ.get("FSB200_RESIDENT", "1") != "0"
         self.stats = {"resident_gathers": 0, "staged_gathers": 0, "dma_gathers": 0, "multimem_reduces": 0,
                       "peer_reduces": 0}
-        # in-switch gradient sum: "1" / "0" force it on / off; default "auto" uses it from 4 ranks up (measured
-        # on 2 ranks the W-way peer loads are faster: one remote row costs less than the switch's reduction)
-        mm = os.environ.get("FSB200_MULTIMEM_REDUCE", "auto")
-        self.multimem_reduce = world_size >= 4 if mm == "auto" else mm != "0"
+        # in-switch gradient sum (multimem.ld_reduce): "1" switches it on. Off by default: measured on 2 and 4
+        # ranks the rank-order peer loads are faster (0.79 / 1.05 ms against 1.38 / 1.31 ms for a Llama layer
+        # bucket; the switch delivers reduced rows at about 670 GB/s whatever the rank count) and their sum has a
+        # fixed, documented order
+        self.multimem_reduce = os.environ.get("FSB200_MULTIMEM_REDUCE", "0") == "1"
         # "dma": segment gathers are issued as copy-engine copies (no SM time); "sm": the pull kernel
         self.gather_engine = os.environ.get("FSB200_GATHER", "dma")
 
