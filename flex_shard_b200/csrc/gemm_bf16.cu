@@ -46,6 +46,7 @@ struct GemmArgs {
   int c_fp32;
   float alpha, beta;
   int accumulate;
+  int upper_only;     // two-SM kernel, M == N: compute only the 256x256 tiles on or above the diagonal
   // When d_block_rows > 0, D is cut into blocks of that many rows and block i starts at
   // element offset i * d_block_stride (the [world, rows/world, N] rows of a reduce-scatter
   // send buffer), so a weight gradient can be written straight into its reduction layout.
@@ -676,6 +677,16 @@ __device__ __forceinline__ int spread_over_row_blocks(int tm, int tiles_m, int n
   return (tm % nblk) * per + tm / nblk;
 }
 
+// Tile `t` of the upper triangle (diagonal included) of a T x T tile grid, row by row.
+__device__ __forceinline__ void upper_tile_coords(int t, int T, int& tm, int& tn) {
+  tm = 0;
+  while (t >= T - tm) {
+    t -= T - tm;
+    ++tm;
+  }
+  tn = tm + t;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const GemmArgs args) {
@@ -695,7 +706,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t rank = cluster_ctarank();
   const int tiles_m = (args.M + 2 * BM - 1) / (2 * BM);   // 256-row tiles
   const int tiles_n = (args.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = args.upper_only ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
   const int num_kb = (args.K + BK - 1) / BK;
   const int tile0 = static_cast<int>(blockIdx.x >> 1);
   const int tile_step = static_cast<int>(gridDim.x >> 1);
@@ -735,8 +746,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       bool ok = true;
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
         int tm2, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm2, tn);
-        if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
+        if (args.upper_only) {
+          upper_tile_coords(tile, tiles_m, tm2, tn);
+        } else {
+          tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+          if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
+        }
         const int m0 = tm2 * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -831,8 +846,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint32_t local_tile = 0;
     for (int tile = tile0; tile < num_tiles; tile += tile_step) {
       int tm2, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm2, tn);
-      if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
+      if (args.upper_only) {
+        upper_tile_coords(tile, tiles_m, tm2, tn);
+      } else {
+        tile_coords(tile, tiles_m, tiles_n, tm2, tn);
+        if (spread) tm2 = spread_over_row_blocks(tm2, tiles_m, args.d_peer_n);
+      }
       const int tm = tm2 * 2 + static_cast<int>(rank);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -951,11 +970,31 @@ int fsb_make_tmap_2d_plain(CUtensorMap* map, const void* base, CUtensorMapDataTy
 static int g_use_pairs_value();
 static inline bool g_use_pairs_fwd() { return g_use_pairs_value() != 0; }
 
+// D[r][c] = D[c][r] for every element of the 256x256 tiles strictly below the diagonal of a square bf16
+// matrix: completes a symmetric product of which only the upper tiles were computed. 32x32 tiles through
+// shared memory, so both the reads and the writes are contiguous.
+__global__ void __launch_bounds__(256)
+mirror_upper_kernel(__nv_bfloat16* __restrict__ d, long long ldd, int n) {
+  __shared__ __nv_bfloat16 t[32][34];
+  const int br = blockIdx.y, bc = blockIdx.x;          // destination block (rows br*32.., columns bc*32..)
+  if ((br * 32) / 256 <= (bc * 32) / 256) return;      // only blocks inside the tiles below the diagonal
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int r = bc * 32 + i, c = br * 32 + tx;       // source element (the transposed position)
+    if (r < n && c < n) t[i][tx] = d[r * ldd + c];
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int r = br * 32 + i, c = bc * 32 + tx;
+    if (r < n && c < n) d[r * ldd + c] = t[tx][i];
+  }
+}
+
 static int gemm_pair_launch(const void* a, const void* b, void* d, const void* c, int M, int N, int K,
                             long long lda, long long ldb, long long ldd, long long ldc, int a_mn, int b_mn,
                             int d_fp32, int c_fp32, float alpha, float beta, int accumulate,
                             long long d_block_rows, long long d_block_stride, const unsigned long long* d_peer,
-                            int d_peer_n, int* status, cudaStream_t stream) {
+                            int d_peer_n, int* status, cudaStream_t stream, int upper_only = 0) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return FSB_ERR_BAD_ARG;
@@ -998,10 +1037,23 @@ static int gemm_pair_launch(const void* a, const void* b, void* d, const void* c
   args.d_block_rows = d_block_rows; args.d_block_stride = d_block_stride; args.d_peer_n = d_peer_n;
   args.status = status;
   for (int i = 0; i < d_peer_n; ++i) args.d_peer[i] = reinterpret_cast<void*>(d_peer[i]);
-  const long long tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  long long tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  // a symmetric product into a plain bf16 matrix: the tiles on or above the diagonal, then their mirror image
+  upper_only = upper_only && M == N && !d_fp32 && !accumulate && d_peer_n == 0 && d_block_rows == 0 && M > 2 * BM;
+  if (upper_only) {
+    const long long T = (M + 2 * BM - 1) / (2 * BM);
+    tiles = T * (T + 1) / 2;
+    args.upper_only = 1;
+  }
   const int clusters = tiles < g_pair_clusters[dev] ? static_cast<int>(tiles) : g_pair_clusters[dev];
   gemm_bf16_2sm_kernel<<<2 * clusters, NUM_THREADS, SMEM2_BYTES, stream>>>(map_a, map_b, args);
-  return cudaGetLastError() == cudaSuccess ? FSB_OK : FSB_ERR_LAUNCH;
+  if (cudaGetLastError() != cudaSuccess) return FSB_ERR_LAUNCH;
+  if (upper_only) {
+    const unsigned nb = static_cast<unsigned>((M + 31) / 32);
+    mirror_upper_kernel<<<dim3(nb, nb), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(d), ldd, M);
+    if (cudaGetLastError() != cudaSuccess) return FSB_ERR_LAUNCH;
+  }
+  return FSB_OK;
 }
 
 // D = alpha * A.B^T + beta * C (+ D). Shapes in elements; see the header comment
@@ -1079,6 +1131,10 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
                           const unsigned long long* d_peer, int d_peer_n, int* status, int max_ctas,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FSB_ERR_BAD_ARG;
+  // bit 1 of `accumulate`: the product is symmetric (A B^T with B = A, or a symmetric A times itself) and only
+  // its upper tiles need computing; honoured by the two-SM kernel for square bf16 outputs, ignored otherwise
+  const int upper_only = (accumulate >> 1) & 1;
+  accumulate &= 1;
   // a negative block count means: the blocks are in this GPU's own memory (no row-segment staging)
   const int d_peer_remote = d_peer_n > 0;
   if (d_peer_n < 0) d_peer_n = -d_peer_n;
@@ -1086,7 +1142,7 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
   if (g_use_pairs_fwd() && M >= 2 * BM && N >= BN && max_ctas <= 0) {
     const int rc2 = gemm_pair_launch(a, b, d, c, M, N, K, lda, ldb, ldd, ldc, a_mn, b_mn, d_fp32, c_fp32, alpha,
                                      beta, accumulate, d_block_rows, d_block_stride, d_peer,
-                                     d_peer_remote ? d_peer_n : -d_peer_n, status, stream);
+                                     d_peer_remote ? d_peer_n : -d_peer_n, status, stream, upper_only);
     if (rc2 != FSB_ERR_TOO_LARGE) return rc2;   // TOO_LARGE here means "pairs unusable on this device"
   }
   CUtensorMap map_a, map_b;

@@ -47,8 +47,12 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
          c: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 1.0,
-         accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
-    """``out = alpha * A @ B^T + beta * c (+ out)`` with bf16 operands, fp32 accumulation."""
+         accumulate: bool = False, max_ctas: int = 0, symmetric: bool = False) -> torch.Tensor:
+    """``out = alpha * A @ B^T + beta * c (+ out)`` with bf16 operands, fp32 accumulation.
+
+    ``symmetric=True`` promises that the result is a symmetric matrix (``X X^T``, or a symmetric matrix times
+    itself, with a symmetric ``c``): for square bf16 outputs the kernel then computes only the tiles on or above
+    the diagonal and mirrors them, which halves the work of a large product."""
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_t else a.shape
     N, Kb = (b.shape[1], b.shape[0]) if b_t else b.shape
@@ -107,7 +111,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         a.data_ptr(), b.data_ptr(), out_ptr, c.data_ptr() if c is not None else None,
         M, N, K, a.stride(0), b.stride(0), ldd, c.stride(0) if c is not None else 0,
         int(a_t), int(b_t), int(out.dtype == torch.float32),
-        int(c is not None and c.dtype == torch.float32), alpha, beta, int(accumulate),
+        int(c is not None and c.dtype == torch.float32), alpha, beta, int(accumulate) | (2 if symmetric else 0),
         block_rows, block_stride, peer_ptrs, peer_n, status.data_ptr(), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(rc, "fsb_gemm_bf16")
     count_launch()

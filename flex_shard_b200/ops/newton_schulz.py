@@ -7,7 +7,8 @@ Per step (coefficients a, b, c), for ``X`` of shape ``[s, l]`` with ``s <= l``::
     X = a*X + B@X                  one GEMM, epilogue  acc + a*X
 
 Tall matrices use ``A = X^T X`` and ``X = a*X + X@B`` instead, through the GEMM's transposed
-operand modes, so no transpose copy is ever made. Math parity with the reference's
+operand modes, so no transpose copy is ever made. ``A`` and ``B`` are symmetric: their GEMMs compute the
+tiles on or above the diagonal only and mirror them (28 % fewer FLOPs per iteration for a 4096 x 14336 matrix). Math parity with the reference's
 ``_zeropower_via_newtonschulz`` (``dist_muon/optimizer.py:2120-2151``): bf16 operands, fp32
 accumulation, Frobenius normalisation first.
 """
@@ -54,12 +55,12 @@ def ns_iterations(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> torch.Te
     nxt = torch.empty_like(x)
     for _ in range(steps):
         if wide:
-            gemm(x, x, out=A)                                   # A = X X^T
-            gemm(A, A, out=B, c=A, alpha=c, beta=b)             # B = b A + c A A   (A symmetric)
+            gemm(x, x, out=A, symmetric=True)                   # A = X X^T
+            gemm(A, A, out=B, c=A, alpha=c, beta=b, symmetric=True)   # B = b A + c A A   (A symmetric)
             gemm(B, x, b_t=True, out=nxt, c=x, alpha=1.0, beta=a)  # X = a X + B X
         else:
-            gemm(x, x, a_t=True, b_t=True, out=A)               # A = X^T X
-            gemm(A, A, out=B, c=A, alpha=c, beta=b)
+            gemm(x, x, a_t=True, b_t=True, out=A, symmetric=True)     # A = X^T X
+            gemm(A, A, out=B, c=A, alpha=c, beta=b, symmetric=True)
             gemm(x, B, out=nxt, c=x, alpha=1.0, beta=a)         # X = a X + X B     (B symmetric)
         x, nxt = nxt, x
     return x

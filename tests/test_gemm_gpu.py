@@ -68,3 +68,26 @@ def test_linear_autograd_matches_torch():
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=3e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=2e-1)
     ops.check_status()
+
+
+@pytest.mark.parametrize("n,k", [(1024, 512), (2304, 1024), (4096, 640)])
+def test_symmetric_product_computes_upper_tiles_and_mirrors(n, k):
+    """``symmetric=True``: X X^T (and a symmetric matrix times itself with a symmetric addend) must equal the
+    full product; the result is exactly symmetric."""
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    x = torch.randn(n, k, device=dev).bfloat16()
+    full = ops.gemm(x, x)
+    sym = ops.gemm(x, x, symmetric=True)
+    ref = x.float() @ x.float().t()
+    torch.testing.assert_close(sym.float(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()) / 16)
+    assert torch.equal(sym, sym.t())
+    assert torch.equal(torch.triu(sym), torch.triu(full))          # the computed half is the same arithmetic
+    a = sym
+    full2 = ops.gemm(a, a, c=a, alpha=0.5, beta=-1.5)
+    sym2 = ops.gemm(a, a, c=a, alpha=0.5, beta=-1.5, symmetric=True)
+    assert torch.equal(torch.triu(sym2), torch.triu(full2)) and torch.equal(sym2, sym2.t())
+    xt = x.t().contiguous()                                          # [k, n]: A = X^T X through the transposed modes
+    sym3 = ops.gemm(xt, xt, a_t=True, b_t=True, symmetric=True)
+    torch.testing.assert_close(sym3.float(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()) / 16)
+    ops.check_status()
