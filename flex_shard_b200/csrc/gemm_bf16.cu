@@ -213,13 +213,13 @@ __device__ __forceinline__ void store_tile(const GemmArgs& args, long long d_row
       const bool full = (col + 32 <= args.N);
       if (args.c != nullptr) {
         if (args.c_fp32) {
-          const float* cp = static_cast<const float*>(args.c) + row * args.ldc + col;
+          const float* cp = static_cast<const float*>(args.c) + (d_row_off + row) * args.ldc + col;
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (full || col + i < args.N) v[i] += args.beta * cp[i];
         } else {
           const __nv_bfloat16* cp =
-              static_cast<const __nv_bfloat16*>(args.c) + row * args.ldc + col;
+              static_cast<const __nv_bfloat16*>(args.c) + (d_row_off + row) * args.ldc + col;
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (full || col + i < args.N) v[i] += args.beta * __bfloat162float(cp[i]);
@@ -1073,11 +1073,31 @@ FSB_API int fsb_gemm_bf16(const void* a, const void* b, void* d, const void* c, 
 //           number of valid m-tiles (device memory: no host synchronisation), max_mtiles bounds it.
 //   mode 2: D[E, M, N] = sum over each expert's rows of A[r, :M]^T B[r, :N] (A, B row-major
 //           [R, M] / [R, N]); group_offs is the int[E+1] array of padded row offsets.
+FSB_API int fsb_gemm_bf16_grouped_ex(const void* a, const void* b, void* d, int mode, int num_groups, int M,
+                                     int N, int K, long long lda, long long ldb, long long ldd, int b_mn,
+                                     int d_fp32, int accumulate, const int* tile_expert,
+                                     const int* num_mtiles, const int* group_offs, int max_rows,
+                                     const void* c, long long ldc, int c_fp32, float alpha, float beta,
+                                     int* status, cudaStream_t stream);
+
 FSB_API int fsb_gemm_bf16_grouped(const void* a, const void* b, void* d, int mode, int num_groups, int M,
                                   int N, int K, long long lda, long long ldb, long long ldd, int b_mn,
                                   int d_fp32, int accumulate, const int* tile_expert,
                                   const int* num_mtiles, const int* group_offs, int max_rows,
                                   int* status, cudaStream_t stream) {
+  return fsb_gemm_bf16_grouped_ex(a, b, d, mode, num_groups, M, N, K, lda, ldb, ldd, b_mn, d_fp32, accumulate,
+                                  tile_expert, num_mtiles, group_offs, max_rows, nullptr, 0, 0, 1.f, 0.f, status,
+                                  stream);
+}
+
+// The same with the dense GEMM's epilogue: D = alpha * product + beta * C, where C has D's layout
+// ([R, N] rows for mode 1, [E, M, N] for mode 2).
+FSB_API int fsb_gemm_bf16_grouped_ex(const void* a, const void* b, void* d, int mode, int num_groups, int M,
+                                     int N, int K, long long lda, long long ldb, long long ldd, int b_mn,
+                                     int d_fp32, int accumulate, const int* tile_expert,
+                                     const int* num_mtiles, const int* group_offs, int max_rows,
+                                     const void* c, long long ldc, int c_fp32, float alpha, float beta,
+                                     int* status, cudaStream_t stream) {
   if (mode != 1 && mode != 2) return FSB_ERR_BAD_ARG;
   CUtensorMap map_a, map_b;
   int rc;
@@ -1101,7 +1121,8 @@ FSB_API int fsb_gemm_bf16_grouped(const void* a, const void* b, void* d, int mod
     if (rc != FSB_OK) return rc;
     args.M = M; args.N = N; args.K = max_rows; args.a_mn = 1; args.b_mn = 1;
   }
-  args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.alpha = 1.f; args.beta = 0.f;
+  args.d = d; args.ldd = ldd; args.d_fp32 = d_fp32; args.alpha = alpha; args.beta = c != nullptr ? beta : 0.f;
+  args.c = c; args.ldc = ldc; args.c_fp32 = c_fp32;
   args.accumulate = accumulate; args.group_mode = mode; args.num_groups = num_groups;
   args.tile_expert = tile_expert; args.num_mtiles = num_mtiles; args.group_offs = group_offs;
   args.status = status;

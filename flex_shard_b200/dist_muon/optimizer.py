@@ -337,6 +337,18 @@ class DistMuon(torch.optim.Optimizer):
         group = self.param_groups[0]
         W, rank = self._world()
         out = torch.empty_like(full)
+        mine = [hi - lo for lo, hi, owner in plan.matrices if owner == rank]
+        if len(mine) > 1 and len(set(mine)) == 1:
+            # equal matrices (heads, experts) stacked back to back: one batched iteration for all of them
+            k, n = len(mine), mine[0]
+            blk = full[:k * n]
+            stack = (blk.reshape(k, blk.shape[-2], blk.shape[-1]) if it.resolved.batch else blk.reshape(k, n, -1))
+            from ..ops.newton_schulz import batched_ns_supported
+
+            if batched_ns_supported(stack):
+                x = newton_schulz(stack, group["ns_steps"], group["ns_coefficients"], group["eps"])
+                out[:k * n].copy_(x.reshape(blk.shape))
+                return out
         pos = 0
         for lo, hi, owner in plan.matrices:
             if owner != rank:

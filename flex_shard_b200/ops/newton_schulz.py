@@ -66,9 +66,85 @@ def ns_iterations(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> torch.Te
     return x
 
 
+_batch_tables: dict = {}
+
+
+def _tables(E: int, rows: int, device):
+    """Grouped-GEMM tables of ``E`` equal groups of ``rows`` rows (``rows`` a multiple of 128): the group of every
+    128-row tile, the tile count and the group offsets, as device tensors."""
+    key = (E, rows, device)
+    t = _batch_tables.get(key)
+    if t is None:
+        tile_group = torch.arange(E, dtype=torch.int32).repeat_interleave(rows // 128).to(device)
+        count = torch.tensor([E * rows // 128], dtype=torch.int32, device=device)
+        offs = (torch.arange(E + 1, dtype=torch.int64) * rows).to(torch.int32).to(device)
+        t = _batch_tables[key] = (tile_group, count, offs)
+        if len(_batch_tables) > 256:
+            _batch_tables.pop(next(iter(_batch_tables)))
+    return t
+
+
+def _grouped(mode, a, b, out, E, M, N, K, b_mn, tables, max_rows, c=None, alpha=1.0, beta=0.0):
+    lib = _lib.load()
+    fn = lib.fsb_gemm_bf16_grouped_ex
+    if not getattr(fn, "_fsb_declared", False):
+        cc = ctypes
+        vp, i32, i64, f32 = cc.c_void_p, cc.c_int, cc.c_longlong, cc.c_float
+        fn.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, i32, i32, vp, vp, vp, i32,
+                       vp, i64, i32, f32, f32, vp, vp]
+        fn.restype = cc.c_int
+        fn._fsb_declared = True
+    tile_group, count, offs = tables
+    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), mode, E, M, N, K, a.stride(0), b.stride(0), out.stride(-2),
+            int(b_mn), 0, 0, tile_group.data_ptr(), count.data_ptr(), offs.data_ptr(), max_rows,
+            c.data_ptr() if c is not None else None, c.stride(-2) if c is not None else 0, 0, alpha, beta,
+            _lib.status_word(a.device).data_ptr(), _lib.stream_ptr(a.device))
+    _lib.check(rc, "fsb_gemm_bf16_grouped_ex")
+    count_launch()
+
+
+def batched_ns_supported(x: torch.Tensor) -> bool:
+    """Stacks of equal matrices whose dimensions are multiples of 128 run every product of an iteration as one
+    grouped launch over the whole stack."""
+    return (x.is_cuda and x.dim() == 3 and x.shape[0] > 1 and x.shape[1] % 128 == 0 and x.shape[2] % 128 == 0)
+
+
+def ns_iterations_batched(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> torch.Tensor:
+    """The iteration on a stack ``[E, rows, cols]`` of normalised bf16 matrices: three grouped GEMM launches per
+    step for all ``E`` matrices (per-head and per-expert matrices are small; one launch each would leave most of
+    the GPU idle and pay 15 launches per matrix).  Same arithmetic per matrix as ``ns_iterations``."""
+    a, b, c = coeffs
+    E, rows, cols = x.shape
+    wide = rows <= cols
+    s = min(rows, cols)
+    x = x.contiguous()
+    dev = x.device
+    A = torch.empty(E, s, s, dtype=x.dtype, device=dev)
+    B = torch.empty(E, s, s, dtype=x.dtype, device=dev)
+    nxt = torch.empty_like(x)
+    t_s, t_rows = _tables(E, s, dev), _tables(E, rows, dev)
+    A2, B2 = A.view(E * s, s), B.view(E * s, s)
+    for _ in range(steps):
+        x2, n2 = x.view(E * rows, cols), nxt.view(E * rows, cols)
+        if wide:
+            _grouped(1, x2, x2, A2, E, E * s, s, cols, False, t_s, E * s)                      # A = X X^T
+            _grouped(1, A2, A2, B2, E, E * s, s, s, False, t_s, E * s, c=A2, alpha=c, beta=b)  # B = b A + c A A
+            _grouped(1, B2, x2, n2, E, E * s, cols, s, True, t_s, E * s, c=x2, alpha=1.0, beta=a)   # X = a X + B X
+        else:
+            _grouped(2, x2, x2, A, E, s, s, E * rows, True, t_rows, E * rows)                   # A = X^T X
+            _grouped(1, A2, A2, B2, E, E * s, s, s, False, t_s, E * s, c=A2, alpha=c, beta=b)
+            _grouped(1, x2, B2, n2, E, E * rows, s, s, False, t_rows, E * rows, c=x2, alpha=1.0, beta=a)  # X = a X + X B
+        x, nxt = nxt, x
+    return x
+
+
 def newton_schulz(g: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
     """Approximate polar factor of ``g`` ([rows, cols] or batched [n, rows, cols]); returns bf16."""
     if g.dim() == 3:
+        if batched_ns_supported(g):
+            x = g.to(torch.bfloat16)
+            norm = x.float().square().sum((1, 2), keepdim=True).sqrt().clamp_min(eps)
+            return ns_iterations_batched((x.float() / norm).to(torch.bfloat16), steps, coeffs)
         return torch.stack([newton_schulz(m, steps, coeffs, eps) for m in g])
     x = g.to(torch.bfloat16)
     x = x / x.float().norm().clamp_min(eps).to(torch.bfloat16) if not x.is_cuda else _normalise_cuda(x, eps)

@@ -3,7 +3,7 @@
     python -m flex_shard_b200.utils.kernel_cases <case> [--iters N]
 
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_bwd_ordered, adamw, rmsnorm, swiglu, cross_entropy,
-newton_schulz, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm, segment_cast. Each prints one JSON line with the CUDA-event time (median of
+newton_schulz, newton_schulz_batched, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm, segment_cast. Each prints one JSON line with the CUDA-event time (median of
 ``iters`` launches after 3 warm-up launches, L2 flushed between launches by writing a 256 MB buffer)
 and the achieved FLOP/s or bytes/s. Inputs are a few hundred MB, larger than the 126 MB L2, so DRAM
 counters of a profiler capture of the same command stay meaningful.
@@ -140,6 +140,16 @@ def main():
         out.update(rows=s, cols=l, ms=ms, tflops=dense / ms / 1e9, tflops_executed=done / ms / 1e9,
                    note="tflops counts the dense algorithm; tflops_executed discounts the mirrored halves "
                         "(diagonal tiles are computed in full, so it is a slight under-count)")
+    elif args.case == "newton_schulz_batched":
+        # sixteen expert-sized matrices: one grouped launch per product against one matrix at a time
+        from flex_shard_b200.ops.newton_schulz import newton_schulz
+
+        E, s, l = 16, 1024, 2048
+        x = torch.randn(E, s, l, device=dev).bfloat16()
+        ms = _time(lambda: newton_schulz(x, steps=5), args.iters)
+        ms_loop = _time(lambda: [newton_schulz(x[i], steps=5) for i in range(E)], args.iters)
+        dense = E * 5 * (2 * 2 * s * s * l + 2 * s * s * s)
+        out.update(matrices=E, rows=s, cols=l, ms=ms, tflops=dense / ms / 1e9, one_at_a_time_ms=ms_loop)
     elif args.case == "fp8_quant":
         from flex_shard_b200.ops.fp8 import quantize_blockwise
 

@@ -71,3 +71,21 @@ def test_prepare_sum_is_reproducible_and_vector_paths_match_scalar():
     ref = torch.lerp(g, 0.05 * g, 0.95).bfloat16().float()
     torch.testing.assert_close(xs[0].float(), ref / ref.norm(), rtol=2e-2, atol=1e-6)
     ops.check_status()
+
+
+@pytest.mark.parametrize("shape", [(6, 256, 512), (4, 512, 256), (3, 384, 384)])
+def test_batched_newton_schulz_matches_one_matrix_at_a_time(shape):
+    """A stack of equal matrices runs each product of an iteration as one grouped launch; every matrix must
+    come out as if it had been orthogonalised alone."""
+    torch.manual_seed(4)
+    g = torch.randn(*shape, device="cuda")
+    assert ns.batched_ns_supported(g)
+    before = ops.launch_count()
+    out = ns.newton_schulz(g)
+    assert ops.launch_count() - before == 15                       # 3 launches per iteration for the whole stack
+    for i in range(shape[0]):
+        one = ns.newton_schulz(g[i])
+        assert (out[i].float() - one.float()).norm() / one.float().norm() < 1e-2
+        ref = ns.newton_schulz(g[i].cpu()).float()
+        assert (out[i].float().cpu() - ref).norm() / ref.norm() < 3e-2
+    ops.check_status()
