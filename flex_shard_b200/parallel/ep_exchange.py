@@ -213,12 +213,22 @@ class SymmDispatcher:
         self._ex: SymmExpertExchange | None = None
         self._symm = None          # attribute the NCCL/peer-pull dispatcher also has (tests look at it)
 
+    # One exchange (symmetric staging areas + tables) serves every MoE layer of a model: layers run one after the
+    # other in the same order on every rank, each use waits for the peers' "done" flags of the previous use, and
+    # the per-layer tables that the backward pass needs are kept outside the region. 26 layers of the 16B example
+    # would otherwise hold 26 x 0.6 GB of staging memory per rank.
+    _shared: dict = {}
+
     def exchange_for(self, xt, k) -> SymmExpertExchange:
         pairs = xt.shape[0] * k
+        key = (id(self.group), self.num_experts, xt.shape[1], pairs, xt.dtype, self.capacity_factor, xt.device)
         ex = self._ex
         if ex is None or ex.D != xt.shape[1] or moe_ops.max_rows_for(pairs, self.num_experts) > ex.send_rows:
-            ex = self._ex = SymmExpertExchange(self.group, self.num_experts, xt.shape[1], pairs, xt.device,
-                                               self.capacity_factor, xt.dtype)
+            ex = SymmDispatcher._shared.get(key)
+            if ex is None:
+                ex = SymmDispatcher._shared[key] = SymmExpertExchange(
+                    self.group, self.num_experts, xt.shape[1], pairs, xt.device, self.capacity_factor, xt.dtype)
+            self._ex = ex
         return ex
 
     def __call__(self, xt, idx, weights, experts):
