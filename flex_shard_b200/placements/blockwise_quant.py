@@ -105,6 +105,16 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
         a, b = self.row_ranges[rank]
         return [Piece(0, a, b - a)] if b > a else []
 
+    @staticmethod
+    def matrix_dims(shape, rows: int) -> tuple[int, int]:
+        """The matrix that ``rows`` leading rows of a weight are quantised as: a 2-D weight ``[out, in]`` is its
+        own matrix; a stacked weight ``[*stack, out, in]`` (experts) is the stack's matrices one under the other,
+        ``[prod(stack) * out, in]``, and ``rows`` counts entries of the leading dimension. ``out`` is a multiple
+        of the block height for stacked weights, so no quantisation block straddles two matrices and the
+        result equals quantising every matrix alone (parity: the reference's "matrix a stacked weight is
+        quantized as", ``custom_placements/blockwise_quant_bucketed_block_shard.py:101``)."""
+        return rows * math.prod(shape[1:-1]), shape[-1]
+
     # ---- format hooks
     def qdata_nbytes(self, rows: int, cols: int) -> int:
         raise NotImplementedError
@@ -126,15 +136,15 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
             items, off = [], 0
             for i, info in enumerate(infos):
                 a, b = info.placement.row_ranges[r]
-                rows, cols = b - a, math.prod(info.global_shape[1:])
-                if rows <= 0:
+                if b - a <= 0:
                     continue
+                rows, cols = self.matrix_dims(info.global_shape, b - a)
                 qb = info.placement.qdata_nbytes(rows, cols)
                 items.append([i, rows, off, qb, 0, 0])
                 off = (off + qb + 15) // 16 * 16
             for it in items:
                 info = infos[it[0]]
-                sb = info.placement.scale_nbytes(it[1], math.prod(info.global_shape[1:]))
+                sb = info.placement.scale_nbytes(it[1], info.global_shape[-1])
                 it[4], it[5] = off, sb
                 off = (off + sb + 15) // 16 * 16
             per_rank.append([tuple(it) for it in items])
@@ -142,7 +152,7 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
         return per_rank, max(sizes) if sizes else 0
 
     def unsharded_buffer_numel(self, info, world_size):
-        rows, cols = info.global_shape[0], math.prod(info.global_shape[1:])
+        rows, cols = self.matrix_dims(info.global_shape, info.global_shape[0])
         nbytes = (self.qdata_nbytes(rows, cols) + 15) // 16 * 16 + (self.scale_nbytes(rows, cols) + 15) // 16 * 16
         return -(-nbytes // info.param_dtype.itemsize)
 
@@ -172,7 +182,7 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
             row = push_row if push_row is not None else recv[rank]
             for i, rows, qo, qb, so, sb in per_rank[rank]:
                 info = infos[i]
-                cols = math.prod(info.global_shape[1:])
+                cols = info.global_shape[-1]
                 w = info.placement.make_local_storage_view(info, byte_storage).reshape(rows, cols)
                 if w.dtype != info.param_dtype:
                     w = w.to(info.param_dtype)  # quantise from the compute dtype, as the dense path would
@@ -214,7 +224,7 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
         with record("FlexShard::copy_out"):
             for i, (info, buf) in enumerate(zip(infos, persistent)):
                 pl = info.placement
-                rows_total, cols = info.global_shape[0], math.prod(info.global_shape[1:])
+                rows_total, cols = self.matrix_dims(info.global_shape, info.global_shape[0])
                 raw = buf.view(torch.uint8)
                 q_total = pl.qdata_nbytes(rows_total, cols)
                 s_start = (q_total + 15) // 16 * 16
@@ -226,8 +236,9 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
                         continue
                     item = next(it for it in prepared.extra["per_rank"][r] if it[0] == i)
                     _, rows, qo, qb, so, sb = item
-                    q_at = pl.qdata_nbytes(a, cols)
-                    s_at = pl.scale_nbytes(a, cols)  # whole blocks precede row a
+                    first = self.matrix_dims(info.global_shape, a)[0]
+                    q_at = pl.qdata_nbytes(first, cols)
+                    s_at = pl.scale_nbytes(first, cols)  # whole blocks precede the first row
                     copies.append((qdst[q_at:q_at + qb], recv[r, qo:qo + qb]))
                     copies.append((sdst[s_at:s_at + sb], recv[r, so:so + sb]))
                 outs.append((pl, qdst, sdst, info))
@@ -267,7 +278,7 @@ class Fp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
         from ..ops.fp8 import FP8
         from ..quant.weight import BlockwiseFp8Weight
 
-        rows, cols = shape[0], math.prod(shape[1:])
+        rows, cols = math.prod(shape[:-1]), shape[-1]
         return BlockwiseFp8Weight(qdata_bytes.view(FP8).view(rows, cols),
                                   scale_bytes.view(torch.float32).view(-(-rows // 128), -(-cols // 128)),
                                   shape, dtype)
@@ -306,7 +317,7 @@ class Mxfp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
         from ..ops.mxfp8 import FP8
         from ..quant.weight import BlockwiseMxfp8Weight
 
-        rows, cols = shape[0], math.prod(shape[1:])
+        rows, cols = math.prod(shape[:-1]), shape[-1]
         return BlockwiseMxfp8Weight.from_tile_exponents(qdata_bytes.view(FP8).view(rows, cols),
                                                         scale_bytes.view(-(-rows // 32), -(-cols // 32)), shape, dtype)
 
@@ -316,10 +327,12 @@ def plan_row_ranges(shapes: Sequence[tuple[int, ...]], world_size: int, block_ro
     """Row range of every parameter on every rank: ``result[param][rank] = (r0, r1)``."""
     units = []  # (param, r0, r1, cost)
     for i, s in enumerate(shapes):
-        cols = math.prod(s[1:])
-        for r0 in range(0, s[0], block_rows):
-            r1 = min(s[0], r0 + block_rows)
-            units.append((i, r0, r1, cost_of(r1 - r0, cols)))
+        # 2-D weights are cut on whole blocks of rows; a stacked weight [*stack, out, in] on whole entries of
+        # its leading dimension (each one or more matrices of `out` rows)
+        step = block_rows if len(s) <= 2 else 1
+        for r0 in range(0, s[0], step):
+            r1 = min(s[0], r0 + step)
+            units.append((i, r0, r1, cost_of(*BlockwiseQuantBucketedBlockShard.matrix_dims(s, r1 - r0))))
     cuts = partition_min_max([u[3] for u in units], world_size)
     out = [[(0, 0)] * world_size for _ in shapes]
     for r in range(world_size):
@@ -338,8 +351,17 @@ def plan_row_ranges(shapes: Sequence[tuple[int, ...]], world_size: int, block_ro
     return out
 
 
+def _check_quantisable(fqn: str, p, block_rows: int, who: str) -> None:
+    if p.dim() < 2:
+        raise ValueError(f"{who} only supports 2-D or stacked 2-D weights, {fqn!r} has shape {tuple(p.shape)}")
+    if p.dim() > 2 and math.prod(p.shape[1:-1]) % block_rows:
+        raise ValueError(f"{who}: the matrices of the stacked weight {fqn!r} {tuple(p.shape)} must have a multiple "
+                         f"of {block_rows} rows, so that no quantisation block straddles two of them")
+
+
 def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
-    """Placement function for FP8 buckets: parameters must be 2-D weights with ``in`` a multiple of 128."""
+    """Placement function for FP8 buckets: 2-D weights ``[out, in]`` or stacked weights ``[*stack, out, in]``
+    whose ``out`` is a multiple of the block size."""
 
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
@@ -347,8 +369,7 @@ def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
         _, _, W, _ = mesh_group(mesh)
         shapes = [tuple(p.shape) for _, p in named_params]
         for (f, p) in named_params:
-            if p.dim() != 2:
-                raise ValueError(f"Fp8BucketedBlockShard needs 2-D weights, {f!r} has shape {tuple(p.shape)}")
+            _check_quantisable(f, p, block_size, "Fp8BucketedBlockShard")
         cost = lambda rows, cols: rows * cols + -(-rows // block_size) * -(-cols // block_size) * 4
         ranges = plan_row_ranges(shapes, W, block_size, cost)
         return {f: Fp8BucketedBlockShard(ranges[i]) for i, (f, _) in enumerate(named_params)}
@@ -357,7 +378,8 @@ def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
 
 
 def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil"):
-    """Placement function for MXFP8 buckets: 2-D weights, rows handed out in whole 128-row units."""
+    """Placement function for MXFP8 buckets: 2-D weights (rows handed out in whole 128-row units) or stacked
+    weights ``[*stack, out, in]`` with ``out`` a multiple of 128 (handed out matrix by matrix)."""
 
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
@@ -365,8 +387,7 @@ def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil"):
         _, _, W, _ = mesh_group(mesh)
         shapes = [tuple(p.shape) for _, p in named_params]
         for (f, p) in named_params:
-            if p.dim() != 2:
-                raise ValueError(f"Mxfp8BucketedBlockShard needs 2-D weights, {f!r} has shape {tuple(p.shape)}")
+            _check_quantisable(f, p, 128, "Mxfp8BucketedBlockShard")
         cost = lambda rows, cols: rows * cols + -(-rows // 32) * -(-cols // 32)
         ranges = plan_row_ranges(shapes, W, 128, cost)
         return {f: Mxfp8BucketedBlockShard(ranges[i], scaling_mode) for i, (f, _) in enumerate(named_params)}

@@ -1,6 +1,7 @@
 """Quantised weight wrappers and the linear layers that consume them."""
 from .linear import (
     FlexShardFloat8BlockwiseLinear,
+    FlexShardFloat8BlockwiseStackedLinear,
     FlexShardMxfp8BlockwiseLinear,
     FlexShardPrequantizedLinear,
     convert_to_flex_shard_float8_blockwise_linear,

@@ -46,6 +46,65 @@ class FlexShardFloat8BlockwiseLinear(FlexShardPrequantizedLinear):
         return fp8_linear(x, w, wq, ws)
 
 
+class _Fp8StackedLinear(torch.autograd.Function):
+    """y[e] = x[e] W[e]^T for a stacked weight ``[E, out, in]`` given as the FP8 payload of the matrices laid one
+    under the other; ``weight`` is the logical parameter that receives the stacked bf16-GEMM weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, wq, ws):
+        from ..ops.fp8 import gemm_fp8, quantize_act
+
+        E, out = x.shape[0], wq.shape[0] // x.shape[0]
+        ctx.save_for_backward(x, wq, ws)
+        ctx.weight_ref, ctx.out = weight, out
+        ys = []
+        for e in range(E):
+            xq, sx = quantize_act(x[e].reshape(-1, x.shape[-1]))
+            ys.append(gemm_fp8(xq, sx, wq[e * out:(e + 1) * out], ws[e * out // 128:(e + 1) * out // 128]))
+        return torch.stack(ys).view(E, *x.shape[1:-1], out)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.fp8 import gemm_fp8, quantize_act
+        from ..ops.gemm import gemm
+
+        x, wq, ws = ctx.saved_tensors
+        E, out, cin = x.shape[0], ctx.out, x.shape[-1]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dxs = []
+            for e in range(E):
+                dyq, sdy = quantize_act(dy[e].reshape(-1, out).contiguous())
+                dxs.append(gemm_fp8(dyq, sdy, wq[e * out:(e + 1) * out], ws[e * out // 128:(e + 1) * out // 128], b_t=True))
+            dx = torch.stack(dxs).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            gd = getattr(ctx.weight_ref, "grad_dtype", None)
+            gd = gd if gd in (torch.bfloat16, torch.float32) else torch.bfloat16
+            dw = torch.empty(E, out, cin, dtype=gd, device=x.device)
+            for e in range(E):
+                gemm(dy[e].reshape(-1, out).contiguous(), x[e].reshape(-1, cin).contiguous(), a_t=True, b_t=True, out=dw[e])
+        return dx, dw, None, None
+
+
+class FlexShardFloat8BlockwiseStackedLinear(nn.Module):
+    """``n`` independent linears held as one stacked weight ``[n, out, in]`` (MoE experts): ``forward(x)`` maps
+    ``x[e]`` through matrix ``e``. Under ``Fp8BucketedBlockShard`` the gathered weight is one FP8 payload of the
+    matrices laid one under the other (``out`` a multiple of 128, so every matrix keeps its own tiles)."""
+
+    def __init__(self, n: int, in_features: int, out_features: int, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.n, self.in_features, self.out_features = n, in_features, out_features
+        self.weight = nn.Parameter(torch.empty(n, out_features, in_features, dtype=dtype, device=device))
+
+    def forward(self, x):
+        w = self.weight
+        if isinstance(w, BlockwiseFp8Weight):
+            wq, ws = w.qdata, w.scale
+        else:
+            wq, ws = quantize_blockwise(w.detach().to(torch.bfloat16).reshape(-1, self.in_features))
+        return _Fp8StackedLinear.apply(x, w, wq, ws)
+
+
 class FlexShardMxfp8BlockwiseLinear(FlexShardPrequantizedLinear):
     """Linear on MXFP8 operands: forward and input-gradient products run on the block-scaled tensor
     core path (``kind::mxf8f6f4``), activations and output gradients are quantised 1x32 on the fly,

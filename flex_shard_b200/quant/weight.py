@@ -56,7 +56,17 @@ class BlockwiseFp8Weight(BlockwiseQuantWeight):
     def dequantize(self, dtype=torch.float32) -> torch.Tensor:
         from ..ops.fp8 import dequantize_blockwise
 
-        return dequantize_blockwise(self.qdata, self.scale, dtype)
+        return dequantize_blockwise(self.qdata, self.scale, dtype).reshape(self.shape)
+
+    def matrix(self, *index: int) -> "BlockwiseFp8Weight":
+        """Matrix ``index`` of a stacked weight ``[*stack, out, in]`` as a 2-D quantised weight (views of the same
+        payload: the stack's matrices lie one under the other and ``out`` is a multiple of 128)."""
+        *stack, out, cin = self.shape
+        flat = 0
+        for i, n in zip(index, stack):
+            flat = flat * n + i
+        return BlockwiseFp8Weight(self.qdata[flat * out:(flat + 1) * out],
+                                  self.scale[flat * out // 128:(flat + 1) * out // 128], (out, cin), self.dtype)
 
 
 class BlockwiseMxfp8Weight(BlockwiseQuantWeight):
@@ -100,6 +110,17 @@ class BlockwiseMxfp8Weight(BlockwiseQuantWeight):
 
     def dequantize(self, dtype=torch.float32) -> torch.Tensor:
         return blockwise_mxfp8_dequant_weight(self.qdata, self.scale).reshape(self.shape).to(dtype)
+
+    def matrix(self, *index: int) -> "BlockwiseMxfp8Weight":
+        """Matrix ``index`` of a stacked weight as a 2-D MXFP8 weight (its blocked scale tensors are rebuilt from
+        the matrix's tile exponents)."""
+        *stack, out, cin = self.shape
+        flat = 0
+        for i, n in zip(index, stack):
+            flat = flat * n + i
+        te = self.extra["tile_exp"]
+        return BlockwiseMxfp8Weight.from_tile_exponents(self.qdata[flat * out:(flat + 1) * out],
+                                                        te[flat * out // 32:(flat + 1) * out // 32], (out, cin), self.dtype)
 
 
 def blockwise_mxfp8_dequant_weight(fp8_data: torch.Tensor, fwd_scale: torch.Tensor) -> torch.Tensor:

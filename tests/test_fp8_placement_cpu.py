@@ -87,3 +87,76 @@ def test_fp8_bucket_trains_like_gather_then_quantize():
         assert r["send_bytes"] < r["bf16_bytes"]       # FP8 + scales is smaller than a bf16 shard
         assert r["master_dtype"] == "torch.bfloat16"
         assert all(r["equal_logits"]), r               # stays bitwise through SGD steps
+
+
+class ExpertNet(nn.Module):
+    """A stacked expert weight [4, 128, 256] next to a plain 2-D weight in the same FP8 bucket."""
+
+    def __init__(self):
+        super().__init__()
+        from flex_shard_b200.quant import FlexShardFloat8BlockwiseLinear, FlexShardFloat8BlockwiseStackedLinear
+
+        self.inp = FlexShardFloat8BlockwiseLinear(256, 256)
+        self.experts = FlexShardFloat8BlockwiseStackedLinear(4, 256, 128)
+
+    def forward(self, x):                       # x [4, T, 256]
+        h = self.inp(x.reshape(-1, 256)).view(x.shape)
+        return self.experts(h)
+
+
+def _run_stacked(rank, world, steps):
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.ops.fp8 import quantize_blockwise
+    from flex_shard_b200.placements import make_fp8_bucketed_block_shard_placement_fn
+
+    model, twin = ExpertNet(), ExpertNet()
+    _init(model)
+    _init(twin)
+    flex_shard(model, [BucketSpec(["*"], placement_fn=make_fp8_bucketed_block_shard_placement_fn())])
+    st = model.sharded_bucket_storages[0]
+    out = {"ranges": [i.placement.row_ranges for i in st.infos], "bitwise": [], "matrix": [], "equal": []}
+    model.unshard()
+    for up, (n, tw) in zip(st.runtime.unsharded_params, twin.named_parameters()):
+        q, sc = quantize_blockwise(tw.detach().reshape(-1, tw.shape[-1]))
+        out["bitwise"].append(bool(torch.equal(up.qdata.view(torch.uint8), q.view(torch.uint8)) and torch.equal(up.scale, sc)))
+        if tw.dim() == 3:
+            for e in range(tw.shape[0]):       # every matrix equals quantising that matrix alone
+                qe, se = quantize_blockwise(tw.detach()[e])
+                m = up.matrix(e)
+                out["matrix"].append(bool(torch.equal(m.qdata.view(torch.uint8), qe.view(torch.uint8))
+                                          and torch.equal(m.scale, se) and tuple(m.shape) == tuple(tw.shape[1:])))
+    model.reshard()
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    topt = torch.optim.SGD(twin.parameters(), lr=0.05)
+    for s in range(steps):
+        xs = [torch.randn(4, 8, 256, generator=torch.Generator().manual_seed(10 * s + r)).bfloat16() for r in range(world)]
+        y = model(xs[rank])
+        y.float().square().mean().backward()
+        opt.step()
+        opt.zero_grad()
+        ty = [twin(x) for x in xs]
+        out["equal"].append(bool(torch.equal(ty[rank], y)))
+        sum(t.float().square().mean() for t in ty).div(world).backward()
+        topt.step()
+        topt.zero_grad()
+    return out
+
+
+def test_stacked_expert_weights_gather_quantised_matrix_by_matrix():
+    res = run_ranks(_run_stacked, 2, 3)
+    for r in res:
+        assert all(r["bitwise"]) and len(r["matrix"]) == 4 and all(r["matrix"]), r
+        assert all(r["equal"]), r
+    # the stacked weight is handed out in whole matrices (entries of its leading dimension)
+    stacked = [rg for rg in res[0]["ranges"] if max(b for _, b in rg) == 4]
+    assert stacked and all(0 <= a <= b <= 4 for rg in stacked for a, b in rg)
+
+
+def test_stacked_weight_whose_matrices_split_a_block_is_refused():
+    import pytest
+    from flex_shard_b200.placements import make_fp8_bucketed_block_shard_placement_fn
+    from tests.common import FakeMesh
+
+    fn = make_fp8_bucketed_block_shard_placement_fn()
+    with pytest.raises(ValueError, match="multiple of 128"):
+        fn([("w", nn.Parameter(torch.zeros(4, 96, 256)))], FakeMesh(2))
