@@ -220,3 +220,19 @@ def test_bucket_debug_names():
     assert bucket_debug_fqn(["layers.1.a.w", "layers.2.a.w"]) == "layers"
     assert bucket_debug_fqn([]) is None
     assert strip_wrapper_path("a._orig_mod.b") == "a.b"
+
+
+def test_failed_wait_record_names_region_slot_epoch_and_peer():
+    """The device status record of a failed peer wait (code, flag address, epoch, peer, value seen) is turned into
+    a message that names the registered symmetric region and the flag slot."""
+    from flex_shard_b200.ops import _lib
+
+    base = 0x7F0012340000
+    _lib.register_flag_range(base, 65536, lambda: "gradient ring (3 entries)", 64)
+    addr = base + 17 * 64 + 4 * 3          # slot 17, the word of group rank 3
+    rec = [32, addr & 0xFFFFFFFF, addr >> 32, 41, 3, 40, 0, 0]
+    msg = _lib._describe([v - (1 << 32) if v >= (1 << 31) else v for v in rec])     # as int32 values
+    assert "gradient ring (3 entries)" in msg and "flag slot 17" in msg
+    assert "epoch 41" in msg and "group rank 3" in msg and "last value seen 40" in msg
+    other = _lib._describe([18, 0, 0, 0, 0, 0, 0, 0])
+    assert "code 18" in other and "flag" not in other

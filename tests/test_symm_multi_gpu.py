@@ -91,7 +91,24 @@ def _worker(rank, world, port, out):
             ops.check_status()
             res["timeout_reported"] = False
         except ops.NativeError as e:
-            res["timeout_reported"] = "peer" in str(e)
+            msg = str(e)
+            # the record names the region, the flag slot, the epoch and the peer that never signalled
+            res["timeout_reported"] = ("peer" in msg and "flag slot 900" in msg and "epoch 1" in msg
+                                       and "all-gather staging region" in msg)
+        # after a first failure every later wait returns at once instead of sitting out its own limit
+        reg.wait(900, 1)                       # fails again (short limit) and sets the status word
+        reg.max_polls = 20_000_000             # several seconds if it were waited out
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        reg.wait(901, 1)
+        t1.record()
+        torch.cuda.synchronize()
+        res["fails_fast_after_first_failure"] = t0.elapsed_time(t1) < 500.0
+        try:
+            ops.check_status()
+        except ops.NativeError:
+            pass
+        reg.max_polls = 2000
         # the context is still usable afterwards
         res["alive"] = float(torch.ones(4, device=dev).sum()) == 4.0
         dist.barrier()
@@ -111,7 +128,7 @@ def test_symm_collectives_match_nccl(tmp_path):
     for r in range(world):
         res = torch.load(tmp_path / f"r{r}.pt")
         for k, v in res.items():
-            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive",
+            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive", "fails_fast_after_first_failure",
                                                                          "mc_bitwise_at_two_ranks"):
                 assert v is True, (k, v)
             elif k.endswith("_close"):
