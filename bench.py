@@ -53,7 +53,7 @@ def parse():
                          "per step instead of two; +2 bytes/param of HBM, affordable on 180 GB); 0: reshard after forward")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers is not the headline config")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--watchdog", type=int, default=1500,
+    ap.add_argument("--watchdog", type=int, default=900,
                     help="seconds after which a run that has not finished prints every thread's Python stack and "
                          "exits with an error (0: off)")
     ap.add_argument("--deterministic", action="store_true",

@@ -75,3 +75,28 @@ def test_fp8_linear_close_to_bf16_linear():
     assert (x.grad.float() - xr.grad).abs().max() < 0.15 * xr.grad.abs().max()
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=3e-2, atol=3e-1)
     ops.check_status()
+
+
+def test_stacked_fp8_linear_runs_every_matrix_through_its_own_tiles():
+    """A stacked weight [E, out, in] quantised as its matrices one under the other: every x[e] goes through matrix e;
+    forward, input gradient and stacked weight gradient against per-matrix fp32 linears."""
+    from flex_shard_b200.quant import FlexShardFloat8BlockwiseStackedLinear
+
+    torch.manual_seed(5)
+    E, T, cin, cout = 3, 128, 512, 256
+    lin = FlexShardFloat8BlockwiseStackedLinear(E, cin, cout, device=DEV)
+    with torch.no_grad():
+        lin.weight.copy_(0.05 * torch.randn(E, cout, cin, device=DEV))
+    x = torch.randn(E, T, cin, device=DEV).bfloat16().requires_grad_()
+    y = lin(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ops.check_status()
+    xr = x.detach().float().requires_grad_()
+    wr = lin.weight.detach().float().requires_grad_()
+    yr = torch.einsum("etk,enk->etn", xr, wr)
+    yr.backward(g.float())
+    assert y.shape == (E, T, cout)
+    assert (y.float() - yr).abs().max() < 0.15 * yr.abs().max()
+    assert (x.grad.float() - xr.grad).abs().max() < 0.15 * xr.grad.abs().max()
+    torch.testing.assert_close(lin.weight.grad.float(), wr.grad, rtol=3e-2, atol=3e-1)
