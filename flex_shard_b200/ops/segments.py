@@ -101,6 +101,39 @@ def _key(ops):
 _plans: dict = {}
 
 
+def _check_table(ops, plan, table) -> None:
+    """Debug check of a descriptor table on the host (``FSB200_CHECK_SEGMENTS=1``): every run must lie inside the
+    storage of the tensor it belongs to, and no two destination runs may overlap. The kernel trusts its table, so
+    this is where a wrong offset is caught before it becomes a stray device write."""
+    unit = {MODE_COPY: (1, 1), MODE_ZERO: (1, 0), MODE_F32_TO_BF16: (2, 4), MODE_BF16_TO_F32: (4, 2)}
+    spans = []
+    for k in range(plan.op.size):
+        d, s = ops[int(plan.op[k])]
+        db, sb = unit[int(table["mode"][k])]
+        n = int(table["n"][k])
+        for what, t, start, nbytes in (("destination", d, int(table["dst"][k]), n * db),
+                                       ("source", s, int(table["src"][k]), n * sb)):
+            if t is None or nbytes == 0:
+                continue
+            st = t.untyped_storage()
+            lo, hi = st.data_ptr(), st.data_ptr() + st.nbytes()
+            if start < lo or start + nbytes > hi:
+                raise RuntimeError(f"segment table: {what} run {k} [{start:#x}, +{nbytes}) leaves its tensor's storage "
+                                   f"[{lo:#x}, {hi:#x})")
+        spans.append((int(table["dst"][k]), int(table["dst"][k]) + n * db, k))
+    spans.sort()
+    for (a0, a1, ka), (b0, b1, kb) in zip(spans, spans[1:]):
+        if b0 < a1:
+            raise RuntimeError(f"segment table: destination runs {ka} and {kb} overlap ([{a0:#x}, {a1:#x}) and "
+                               f"[{b0:#x}, {b1:#x}))")
+
+
+def _checking() -> bool:
+    import os
+
+    return os.environ.get("FSB200_CHECK_SEGMENTS", "0") == "1"
+
+
 def run_segment_ops(ops, cache: dict | None = None) -> int:
     """Execute ``ops`` = [(dst view, src view or None)]: copy (casting fp32<->bf16 when the dtypes differ) or
     zero-fill.  Destinations must not overlap.  On CUDA this is one launch (per 65 535 runs); returns the
@@ -133,6 +166,8 @@ def run_segment_ops(ops, cache: dict | None = None) -> int:
     table["dst"] = dbase[plan.op] + plan.doff.astype(np.uint64)
     table["src"] = sbase[plan.op] + plan.soff.astype(np.uint64)
     table["n"], table["mode"], table["pad"] = plan.n, plan.mode, 0
+    if _checking():
+        _check_table(ops, plan, table)
     dev = ops[0][0].device
     host = torch.from_numpy(table.view(np.uint8)).pin_memory()
     lib, stream, launches = _lib.load(), _lib.stream_ptr(dev), 0

@@ -6,6 +6,9 @@ import pytest
 # inherited by the worker processes of the multi-GPU tests, which select their device (and so initialise CUDA)
 # before they import the package: kernels that wait for a peer must not meet lazy kernel loading
 os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+# the tests run with the host-side check of every segment-copy descriptor table switched on (bounds of every run,
+# no overlapping destinations): the stand-in for a device sanitizer, which this pool does not offer
+os.environ.setdefault("FSB200_CHECK_SEGMENTS", "1")
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 

@@ -74,3 +74,37 @@ def test_cpu_path_and_cache_key():
     assert torch.equal(ops[1][0], ops[1][1])
     k1, k2 = sg._key(_cases()), sg._key(_cases())
     assert k1 == k2                              # geometry only: addresses are not part of the key
+
+
+def _table_of(ops):
+    ops = [(d, s) for d, s in ops if d.numel()]
+    plan = sg._Plan(ops)
+    table = np.empty(plan.op.size, sg._DESC)
+    dbase = np.asarray([d.data_ptr() for d, _ in ops], np.uint64)
+    sbase = np.asarray([0 if s is None else s.data_ptr() for _, s in ops], np.uint64)
+    table["dst"] = dbase[plan.op] + plan.doff.astype(np.uint64)
+    table["src"] = sbase[plan.op] + plan.soff.astype(np.uint64)
+    table["n"], table["mode"], table["pad"] = plan.n, plan.mode, 0
+    return ops, plan, table
+
+
+def test_debug_check_catches_stray_and_overlapping_runs():
+    """The host-side check of a descriptor table (the debug mode that stands in for a device sanitizer): a valid
+    table passes, a run moved outside its tensor's storage and two overlapping destinations are refused."""
+    import pytest
+
+    ops, plan, table = _table_of(_cases())
+    sg._check_table(ops, plan, table)                       # the valid table
+    bad = table.copy()
+    bad["dst"][0] += np.uint64(400 * 4)                     # 60 floats starting at the end of a 400-float row
+    with pytest.raises(RuntimeError, match="leaves its tensor's storage"):
+        sg._check_table(ops, plan, bad)
+    bad = table.copy()
+    bad["src"][1] -= np.uint64(4096)
+    with pytest.raises(RuntimeError, match="source run"):
+        sg._check_table(ops, plan, bad)
+    row = torch.zeros(64)
+    a = torch.randn(4, 8)
+    ops2, plan2, table2 = _table_of([(row[0:32].view(4, 8), a), (row[24:56].view(4, 8), a)])
+    with pytest.raises(RuntimeError, match="overlap"):
+        sg._check_table(ops2, plan2, table2)
