@@ -1,0 +1,227 @@
+"""The module-level control surface on a one-rank CPU mesh (no worker processes): bucket validation, class
+swizzle, meta materialisation, state dicts, explicit unshard handles, setters, frozen parameters, and the rule
+that a one-rank mesh issues no collective.  Parity: the role of the reference's ``tests/test_flex_shard_api.py``
+and ``tests/test_flex_shard_state_dict.py`` (single-rank harness, ``tests/common.py:31-51``)."""
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+class Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(8, 16)
+        self.b = nn.Linear(16, 4)
+
+    def forward(self, x):
+        return self.b(torch.relu(self.a(x)))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def one_rank_group():
+    if dist.is_initialized():
+        yield
+        return
+    store = dist.FileStore(tempfile.NamedTemporaryFile(delete=False).name, 1)
+    dist.init_process_group("gloo", store=store, rank=0, world_size=1)
+    yield
+    dist.destroy_process_group()
+
+
+def _sharded(buckets=None, **kw):
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    torch.manual_seed(0)
+    m = Net()
+    flex_shard(m, buckets or [BucketSpec(["a.*"], **kw), BucketSpec(["b.*"], **kw)])
+    return m
+
+
+def test_every_parameter_belongs_to_exactly_one_bucket():
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    with pytest.raises(ValueError, match="matches no BucketSpec"):
+        flex_shard(Net(), [BucketSpec(["a.*"])])
+    with pytest.raises(ValueError, match="more than one BucketSpec"):
+        flex_shard(Net(), [BucketSpec(["a.*"]), BucketSpec(["*"])])
+    with pytest.raises((ValueError, TypeError)):
+        flex_shard(Net(), [])
+
+
+def test_flex_shard_applies_once():
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    m = _sharded()
+    with pytest.raises(ValueError, match="already applied"):
+        flex_shard(m, [BucketSpec(["*"])])
+
+
+def test_class_swizzle_keeps_the_original_class():
+    from flex_shard_b200 import FlexShardModule
+
+    m = _sharded()
+    assert isinstance(m, Net) and isinstance(m, FlexShardModule)
+    assert type(m).__name__ == "FlexShardNet"
+    assert [st.name for st in m.sharded_bucket_storages] == ["a", "b"]
+    assert [[i.fqn for i in st.infos] for st in m.sharded_bucket_storages] == [["a.weight", "a.bias"], ["b.weight", "b.bias"]]
+
+
+def test_training_step_matches_the_plain_module():
+    m = _sharded()
+    torch.manual_seed(0)
+    ref = Net()
+    opt, ropt = torch.optim.SGD(m.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    ids = [id(p) for p in m.parameters()]
+    for s in range(3):
+        x = torch.randn(4, 8, generator=torch.Generator().manual_seed(s))
+        for mod, o in ((m, opt), (ref, ropt)):
+            mod(x).square().mean().backward()
+            o.step()
+            o.zero_grad()
+    assert ids == [id(p) for p in m.parameters()]            # the optimizer keeps seeing the same parameters
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        assert torch.equal(p.detach(), q.detach()), n
+
+
+def test_one_rank_mesh_issues_no_collective(monkeypatch):
+    def boom(*a, **k):
+        raise AssertionError("a one-rank mesh must not call a collective")
+
+    for name in ("all_gather_into_tensor", "reduce_scatter_tensor", "all_reduce", "all_gather", "all_to_all_single"):
+        monkeypatch.setattr(dist, name, boom)
+    m = _sharded()
+    m(torch.randn(4, 8)).square().mean().backward()
+    assert all(p.grad is not None for p in m.parameters())
+
+
+def test_state_dict_has_the_plain_keys_and_reshards_first():
+    m = _sharded()
+    plain = Net().state_dict()
+    m.unshard()
+    assert m.sharded_bucket_storages[0].runtime.is_unsharded
+    sd = m.state_dict()
+    assert not m.sharded_bucket_storages[0].runtime.is_unsharded      # the pre-hook put the shards back
+    assert list(sd) == list(plain) and all(sd[k].shape == plain[k].shape for k in sd)
+    other = _sharded()
+    with torch.no_grad():
+        for p in other.parameters():
+            p.zero_()
+    other.load_state_dict(sd)
+    x = torch.randn(4, 8)
+    assert torch.equal(other(x), m(x))
+
+
+def test_explicit_unshard_returns_a_handle_and_rejects_backward():
+    m = _sharded()
+    h = m.unshard(async_op=True)
+    assert type(h).__name__ == "ModuleUnshardHandle"
+    h.wait()
+    assert all(st.runtime.is_unsharded for st in m.sharded_bucket_storages)
+    m.reshard()
+    assert not any(st.runtime.is_unsharded for st in m.sharded_bucket_storages)
+    assert m.unshard() is None
+    m.reshard()
+    seen = []
+
+    def hook(g):
+        try:
+            m.unshard()
+        except RuntimeError as e:
+            seen.append(str(e))
+        return g
+
+    y = m(torch.randn(4, 8))
+    y.register_hook(hook)
+    y.square().mean().backward()
+    assert seen and "cannot run in backward" in seen[0]
+
+
+def test_setters_validate_their_arguments():
+    m = _sharded()
+    with pytest.raises(ValueError, match=">= 1"):
+        m.set_max_pending_reduce_grads(0)
+    with pytest.raises(ValueError, match="AVG or SUM"):
+        m.set_gradient_reduce_op("sum")
+    m.set_gradient_reduce_op(dist.ReduceOp.SUM)
+    m.set_gradient_divide_factor(4.0)
+    m.set_max_pending_reduce_grads(2)
+    m.set_reshard_after_backward(False)
+    m.set_reshard_after_forward(False)
+    m.set_requires_gradient_sync(True)
+    assert m.sharded_bucket_storages[0].runtime.context.max_pending_reduce_grads == 2
+    with pytest.raises(ValueError, match="not managed"):
+        m.bucket_storage_of(nn.Parameter(torch.zeros(1)))
+    st = m.sharded_bucket_storages[1]
+    assert m.bucket_storage_of(st.sharded_params[0]) is st
+
+
+def test_divide_factor_scales_the_reduced_gradient():
+    """With SUM and a divide factor f the sharded gradient is the local gradient / f (one rank)."""
+    m, ref = _sharded(), _sharded()
+    m.set_gradient_reduce_op(dist.ReduceOp.SUM)
+    m.set_gradient_divide_factor(4.0)
+    x = torch.randn(4, 8)
+    for mod in (m, ref):
+        mod(x).square().mean().backward()
+    for p, q in zip(m.parameters(), ref.parameters()):
+        torch.testing.assert_close(p.grad, q.grad / 4.0)
+
+
+def test_meta_module_is_materialised_by_to_empty():
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    with torch.device("meta"):
+        m = Net()
+    flex_shard(m, [BucketSpec(["*"])])
+    with pytest.raises(RuntimeError, match="to_empty"):
+        m.unshard()
+    assert all(p.device.type == "meta" for p in m.parameters())
+    m.to_empty(device="cpu")
+    assert all(p.device.type == "cpu" for p in m.parameters())
+    with torch.no_grad():
+        for p in m.parameters():
+            p.normal_()
+    assert m(torch.randn(2, 8)).shape == (2, 4)
+    m(torch.randn(2, 8)).sum().backward()
+    assert all(p.grad is not None for p in m.parameters())
+
+
+def test_frozen_parameters_get_no_gradient_and_no_reduction():
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    torch.manual_seed(0)
+    m = Net()
+    for p in m.a.parameters():
+        p.requires_grad_(False)
+    flex_shard(m, [BucketSpec(["a.*"]), BucketSpec(["b.*"])])
+    ctx = m.sharded_bucket_storages[0].runtime.context
+    before = ctx.stats["reduces"]
+    m(torch.randn(4, 8)).square().mean().backward()
+    assert all(p.grad is None for p in m.a.parameters()) and all(p.grad is not None for p in m.b.parameters())
+    assert ctx.stats["reduces"] - before == 1          # only the trainable bucket reduced
+    assert ctx.idle()
+
+
+def test_shared_parameter_is_stored_once():
+    """Tied weights (one Parameter under two names) land in one bucket slot and stay tied after sharding."""
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    class Tied(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(10, 8)
+            self.out = nn.Linear(8, 10, bias=False)
+            self.out.weight = self.emb.weight
+
+        def forward(self, t):
+            return self.out(self.emb(t))
+
+    m = Tied()
+    flex_shard(m, [BucketSpec(["*"])])
+    assert m.out.weight is m.emb.weight
+    assert len(list(m.parameters())) == 1
+    m(torch.randint(0, 10, (3, 5))).square().mean().backward()
+    assert m.emb.weight.grad is not None and m.out.weight is m.emb.weight
