@@ -153,77 +153,89 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // the reduction and the output pass; the weights are loaded once per CTA.
 constexpr int NORM_BWD_ROWS = 32;
 
-__global__ void __launch_bounds__(NORM_THREADS, 2)
+// G = number of 2048-column groups a thread touches (D <= 2048 G). The CTAs form a persistent grid that walks the
+// rows with stride gridDim.x; the next row's dy / x / residual-gradient vectors are loaded before the current row
+// is reduced, so a CTA always has two rows of loads in flight (without that the row loop is a chain of
+// load -> barrier -> store latencies: 0.175 ms for 8192 x 4096, four times the traffic's time).
+template <int G>
+__global__ void __launch_bounds__(NORM_THREADS, G <= 2 ? 2 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, long long T, int D) {
   __shared__ float red[16];
-  // Per-thread dw accumulators for up to 4 column groups (D <= 8192).
-  float dwacc[4][8];
-  uint4 wv[4];
+  float dwacc[G][8];
+  uint4 wv[G];
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
+  for (int g = 0; g < G; ++g) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[g][j] = 0.f;
     const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
     wv[g] = i < D ? *reinterpret_cast<const uint4*>(w + i) : make_uint4(0, 0, 0, 0);
   }
-  const long long row0 = static_cast<long long>(blockIdx.x) * NORM_BWD_ROWS;
-  int ph = 0;
-  for (int rr = 0; rr < NORM_BWD_ROWS; ++rr) {
-    const long long row = row0 + rr;
-    if (row >= T) break;
-    const float r = rstd[row];
-    uint4 av[4], bv[4];
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  uint4 av[G], bv[G], ev[G];
+  float r = 0.f;
+  auto load_row = [&](long long row, uint4 (&a)[G], uint4 (&b)[G], uint4 (&e)[G], float& rs) {
+    rs = rstd[row];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
+    for (int g = 0; g < G; ++g) {
       const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
-      if (i < D) {
-        av[g] = *reinterpret_cast<const uint4*>(dy + row * D + i);
-        bv[g] = *reinterpret_cast<const uint4*>(x + row * D + i);
-      }
+      const bool in = i < D;
+      a[g] = in ? *reinterpret_cast<const uint4*>(dy + row * D + i) : zero4;
+      b[g] = in ? *reinterpret_cast<const uint4*>(x + row * D + i) : zero4;
+      e[g] = (in && dres != nullptr) ? *reinterpret_cast<const uint4*>(dres + row * D + i) : zero4;
     }
+  };
+  long long row = blockIdx.x;
+  if (row < T) load_row(row, av, bv, ev, r);
+  int ph = 0;
+  for (; row < T; row += gridDim.x) {
+    const long long next = row + gridDim.x;
+    uint4 an[G], bn[G], en[G];
+    float rn = 0.f;
+    if (next < T) load_row(next, an, bn, en, rn);
     float dot = 0.f;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
-      if (i < D) {
-        float a[8], b[8], c[8];
-        unpack8(av[g], a);
-        unpack8(bv[g], b);
-        unpack8(wv[g], c);
+    for (int g = 0; g < G; ++g) {
+      float a[8], b[8], c[8];
+      unpack8(av[g], a);
+      unpack8(bv[g], b);
+      unpack8(wv[g], c);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dot += a[j] * c[j] * b[j];
-      }
+      for (int j = 0; j < 8; ++j) dot += a[j] * c[j] * b[j];
     }
     dot = block_sum_once(dot, red, ph);
     const float coef = dot * r * r * r / D;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
+    for (int g = 0; g < G; ++g) {
       const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
       if (i < D) {
-        float a[8], b[8], c[8], o[8];
+        float a[8], b[8], c[8], e[8], o[8];
         unpack8(av[g], a);
         unpack8(bv[g], b);
         unpack8(wv[g], c);
+        unpack8(ev[g], e);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          o[j] = a[j] * c[j] * r - b[j] * coef;
+          o[j] = a[j] * c[j] * r - b[j] * coef + e[j];
           dwacc[g][j] += a[j] * b[j] * r;
-        }
-        if (dres) {
-          float e[8];
-          unpack8(*reinterpret_cast<const uint4*>(dres + row * D + i), e);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += e[j];
         }
         *reinterpret_cast<uint4*>(dx + row * D + i) = pack8(o);
       }
     }
+    if (next < T) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        av[g] = an[g];
+        bv[g] = bn[g];
+        ev[g] = en[g];
+      }
+      r = rn;
+    }
   }
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
+  for (int g = 0; g < G; ++g) {
     const int i = threadIdx.x * 8 + g * NORM_THREADS * 8;
     if (i < D) {
       float* p = dw_partial + static_cast<long long>(blockIdx.x) * D + i;
@@ -679,11 +691,24 @@ FSB_API int fsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const 
                             int dw_fp32, int dw_accumulate, long long T, int D,
                             cudaStream_t stream) {
   if (D % 8 != 0 || D > 8192 || T <= 0) return FSB_ERR_BAD_ARG;
-  const int blocks = static_cast<int>((T + NORM_BWD_ROWS - 1) / NORM_BWD_ROWS);
-  rmsnorm_bwd_kernel<<<blocks, NORM_THREADS, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
-      static_cast<__nv_bfloat16*>(dx), dw_partial, T, D);
+  // dw_partial holds ceil(T / 32) rows (the caller's contract); the persistent grid uses at most that many CTAs
+  // and at most two per SM
+  int blocks = static_cast<int>((T + NORM_BWD_ROWS - 1) / NORM_BWD_ROWS);
+  static int sms = 0;
+  if (sms == 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0) != cudaSuccess) sms = 148;
+  const int groups = (D + NORM_THREADS * 8 - 1) / (NORM_THREADS * 8);
+  const int per_sm = groups <= 2 ? 2 : 1;     // wide rows keep three double-buffered vectors per group in registers
+  if (blocks > per_sm * sms) blocks = per_sm * sms;
+  auto launch = [&](auto kernel) {
+    kernel<<<blocks, NORM_THREADS, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+        static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
+        static_cast<__nv_bfloat16*>(dx), dw_partial, T, D);
+  };
+  if (groups == 1) launch(rmsnorm_bwd_kernel<1>);
+  else if (groups == 2) launch(rmsnorm_bwd_kernel<2>);
+  else if (groups == 3) launch(rmsnorm_bwd_kernel<3>);
+  else launch(rmsnorm_bwd_kernel<4>);
   colsum_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dw_partial, dw_out, blocks, D, dw_fp32,
                                                       dw_accumulate);
   return launch_ok();

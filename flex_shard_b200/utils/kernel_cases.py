@@ -2,7 +2,7 @@
 
     python -m flex_shard_b200.utils.kernel_cases <case> [--iters N]
 
-Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_bwd_ordered, adamw, rmsnorm, swiglu, cross_entropy,
+Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_bwd_ordered, adamw, rmsnorm, rmsnorm_bwd, swiglu, cross_entropy,
 newton_schulz, newton_schulz_batched, fp8_quant, fp8_gemm, mxfp8_gemm, allgather_gemm, segment_cast. Each prints one JSON line with the CUDA-event time (median of
 ``iters`` launches after 3 warm-up launches, L2 flushed between launches by writing a 256 MB buffer)
 and the achieved FLOP/s or bytes/s. Inputs are a few hundred MB, larger than the 126 MB L2, so DRAM
@@ -116,6 +116,18 @@ def main():
         with torch.no_grad():
             ms = _time(lambda: ew.rmsnorm(x, w), args.iters)
         out.update(T=T, D=D, ms=ms, gbs=T * D * 4 / ms / 1e6)
+    elif args.case == "rmsnorm_bwd":
+        # the Llama step's shape: one sequence of 8192 tokens, with the residual-stream gradient added in
+        T, D = 8192, 4096
+        x = torch.randn(T, D, device=dev).bfloat16().requires_grad_()
+        res = torch.randn(T, D, device=dev).bfloat16().requires_grad_()
+        w = torch.ones(D, device=dev).bfloat16().requires_grad_()
+        y, s2 = ew.add_rmsnorm(x, res, w)
+        gy, gs = torch.randn_like(y), torch.randn_like(s2)
+        fn = lambda: torch.autograd.grad((y, s2), (x, res, w), (gy, gs), retain_graph=True)
+        ms = _time(fn, args.iters)
+        out.update(T=T, D=D, ms=ms, gbs=T * D * 2 * 4 / ms / 1e6,
+                   note="bytes: dy, x, residual gradient in, dx out; time includes the column-sum kernel of dw")
     elif args.case == "swiglu":
         T, F = 16384, 14336
         gu = torch.randn(T, 2 * F, device=dev).bfloat16()
