@@ -458,10 +458,16 @@ def assign_params_to_buckets(root: nn.Module, named_params: list[tuple[str, nn.P
                        if any(_matches(n, pat, modules) for pat in b.patterns)})
         if not hits:
             raise ValueError(f"Parameter {fqn!r} matches no BucketSpec; every parameter must be in exactly one bucket.")
+        if len(names) > 1:
+            # every name of a tied parameter must land in the same bucket (as FSDP2 requires of a group)
+            where = {n: sorted({i for i, b in enumerate(buckets) if any(_matches(n, pat, modules) for pat in b.patterns)})
+                     for n in names}
+            if len(hits) > 1 or any(not w for w in where.values()):
+                listing = ", ".join(f"{n} -> " + (f"bucket {w[0]}" if len(w) == 1 else "no bucket" if not w else f"buckets {w}")
+                                    for n, w in where.items())
+                raise ValueError(f"Tied parameter {fqn!r} is shared with {list(names[1:])!r} ({listing}); put every name "
+                                 "that refers to the parameter in the same BucketSpec.")
         if len(hits) > 1:
-            if len(names) > 1:
-                raise ValueError(
-                    f"Tied parameter {names!r} is split across buckets {hits}; all of its names must fall in one bucket.")
             raise ValueError(f"Parameter {fqn!r} matches more than one BucketSpec (buckets {hits}).")
         owner[fqn] = hits[0]
         assigned[hits[0]].append((fqn, p))

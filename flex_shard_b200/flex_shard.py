@@ -266,6 +266,10 @@ def _validate_bucket(spec: BucketSpec, named, placements, comm) -> None:
     missing = [f for f, _ in named if f not in placements]
     if missing:
         raise ValueError(f"placement_fn returned no placement for {missing}")
+    known = {f for f, _ in named}
+    extra = [f for f in placements if f not in known]
+    if extra:
+        raise ValueError(f"placement_fn returned placements for names that are not in the bucket: {extra}")
     for f, _ in named:
         if not isinstance(placements[f], Placement):
             raise TypeError(f"placement for {f!r} is not a Placement: {placements[f]!r}")
