@@ -39,6 +39,15 @@ def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, r
     hosts = mesh_rank_hosts(num_ranks, ranks_per_host)
     loads = [0.0] * num_ranks
     out: dict[str, int | tuple[int, ...]] = {}
+    seen: set[str] = set()
+    for group in groups:
+        for m in group:
+            if m.fqn in seen:
+                raise ValueError(f"matrix {m.fqn!r} is listed more than once: every matrix gets exactly one owner")
+            seen.add(m.fqn)
+    for fqn, r in (fixed_owners or {}).items():
+        if not 0 <= int(r) < num_ranks:
+            raise ValueError(f"fixed owner {r} of {fqn!r} is not a rank of the {num_ranks}-rank mesh")
     for group in groups:
         if not carry_loads:
             loads = [0.0] * num_ranks

@@ -1,0 +1,114 @@
+"""Owner assignment for Muon matrices: hosts before ranks, alternating positions on ties, loads carried from
+bucket to bucket, block groups, fixed owners.  Pure planning, no process group.
+Parity: the behaviours pinned by the reference's ``tests/test_matrix_assignment.py:72-361``."""
+import pytest
+
+
+def test_mesh_rank_hosts(monkeypatch):
+    from flex_shard_b200.utils.validation import mesh_rank_hosts
+
+    assert mesh_rank_hosts(8, 4) == (0, 0, 0, 0, 1, 1, 1, 1)
+    assert mesh_rank_hosts(6, 4) == (0, 0, 0, 0, 1, 1)               # the last host may be smaller
+    assert mesh_rank_hosts(4, 16) == (0, 0, 0, 0)                    # more slots than ranks: one host
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")
+    assert mesh_rank_hosts(4) == (0, 0, 1, 1)                        # torchrun's value when nothing is given
+    monkeypatch.delenv("LOCAL_WORLD_SIZE")
+    assert mesh_rank_hosts(4) == (0, 0, 0, 0)
+
+
+def test_one_host_alternates_ranks_and_equal_items_fill_even_positions_first():
+    from flex_shard_b200.utils.validation import assign_to_hosts_then_ranks
+
+    # 8 equal items on one host of 8 ranks: ranks are taken in the order 0, 2, 4, 6, 1, 3, 5, 7
+    assert assign_to_hosts_then_ranks([1.0] * 8, [0] * 8) == [0, 2, 4, 6, 1, 3, 5, 7]
+    # the ninth item lands on the first rank again
+    assert assign_to_hosts_then_ranks([1.0] * 9, [0] * 8)[-1] == 0
+
+
+def test_heavy_and_light_items_alternate_over_hosts():
+    from flex_shard_b200.utils.validation import assign_to_hosts_then_ranks
+
+    hosts = [0, 0, 1, 1, 2, 2, 3, 3]
+    owners = assign_to_hosts_then_ranks([8.0, 8.0, 8.0, 8.0, 1.0, 1.0, 1.0, 1.0], hosts)
+    heavy_hosts = [hosts[r] for r in owners[:4]]
+    light_hosts = [hosts[r] for r in owners[4:]]
+    assert sorted(heavy_hosts) == [0, 1, 2, 3] and sorted(light_hosts) == [0, 1, 2, 3]   # one of each per host
+    assert heavy_hosts == [0, 2, 1, 3]                                                    # even hosts first on ties
+    # a light item never shares a rank with a heavy one while a free rank exists on that host
+    assert not set(owners[:4]) & set(owners[4:])
+
+
+def test_loads_are_updated_in_place_and_steer_the_next_call():
+    from flex_shard_b200.utils.validation import assign_to_hosts_then_ranks
+
+    loads = [0.0, 0.0, 0.0, 0.0]
+    first = assign_to_hosts_then_ranks([5.0], [0, 0, 1, 1], loads)
+    assert first == [0] and loads == [5.0, 0.0, 0.0, 0.0]
+    second = assign_to_hosts_then_ranks([5.0], [0, 0, 1, 1], loads)
+    assert second == [2] and loads == [5.0, 0.0, 5.0, 0.0]        # the lighter host first, then its first rank
+    third = assign_to_hosts_then_ranks([1.0, 1.0], [0, 0, 1, 1], loads)
+    assert sorted(third) == [1, 3]
+
+
+def test_groups_balance_separately_unless_loads_are_carried():
+    from flex_shard_b200.dist_muon import MatrixSpec, assign_matrices
+
+    big, small = (256, 256), (64, 64)
+    groups = [[MatrixSpec(f"l{i}.big", big), MatrixSpec(f"l{i}.small", small)] for i in range(4)]
+    apart = assign_matrices(groups, 4, ranks_per_host=4, carry_loads=False)
+    # every group starts from empty loads: all big matrices land on the same rank
+    assert len({apart[f"l{i}.big"] for i in range(4)}) == 1
+    carried = assign_matrices(groups, 4, ranks_per_host=4, carry_loads=True)
+    assert len({carried[f"l{i}.big"] for i in range(4)}) == 4       # spread over the mesh
+    # the order of the groups decides who gets what when loads are carried
+    flipped = assign_matrices(list(reversed(groups)), 4, ranks_per_host=4, carry_loads=True)
+    assert flipped["l3.big"] == carried["l0.big"]
+
+
+def test_block_groups_use_the_accumulated_load():
+    from flex_shard_b200.dist_muon import MatrixSpec, assign_matrices
+
+    whole = MatrixSpec("dense", (512, 512))
+    heads = MatrixSpec("wq", (8 * 64, 512), num_blocks=8)
+    out = assign_matrices([[whole, heads]], 4, ranks_per_host=4)
+    counts = out["wq"]
+    assert sum(counts) == 8 and len(counts) == 4
+    assert counts[out["dense"]] == min(counts)                       # the rank that owns the dense matrix gets fewest heads
+
+
+def test_fixed_owners_are_kept_and_counted():
+    from flex_shard_b200.dist_muon import MatrixSpec, assign_matrices
+
+    ms = [MatrixSpec(f"m{i}", (128, 128)) for i in range(4)]
+    out = assign_matrices([ms], 2, fixed_owners={"m0": 1, "m1": 1})
+    assert out["m0"] == 1 and out["m1"] == 1
+    assert out["m2"] == 0 and out["m3"] == 0                          # the free ones fill the lighter rank
+    with pytest.raises(ValueError, match="not a rank"):
+        assign_matrices([ms], 2, fixed_owners={"m0": 5})
+
+
+def test_duplicate_names_are_rejected():
+    from flex_shard_b200.dist_muon import MatrixSpec, assign_matrices
+
+    with pytest.raises(ValueError, match="more than once"):
+        assign_matrices([[MatrixSpec("w", (8, 8))], [MatrixSpec("w", (8, 8))]], 2)
+
+
+def test_owned_placement_fn_carries_loads_across_buckets_and_puts_hosts_first():
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+    from tests.common import FakeMesh
+
+    fn = make_bucketed_owned_full_param_placement_fn(carry_loads=True, ranks_per_host=2)
+    owners = []
+    for b in range(4):                                               # four identical one-matrix buckets
+        named = [(f"b{b}.w", nn.Parameter(torch.zeros(64, 64)))]
+        pl = fn(named, FakeMesh(4))[f"b{b}.w"]
+        owners.append(pl.segments[0][0])
+    assert sorted(owners) == [0, 1, 2, 3]                            # carried loads spread them over all ranks
+    assert owners[:2] in ([0, 2], [2, 0])                            # the two hosts are used before a host's second rank
+    fresh = make_bucketed_owned_full_param_placement_fn(carry_loads=False, ranks_per_host=2)
+    same = {fresh([(f"b{b}.w", nn.Parameter(torch.zeros(64, 64)))], FakeMesh(4))[f"b{b}.w"].segments[0][0] for b in range(4)}
+    assert len(same) == 1
