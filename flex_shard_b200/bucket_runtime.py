@@ -254,8 +254,8 @@ class BucketRuntime:
         self._triggers_fired = 0
         self._pre_backward_done = False
         self._post_backward_done = False
+        self._ran_forward = False      # a member module ran forward with gradients enabled since the last backward
         self.needs_sync = False        # holds unreduced unsharded grads (no-sync accumulation)
-        self.deferred_params: set[int] = set()
         self._handles: list = []
         self._bucket_base = None
         self._bucket_nbytes = 0
@@ -528,6 +528,8 @@ class BucketRuntime:
             if not in_bwd:
                 self._prefetch(forward=True)
         self._forwards_in_pass += 1
+        if torch.is_grad_enabled() and not in_bwd:
+            self._ran_forward = True
         if torch.is_grad_enabled() and not (in_bwd and self._triggers_registered > 0):
             flat, spec = tree_flatten((args, kwargs))
             idx = [i for i, t in enumerate(flat) if isinstance(t, torch.Tensor) and t.requires_grad]
@@ -597,11 +599,17 @@ class BucketRuntime:
             self.post_backward()
 
     def finish_deferred(self, param) -> None:
-        self.deferred_params.add(id(param))
-        if len(self.deferred_params) >= len([p for p in self.storage.sharded_params if p.requires_grad]):
-            self.deferred_params.clear()
+        """The late gradients of a deferring bucket exist: run its post-backward now (reduce into the shards and
+        reshard with gradient sync on; keep the gradients for the next syncing backward without). Calls after the
+        bucket has finished do nothing, so a hook per parameter may call it.
+        Parity: ``flex_shard/flex_shard.py:215-235`` of the reference."""
+        if not self.storage.spec.defer_post_backward:
+            raise ValueError(f"bucket {self.storage.name!r} does not defer its post-backward "
+                             "(BucketSpec.defer_post_backward)")
+        if self._pre_backward_done and not self._post_backward_done:
             self.post_backward()
-            self.context.drain_reduces(0)
+            if not _in_backward():
+                self.context.drain_reduces(0)
 
     # ------------------------------------------------------------------ post-backward
     def _take_grads(self) -> list[torch.Tensor] | None:
@@ -729,13 +737,25 @@ class BucketRuntime:
                     sp.grad.add_(g.to(sp.grad.dtype) if g.dtype != sp.grad.dtype else g)
 
     def finish_backward(self) -> None:
-        """End of backward: run the post-backward step if its trigger never fired (inputs that
-        do not require grad) and the bucket took part in this backward."""
+        """End of backward: run the post-backward step if its trigger never fired (inputs that do not require
+        grad) and the bucket took part in this backward.  A bucket whose forward ran but whose outputs this rank
+        did not use (or that still holds kept gradients from a backward without sync) reduces too, with zeros for
+        the gradients it does not have: its peers may have used it, and every rank must issue the same
+        collectives (parity: the reference's rank-dependent unused parameters,
+        ``tests/test_flex_shard_training.py:1722-1761``).  ``fsdp2_compatible`` buckets keep FSDP2's rule instead:
+        a group without gradients takes no part."""
+        ran, self._ran_forward = self._ran_forward, False
         if self._pre_backward_done and not self._post_backward_done:
             if self.storage.spec.defer_post_backward and self.storage.requires_gradient_sync:
                 raise RuntimeError(
                     f"bucket {self.storage.name!r} has defer_post_backward=True but its backward ended "
                     "without finish_deferred_backward() for every parameter")
+            self.post_backward()
+        elif (not self._pre_backward_done and (ran or self.needs_sync) and self.unsharded_params is not None
+              and self.storage.requires_gradient_sync and not self.storage.spec.fsdp2_compatible
+              and not self.storage.spec.defer_post_backward
+              and any(i.requires_grad for i in self.storage.infos)):
+            self._post_backward_done = False
             self.post_backward()
 
     def end_of_backward_without_finalize(self) -> None:

@@ -334,11 +334,20 @@ class ShardedBucketStorage:
     def set_gradient_divide_factor(self, factor: float | None) -> None:
         self.reduction = GradientReduction(dist.ReduceOp.AVG, factor)
 
+    @staticmethod
+    def _prefetch_targets(buckets) -> list["ShardedBucketStorage"]:
+        buckets = list(buckets)
+        for b in buckets:
+            if not isinstance(b, ShardedBucketStorage):
+                raise TypeError(f"prefetch targets must be ShardedBucketStorage objects (module.sharded_bucket_storages), "
+                                f"got {type(b).__name__}")
+        return buckets
+
     def set_buckets_to_forward_prefetch(self, buckets: Sequence["ShardedBucketStorage"]) -> None:
-        self.forward_prefetch = list(buckets)
+        self.forward_prefetch = self._prefetch_targets(buckets)
 
     def set_buckets_to_backward_prefetch(self, buckets: Sequence["ShardedBucketStorage"]) -> None:
-        self.backward_prefetch = list(buckets)
+        self.backward_prefetch = self._prefetch_targets(buckets)
 
     @property
     def bucket_reduce_dtype(self) -> torch.dtype:

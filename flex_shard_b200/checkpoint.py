@@ -50,35 +50,48 @@ def set_state_dict_global_layouts(module: nn.Module, state_dict: Mapping[str, An
 
 def register_optimizer_checkpoint_hook(optimizer: torch.optim.Optimizer, module: nn.Module):
     """Tag Adam/AdamW state tensors in ``optimizer.state_dict()`` with their parameter's layout.
-    ``step`` stays untagged (replicated)."""
+    ``step`` stays untagged (replicated).  Every parameter of the optimizer must be a sharded parameter of
+    ``module``; a state tensor whose shape is not its parameter's local shape cannot be described and raises when
+    the state dict is taken; registering again replaces the earlier hook.
+    Parity: ``flex_shard/checkpoint.py`` of the reference (behaviours pinned by
+    ``tests/test_flex_shard_checkpoint.py:275-378``)."""
     if not isinstance(optimizer, (torch.optim.Adam, torch.optim.AdamW)) and not getattr(
             optimizer, "_fsb_adam_like", False):
-        raise ValueError("register_optimizer_checkpoint_hook supports Adam and AdamW only")
-    if getattr(optimizer, "_fsb_ckpt_hook", None) is not None:
-        raise ValueError("optimizer already has a flex_shard checkpoint hook")
-    layouts_by_param: dict[int, GlobalLayout] = {}
+        raise NotImplementedError(
+            f"register_optimizer_checkpoint_hook supports Adam and AdamW, got {type(optimizer).__name__}")
+    layouts_by_param: dict[int, tuple[GlobalLayout, str]] = {}
     for st in module.sharded_bucket_storages:
         for info, sp in zip(st.infos, st.sharded_params):
-            layouts_by_param[id(sp)] = st.global_layout_of(info)
-    managed = [p for g in optimizer.param_groups for p in g["params"]]
-    if not any(id(p) in layouts_by_param for p in managed):
-        raise ValueError("optimizer holds none of the module's flex_shard parameters; build it after flex_shard()")
+            layouts_by_param[id(sp)] = (st.global_layout_of(info), info.fqn)
+    for g in optimizer.param_groups:
+        for p in g["params"]:
+            if id(p) not in layouts_by_param:
+                raise ValueError(f"optimizer parameter of shape {tuple(p.shape)} is not a sharded parameter of the "
+                                 "module; build the optimizer from module.parameters() after flex_shard()")
+    old = getattr(optimizer, "_fsb_ckpt_hook", None)
+    if old is not None:
+        old.remove()
 
     def post_hook(opt, sd):
         idx = 0
-        index_layout = {}
+        index_info = {}
         for g in opt.param_groups:
             for p in g["params"]:
                 if id(p) in layouts_by_param:
-                    index_layout[idx] = layouts_by_param[id(p)]
+                    index_info[idx] = (*layouts_by_param[id(p)], tuple(p.shape))
                 idx += 1
         for pid, st in sd.get("state", {}).items():
-            lay = index_layout.get(pid)
-            if lay is None:
+            hit = index_info.get(pid)
+            if hit is None:
                 continue
+            lay, fqn, shape = hit
             for key in _ADAM_STATE_KEYS:
                 t = st.get(key)
                 if isinstance(t, torch.Tensor):
+                    if tuple(t.shape) != shape:
+                        raise NotImplementedError(
+                            f"optimizer state {key!r} of FlexShard parameter {fqn!r} has shape {tuple(t.shape)}, "
+                            f"not the parameter's local shape {shape}: it cannot take the parameter's layout")
                     set_global_layout(t, lay)
         return sd
 

@@ -325,7 +325,9 @@ def flex_shard(module: nn.Module, buckets: Sequence[BucketSpec], *,
         fn = spec.placement_fn or shard_placement_fn(0)
         placements = dict(fn(group, spec.mesh))
         _validate_bucket(spec, group, placements, comm)
-        mods, is_group, name = _hook_modules_for(module, spec, [f for f, _ in group])
+        # every name of a tied parameter counts: the bucket must be gathered around all the modules that use it
+        all_names = [n for f, _ in group for n in (f, *shared.get(f, ()))]
+        mods, is_group, name = _hook_modules_for(module, spec, all_names)
         plans.append((spec, comm, group, placements, mods, is_group, name))
 
     # everything validated: materialise

@@ -29,11 +29,8 @@ def _train_and_save(rank, world, path):
     flex_shard(m, [BucketSpec(["*"])])
     opt = torch.optim.AdamW(m.parameters(), lr=0.05)
     register_optimizer_checkpoint_hook(opt, m)
-    try:
-        register_optimizer_checkpoint_hook(opt, m)
-        second = ""
-    except ValueError as e:
-        second = str(e)
+    register_optimizer_checkpoint_hook(opt, m)          # registering again replaces the earlier hook
+    second = str(len(opt._optimizer_state_dict_post_hooks))
     for s in range(3):
         x = torch.randn(4, 6, generator=torch.Generator().manual_seed(100 + s))   # same data on both ranks
         m(x).square().mean().backward()
@@ -52,7 +49,7 @@ def test_save_on_two_ranks_load_on_one():
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "ckpt")
         res = run_ranks(_train_and_save, 2, path)
-        assert all("already has" in r for r in res)
+        assert all(r == "1" for r in res)      # registered twice, one hook
         # the same three steps without sharding
         torch.manual_seed(0)
         ref = Net()
@@ -104,11 +101,37 @@ def test_optimizer_hook_rejects_foreign_optimizers():
 
     m = Net()
     flex_shard(m, [BucketSpec(["*"])])
-    with pytest.raises(ValueError, match="Adam"):
-        register_optimizer_checkpoint_hook(torch.optim.SGD(m.parameters(), lr=0.1), m)
+    with pytest.raises(NotImplementedError, match="supports Adam and AdamW, got SGD"):
+        register_optimizer_checkpoint_hook(torch.optim.SGD(m.parameters(), lr=0.1, momentum=0.9), m)
     other = Net()
-    with pytest.raises(ValueError, match="none of the module"):
+    with pytest.raises(ValueError, match="not a sharded parameter of the module"):
         register_optimizer_checkpoint_hook(torch.optim.AdamW(other.parameters(), lr=0.1), m)
+    # one foreign parameter among the module's own is refused too
+    with pytest.raises(ValueError, match="not a sharded parameter of the module"):
+        register_optimizer_checkpoint_hook(torch.optim.AdamW([*m.parameters(), *other.parameters()], lr=0.1), m)
+
+
+def test_optimizer_state_of_another_shape_cannot_take_the_layout():
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.checkpoint import register_optimizer_checkpoint_hook
+    from flex_shard_b200.placement_contract import get_global_layout
+
+    m = Net()
+    flex_shard(m, [BucketSpec(["*"])])
+    opt = torch.optim.Adam(m.parameters(), amsgrad=True)
+    register_optimizer_checkpoint_hook(opt, m)
+    for p in m.parameters():
+        p.grad = torch.ones_like(p)
+    opt.step()
+    state = opt.state_dict()["state"]
+    for pid in state:
+        for key in ("exp_avg", "exp_avg_sq", "max_exp_avg_sq"):
+            assert get_global_layout(state[pid][key]) is not None
+        assert get_global_layout(state[pid]["step"]) is None
+    first = next(iter(m.parameters()))
+    opt.state[first]["exp_avg"] = torch.zeros(1)
+    with pytest.raises(NotImplementedError, match=r"'exp_avg' of FlexShard parameter '.*' has shape \(1,\)"):
+        opt.state_dict()
 
 
 def _bf16_net(seed):
