@@ -292,11 +292,33 @@ class DistMuon(torch.optim.Optimizer):
         return loss
 
     # ---- parameters computed where they are stored
+    def _stack_step(self, p3, g3, m3, group) -> bool:
+        """One step for a stack ``[n, rows, cols]`` of equal matrices in one go (momentum over the whole stack,
+        per-matrix normalisation, the batched Newton-Schulz iteration, one update): used when the batched
+        iteration applies (CUDA, dimensions multiples of 128), else the caller loops over the matrices."""
+        from ..ops.newton_schulz import batched_ns_supported, muon_momentum_direction_, newton_schulz
+
+        if not (p3.dim() == 3 and p3.is_contiguous() and m3.is_contiguous() and batched_ns_supported(p3)):
+            return False
+        u = muon_momentum_direction_(m3, g3.contiguous(), group["momentum"], group["nesterov"])
+        x = newton_schulz(u, group["ns_steps"], group["ns_coefficients"], group["eps"])
+        muon_apply_(p3, x.contiguous(), float(group["lr"]), group["weight_decay"],
+                    lr_ratio(group["adjust_lr_fn"], p3.shape[1], p3.shape[2]))
+        return True
+
     def _local_step(self, it: _Item) -> None:
         p, lay, group = it.param, it.storage, self.param_groups[0]
         if p.numel() == 0:
             return
         g, m = p.grad, self._momentum(p)
+        if lay.kind in ("owned", "matrix_batch") and p.dim() == 3 and self._stack_step(p.data, g, m, group):
+            return
+        if lay.kind == "row_blocks":
+            blocks = lay.block_rows or (p.shape[0],)
+            if len(blocks) > 1 and len(set(blocks)) == 1 and p.data.is_contiguous():
+                n, rows = len(blocks), blocks[0]
+                if self._stack_step(p.data.view(n, rows, -1), g.reshape(n, rows, -1), m.view(n, rows, -1), group):
+                    return
         if lay.kind == "owned":
             if p.dim() == 2:
                 self._matrix_step(p.data, g, m, group)

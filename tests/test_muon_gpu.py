@@ -89,3 +89,33 @@ def test_batched_newton_schulz_matches_one_matrix_at_a_time(shape):
         ref = ns.newton_schulz(g[i].cpu()).float()
         assert (out[i].float().cpu() - ref).norm() / ref.norm() < 3e-2
     ops.check_status()
+
+
+def test_dist_muon_steps_a_stack_of_equal_matrices_in_one_go():
+    """A 3-D parameter (experts) takes the batched path: same update, up to the arithmetic of the iteration, as the
+    same matrices held as separate 2-D parameters; far fewer launches."""
+    import torch.nn as nn
+
+    from flex_shard_b200.dist_muon import DistMuon
+
+    torch.manual_seed(6)
+    E, r, c = 6, 256, 384
+    w = torch.randn(E, r, c, device="cuda")
+    stacked = nn.Parameter(w.clone())
+    singles = [nn.Parameter(w[i].clone()) for i in range(E)]
+    opt_a = DistMuon([stacked], param_names=["experts"], lr=0.02)
+    opt_b = DistMuon(singles, param_names=[f"e{i}" for i in range(E)], lr=0.02)
+    launches = []
+    for step in range(2):
+        g = torch.randn(E, r, c, device="cuda")
+        stacked.grad = g.clone()
+        for i, p in enumerate(singles):
+            p.grad = g[i].clone()
+        for opt in (opt_a, opt_b):
+            before = ops.launch_count()
+            opt.step()
+            launches.append(ops.launch_count() - before)
+    for i, p in enumerate(singles):
+        torch.testing.assert_close(stacked.detach()[i], p.detach(), rtol=0, atol=2e-3)
+    assert launches[0] * 3 < launches[1]            # 1 + 15 + 1 launches (plus normalisation) against 6 x 18
+    ops.check_status()
