@@ -301,6 +301,8 @@ def make_bucketed_block_shard_placement_fn(blocks_per_rank: Sequence[int] | None
         from ..parallel.comm import mesh_group
 
         _, _, W, _ = mesh_group(mesh)
+        if blocks_per_rank and len(blocks_per_rank) != W:
+            raise ValueError(f"blocks_per_rank names {len(blocks_per_rank)} ranks, the mesh has {W}")
         pl = BucketedBlockShard(tuple(blocks_per_rank) if blocks_per_rank else (1,) * W)
         return {f: pl for f, _ in named_params}
 
