@@ -357,7 +357,9 @@ def relayout_bucket(module: nn.Module, storage: ShardedBucketStorage, placement_
     """Move one bucket to a new placement, bitwise (gathers in the storage dtype, repacks, frees the
     old buffer). Must run before the first unshard of the bucket and before optimizers are built."""
     state: _FlexShardState = getattr(module, _STATE_ATTR)
-    idx = state.storages.index(storage)
+    if not any(s is storage for s in state.storages):
+        raise ValueError("relayout_bucket(): the storage is not one of the module's bucket storages")
+    idx = next(i for i, s in enumerate(state.storages) if s is storage)
     rt = storage.runtime
     if rt is not None and (rt.is_unsharded or rt.unsharded_params is not None or rt.pending is not None):
         raise RuntimeError("relayout_bucket() must run before the bucket's first unshard")
