@@ -167,9 +167,12 @@ def check_status(device=None) -> None:
     if rec[0] != 0:
         t.zero_()
         raise NativeError(_describe(rec))
+    for hook in _check_hooks:
+        hook()
 
 
 _polls: dict[int, tuple] = {}
+_check_hooks: list = []      # extra debug checks run by check_status (e.g. guard bytes behind symmetric regions)
 
 
 def poll_status(device=None) -> None:

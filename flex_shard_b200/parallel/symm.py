@@ -17,6 +17,7 @@ one hop away, so its host/relay planning reduces to direct peer access.
 from __future__ import annotations
 
 import os
+import weakref
 
 import ctypes
 
@@ -49,6 +50,29 @@ def _ensure():
     _lib.declare("fsb_comm_wait_many", [vp, vp, i32, i32, u32, vp, vp])
     _lib.declare("fsb_comm_copy_segments_dma", [vp, vp, vp, i32, vp])
     _declared = True
+
+
+CANARY_BYTES, CANARY_VALUE = 256, 0xA5
+_canary_regions: list = []
+
+
+def _install_canary_hook() -> None:
+    if check_canaries not in _lib._check_hooks:
+        _lib._check_hooks.append(check_canaries)
+
+
+def check_canaries() -> None:
+    """Debug mode only: raise if the guard bytes behind any live symmetric region's payload were overwritten."""
+    alive = []
+    for ref in _canary_regions:
+        reg = ref()
+        if reg is None:
+            continue
+        alive.append(ref)
+        if not reg.canary_intact():
+            raise RuntimeError(f"guard bytes behind the payload of {reg.name} were overwritten: something wrote past "
+                               f"the end of its {reg.payload_bytes} payload bytes")
+    _canary_regions[:] = alive
 
 
 _warned_lazy = False
@@ -93,9 +117,16 @@ class SymmRegion:
             raise ValueError(f"symmetric regions support up to {MAX_RANKS} ranks")
         self.device = device
         self.payload_bytes = (payload_bytes + 255) // 256 * 256
-        total = FLAG_BYTES + self.payload_bytes
+        # debug mode (FSB200_CANARY=1): 256 bytes of a fixed pattern behind the payload; check_canaries() (called by
+        # ops.check_status) raises if a kernel or a peer wrote past the end of the payload
+        self.canary_bytes = CANARY_BYTES if os.environ.get("FSB200_CANARY", "0") == "1" else 0
+        total = FLAG_BYTES + self.payload_bytes + self.canary_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.buf[:FLAG_BYTES].zero_()
+        if self.canary_bytes:
+            self.buf[FLAG_BYTES + self.payload_bytes:].fill_(CANARY_VALUE)
+            _canary_regions.append(weakref.ref(self))
+            _install_canary_hook()
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
         # address of the same buffer in the NVSwitch multicast mapping (0: not available or switched off);
@@ -127,7 +158,13 @@ class SymmRegion:
     # ---- addressing
     @property
     def payload(self) -> torch.Tensor:
-        return self.buf[FLAG_BYTES:]
+        return self.buf[FLAG_BYTES:FLAG_BYTES + self.payload_bytes]
+
+    def canary_intact(self) -> bool:
+        if not self.canary_bytes:
+            return True
+        tail = self.buf[FLAG_BYTES + self.payload_bytes:]
+        return bool((tail == CANARY_VALUE).all())
 
     def peer_payload_addr(self, r: int, offset: int = 0) -> int:
         return self.peer_base[r] + FLAG_BYTES + offset

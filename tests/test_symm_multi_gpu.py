@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 def _worker(rank, world, port, out):
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    # guard bytes behind every symmetric payload, checked by every ops.check_status() below
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", FSB200_CANARY="1")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -111,6 +112,19 @@ def _worker(rank, world, port, out):
         reg.max_polls = 2000
         # the context is still usable afterwards
         res["alive"] = float(torch.ones(4, device=dev).sum()) == 4.0
+        # guard bytes: intact after all of the above; a write just past the payload (made here through a view of
+        # this rank's own buffer) is reported by the next status check
+        from flex_shard_b200.parallel.symm import FLAG_BYTES
+
+        ops.check_status()
+        res["canary_armed"] = reg.canary_bytes == 256 and reg.canary_intact()
+        reg.buf[FLAG_BYTES + reg.payload_bytes + 3] = 0
+        try:
+            ops.check_status()
+            res["canary_reported"] = False
+        except RuntimeError as e:
+            res["canary_reported"] = "guard bytes" in str(e) and "all-gather staging region" in str(e)
+        reg.buf[FLAG_BYTES + reg.payload_bytes + 3] = 0xA5
         dist.barrier()
         torch.save(res, os.path.join(out, f"r{rank}.pt"))
     finally:
@@ -128,7 +142,7 @@ def test_symm_collectives_match_nccl(tmp_path):
     for r in range(world):
         res = torch.load(tmp_path / f"r{r}.pt")
         for k, v in res.items():
-            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive", "fails_fast_after_first_failure",
+            if k.startswith("ag") or k.endswith("deterministic") or k in ("timeout_reported", "alive", "fails_fast_after_first_failure", "canary_armed", "canary_reported",
                                                                          "mc_bitwise_at_two_ranks"):
                 assert v is True, (k, v)
             elif k.endswith("_close"):
