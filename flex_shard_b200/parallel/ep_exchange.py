@@ -221,7 +221,8 @@ class SymmDispatcher:
 
     def exchange_for(self, xt, k) -> SymmExpertExchange:
         pairs = xt.shape[0] * k
-        key = (id(self.group), self.num_experts, xt.shape[1], pairs, xt.dtype, self.capacity_factor, xt.device)
+        # the group object itself is part of the key (and so stays alive): an id() could be reused by a later group
+        key = (self.group, self.num_experts, xt.shape[1], pairs, xt.dtype, self.capacity_factor, xt.device)
         ex = self._ex
         if ex is None or ex.D != xt.shape[1] or moe_ops.max_rows_for(pairs, self.num_experts) > ex.send_rows:
             ex = SymmDispatcher._shared.get(key)
