@@ -1,7 +1,8 @@
 // Causal flash-attention backward for sm_100a (head_dim 128, GQA), bf16.
 //
-// One CTA owns a 128-row key/value tile of one KV head and walks every query
-// tile (64 rows) at or below the diagonal, for each query head of the group.
+// One CTA owns a 128-row key/value tile of one KV head and walks every (query tile of 64 rows at or
+// below the diagonal, query head of the group) pair, in the order TileWalk defines (by default from the
+// last query tile down, the heads of the group inside).
 // Everything is computed transposed so that the kv index is the MMA M dimension
 // (= TMEM lane = softmax thread) and no operand needs a transpose copy:
 //   S^T  = K Q^T          A = K  (K-major)      B = Q  (K-major)        -> TMEM S   (64 columns)
