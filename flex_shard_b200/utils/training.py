@@ -30,20 +30,22 @@ def lr_lambda(step: int, warmup_steps: int, total_steps: int, decay_ratio: float
 @torch.no_grad()
 def clip_grad_norm_(module, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
     """Global gradient norm over every bucket's local shards (one all-reduce per distinct mesh), then
-    scale the local gradients in place. Returns the total norm."""
+    scale the local gradients in place. Returns the total norm.  The per-parameter norms and the scaling run as
+    multi-tensor (``_foreach``) operations: a handful of launches instead of several per parameter."""
     by_group: dict = {}
+    all_grads = []
     for st in module.sharded_bucket_storages:
-        key = id(st.comm.group)
-        acc = by_group.setdefault(key, [st.comm, None])
-        for p in st.sharded_params:
-            if p.grad is None or p.grad.numel() == 0:
-                continue
-            v = p.grad.float().norm(norm_type) ** norm_type
-            acc[1] = v if acc[1] is None else acc[1] + v
+        # every rank takes part in every mesh's all-reduce, with zero when it holds no gradient there (an owner
+        # placement can leave a rank without any local rows)
+        acc = by_group.setdefault(id(st.comm.group), [st.comm, torch.zeros((), dtype=torch.float32, device=st.device)])
+        grads = [p.grad for p in st.sharded_params if p.grad is not None and p.grad.numel() > 0]
+        if not grads:
+            continue
+        all_grads += grads
+        norms = torch.stack(torch._foreach_norm(grads, norm_type, dtype=torch.float32))
+        acc[1] = acc[1] + (norms ** norm_type).sum()
     total = None
     for comm, v in by_group.values():
-        if v is None:
-            continue
         if comm.world_size > 1:
             dist.all_reduce(v, group=comm.group)
         total = v if total is None else total + v
@@ -51,10 +53,8 @@ def clip_grad_norm_(module, max_norm: float, norm_type: float = 2.0) -> torch.Te
         return torch.zeros(())
     total_norm = total ** (1.0 / norm_type)
     coef = (max_norm / (total_norm + 1e-6)).clamp(max=1.0)
-    for st in module.sharded_bucket_storages:
-        for p in st.sharded_params:
-            if p.grad is not None:
-                p.grad.mul_(coef.to(p.grad.dtype))
+    if all_grads:
+        torch._foreach_mul_(all_grads, coef)
     return total_norm
 
 
