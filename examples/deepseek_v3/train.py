@@ -20,7 +20,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-from data import SyntheticBatches  # noqa: E402
+from data import PackedDocumentBatches, SyntheticBatches  # noqa: E402
 from muon import build_muon, store_heads_blockwise, store_on_owners  # noqa: E402
 
 from flex_shard_b200 import (checkpoint, flex_shard, register_optimizer_checkpoint_hook,  # noqa: E402
@@ -40,7 +40,12 @@ def parse():
     ap.add_argument("--local-batch-size", type=int, default=2)
     ap.add_argument("--ep", type=int, default=0, help="expert-parallel degree (0: all ranks, 1: off)")
     ap.add_argument("--optimizer", choices=["adamw", "muon"], default="adamw")
-    ap.add_argument("--data", choices=["synthetic"], default="synthetic")
+    ap.add_argument("--data", choices=["synthetic", "files"], default="synthetic",
+                    help="synthetic: resumable random tokens; files: documents packed from local token files "
+                         "(--data-files), labels stop at document ends and positions restart per document")
+    ap.add_argument("--data-files", default=None, help="file, directory or glob of .npy / .pt token files (--data files)")
+    ap.add_argument("--bos-id", type=int, default=0)
+    ap.add_argument("--eos-id", type=int, default=1)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--warmup-steps", type=int, default=2)
@@ -150,7 +155,14 @@ def main():
     scheds = [torch.optim.lr_scheduler.LambdaLR(o, lambda s: lr_lambda(s, args.warmup_steps, args.steps,
                                                                        args.decay_ratio, args.min_lr_factor))
               for o in opts]
-    data = SyntheticBatches(cfg.vocab_size, args.local_batch_size, args.seq_len, args.seed, rank, pin_memory=cuda)
+    if args.data == "files":
+        if not args.data_files:
+            raise SystemExit("--data files needs --data-files")
+        data = PackedDocumentBatches(args.data_files, args.local_batch_size, args.seq_len, rank=rank, world_size=world,
+                                     bos_id=args.bos_id, eos_id=args.eos_id)
+    else:
+        data = SyntheticBatches(cfg.vocab_size, args.local_batch_size, args.seq_len, args.seed, rank, pin_memory=cuda)
+    steps_done = [0]
     positions = None
     if args.document_length > 0:
         positions = (torch.arange(args.seq_len, device=dev) % args.document_length).expand(args.local_batch_size, -1)
@@ -158,8 +170,9 @@ def main():
     def state():
         sd = model.state_dict()
         set_state_dict_global_layouts(model, sd)
-        out = {"model": sd, "adam": adam.state_dict(), "data": data.state_dict(),
-               "sched": [s.state_dict() for s in scheds]}
+        # the data position differs between ranks (each reads its own files): saved per rank
+        out = {"model": sd, "adam": adam.state_dict(), "data": checkpoint.PerRank(data.state_dict()),
+               "sched": [s.state_dict() for s in scheds], "step": steps_done[0]}
         if args.optimizer == "muon":    # momentum buffers, tagged with their parameters' layouts
             out["muon"] = muon_checkpoint_state(muon, model)
         return out
@@ -183,10 +196,10 @@ def main():
         adam.load_state_dict(sd["adam"])
         if args.optimizer == "muon":
             load_muon_checkpoint_state(muon, sd["muon"])
-        data.load_state_dict(sd["data"])
+        data.load_state_dict(sd["data"].value)
         for s_, ssd in zip(scheds, sd["sched"]):
             s_.load_state_dict(ssd)
-        start = data.step
+        start = int(sd.get("step", getattr(data, "step", 0)))
 
     metrics = JsonMetrics(rank=rank, module=model)
     for step in range(start, args.steps):
@@ -195,15 +208,21 @@ def main():
             prof = torch.profiler.profile()
             prof.__enter__()
         metrics.start_step()
-        tok = next(data).to(dev, non_blocking=True)
-        ntok = torch.tensor([tok[:, 1:].numel()], dtype=torch.float32, device=dev)
+        batch = next(data)
+        if isinstance(batch, dict):      # packed documents: inputs, next-token labels and per-document positions
+            inputs, labels = batch["input"].to(dev, non_blocking=True), batch["labels"].to(dev, non_blocking=True)
+            step_positions = batch["positions"].to(dev, non_blocking=True)
+        else:
+            tok = batch.to(dev, non_blocking=True)
+            inputs, labels, step_positions = tok[:, :-1], tok[:, 1:], positions
+        ntok = torch.tensor([labels.numel()], dtype=torch.float32, device=dev)
         dist.all_reduce(ntok)
         # sum of token losses divided by the global token count (buckets sum gradients)
         if args.aux_loss_coeff > 0:
             for moe in model.moe_layers():
                 moe.aux_loss_denominator = float(ntok)
-        loss = model.loss(tok[:, :-1], tok[:, 1:], loss_is_root=False, positions=positions) * (
-            tok[:, 1:].numel() / ntok.squeeze())
+        loss = model.loss(inputs, labels, loss_is_root=False, positions=step_positions) * (
+            labels.numel() / ntok.squeeze())
         loss.backward()
         gnorm = clip_grad_norm_(model, args.max_norm)
         for m in model.moe_layers():
@@ -216,7 +235,8 @@ def main():
             o.zero_grad(set_to_none=True)
         red = loss.detach().clone()
         dist.all_reduce(red)
-        metrics.end_step(step, tok[:, 1:].numel(), loss=red, grad_norm=gnorm, lr=scheds[0].get_last_lr()[0])
+        metrics.end_step(step, labels.numel(), loss=red, grad_norm=gnorm, lr=scheds[0].get_last_lr()[0])
+        steps_done[0] = step + 1
         if prof is not None:
             prof.__exit__(None, None, None)
             os.makedirs(args.profile_dir, exist_ok=True)

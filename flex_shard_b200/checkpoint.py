@@ -111,6 +111,19 @@ def _flatten(d, prefix=""):
     return out
 
 
+class PerRank:
+    """Marks a non-tensor value of a state dict that differs between ranks (a data loader's position, a
+    generator state): ``save`` writes every rank's value into that rank's file, ``load`` gives each rank its own
+    back.  Plain objects are taken from rank 0 (they are expected to be the same everywhere).  Loading at another
+    world size raises: such a value has no meaning for a different rank count."""
+
+    def __init__(self, value):
+        self.value = value
+
+    def __repr__(self):
+        return f"PerRank({self.value!r})"
+
+
 def _walk(d, path=()):
     if isinstance(d, Mapping):
         for k, v in d.items():
@@ -141,6 +154,8 @@ def save(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
                 chunks.append((tuple(goff), tuple(size), t.cpu().clone()))
             entries[key] = {"kind": "sharded", "global_shape": tuple(lay.global_shape), "dtype": v.dtype,
                             "chunks": chunks}
+        elif isinstance(v, PerRank):
+            entries[key] = {"kind": "per_rank", "value": v.value}
         elif rank == 0:
             entries[key] = {"kind": "object", "value": v}
     tmp = os.path.join(checkpoint_id, f"rank{rank}.pt.tmp")
@@ -153,10 +168,13 @@ def save(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
 def load(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
     """Fill the tagged tensors of ``state_dict`` in place from a checkpoint written by ``save`` at
     any world size / placement. Untagged tensors are loaded as replicated values."""
-    files = sorted(f for f in os.listdir(checkpoint_id) if f.startswith("rank") and f.endswith(".pt"))
+    files = sorted((f for f in os.listdir(checkpoint_id) if f.startswith("rank") and f.endswith(".pt")),
+                   key=lambda f: int(f[4:-3]))
     if not files:
         raise FileNotFoundError(f"no rank files under {checkpoint_id}")
     blobs = [torch.load(os.path.join(checkpoint_id, f), map_location="cpu", weights_only=False) for f in files]
+    my_rank = dist.get_rank(group) if dist.is_initialized() else 0
+    my_world = dist.get_world_size(group) if dist.is_initialized() else 1
     if len(blobs) != blobs[0]["world_size"]:
         raise RuntimeError(f"checkpoint {checkpoint_id} is incomplete: {len(blobs)} of {blobs[0]['world_size']} rank files")
 
@@ -187,6 +205,14 @@ def load(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
                         _fill_boxes(v, lay, key, blobs)
                     continue
                 _fill_boxes(v, lay, key, blobs)
+            elif isinstance(v, PerRank):
+                if my_world != len(blobs):
+                    raise RuntimeError(f"{key} is per-rank state saved by {len(blobs)} ranks; it cannot be loaded by "
+                                       f"{my_world} ranks")
+                src = blobs[my_rank]["entries"].get(key)
+                if src is None or src["kind"] != "per_rank":
+                    raise KeyError(f"{key} (per-rank state) not in checkpoint")
+                v.value = src["value"]
             else:
                 src = next((b["entries"][key] for b in blobs if key in b["entries"]), None)
                 if src is not None and src["kind"] == "object":

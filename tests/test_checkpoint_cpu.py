@@ -200,3 +200,25 @@ def test_adamw_kernel_wrapper_rejects_narrow_moments():
     with pytest.raises(ValueError, match="at least"):
         adamw_step_(p, g, torch.zeros(4), torch.zeros(8), lr=1e-3, beta1=0.9, beta2=0.99, eps=1e-8,
                     weight_decay=0.0, step=1)
+
+
+def _per_rank(rank, world, path):
+    from flex_shard_b200 import checkpoint
+
+    state = {"pos": checkpoint.PerRank({"file": rank, "seen": [rank] * 3}), "step": 7}
+    checkpoint.save(state, path)
+    back = {"pos": checkpoint.PerRank(None), "step": 0}
+    checkpoint.load(back, path)
+    return back["pos"].value, back["step"]
+
+
+def test_per_rank_objects_come_back_to_their_rank(tmp_path):
+    """Plain objects are taken from rank 0; values wrapped in ``PerRank`` are saved and restored rank by rank, and
+    refuse to load at another world size."""
+    from flex_shard_b200 import checkpoint
+
+    path = str(tmp_path / "ckpt")
+    res = run_ranks(_per_rank, 2, path)
+    assert res[0] == ({"file": 0, "seen": [0, 0, 0]}, 7) and res[1] == ({"file": 1, "seen": [1, 1, 1]}, 7)
+    with pytest.raises(RuntimeError, match="per-rank state saved by 2 ranks"):
+        checkpoint.load({"pos": checkpoint.PerRank(None)}, path)       # one process, no group: world size 1

@@ -89,3 +89,29 @@ def test_muon_head_block_storage_trains_like_owner_storage(tmp_path):
     owners = _run(str(tmp_path / "o"), ["--optimizer", "muon", "--max-norm", "1e9"])
     heads = _run(str(tmp_path / "h"), ["--optimizer", "muon", "--muon-storage", "heads", "--max-norm", "1e9"])
     assert [heads[s]["loss"] for s in range(4)] == [owners[s]["loss"] for s in range(4)]
+
+
+def test_training_on_packed_document_files_resumes_bitwise(tmp_path):
+    """``--data files``: documents from local token files, packed with per-document positions (document-masked
+    attention) and split across ranks file by file; a run resumed from its checkpoint continues with the same
+    batches and prints the same losses."""
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    files = tmp_path / "tokens"
+    files.mkdir()
+    for f in range(4):                                   # two files per rank, ragged documents
+        docs = np.empty(12, dtype=object)
+        for i in range(12):
+            docs[i] = rng.integers(2, 256, size=int(rng.integers(5, 40)))
+        np.save(files / f"part{f}.npy", docs, allow_pickle=True)
+    extra = ["--optimizer", "adamw", "--data", "files", "--data-files", str(files)]
+    full_dir, part_dir = str(tmp_path / "full"), str(tmp_path / "part")
+    full = _run(full_dir, extra)
+    assert sorted(full) == [0, 1, 2, 3]
+    os.makedirs(part_dir)
+    shutil.copytree(os.path.join(full_dir, "step00000002"), os.path.join(part_dir, "step00000002"))
+    resumed = _run(part_dir, extra)
+    assert sorted(resumed) == [2, 3]
+    for s in (2, 3):
+        assert resumed[s]["loss"] == full[s]["loss"] and resumed[s]["grad_norm"] == full[s]["grad_norm"]
