@@ -13,6 +13,8 @@ same runtime without streams and are what the CPU test-suite uses.
 """
 from __future__ import annotations
 
+import math
+
 from typing import Any, Callable, Sequence
 
 import torch
@@ -415,32 +417,59 @@ def relayout_bucket(module: nn.Module, storage: ShardedBucketStorage, placement_
 
 
 def _gather_full(info, local: torch.Tensor, comm) -> torch.Tensor:
-    """All-gather one parameter through its placement's layout (setup-time helper, not a hot path)."""
+    """All-gather one parameter through its placement's layout (set-up helper of ``relayout_bucket``).
+
+    Every rank sends its local tensor as bytes, padded to the largest local size, in one ``all_gather_into_tensor``;
+    the boxes of every rank's layout are then copied out of its row.  That moves (W-1)/W of the parameter into each
+    rank and widens nothing.  When the local sizes are very uneven (an owner holds the whole parameter: the padded
+    rows would carry W copies) or the placement cuts the parameter through a bucket-level plan, the pieces are
+    summed as integers over zero-padded full tensors instead (every element has exactly one owner, so that sum is a
+    bitwise gather too)."""
     W = comm.world_size
     full = torch.zeros(info.global_shape, dtype=info.storage_dtype, device=local.device)
-    lay = info.placement.global_layout(info.global_shape, comm.rank, W)
-    if info.bucket_layout is not None and hasattr(info.placement, "bucket_global_layout"):
-        lay = info.placement.bucket_global_layout(info, comm.rank, W)
-    loc = local
-    for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
-        src = loc
-        dst = full
-        for d, (g, l, s) in enumerate(zip(goff, loff, size)):
-            src = src.narrow(d, l, s)
-            dst = dst.narrow(d, g, s)
-        dst.copy_(src)
-    if W > 1:
-        # every element has exactly one owner, so a sum of zero-padded pieces is a bitwise gather
-        as_int = full.view(torch.int32) if full.element_size() == 4 else (
-            full.view(torch.int16) if full.element_size() == 2 else full.view(torch.uint8))
-        if as_int.dtype == torch.int16:
-            wide = as_int.to(torch.int32)
-            dist.all_reduce(wide, group=comm.group)
-            as_int.copy_(wide.to(torch.int16))
-        elif as_int.dtype == torch.uint8:
-            wide = as_int.to(torch.int32)
-            dist.all_reduce(wide, group=comm.group)
-            as_int.copy_(wide.to(torch.uint8))
-        else:
-            dist.all_reduce(as_int, group=comm.group)
+    bucket_level = info.bucket_layout is not None and hasattr(info.placement, "bucket_global_layout")
+
+    def layout_of(r):
+        if bucket_level:
+            return info.placement.bucket_global_layout(info, r, W)
+        return info.placement.global_layout(info.global_shape, r, W)
+
+    def place(src_local, lay):
+        for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
+            src, dst = src_local, full
+            for d, (g, l, s) in enumerate(zip(goff, loff, size)):
+                src = src.narrow(d, l, s)
+                dst = dst.narrow(d, g, s)
+            dst.copy_(src)
+
+    if W == 1:
+        place(local, layout_of(comm.rank))
+        return full
+    shapes = None if bucket_level else [tuple(info.placement.compute_local_shape(info.global_shape, r, W)) for r in range(W)]
+    if shapes is not None:
+        numels = [math.prod(sh) for sh in shapes]
+        biggest = max(numels)
+        if biggest > 0 and biggest * W <= 2 * full.numel() and tuple(local.shape) == shapes[comm.rank]:
+            esize = full.element_size()
+            send = torch.zeros(biggest * esize, dtype=torch.uint8, device=local.device)
+            mine = local.contiguous().view(-1).view(torch.uint8)
+            send[:mine.numel()].copy_(mine)
+            rows = torch.empty(W * biggest * esize, dtype=torch.uint8, device=local.device)
+            dist.all_gather_into_tensor(rows, send, group=comm.group)
+            rows = rows.view(W, biggest * esize)
+            for r in range(W):
+                if numels[r] == 0:
+                    continue
+                piece = rows[r, :numels[r] * esize].view(info.storage_dtype).view(shapes[r])
+                place(piece, layout_of(r))
+            return full
+    place(local, layout_of(comm.rank))
+    as_int = full.view(torch.int32) if full.element_size() == 4 else (
+        full.view(torch.int16) if full.element_size() == 2 else full.view(torch.uint8))
+    if as_int.dtype == torch.int32:
+        dist.all_reduce(as_int, group=comm.group)
+    else:
+        wide = as_int.to(torch.int32)
+        dist.all_reduce(wide, group=comm.group)
+        as_int.copy_(wide.to(as_int.dtype))
     return full

@@ -143,3 +143,34 @@ def test_relayout_bucket_preconditions_and_result():
         assert "not one of the module's bucket storages" in r["foreign"], r
         assert "before the bucket's first unshard" in r["late"]
         assert r["replaced"] and r["bitwise"] and r["forward"], r
+
+
+def _gather_paths(rank, world):
+    """``relayout_bucket`` from an uneven Shard(0) layout (byte all-gather path) and from an owner layout (integer-sum
+    path): both give back the full tensors bit for bit."""
+    from flex_shard_b200 import BucketSpec, flex_shard, relayout_bucket
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn, shard_placement_fn
+
+    class Odd(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = nn.Parameter(torch.randn(5, 3))
+            self.v = nn.Parameter(torch.randn(7))
+
+        def forward(self, x):
+            return x @ self.w.t() + self.v[:5]
+
+    torch.manual_seed(0)
+    m = Odd()
+    full = {k: v.clone() for k, v in m.state_dict().items()}
+    flex_shard(m, [BucketSpec(["*"])])
+    st = relayout_bucket(m, m.sharded_bucket_storages[0], make_bucketed_owned_full_param_placement_fn())   # uneven rows
+    st = relayout_bucket(m, st, shard_placement_fn(0))                                                     # from owners
+    m.unshard()
+    ok = all(torch.equal(p.detach(), full[n]) for n, p in m.named_parameters())
+    m.reshard()
+    return ok
+
+
+def test_relayout_gathers_bitwise_from_uneven_and_owner_layouts():
+    assert all(run_ranks(_gather_paths, 2))
