@@ -19,11 +19,24 @@ from .owned import (
 )
 from .shard import Shard, shard_placement_fn
 
+# the names these factories have in the reference package (``custom_placements/__init__.py``)
+make_shard_placement_fn = shard_placement_fn
+make_bucketed_block_placement_fn = make_bucketed_block_shard_placement_fn
+make_fp8_bucketed_block_placement_fn = make_fp8_bucketed_block_shard_placement_fn
+make_mxfp8_bucketed_block_placement_fn = make_mxfp8_bucketed_block_shard_placement_fn
+
+
+def per_param_placements(named_params, mesh):
+    """``Shard(0)`` for every parameter (FSDP2-style)."""
+    return shard_placement_fn(0)(named_params, mesh)
+
+
 __all__ = [
     "BlockShard", "BlockwiseQuantBucketedBlockShard", "Fp8BucketedBlockShard", "make_fp8_bucketed_block_shard_placement_fn",
     "Mxfp8BucketedBlockShard", "make_mxfp8_bucketed_block_shard_placement_fn",
     "partition_min_max", "plan_row_ranges", "BucketedBlockShard", "BucketedOwned", "FlatBucketPlan", "make_bucketed_block_shard_placement_fn", "MixedBucketPlacement", "Shard", "ShardSlice",
     "make_block_shard_placement_fn", "make_bucketed_owned_expert_block_placement_fn",
     "make_bucketed_owned_full_param_placement_fn", "make_mixed_placement_fn", "newton_schulz_cost",
-    "shard_placement_fn",
+    "shard_placement_fn", "make_shard_placement_fn", "per_param_placements", "make_bucketed_block_placement_fn",
+    "make_fp8_bucketed_block_placement_fn", "make_mxfp8_bucketed_block_placement_fn",
 ]

@@ -186,3 +186,23 @@ def test_sharded_parameters_are_views_of_the_bucket_storage():
         # writing through the storage is writing the parameters
         st.byte_storage.zero_()
         assert all(float(sp.detach().abs().sum()) == 0.0 for sp in st.sharded_params)
+
+
+def test_reference_style_placement_functions_are_accepted():
+    """The reference's factory names exist, and a placement function that returns one-element tuples
+    ``{fqn: (placement,)}`` (its convention for a 1-D mesh) is accepted like one that returns bare placements."""
+    from flex_shard_b200 import flex_shard
+    from flex_shard_b200 import placements as P
+
+    assert P.make_shard_placement_fn is P.shard_placement_fn
+    assert P.make_bucketed_block_placement_fn is P.make_bucketed_block_shard_placement_fn
+    assert P.make_fp8_bucketed_block_placement_fn is P.make_fp8_bucketed_block_shard_placement_fn
+    assert P.make_mxfp8_bucketed_block_placement_fn is P.make_mxfp8_bucketed_block_shard_placement_fn
+    named = [("w", nn.Parameter(torch.zeros(4, 4)))]
+    assert P.per_param_placements(named, None) == {"w": P.Shard(0)}
+    torch.manual_seed(0)
+    m, ref = Net(), Net()
+    ref.load_state_dict(m.state_dict())
+    flex_shard(m, [_spec(["*"], placement_fn=lambda named, mesh: {f: (P.Shard(0),) for f, _ in named})])
+    x = torch.randn(3, 8)
+    assert torch.equal(m(x), ref(x))
