@@ -30,6 +30,32 @@ class MatrixSpec:
     fqn: str
     shape: tuple[int, ...]
     num_blocks: int = 1   # > 1: a block group (e.g. heads) spread over ranks block by block
+    eligible_ranks: tuple[int, ...] | None = None   # block groups only: the ranks that may hold blocks (default: all)
+
+
+def validate_assignment(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int,
+                        owners: Mapping[str, int | tuple[int, ...]]) -> None:
+    """Check an assignment (from ``assign_matrices`` or a custom function): every matrix has exactly one entry, whole
+    matrices name a rank of the mesh, block groups give one non-negative count per rank that sum to the number of
+    blocks and are zero outside the eligible ranks.  Parity: the checks the reference applies to a custom
+    ``MatrixAssignmentFn`` (``dist_muon/bucket_planner.py:260-330``)."""
+    expected = {m.fqn: m for g in groups for m in g}
+    missing = sorted(set(expected) - set(owners))
+    unexpected = sorted(set(owners) - set(expected))
+    if missing or unexpected:
+        raise ValueError(f"matrix assignment does not match the recipe: missing {missing}, unexpected {unexpected}")
+    for fqn, m in expected.items():
+        o = owners[fqn]
+        if m.num_blocks <= 1:
+            if isinstance(o, bool) or not isinstance(o, int) or not 0 <= o < num_ranks:
+                raise ValueError(f"owner of {fqn!r} must be a rank in [0, {num_ranks}), got {o!r}")
+            continue
+        if (not isinstance(o, (tuple, list)) or len(o) != num_ranks
+                or any((not isinstance(c, int)) or c < 0 for c in o) or sum(o) != m.num_blocks):
+            raise ValueError(f"block group {fqn!r} needs {num_ranks} non-negative block counts that sum to "
+                             f"{m.num_blocks}, got {o!r}")
+        if m.eligible_ranks is not None and any(c and r not in m.eligible_ranks for r, c in enumerate(o)):
+            raise ValueError(f"block group {fqn!r} places blocks outside its eligible ranks {m.eligible_ranks}: {o!r}")
 
 
 def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, ranks_per_host: int | None = None,
@@ -65,22 +91,34 @@ def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, r
                 continue
             rows = m.shape[0] // m.num_blocks
             cost = newton_schulz_cost((rows, *m.shape[1:]), ns_steps)
-            per_block = assign_to_hosts_then_ranks([cost] * m.num_blocks, hosts, loads)
+            if m.eligible_ranks is None:
+                per_block = assign_to_hosts_then_ranks([cost] * m.num_blocks, hosts, loads)
+            else:
+                ranks = sorted(set(int(r) for r in m.eligible_ranks))
+                if not ranks or ranks[0] < 0 or ranks[-1] >= num_ranks:
+                    raise ValueError(f"eligible_ranks of {m.fqn!r} must name ranks of the {num_ranks}-rank mesh")
+                sub = [loads[r] for r in ranks]
+                local = assign_to_hosts_then_ranks([cost] * m.num_blocks, [hosts[r] for r in ranks], sub)
+                per_block = [ranks[i] for i in local]
+                for i, r in enumerate(ranks):
+                    loads[r] = sub[i]
             counts = [0] * num_ranks
             for r in per_block:
                 counts[r] += 1
             out[m.fqn] = tuple(counts)
+    validate_assignment(groups, num_ranks, out)
     return out
 
 
 def materialize_dist_muon_buckets(named_params, mesh, *, initial: Sequence[str], blocks: Sequence[Sequence[str]],
                                   final: Sequence[str], is_matrix=None, num_blocks_of=None,
                                   mp_policy: MixedPrecisionPolicy | None = None, carry_loads: bool = True,
-                                  ranks_per_host: int | None = None) -> list[BucketSpec]:
+                                  ranks_per_host: int | None = None, assignment_fn=None) -> list[BucketSpec]:
     """BucketSpecs for a Muon-trained model: ``initial`` / ``final`` pattern groups stay ``Shard(0)``
     (AdamW parameters); each entry of ``blocks`` becomes one mixed bucket whose matrices are owned
     whole (or block-sharded when ``num_blocks_of`` says so) and whose vectors are ``Shard(0)``.
-    All buckets sum gradients (``ReduceOp.SUM``), as the reference's recipe does."""
+    All buckets sum gradients (``ReduceOp.SUM``), as the reference's recipe does.  ``assignment_fn(groups,
+    num_ranks=W) -> {fqn: rank | blocks per rank}`` replaces the built-in balancer."""
     from ..parallel.comm import mesh_group
 
     _, _, W, _ = mesh_group(mesh)
@@ -95,7 +133,13 @@ def materialize_dist_muon_buckets(named_params, mesh, *, initial: Sequence[str],
                 nb = num_blocks_of(n, p) if num_blocks_of else 1
                 g.append(MatrixSpec(n, tuple(p.shape), nb))
         groups.append(g)
-    owners = assign_matrices(groups, W, ranks_per_host=ranks_per_host, carry_loads=carry_loads)
+    if assignment_fn is not None:
+        # a custom balancer: called with the groups and the mesh size on every rank (it must be deterministic); its
+        # answer is checked before anything is built
+        owners = dict(assignment_fn(groups, num_ranks=W))
+        validate_assignment(groups, W, owners)
+    else:
+        owners = assign_matrices(groups, W, ranks_per_host=ranks_per_host, carry_loads=carry_loads)
 
     def block_fn(named_in, mesh_in):
         res = {}

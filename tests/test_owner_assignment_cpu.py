@@ -112,3 +112,48 @@ def test_owned_placement_fn_carries_loads_across_buckets_and_puts_hosts_first():
     fresh = make_bucketed_owned_full_param_placement_fn(carry_loads=False, ranks_per_host=2)
     same = {fresh([(f"b{b}.w", nn.Parameter(torch.zeros(64, 64)))], FakeMesh(4))[f"b{b}.w"].segments[0][0] for b in range(4)}
     assert len(same) == 1
+
+
+def test_block_groups_can_be_confined_to_eligible_ranks():
+    from flex_shard_b200.dist_muon import MatrixSpec, assign_matrices
+
+    heads = MatrixSpec("wq", (8 * 64, 256), num_blocks=8, eligible_ranks=(2, 3))
+    out = assign_matrices([[heads]], 4, ranks_per_host=4)
+    assert out["wq"] == (0, 0, 4, 4)
+    with pytest.raises(ValueError, match="eligible_ranks"):
+        assign_matrices([[MatrixSpec("wq", (512, 256), num_blocks=8, eligible_ranks=(7,))]], 4)
+
+
+def test_custom_assignment_is_used_and_checked():
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200.dist_muon import MatrixSpec, materialize_dist_muon_buckets, validate_assignment
+    from flex_shard_b200.placements import BucketedOwned
+    from tests.common import FakeMesh
+
+    named = [("emb.weight", nn.Parameter(torch.zeros(32, 8))), ("l0.w", nn.Parameter(torch.zeros(16, 8))),
+             ("l0.v", nn.Parameter(torch.zeros(8, 16))), ("l0.norm", nn.Parameter(torch.zeros(8)))]
+    seen = {}
+
+    def everything_on_the_last_rank(groups, *, num_ranks):
+        seen["groups"] = [[m.fqn for m in g] for g in groups]
+        return {m.fqn: num_ranks - 1 for g in groups for m in g}
+
+    specs = materialize_dist_muon_buckets(named, FakeMesh(4), initial=["emb"], blocks=[["l0"]], final=[],
+                                          assignment_fn=everything_on_the_last_rank)
+    assert seen["groups"] == [["l0.w", "l0.v"]]                       # matrices of the block buckets only
+    block_spec = specs[1]
+    pls = block_spec.placement_fn([n for n in named if n[0].startswith("l0")], FakeMesh(4))
+    owned = {f: pl.member for f, pl in pls.items() if isinstance(pl.member, BucketedOwned)}
+    assert {f: pl.segments[0][0] for f, pl in owned.items()} == {"l0.w": 3, "l0.v": 3}
+    # answers that do not fit the recipe are refused before any bucket exists
+    groups = [[MatrixSpec("a", (8, 8)), MatrixSpec("h", (64, 8), num_blocks=4)]]
+    validate_assignment(groups, 2, {"a": 1, "h": (1, 3)})
+    for bad, msg in (({"a": 1}, "missing"), ({"a": 1, "h": (2, 2), "x": 0}, "unexpected"), ({"a": 2, "h": (2, 2)}, "rank in"),
+                     ({"a": 0, "h": (1, 2)}, "sum to 4"), ({"a": 0, "h": (4,)}, "2 non-negative")):
+        with pytest.raises(ValueError, match=msg):
+            validate_assignment(groups, 2, bad)
+    with pytest.raises(ValueError, match="missing"):
+        materialize_dist_muon_buckets(named, FakeMesh(4), initial=["emb"], blocks=[["l0"]], final=[],
+                                      assignment_fn=lambda groups, *, num_ranks: {})
