@@ -206,3 +206,17 @@ def test_reference_style_placement_functions_are_accepted():
     flex_shard(m, [_spec(["*"], placement_fn=lambda named, mesh: {f: (P.Shard(0),) for f, _ in named})])
     x = torch.randn(3, 8)
     assert torch.equal(m(x), ref(x))
+
+
+def test_module_name_patterns_may_not_mix_with_parameter_patterns_or_name_containers():
+    from flex_shard_b200 import flex_shard
+
+    seq = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 8))
+    with pytest.raises(ValueError, match="mixes module names and parameter patterns"):
+        flex_shard(seq, [_spec(["0", "2.*"]), _spec(["4.*"])])
+    with pytest.raises(ValueError, match="without a forward"):
+        flex_shard(nn.Sequential(nn.ModuleList([nn.Linear(8, 8)])), [_spec(["0"])])
+    flex_shard(seq, [_spec(["0", "2"]), _spec(["4"])])            # sibling modules in one bucket
+    assert [[i.fqn for i in st.infos] for st in seq.sharded_bucket_storages] == [
+        ["0.weight", "0.bias", "2.weight", "2.bias"], ["4.weight", "4.bias"]]
+    assert seq(torch.randn(2, 8)).shape == (2, 8)

@@ -1,0 +1,111 @@
+"""Per-bucket behaviour of the runtime on 2 gloo ranks: module-name patterns, the per-bucket unshard / reshard calls,
+one gathered bucket at a time with ``reshard_after_forward``, persistent unsharded parameters whose storage is freed
+and refilled, a head applied chunk by chunk, and the per-bucket switches.
+Parity: the behaviours pinned by the reference's ``tests/test_flex_shard_runtime.py:348-407,409-569,709-870,921-970``."""
+import torch
+import torch.nn as nn
+
+from tests.common import run_ranks
+
+
+class Block(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.lin = nn.Linear(d, d)
+        self.norm = nn.LayerNorm(d)
+
+    def forward(self, x):
+        return self.norm(torch.relu(self.lin(x)))
+
+
+class Stack(nn.Module):
+    def __init__(self, d=8, n=3, vocab=16):
+        super().__init__()
+        self.emb = nn.Embedding(vocab, d)
+        self.layers = nn.ModuleList([Block(d) for _ in range(n)])
+        self.head = nn.Linear(d, vocab, bias=False)
+
+    def hidden(self, t):
+        h = self.emb(t)
+        for l in self.layers:
+            h = l(h)
+        return h
+
+    def forward(self, t):
+        return self.head(self.hidden(t))
+
+
+def _work(rank, world):
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    out = {}
+    torch.manual_seed(0)
+    m, ref = Stack(), Stack()
+    ref.load_state_dict(m.state_dict())
+    # module names as patterns: "layers.0" takes every parameter below that module; two sibling modules form one
+    # bucket that is hooked on both of them (gathered in the first one's forward, resharded after the last one's)
+    flex_shard(m, [BucketSpec(["emb"]), BucketSpec(["layers.0"]), BucketSpec(["layers.1", "layers.2"]),
+                   BucketSpec(["head"], reshard_after_forward=False)])
+    sts = m.sharded_bucket_storages
+    out["members"] = [[i.fqn for i in st.infos] for st in sts]
+    # one gathered bucket at a time in forward (the kept head aside)
+    gathered_at = []
+    for i, l in enumerate(m.layers):
+        l.register_forward_hook(lambda mod, a, o: gathered_at.append([st.runtime.is_unsharded for st in sts]))
+    tok = torch.randint(0, 16, (4, 5), generator=torch.Generator().manual_seed(rank))
+    with torch.no_grad():
+        m(tok)
+    out["one_at_a_time"] = all(sum(flags[:3]) <= 1 for flags in gathered_at) and len(gathered_at) == 3
+    m.reshard()
+    # per-bucket unshard / reshard, identity and storage of the persistent unsharded parameters
+    st = sts[1]
+    st.unshard()
+    ups = list(st.runtime.unsharded_params)
+    out["unsharded_shapes"] = [tuple(u.shape) for u in ups] == [tuple(i.global_shape) for i in st.infos]
+    out["others_stay_sharded"] = not sts[2].runtime.is_unsharded
+    full_ref = [p.detach().clone() for p in ref.layers[0].parameters()]
+    out["values"] = all(torch.equal(u.detach(), f) for u, f in zip(ups, full_ref))
+    st.reshard()
+    out["freed"] = [u.untyped_storage().size() for u in ups] == [0] * len(ups)
+    st.unshard()
+    out["same_objects_refilled"] = ([id(u) for u in st.runtime.unsharded_params] == [id(u) for u in ups]
+                                    and all(torch.equal(u.detach(), f) for u, f in zip(ups, full_ref)))
+    st.reshard()
+    # a head applied chunk by chunk (loss over sequence chunks): same gradients as one call, one reduction of the head
+    ctx = sts[0].runtime.context
+    before = ctx.stats["reduces"]
+    h = m.hidden(tok)
+    loss = sum(m.head(c).square().mean() for c in h.chunk(5, dim=1)) / 5
+    loss.backward()
+    out["reduces"] = ctx.stats["reduces"] - before
+    toks = [torch.randint(0, 16, (4, 5), generator=torch.Generator().manual_seed(r)) for r in range(world)]
+    sum(sum(ref.head(c).square().mean() for c in ref.hidden(t).chunk(5, dim=1)) / 5 for t in toks).div(world).backward()
+    n = -(-ref.head.weight.shape[0] // world)
+    want = ref.head.weight.grad[rank * n:(rank + 1) * n]
+    out["chunked_head_grad"] = bool(torch.allclose(m.head.weight.grad, want, atol=1e-6))
+    out["idle"] = ctx.idle()
+    m.reshard()
+    # per-bucket switches: one bucket keeps its gradients (no sync) while the others reduce
+    for p in m.parameters():
+        p.grad = None
+    sts[2].set_requires_gradient_sync(False)
+    before = ctx.stats["reduces"]
+    m(tok).square().mean().backward()
+    out["partial_sync_reduces"] = ctx.stats["reduces"] - before
+    out["kept_bucket_has_no_sharded_grad"] = all(sp.grad is None for sp in sts[2].sharded_params)
+    sts[2].set_requires_gradient_sync(True)
+    m(tok).square().mean().backward()
+    out["kept_bucket_reduced_later"] = all(sp.grad is not None for sp in sts[2].sharded_params)
+    return out
+
+
+def test_per_bucket_runtime_contracts():
+    for r in run_ranks(_work, 2):
+        assert r["members"] == [["emb.weight"],
+                                ["layers.0.lin.weight", "layers.0.lin.bias", "layers.0.norm.weight", "layers.0.norm.bias"],
+                                [f"layers.{i}.{n}" for i in (1, 2) for n in ("lin.weight", "lin.bias", "norm.weight", "norm.bias")],
+                                ["head.weight"]]
+        assert r["one_at_a_time"] and r["unsharded_shapes"] and r["others_stay_sharded"] and r["values"]
+        assert r["freed"] and r["same_objects_refilled"]
+        assert r["reduces"] == 4 and r["chunked_head_grad"] and r["idle"]
+        assert r["partial_sync_reduces"] == 3 and r["kept_bucket_has_no_sharded_grad"] and r["kept_bucket_reduced_later"]
