@@ -28,7 +28,6 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 
 import torch
 import torch.distributed as dist

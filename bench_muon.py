@@ -23,7 +23,6 @@ os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")   # before CUDA initialise
 
 import torch
 import torch.distributed as dist
-import torch.nn as nn
 
 
 def main():

@@ -6,7 +6,6 @@ gates and the output projection train with AdamW. Role parity: ``examples/deepse
 """
 from __future__ import annotations
 
-import torch
 
 from flex_shard_b200 import relayout_bucket
 from flex_shard_b200.dist_muon import build_local_dist_muon

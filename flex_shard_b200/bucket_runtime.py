@@ -18,7 +18,7 @@ finalization, error poisoning after a raised backward).
 from __future__ import annotations
 
 import weakref
-from typing import Any, Sequence
+from typing import Sequence
 
 import torch
 import torch.nn as nn

@@ -22,7 +22,6 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .placement_contract import GlobalLayout, get_global_layout, set_global_layout
-from .sharded_param import is_flex_shard_param
 
 _ADAM_STATE_KEYS = ("exp_avg", "exp_avg_sq", "max_exp_avg_sq")
 

@@ -5,7 +5,6 @@ Parity: ``layout_adapters/dtensor.py:24-64`` of the reference.
 """
 from __future__ import annotations
 
-import torch
 import torch.nn as nn
 
 from ..placement_contract import GlobalLayout, set_global_layout

@@ -12,7 +12,6 @@ stored stacked (``w13``: gate and up projections) as the reference's grouped-mm 
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch

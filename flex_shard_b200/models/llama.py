@@ -15,7 +15,6 @@ from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops import elementwise as ew
 from ..ops.attention import qkv_attention

@@ -7,7 +7,6 @@ sparsely instead of evaluating every expert densely.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch

@@ -10,8 +10,7 @@ from typing import Callable
 
 import torch
 
-from .placement_contract import get_global_layout
-from .sharded_param import get_global_shape, is_flex_shard_param
+from .sharded_param import is_flex_shard_param
 
 
 @torch.no_grad()

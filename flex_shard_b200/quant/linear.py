@@ -15,7 +15,7 @@ import torch.nn as nn
 
 from ..ops.fp8 import fp8_linear, quantize_blockwise
 from ..ops.mxfp8 import mx_expand_scales, mx_quantize_weight, mxfp8_linear
-from .weight import BlockwiseFp8Weight, BlockwiseMxfp8Weight, BlockwiseQuantWeight
+from .weight import BlockwiseFp8Weight, BlockwiseMxfp8Weight
 
 
 class FlexShardPrequantizedLinear(nn.Module):

@@ -6,10 +6,8 @@ warm-up / stable / decay LR schedule, sharded grad-norm clip with one all-reduce
 from __future__ import annotations
 
 import json
-import math
 import sys
 import time
-from typing import Iterable
 
 import torch
 import torch.distributed as dist

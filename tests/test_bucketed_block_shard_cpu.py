@@ -1,7 +1,6 @@
 """``BucketedBlockShard`` (flat parameter-major buckets): plan geometry, identity of placements, rejected
 configurations, views into the bucket, local shapes that keep the parameter's rank.  One-rank mesh or no mesh at all.
 Parity: the behaviours pinned by the reference's ``tests/test_flex_shard_block_shard.py:60-380``."""
-import math
 import tempfile
 
 import pytest

@@ -13,7 +13,7 @@ def _tokens(step, rank):
 
 
 def _sharded(rank, world, steps, grad_bucket):
-    from flex_shard_b200 import BucketSpec, MixedPrecisionPolicy, flex_shard
+    from flex_shard_b200 import BucketSpec, flex_shard
     from flex_shard_b200.models.llama import Llama, LlamaConfig
     from flex_shard_b200.optim.adamw import FusedAdamW
     from flex_shard_b200.placements.shard import shard_placement_fn

@@ -3,7 +3,6 @@ are refused, owner-stored ones step without a collective, the momentum (tagged w
 a save / load into a fresh optimizer so that the next step is the same bits, and bad states are refused.
 Parity: the behaviours pinned by the reference's ``tests/test_dist_muon.py:404-560`` and the adapter's momentum
 translation (``dist_muon/comm_free_adapter.py:103-131``)."""
-import pytest
 import torch
 import torch.nn as nn
 

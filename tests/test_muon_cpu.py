@@ -1,6 +1,5 @@
 """DistMuon on CPU: math against a restated reference, owned vs redistributed storage on 2 gloo
 ranks, planner goldens."""
-import math
 
 import torch
 import torch.nn as nn

@@ -59,8 +59,6 @@ def test_block_scaled_gemm_matches_dequantised_product(M, N, K):
 
 
 def test_mxfp8_linear_gpu_matches_cpu_restatement():
-    import torch.nn as nn
-
     from flex_shard_b200.quant import FlexShardMxfp8BlockwiseLinear
 
     torch.manual_seed(4)

@@ -5,7 +5,6 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from tests.common import FakeMesh
 
 
 def test_transport_plan_writes_every_position_once_and_counts_crossing():
@@ -176,8 +175,6 @@ def test_router_reference_gradients_match_autograd_of_the_plain_formula():
 
 
 def test_yarn_table_and_fp32_output_linear():
-    import math
-
     import torch
 
     from flex_shard_b200.ops.elementwise import rope_table, yarn_attention_scale

@@ -5,7 +5,6 @@ Parity: the behaviours pinned by the reference's ``tests/test_flex_shard_trainin
 1722-1833,2439-2480`` and ``tests/test_flex_shard_runtime.py:233-254,697-707``."""
 import copy
 
-import pytest
 import torch
 import torch.nn as nn
 

@@ -22,8 +22,6 @@ def test_lr_schedule_warms_up_holds_and_decays():
 
 
 def _clip(rank, world):
-    import torch.distributed as dist
-
     from flex_shard_b200 import BucketSpec, flex_shard
     from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
     from flex_shard_b200.utils.training import clip_grad_norm_
