@@ -56,3 +56,41 @@ def test_compat_shims_install_the_promised_names():
     want = torch.stack([src[r, 2:].view(2, 2) for r in range(2)], dim=1).reshape(2, 4)
     assert torch.equal(inner[0], want)
     compat.install()                                  # installing twice is harmless
+
+
+def test_clock_sampler_reads_clocks_and_throttle_reasons_from_a_fake_nvml(monkeypatch):
+    """The benchmark only reads the GPU's state (clocks, throttle reasons) while the timed region runs; against a fake
+    NVML module: the median SM clock, the maximum clock, the reasons decoded from the bit mask, the physical index taken
+    from CUDA_VISIBLE_DEVICES, and no call that would change a setting."""
+    import sys
+    import time
+    import types
+
+    calls = []
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: calls.append("init")
+    fake.nvmlDeviceGetHandleByIndex = lambda i: calls.append(("handle", i)) or f"gpu{i}"
+    seq = iter([1300.0, 1400.0, 1350.0] + [1350.0] * 1000)
+    fake.nvmlDeviceGetClockInfo = lambda h, kind: next(seq)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965.0
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4 | 0x1      # power cap + "gpu idle" (not a reported reason)
+
+    def forbidden(*a, **k):
+        raise AssertionError("the benchmark must not change a GPU setting")
+
+    for name in ("nvmlDeviceSetApplicationsClocks", "nvmlDeviceSetGpuLockedClocks", "nvmlDeviceResetGpuLockedClocks",
+                 "nvmlDeviceSetPowerManagementLimit", "nvmlDeviceSetPersistenceMode"):
+        setattr(fake, name, forbidden)
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "5,6")
+    import bench
+
+    s = bench.ClockSampler(1)
+    assert ("handle", 6) in calls                                            # local index 1 is physical GPU 6
+    s.start()
+    time.sleep(0.35)
+    rec = s.stop()
+    assert rec["source"] == "nvml" and rec["samples"] >= 3
+    assert rec["sm_mhz"] == 1350.0 and rec["sm_max_mhz"] == 1965.0
+    assert rec["reasons"] == ["sw_power_cap"]
