@@ -26,25 +26,52 @@ from .placement_contract import GlobalLayout, get_global_layout, set_global_layo
 _ADAM_STATE_KEYS = ("exp_avg", "exp_avg_sq", "max_exp_avg_sq")
 
 
+_WRAPPER_PART = "_checkpoint_wrapped_module"
+
+
+def _strip_wrapper_parts(fqn: str) -> str:
+    """The name ``state_dict()`` shows for a parameter under activation-checkpoint wrappers (their
+    state-dict hooks drop the wrapper's attribute from every key)."""
+    return ".".join(part for part in fqn.split(".") if part != _WRAPPER_PART)
+
+
+def _sharded_modules(module: nn.Module):
+    """(prefix, sharded module) for ``module`` itself and for every sharded module below it, so that the
+    helpers here work on a parent whose children went through ``flex_shard`` one by one."""
+    for name, sub in module.named_modules(remove_duplicate=True):
+        if isinstance(getattr(type(sub), "sharded_bucket_storages", None), property):
+            yield (name + "." if name else ""), sub
+
+
+def _storages_with_prefix(module: nn.Module):
+    for prefix, sub in _sharded_modules(module):
+        for st in sub.sharded_bucket_storages:
+            yield prefix, sub, st
+
+
 def get_flex_shard_global_layouts(module: nn.Module) -> dict[str, GlobalLayout]:
-    """FQN -> layout for every managed parameter, including the extra names of tied weights."""
+    """FQN -> layout for every managed parameter of ``module`` and of its sharded submodules, including the
+    extra names of tied weights.  Names are relative to ``module``."""
     out: dict[str, GlobalLayout] = {}
-    for st in module.sharded_bucket_storages:
+    for prefix, _, st in _storages_with_prefix(module):
         for info in st.infos:
             lay = st.global_layout_of(info)
-            out[info.fqn] = lay
+            out[prefix + info.fqn] = lay
             for other in info.shared_fqns:
-                out[other] = lay
+                out[prefix + other] = lay
     return out
 
 
 def set_state_dict_global_layouts(module: nn.Module, state_dict: Mapping[str, Any]) -> None:
     """Tag the tensors of ``module.state_dict()`` with their layouts (attributes do not survive a
-    copy such as ``.to(dtype)``: tag again afterwards)."""
-    layouts = get_flex_shard_global_layouts(module)
-    for k, v in state_dict.items():
-        if isinstance(v, torch.Tensor) and k in layouts:
-            set_global_layout(v, layouts[k])
+    copy such as ``.to(dtype)``: tag again afterwards).  A parameter under an activation-checkpoint wrapper
+    is found under the key without the wrapper's name; parameters missing from ``state_dict`` are skipped
+    (parity: ``flex_shard/checkpoint.py:57-69`` of the reference)."""
+    for fqn, lay in get_flex_shard_global_layouts(module).items():
+        key = fqn if fqn in state_dict else _strip_wrapper_parts(fqn)
+        v = state_dict.get(key)
+        if isinstance(v, torch.Tensor):
+            set_global_layout(v, lay)
 
 
 def register_optimizer_checkpoint_hook(optimizer: torch.optim.Optimizer, module: nn.Module):
@@ -59,9 +86,9 @@ def register_optimizer_checkpoint_hook(optimizer: torch.optim.Optimizer, module:
         raise NotImplementedError(
             f"register_optimizer_checkpoint_hook supports Adam and AdamW, got {type(optimizer).__name__}")
     layouts_by_param: dict[int, tuple[GlobalLayout, str]] = {}
-    for st in module.sharded_bucket_storages:
+    for prefix, _, st in _storages_with_prefix(module):
         for info, sp in zip(st.infos, st.sharded_params):
-            layouts_by_param[id(sp)] = (st.global_layout_of(info), info.fqn)
+            layouts_by_param[id(sp)] = (st.global_layout_of(info), prefix + info.fqn)
     for g in optimizer.param_groups:
         for p in g["params"]:
             if id(p) not in layouts_by_param:
@@ -325,12 +352,13 @@ def to_dtensor_state_dict(module: nn.Module, state_dict: Mapping[str, Any], opti
     Parity: the reference hands tagged tensors to DCP directly (``flex_shard/checkpoint.py:57-69``), which
     needs a newer torch; the FSDP2 <-> flex round trips of its tests
     (``tests/test_flex_shard_checkpoint.py:483-538``) are what this provides."""
-    layouts = get_flex_shard_global_layouts(module)
-    mesh_by_fqn = {}
-    for st in module.sharded_bucket_storages:
+    layouts, mesh_by_fqn = {}, {}
+    for prefix, sub, st in _storages_with_prefix(module):
         for info in st.infos:
             for name in (info.fqn, *info.shared_fqns):
-                mesh_by_fqn[name] = _mesh_of(module, st)
+                for key in {prefix + name, _strip_wrapper_parts(prefix + name)}:
+                    layouts[key] = st.global_layout_of(info)
+                    mesh_by_fqn[key] = _mesh_of(sub, st)
     out = {}
     for k, v in state_dict.items():
         if isinstance(v, torch.Tensor) and k in layouts:
@@ -345,7 +373,7 @@ def to_dtensor_state_dict(module: nn.Module, state_dict: Mapping[str, Any], opti
     if optimizer is None:
         return out
     osd = optim_state_dict if optim_state_dict is not None else optimizer.state_dict()
-    names = {id(p): n for n, p in module.named_parameters()}
+    names = {id(p): _strip_wrapper_parts(n) for n, p in module.named_parameters()}
     index_name = {}
     idx = 0
     for g in optimizer.param_groups:
@@ -379,7 +407,7 @@ def to_dtensor_state_dict(module: nn.Module, state_dict: Mapping[str, Any], opti
 def load_dtensor_optim_state(optimizer, module: nn.Module, dcp_optim_state: Mapping[str, Any]) -> None:
     """Install optimizer state keyed by FQN (as ``to_dtensor_state_dict`` writes it and as
     ``get_optimizer_state_dict`` of an FSDP2 model does) into ``optimizer``."""
-    names = {n: p for n, p in module.named_parameters()}
+    names = {_strip_wrapper_parts(n): p for n, p in module.named_parameters()}
     for name, entry in dcp_optim_state["state"].items():
         p = names.get(name)
         if p is None:

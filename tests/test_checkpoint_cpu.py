@@ -222,3 +222,72 @@ def test_per_rank_objects_come_back_to_their_rank(tmp_path):
     assert res[0] == ({"file": 0, "seen": [0, 0, 0]}, 7) and res[1] == ({"file": 1, "seen": [1, 1, 1]}, 7)
     with pytest.raises(RuntimeError, match="per-rank state saved by 2 ranks"):
         checkpoint.load({"pos": checkpoint.PerRank(None)}, path)       # one process, no group: world size 1
+
+
+def _wrapped_and_tied(rank, world, path):
+    from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import checkpoint_wrapper
+
+    from flex_shard_b200 import BucketSpec, checkpoint, flex_shard
+    from flex_shard_b200.placement_contract import get_global_layout
+
+    expected = torch.arange(20, dtype=torch.float32).view(5, 4)
+    rows = [(0, 5)] if world == 1 else [(0, 3), (3, 5)]
+    lo, hi = rows[rank]
+    out = {}
+
+    # (a) a sharded module under an activation-checkpoint wrapper, seen from a plain parent
+    linear = nn.Linear(4, 5, bias=False)
+    with torch.no_grad():
+        linear.weight.copy_(expected)
+    parent = nn.Module()
+    parent.layer = checkpoint_wrapper(linear)
+    flex_shard(parent.layer, [BucketSpec(["*"])])
+
+    def tagged(m):
+        sd = m.state_dict()
+        checkpoint.set_state_dict_global_layouts(m, sd)
+        return sd
+
+    sd = tagged(parent)
+    out["keys"] = list(sd)
+    lay = get_global_layout(sd["layer.weight"])
+    out["layout"] = (lay.global_shape, lay.global_offsets, lay.local_sizes)
+    checkpoint.save(sd, os.path.join(path, "wrapped"))
+    next(parent.parameters()).detach().fill_(-1)
+    sd = tagged(parent)
+    checkpoint.load(sd, os.path.join(path, "wrapped"))
+    parent.load_state_dict(sd)
+    out["wrapped_ok"] = torch.equal(next(parent.parameters()).detach(), expected[lo:hi])
+
+    # (b) a tied weight: both names carry the layout, each is saved and loaded as the shard it is, and
+    # the weight stays shared
+    tied = nn.Module()
+    tied.embed = nn.Embedding(5, 4)
+    tied.head = nn.Linear(4, 5, bias=False)
+    tied.head.weight = tied.embed.weight
+    with torch.no_grad():
+        tied.embed.weight.copy_(expected)
+    flex_shard(tied, [BucketSpec(["*"])])
+    sd = tagged(tied)
+    out["tied_layouts"] = [get_global_layout(sd[k]) is not None
+                           and get_global_layout(sd[k]) == get_global_layout(sd["embed.weight"])
+                           for k in ("embed.weight", "head.weight")]
+    checkpoint.save(sd, os.path.join(path, "tied"))
+    tied.embed.weight.detach().fill_(-1)
+    sd = tagged(tied)
+    checkpoint.load(sd, os.path.join(path, "tied"))
+    tied.load_state_dict(sd)
+    out["still_shared"] = tied.head.weight is tied.embed.weight
+    out["tied_ok"] = torch.equal(tied.embed.weight.detach(), expected[lo:hi])
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_round_trip_of_a_checkpoint_wrapped_submodule_and_of_tied_weights(world, tmp_path):
+    """Parity: ``flex_shard/tests/test_flex_shard_checkpoint.py:192-245`` of the reference."""
+    for r, out in enumerate(run_ranks(_wrapped_and_tied, world, str(tmp_path))):
+        assert out["keys"] == ["layer.weight"]
+        lo, hi = ((0, 5),)[r] if world == 1 else ((0, 3), (3, 5))[r]
+        assert out["layout"] == ((5, 4), ((lo, 0),), ((hi - lo, 4),))
+        assert out["wrapped_ok"] and out["tied_ok"] and out["still_shared"]
+        assert out["tied_layouts"] == [True, True]

@@ -168,3 +168,84 @@ def test_flat_bucket_plan_formulas():
     for i in range(3):
         rows = sum(plan.local_rows(i, r)[1] - plan.local_rows(i, r)[0] for r in range(2))
         assert rows == plan.shapes[i][0]
+
+
+class _TwoDtypes(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(8, 6)
+        self.b = nn.Linear(6, 4).to(torch.bfloat16)
+
+    def forward(self, x):
+        return self.b(self.a(x).to(torch.bfloat16))
+
+
+def _mixed_dtype_bucket(rank, world):
+    import torch.distributed as dist
+
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.placements import BlockShard, BucketedOwned, MixedBucketPlacement, Shard
+
+    torch.manual_seed(0)
+    model, ref = _TwoDtypes(), _TwoDtypes()
+    ref.load_state_dict(model.state_dict())
+
+    def fn(named, mesh):
+        out = {}
+        for f, p in named:
+            if f == "a.weight":
+                out[f] = MixedBucketPlacement(BucketedOwned(((1, 0, p.shape[0]),)))
+            elif f == "b.weight":
+                out[f] = MixedBucketPlacement(BlockShard((1, 1), 1))
+            else:
+                out[f] = MixedBucketPlacement(Shard(0))
+        return out
+
+    flex_shard(model, [BucketSpec(["*"], placement_fn=fn)])
+    (st,) = model.sharded_bucket_storages
+    local_dtypes = sorted({str(sp.dtype) for sp in st.sharded_params})
+    gathered = []
+    plain = dist.all_gather_into_tensor
+
+    def spy(out, inp, *a, **k):
+        gathered.append((out.dtype, out.numel()))
+        return plain(out, inp, *a, **k)
+
+    dist.all_gather_into_tensor = spy
+    try:
+        model.unshard()
+    finally:
+        dist.all_gather_into_tensor = plain
+    same = all(p.dtype == q.dtype and torch.equal(p.detach(), q.detach())
+               for (_, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()))
+    model.reshard()
+    xs = [torch.randn(4, 8, generator=torch.Generator().manual_seed(3 + r)) for r in range(world)]
+    model(xs[rank]).float().sum().backward()
+    sum(ref(x).float().sum() for x in xs).div(world).backward()
+    grad_dtypes = {n: p.grad.dtype for n, p in model.named_parameters()}
+    from flex_shard_b200.checkpoint import get_flex_shard_global_layouts
+
+    layouts = get_flex_shard_global_layouts(model)
+    err = 0.0
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        lay = layouts[n]
+        for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
+            mine, want = p.grad, q.grad
+            for d, (g0, l0, sz) in enumerate(zip(goff, loff, size)):
+                mine, want = mine.narrow(d, l0, sz), want.narrow(d, g0, sz)
+            if mine.numel():
+                err = max(err, float((mine.float() - want.float()).abs().max()))
+    return local_dtypes, gathered, st.total_bytes, same, grad_dtypes, err
+
+
+def test_mixed_bucket_holds_two_dtypes_and_gathers_bytes_once():
+    """fp32 and bf16 members of one mixed bucket travel as one byte all-gather and come back in their own
+    dtypes with every rank's values (parity: ``flex_shard/tests/test_flex_shard_buckets.py``
+    ``test_mixed_payload_dtypes_use_one_byte_all_gather`` and ``..._reconstruct_rank_distinct_values``)."""
+    res = run_ranks(_mixed_dtype_bucket, 2)
+    for local_dtypes, gathered, nbytes, same, grad_dtypes, err in res:
+        assert local_dtypes == ["torch.bfloat16", "torch.float32"]
+        assert len(gathered) == 1 and gathered[0][0] == torch.uint8
+        assert same
+        assert grad_dtypes["a.weight"] == torch.float32 and grad_dtypes["b.weight"] == torch.bfloat16
+        assert err < 2e-2, err
