@@ -19,6 +19,7 @@ host memory, ``:362-461`` long segments split over the grid).
 from __future__ import annotations
 
 import math
+import threading
 
 import numpy as np
 import torch
@@ -195,6 +196,7 @@ def run_segment_ops(ops, cache: dict | None = None) -> int:
 
 
 _parked: list = []
+_parked_lock = threading.Lock()      # forward (caller's thread) and backward hooks (autograd's thread) both park tables
 _host_tables = True
 _HOST_TABLE_MAX = 512
 
@@ -202,6 +204,7 @@ _HOST_TABLE_MAX = 512
 def _park(host, descs, dev) -> None:
     ev = torch.cuda.Event()
     ev.record(torch.cuda.current_stream(dev))
-    _parked.append((ev, host, descs))
-    while _parked and _parked[0][0].query():
-        _parked.pop(0)
+    with _parked_lock:
+        _parked.append((ev, host, descs))
+        while _parked and _parked[0][0].query():
+            _parked.pop(0)
