@@ -20,9 +20,19 @@ def is_muon_param(name: str, p) -> bool:
     return not (name.startswith("tok_embeddings") or name == "output" or name.endswith(".gate"))
 
 
-def kimi_block_rows(cfg) -> dict:
-    """Rows of one orthogonalisation block for the per-head attention matrices."""
-    return {"wq_b": cfg.qk_dim, "wkv_b": cfg.qk_nope_dim + cfg.v_dim}
+def kimi_block_rows(cfg, split: str = "head") -> dict:
+    """Rows of the orthogonalisation blocks of the attention projections.
+
+    ``"head"``: one matrix per attention head (``wq_b``, ``wkv_b``).  ``"role"``: a head's parts are matrices of
+    their own, as in the Kimi-K2 recipe: the no-position and rotary rows of ``wq_b``, the key and value rows of
+    ``wkv_b``, and the latent and shared-rotary rows of ``wkv_a`` (parity: ``kimi_matrices`` of the reference's
+    ``examples/deepseek_v3/muon.py:29-48``)."""
+    if split == "head":
+        return {"wq_b": cfg.qk_dim, "wkv_b": cfg.qk_nope_dim + cfg.v_dim}
+    if split == "role":
+        return {"wq_b": (cfg.qk_nope_dim, cfg.qk_rope_dim), "wkv_b": (cfg.qk_nope_dim, cfg.v_dim),
+                "wkv_a": (cfg.kv_lora_rank, cfg.qk_rope_dim)}
+    raise ValueError(f"split must be 'head' or 'role', got {split!r}")
 
 
 def store_on_owners(model) -> None:
@@ -64,11 +74,11 @@ def store_heads_blockwise(model) -> None:
             relayout_bucket(model, st, fn)
 
 
-def build_muon(model, lr: float, weight_decay: float, adamw_lr: float | None = None):
-    """Muon over every matrix (per head for the attention up-projections, per expert for routed experts,
-    whole otherwise) + AdamW for the rest. The per-head split needs the model's config (``model.cfg``)."""
+def build_muon(model, lr: float, weight_decay: float, adamw_lr: float | None = None, split: str = "head"):
+    """Muon over every matrix (per head, or per head and role, for the attention up-projections, per expert for
+    routed experts, whole otherwise) + AdamW for the rest. The split needs the model's config (``model.cfg``)."""
     cfg = getattr(model, "cfg", None)
-    heads = kimi_block_rows(cfg) if cfg is not None and hasattr(cfg, "qk_nope_dim") else None
+    heads = kimi_block_rows(cfg, split) if cfg is not None and hasattr(cfg, "qk_nope_dim") else None
     muon = build_local_dist_muon(model, is_muon_param=is_muon_param, block_rows_by_fqn=heads, lr=lr,
                                  weight_decay=weight_decay, adjust_lr_fn="match_rms_adamw")
     rest = [p for n, p in model.named_parameters() if not is_muon_param(n, p)]

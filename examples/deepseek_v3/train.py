@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--aux-loss-coeff", type=float, default=0.0, help="weight of the sequence-wise router balance loss")
     ap.add_argument("--no-explicit-prefetch", action="store_true",
                     help="leave prefetching to the learned order instead of block-by-block prefetch lists")
+    ap.add_argument("--muon-split", choices=["head", "role"], default="head",
+                    help="Muon's matrices inside the attention projections: one per head, or one per head and role "
+                         "(no-position / rotary / value rows apart, the Kimi-K2 recipe)")
     ap.add_argument("--muon-storage", choices=["owners", "heads"], default="owners",
                     help="owners: every matrix whole on an owner rank; heads: per-head matrices in head blocks "
                          "spread over the ranks (BlockShard by attention head), the rest on owners")
@@ -146,7 +149,7 @@ def main():
 
     if args.optimizer == "muon":
         (store_heads_blockwise if args.muon_storage == "heads" else store_on_owners)(model)
-        muon, adam = build_muon(model, args.lr, args.weight_decay)
+        muon, adam = build_muon(model, args.lr, args.weight_decay, split=args.muon_split)
         opts = [muon, adam]
     else:
         adam = FusedAdamW(model.parameters(), lr=args.lr, betas=(0.9, 0.95), weight_decay=args.weight_decay)

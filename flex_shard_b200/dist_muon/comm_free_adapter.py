@@ -18,7 +18,7 @@ from .storage_layout import get_flex_shard_muon_compute_layouts
 
 
 def build_local_dist_muon(module: nn.Module, *, is_muon_param: Callable[[str, nn.Parameter], bool] | None = None,
-                          block_rows_by_fqn: Mapping[str, int] | None = None, **muon_kwargs) -> DistMuon:
+                          block_rows_by_fqn: Mapping[str, int | tuple[int, ...]] | None = None, **muon_kwargs) -> DistMuon:
     """DistMuon over the local shards of ``module``'s matrix parameters; raises if any of them is
     stored in a layout that would need communication (``Shard(0)`` on more than one rank)."""
     is_muon_param = is_muon_param or (lambda n, p: len(getattr(p, "_fsb_global_shape", p.shape)) >= 2)

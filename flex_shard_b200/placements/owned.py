@@ -81,9 +81,6 @@ def newton_schulz_cost(shape: Sequence[int], ns_steps: int = 5) -> float:
     return float(ns_steps * s * s * (2 * l + s) * math.prod(shape[:-2]))
 
 
-_CARRIED: dict[int, list[float]] = {}
-
-
 def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_fn=None,
                                                 owner_by_fqn: Mapping[str, int] | None = None,
                                                 ranks_per_host: int | None = None):
@@ -91,13 +88,19 @@ def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_
     ``carry_loads`` the per-rank loads persist across calls (buckets), which spreads many
     identical buckets over the whole mesh instead of reusing the same few owners."""
     cost_fn = cost_fn or (lambda fqn, p: newton_schulz_cost(tuple(p.shape)))
+    carried: list[float] = []       # lives with this function (not in a registry keyed by an address that a later function could reuse)
 
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
 
         _, _, W, _ = mesh_group(mesh)
         hosts = mesh_rank_hosts(W, ranks_per_host)
-        loads = _CARRIED.setdefault(id(fn), [0.0] * W) if carry_loads else [0.0] * W
+        if carry_loads:
+            if len(carried) != W:
+                carried[:] = [0.0] * W
+            loads = carried
+        else:
+            loads = [0.0] * W
         fixed = {f: owner_by_fqn[f] for f, _ in named_params if owner_by_fqn and f in owner_by_fqn}
         for f, p in named_params:
             if f in fixed:
@@ -112,7 +115,7 @@ def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_
                 out[f] = BucketedOwned(((fixed[f], 0, p.shape[0]),), "full_param")
         return out
 
-    fn.reset_loads = lambda: _CARRIED.pop(id(fn), None)
+    fn.reset_loads = carried.clear
     return fn
 
 

@@ -81,13 +81,16 @@ def test_packed_document_batches_pack_label_and_resume(tmp_path):
     assert next(r1)["input"].tolist() == [[0, 50, 51, 52]]
 
 
-def test_muon_head_block_storage_trains_like_owner_storage(tmp_path):
+@pytest.mark.parametrize("split", ["head", "role"])
+def test_muon_head_block_storage_trains_like_owner_storage(tmp_path, split):
     """Per-head matrices stored in head blocks over the ranks (BlockShard by attention head) or whole on owners:
-    the same per-head Newton-Schulz either way, so the same losses."""
+    the same per-head Newton-Schulz either way, so the same losses; also with every head cut into its roles
+    (no-position / rotary / value rows as matrices of their own)."""
     # clipping off: the global gradient norm is summed in storage order, its last bit differs between the two
     # layouts, and Newton-Schulz rounds its input to bf16, which turns that bit into visible differences
-    owners = _run(str(tmp_path / "o"), ["--optimizer", "muon", "--max-norm", "1e9"])
-    heads = _run(str(tmp_path / "h"), ["--optimizer", "muon", "--muon-storage", "heads", "--max-norm", "1e9"])
+    common = ["--optimizer", "muon", "--max-norm", "1e9", "--muon-split", split]
+    owners = _run(str(tmp_path / "o"), common)
+    heads = _run(str(tmp_path / "h"), [*common, "--muon-storage", "heads"])
     assert [heads[s]["loss"] for s in range(4)] == [owners[s]["loss"] for s in range(4)]
 
 

@@ -71,7 +71,7 @@ class Net(nn.Module):
         return self.w2(torch.relu(self.w1(x))) + self.heads(x)[:, :32]
 
 
-def _train(rank, world, storage, steps):
+def _train(rank, world, storage, steps, head_blocks=16):
     from flex_shard_b200 import BucketSpec, flex_shard
     from flex_shard_b200.dist_muon import DistMuon, build_local_dist_muon, get_flex_shard_muon_compute_layouts
     from flex_shard_b200.placements import BlockShard, BucketedOwned
@@ -86,7 +86,7 @@ def _train(rank, world, storage, steps):
                 out[n] = BlockShard((2, 2), 0) if n.startswith("heads") else BucketedOwned(((i % 2, 0, p.shape[0]),))
             return out
         flex_shard(model, [BucketSpec(["*"], placement_fn=fn, gradient_reduce_op=dist.ReduceOp.AVG)])
-        opt = build_local_dist_muon(model, lr=0.02, block_rows_by_fqn={"heads.weight": 16})
+        opt = build_local_dist_muon(model, lr=0.02, block_rows_by_fqn={"heads.weight": head_blocks})
     else:
         flex_shard(model, [BucketSpec(["*"])])
         lays = get_flex_shard_muon_compute_layouts(model)
@@ -103,7 +103,7 @@ def _train(rank, world, storage, steps):
     return full, opt.collectives_issued
 
 
-def _reference(world, steps):
+def _reference(world, steps, head_blocks=(16,)):
     torch.manual_seed(0)
     model = Net()
     moms = {n: torch.zeros_like(p) for n, p in model.named_parameters()}
@@ -113,9 +113,12 @@ def _reference(world, steps):
         with torch.no_grad():
             for n, p in model.named_parameters():
                 if n.startswith("heads"):
-                    for h in range(4):
-                        sl = slice(16 * h, 16 * h + 16)
-                        _ref_muon_step(p[sl], p.grad[sl], moms[n][sl], mode=None)
+                    pos = 0
+                    while pos < p.shape[0]:
+                        for rows in head_blocks:
+                            sl = slice(pos, pos + rows)
+                            _ref_muon_step(p[sl], p.grad[sl], moms[n][sl], mode=None)
+                            pos += rows
                 else:
                     _ref_muon_step(p, p.grad, moms[n], mode=None)
         model.zero_grad()
@@ -129,6 +132,27 @@ def test_muon_owned_storage_is_comm_free_and_matches():
         assert ncoll == 0
         for n in ref:
             torch.testing.assert_close(full[n], ref[n], rtol=0, atol=3e-2)
+
+
+def test_blocks_of_two_sizes_repeat_down_the_rows():
+    """``block_rows_by_fqn = {name: (12, 4)}``: every head is two matrices (12 rows, then 4 rows), each orthogonalised
+    on its own, whether the head blocks are spread over the ranks or not; rows that are not whole periods are refused.
+    Parity: ``BlockShard(dim=0, block_sizes=(a, b))`` compute layouts of the reference's Kimi recipe
+    (``examples/deepseek_v3/muon.py:29-48``)."""
+    import pytest
+
+    ref = _reference(2, 3, head_blocks=(12, 4))
+    plain = _reference(2, 3)
+    assert not torch.equal(ref["heads.weight"], plain["heads.weight"])
+    for full, ncoll in run_ranks(_train, 2, "owned", 3, (12, 4)):
+        assert ncoll == 0
+        for n in ref:
+            torch.testing.assert_close(full[n], ref[n], rtol=0, atol=3e-2)
+    err = float((full["heads.weight"] - ref["heads.weight"]).abs().max())
+    other = float((full["heads.weight"] - plain["heads.weight"]).abs().max())
+    assert err < other          # closer to the two-matrix reference than to the one-matrix-per-head one
+    with pytest.raises(AssertionError, match="whole blocks|whole repetitions"):
+        run_ranks(_train, 2, "owned", 1, (12, 5))
 
 
 def test_muon_row_shard_storage_redistributes_and_matches():
