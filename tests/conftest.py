@@ -26,3 +26,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _fresh_rank_processes_per_module():
+    """The gloo rank processes of ``tests.common.run_ranks`` are reused within a test module and ended after it."""
+    yield
+    from tests import common
+
+    common.shutdown_pools()
