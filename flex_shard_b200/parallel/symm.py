@@ -295,6 +295,8 @@ class SymmComm(Comm):
         ptr = buf.data_ptr()
         self._resident.pop(ptr, None)
         self._unfenced.discard(ptr)
+        # cached descriptor tables are keyed by the region object's identity, which a later region may reuse
+        self._desc_cache.clear()
 
     def _resident_region(self, inp: torch.Tensor):
         reg = self._resident.get(inp.data_ptr())
