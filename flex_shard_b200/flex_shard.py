@@ -295,6 +295,33 @@ def _validate_bucket(spec: BucketSpec, named, placements, comm) -> None:
         placements[f].compute_local_shape(tuple(p.shape), comm.rank, comm.world_size)  # raises on bad dims
 
 
+def _validate_dtype_overrides(buckets: Sequence[BucketSpec], assigned) -> None:
+    """Every ``param_dtype_overrides`` pattern must name a parameter of some bucket that uses an equal policy
+    (builders often share one policy across buckets, so the parameter may sit in any of them); a pattern that
+    matches nothing there would silently leave the parameter in the policy's default dtype.
+    Parity: ``flex_shard/flex_shard.py:756-789`` of the reference (exact names there, fnmatch patterns here)."""
+    import fnmatch
+
+    groups: list[tuple[Any, list[int], set[str]]] = []
+    for idx, (spec, group) in enumerate(zip(buckets, assigned)):
+        policy = spec.mp_policy
+        if policy is None or not getattr(policy, "param_dtype_overrides", None):
+            continue
+        for known, indices, fqns in groups:
+            if known == policy:
+                indices.append(idx)
+                fqns.update(f for f, _ in group)
+                break
+        else:
+            groups.append((policy, [idx], {f for f, _ in group}))
+    for policy, indices, fqns in groups:
+        unknown = sorted(pat for pat in policy.param_dtype_overrides
+                         if not any(fnmatch.fnmatchcase(f, pat) for f in fqns))
+        if unknown:
+            raise ValueError(f"param_dtype_overrides of buckets {indices} names parameters that are in no bucket "
+                             f"using that policy: {unknown}")
+
+
 def _install_runtime(module: nn.Module, state: _FlexShardState) -> None:
     state.context = install_bucket_hooks(module, state.storages, state.hook_modules)
 
@@ -323,6 +350,7 @@ def flex_shard(module: nn.Module, buckets: Sequence[BucketSpec], *,
         named, shared, slots = _managed_named_params(module)
         assigned = assign_params_to_buckets(module, named, buckets, shared)
 
+    _validate_dtype_overrides(buckets, assigned)
     state = _FlexShardState()
     plans = []
     for spec, comm, group in zip(buckets, comms, assigned):

@@ -285,13 +285,12 @@ class DeepSeekV3(nn.Module):
 def deepseek_buckets(model: DeepSeekV3, mesh=None, expert_mesh=None, mp_policy=None, dense_dp_size=None):
     """tok_embeddings | per block: non-expert params (+ an expert bucket on ``expert_mesh``) | norm+output.
     Routed-expert weights are ``Shard(1)`` (their dim 0 is the expert axis), everything else
-    ``Shard(0)``; router gates stay fp32. Mirrors the bucket recipe of the reference's example
+    ``Shard(0)``; router gates stay fp32 (a bucket of their own without a compute dtype). Mirrors the bucket recipe of the reference's example
     (``examples/deepseek_v3/train.py:114-175``)."""
     from ..bucket_storage import BucketSpec, MixedPrecisionPolicy
     from ..placements.shard import Shard
 
-    mp = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
-                                           param_dtype_overrides={"*.gate": torch.float32})
+    mp = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
 
     def fn(named, m):
         return {n: Shard(1) if ".routed_experts." in n else Shard(0) for n, _ in named}

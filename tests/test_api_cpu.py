@@ -51,6 +51,36 @@ def test_every_parameter_belongs_to_exactly_one_bucket():
         flex_shard(Net(), [])
 
 
+def test_dtype_overrides_span_the_buckets_that_share_the_policy():
+    """An override may name a parameter of any bucket whose policy is equal; one that no such bucket holds is an
+    error that names it (parity: ``tests/test_flex_shard_api.py:153-187`` of the reference), and nested wrapping
+    is refused in both orders (``:53-109``)."""
+    from dataclasses import replace
+
+    from flex_shard_b200 import BucketSpec, MixedPrecisionPolicy, flex_shard
+
+    bf16 = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
+    override = replace(bf16, param_dtype_overrides={"b.weight": torch.float32})
+
+    def shard(*policies):
+        return flex_shard(Net(), [BucketSpec([f"{name}.*"], mp_policy=p) for name, p in zip("ab", policies)])
+
+    m = shard(override, replace(bf16, param_dtype_overrides={"b.weight": torch.float32}))
+    dtypes = {i.fqn: i.param_dtype for st in m.sharded_bucket_storages for i in st.infos}
+    assert dtypes == {"a.weight": torch.bfloat16, "a.bias": torch.bfloat16,
+                      "b.weight": torch.float32, "b.bias": torch.bfloat16}
+    with pytest.raises(ValueError, match=r"buckets \[0\].*\['b\.weight'\]"):
+        shard(override, bf16)
+
+    child_first = nn.Sequential(nn.Linear(2, 2), nn.Linear(2, 2))
+    flex_shard(child_first[0], [BucketSpec(["*"])])
+    with pytest.raises(ValueError, match="already applied to submodule"):
+        flex_shard(child_first, [BucketSpec(["*"])])
+    root_first = flex_shard(nn.Sequential(nn.Linear(2, 2), nn.Linear(2, 2)), [BucketSpec(["*"])])
+    with pytest.raises(ValueError, match="ancestor or descendant"):
+        flex_shard(root_first[0], [BucketSpec(["*"])])
+
+
 def test_flex_shard_applies_once():
     from flex_shard_b200 import BucketSpec, flex_shard
 
