@@ -224,7 +224,9 @@ class SymmDispatcher:
         # the group object itself is part of the key (and so stays alive): an id() could be reused by a later group
         key = (self.group, self.num_experts, xt.shape[1], pairs, xt.dtype, self.capacity_factor, xt.device)
         ex = self._ex
-        if ex is None or ex.D != xt.shape[1] or moe_ops.max_rows_for(pairs, self.num_experts) > ex.send_rows:
+        # a batch of another size (an evaluation batch, say) takes the exchange built for that size; every rank of the
+        # group must see the same sizes in the same order, since building an exchange is a collective step
+        if ex is None or ex.D != xt.shape[1] or moe_ops.max_rows_for(pairs, self.num_experts) != ex.send_rows:
             ex = SymmDispatcher._shared.get(key)
             if ex is None:
                 ex = SymmDispatcher._shared[key] = SymmExpertExchange(
