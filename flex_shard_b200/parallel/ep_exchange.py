@@ -226,7 +226,7 @@ class SymmDispatcher:
         ex = self._ex
         # a batch of another size (an evaluation batch, say) takes the exchange built for that size; every rank of the
         # group must see the same sizes in the same order, since building an exchange is a collective step
-        if ex is None or ex.D != xt.shape[1] or moe_ops.max_rows_for(pairs, self.num_experts) != ex.send_rows:
+        if ex is None or ex.D != xt.shape[1] or ex.dtype != xt.dtype or moe_ops.max_rows_for(pairs, self.num_experts) != ex.send_rows:
             ex = SymmDispatcher._shared.get(key)
             if ex is None:
                 ex = SymmDispatcher._shared[key] = SymmExpertExchange(
