@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import fnmatch
 from dataclasses import dataclass
-from typing import Mapping, Sequence
+from typing import Mapping, Protocol, Sequence
 
 import torch.distributed as dist
 
@@ -31,6 +31,107 @@ class MatrixSpec:
     shape: tuple[int, ...]
     num_blocks: int = 1   # > 1: a block group (e.g. heads) spread over ranks block by block
     eligible_ranks: tuple[int, ...] | None = None   # block groups only: the ranks that may hold blocks (default: all)
+    cost: float | None = None   # load of the matrix (of one block, for a block group); default: its Newton-Schulz cost
+
+    def load(self, ns_steps: int = 5) -> float:
+        if self.cost is not None:
+            return float(self.cost)
+        if self.num_blocks <= 1:
+            return newton_schulz_cost(self.shape, ns_steps)
+        return newton_schulz_cost((self.shape[0] // self.num_blocks, *self.shape[1:]), ns_steps)
+
+
+# ---- the planner's inputs and answer in the shape the reference's recipes use (``dist_muon/bucket_planner.py:33-82``
+# of the reference): loads are element counts, block counts follow each group's ``eligible_ranks`` order
+@dataclass(frozen=True)
+class WholeMatrixSpec:
+    """One complete matrix stored on one rank."""
+    name: str
+    numel: int
+
+
+@dataclass(frozen=True)
+class MatrixBlockGroupSpec:
+    """Equal blocks (possibly of several matrices) spread over the eligible ranks."""
+    name: str
+    num_blocks: int
+    block_numel: int
+    eligible_ranks: tuple[int, ...]
+
+
+@dataclass(frozen=True)
+class AssignmentGroup:
+    """Whole matrices and block groups that are balanced in one step (one transformer block, say)."""
+    matrices: tuple[WholeMatrixSpec, ...] = ()
+    block_groups: tuple[MatrixBlockGroupSpec, ...] = ()
+
+
+@dataclass(frozen=True)
+class MatrixAssignment:
+    """Owners of whole matrices and, per block group, blocks per rank in its ``eligible_ranks`` order."""
+    rank_by_matrix: dict
+    blocks_per_rank_by_group: dict
+
+
+class MatrixAssignmentFn(Protocol):
+    """A custom balancer: runs on every rank and must give the same answer everywhere."""
+
+    def __call__(self, groups: Sequence[AssignmentGroup], *, num_ranks: int) -> MatrixAssignment: ...
+
+
+def _assign_groups(groups: Sequence[AssignmentGroup], num_ranks: int, hosts: Sequence[int] | None) -> MatrixAssignment:
+    """Groups are balanced one after the other on top of the loads the earlier ones left.  Whole matrices of a group:
+    without ``hosts``, packed into one pile per rank (largest first onto the lightest pile), then the heaviest pile
+    goes to the rank that carries least so far; with ``hosts``, host first and then rank (``assign_to_hosts_then_ranks``).
+    Blocks of a block group go one by one to the least loaded eligible rank (ties: the earlier eligible rank)."""
+    if num_ranks <= 0:
+        raise ValueError("num_ranks must be positive")
+    if hosts is not None and len(hosts) != num_ranks:
+        raise ValueError(f"hosts must give each of the {num_ranks} ranks a host, got {len(hosts)} entries")
+    seen: set[str] = set()
+    for g in groups:
+        for m in g.matrices:
+            if m.numel <= 0:
+                raise ValueError(f"whole matrix {m.name!r} must have a positive numel")
+        for b in g.block_groups:
+            if b.num_blocks <= 0 or b.block_numel <= 0:
+                raise ValueError(f"block group {b.name!r} needs positive num_blocks and block_numel")
+            ranks = tuple(b.eligible_ranks)
+            if (not ranks or len(set(ranks)) != len(ranks) or any(not isinstance(r, int) for r in ranks)
+                    or min(ranks) < 0 or max(ranks) >= num_ranks):
+                raise ValueError(f"eligible_ranks of block group {b.name!r} must be distinct ranks of the "
+                                 f"{num_ranks}-rank mesh, got {b.eligible_ranks!r}")
+        for item in (*g.matrices, *g.block_groups):
+            if item.name in seen:
+                raise ValueError(f"Duplicate assignment name {item.name!r}: every matrix and block group gets one entry")
+            seen.add(item.name)
+    loads = [0.0] * num_ranks
+    whole: dict[str, int] = {}
+    blocks: dict[str, tuple[int, ...]] = {}
+    for g in groups:
+        if g.matrices and hosts is None:
+            piles = [[0.0, []] for _ in range(num_ranks)]
+            for m in sorted(g.matrices, key=lambda m: -m.numel):
+                pile = min(piles, key=lambda p: p[0])          # min keeps the first of equals: the lowest pile index
+                pile[0] += m.numel
+                pile[1].append(m.name)
+            lightest_first = sorted(range(num_ranks), key=lambda r: loads[r])
+            for pile, r in zip(sorted(piles, key=lambda p: -p[0]), lightest_first):
+                for name in pile[1]:
+                    whole[name] = r
+                loads[r] += pile[0]
+        elif g.matrices:
+            owners = assign_to_hosts_then_ranks([float(m.numel) for m in g.matrices], list(hosts), loads)
+            for m, r in zip(g.matrices, owners):
+                whole[m.name] = r
+        for b in g.block_groups:
+            counts = [0] * len(b.eligible_ranks)
+            for _ in range(b.num_blocks):
+                pos = min(range(len(counts)), key=lambda i: loads[b.eligible_ranks[i]])
+                counts[pos] += 1
+                loads[b.eligible_ranks[pos]] += b.block_numel
+            blocks[b.name] = tuple(counts)
+    return MatrixAssignment(whole, blocks)
 
 
 def validate_assignment(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int,
@@ -58,10 +159,19 @@ def validate_assignment(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int,
             raise ValueError(f"block group {fqn!r} places blocks outside its eligible ranks {m.eligible_ranks}: {o!r}")
 
 
-def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, ranks_per_host: int | None = None,
+def assign_matrices(groups, num_ranks: int, *, ranks_per_host: int | None = None,
                     ns_steps: int = 5, carry_loads: bool = False,
-                    fixed_owners: Mapping[str, int] | None = None) -> dict[str, int | tuple[int, ...]]:
-    """Owner rank per matrix (or per block, as a tuple of blocks-per-rank, for block groups)."""
+                    fixed_owners: Mapping[str, int] | None = None, hosts: Sequence[int] | None = None):
+    """Owner rank per matrix (or per block, as a tuple of blocks-per-rank, for block groups).
+
+    ``groups`` of ``MatrixSpec`` lists return ``{fqn: rank | blocks per rank}``.  ``groups`` of ``AssignmentGroup``
+    (the reference's recipe types: loads are element counts, carried from group to group; ``hosts`` as
+    ``mesh_rank_hosts`` gives them) return a ``MatrixAssignment``."""
+    groups = list(groups)
+    if groups and all(isinstance(g, AssignmentGroup) for g in groups):
+        if fixed_owners:
+            raise ValueError("fixed_owners goes with MatrixSpec groups")
+        return _assign_groups(groups, num_ranks, hosts)
     hosts = mesh_rank_hosts(num_ranks, ranks_per_host)
     loads = [0.0] * num_ranks
     out: dict[str, int | tuple[int, ...]] = {}
@@ -81,16 +191,15 @@ def assign_matrices(groups: Sequence[Sequence[MatrixSpec]], num_ranks: int, *, r
         for m in whole:
             if fixed_owners and m.fqn in fixed_owners:
                 out[m.fqn] = fixed_owners[m.fqn]
-                loads[out[m.fqn]] += newton_schulz_cost(m.shape, ns_steps)
+                loads[out[m.fqn]] += m.load(ns_steps)
         free = [m for m in whole if m.fqn not in out]
-        owners = assign_to_hosts_then_ranks([newton_schulz_cost(m.shape, ns_steps) for m in free], hosts, loads)
+        owners = assign_to_hosts_then_ranks([m.load(ns_steps) for m in free], hosts, loads)
         for m, r in zip(free, owners):
             out[m.fqn] = r
         for m in group:
             if m.num_blocks <= 1:
                 continue
-            rows = m.shape[0] // m.num_blocks
-            cost = newton_schulz_cost((rows, *m.shape[1:]), ns_steps)
+            cost = m.load(ns_steps)
             if m.eligible_ranks is None:
                 per_block = assign_to_hosts_then_ranks([cost] * m.num_blocks, hosts, loads)
             else:
@@ -136,7 +245,21 @@ def materialize_dist_muon_buckets(named_params, mesh, *, initial: Sequence[str],
     if assignment_fn is not None:
         # a custom balancer: called with the groups and the mesh size on every rank (it must be deterministic); its
         # answer is checked before anything is built
-        owners = dict(assignment_fn(groups, num_ranks=W))
+        answer = assignment_fn(groups, num_ranks=W)
+        if isinstance(answer, MatrixAssignment):
+            # block counts of a MatrixAssignment follow each group's eligible ranks (all ranks unless the spec says otherwise)
+            eligible = {m.fqn: (m.eligible_ranks or tuple(range(W))) for g in groups for m in g}
+            owners = dict(answer.rank_by_matrix)
+            for name, counts in answer.blocks_per_rank_by_group.items():
+                ranks = eligible.get(name, tuple(range(W)))
+                if len(counts) != len(ranks):
+                    raise ValueError(f"block group {name!r} needs one count per eligible rank ({len(ranks)}), got {counts!r}")
+                full = [0] * W
+                for r, c in zip(ranks, counts):
+                    full[r] = c
+                owners[name] = tuple(full)
+        else:
+            owners = dict(answer)
         validate_assignment(groups, W, owners)
     else:
         owners = assign_matrices(groups, W, ranks_per_host=ranks_per_host, carry_loads=carry_loads)

@@ -157,3 +157,54 @@ def test_custom_assignment_is_used_and_checked():
     with pytest.raises(ValueError, match="missing"):
         materialize_dist_muon_buckets(named, FakeMesh(4), initial=["emb"], blocks=[["l0"]], final=[],
                                       assignment_fn=lambda groups, *, num_ranks: {})
+
+
+def test_recipe_types_of_the_reference_are_accepted():
+    """``assign_matrices`` over ``AssignmentGroup``s (element counts as loads, carried from group to group) answers
+    with a ``MatrixAssignment``; goldens restated from ``tests/test_matrix_assignment.py:73-165`` of the reference.
+    A custom balancer may answer ``materialize_dist_muon_buckets`` in that form too."""
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200.dist_muon import (AssignmentGroup, MatrixAssignment, MatrixBlockGroupSpec, WholeMatrixSpec,
+                                           assign_matrices, materialize_dist_muon_buckets)
+    from flex_shard_b200.placements import BlockShard
+    from tests.common import FakeMesh
+
+    a = assign_matrices((AssignmentGroup((WholeMatrixSpec("attention", 100),)),
+                         AssignmentGroup((WholeMatrixSpec("ff0", 60), WholeMatrixSpec("ff1", 60)))), num_ranks=2)
+    assert a.rank_by_matrix["attention"] == 0 and {a.rank_by_matrix["ff0"], a.rank_by_matrix["ff1"]} == {0, 1}
+    q, w = AssignmentGroup((WholeMatrixSpec("q", 100),)), AssignmentGroup((WholeMatrixSpec("w", 60),))
+    assert assign_matrices((q, w), num_ranks=2).rank_by_matrix == {"q": 0, "w": 1}
+    assert assign_matrices((w, q), num_ranks=2).rank_by_matrix == {"w": 0, "q": 1}
+    with pytest.raises(ValueError, match="Duplicate assignment name"):
+        assign_matrices((q, q), num_ranks=2)
+    b = assign_matrices((AssignmentGroup((WholeMatrixSpec("matrix", 100),),
+                                         (MatrixBlockGroupSpec("heads", 2, 60, (0, 1)),)),), num_ranks=2)
+    assert b.rank_by_matrix == {"matrix": 0} and b.blocks_per_rank_by_group == {"heads": (0, 2)}
+    # counts follow the order of eligible_ranks, and blocks stay inside them
+    c = assign_matrices((AssignmentGroup((), (MatrixBlockGroupSpec("heads", 5, 10, (3, 1)),)),), num_ranks=4)
+    assert c.blocks_per_rank_by_group == {"heads": (3, 2)}
+    # with hosts, the two heaviest matrices land on different hosts
+    d = assign_matrices((AssignmentGroup(tuple(WholeMatrixSpec(f"m{i}", 100 - i) for i in range(4))),), num_ranks=4,
+                        hosts=(0, 0, 1, 1))
+    assert {d.rank_by_matrix["m0"] // 2, d.rank_by_matrix["m1"] // 2} == {0, 1}
+    for bad in ((AssignmentGroup((WholeMatrixSpec("z", 0),)),),
+                (AssignmentGroup((), (MatrixBlockGroupSpec("h", 2, 8, (0, 0)),)),),
+                (AssignmentGroup((), (MatrixBlockGroupSpec("h", 2, 8, (5,)),)),)):
+        with pytest.raises(ValueError):
+            assign_matrices(bad, num_ranks=2)
+    with pytest.raises(ValueError, match="hosts"):
+        assign_matrices((q,), num_ranks=2, hosts=(0,))
+
+    named = [("l0.w", nn.Parameter(torch.zeros(16, 8))), ("l0.heads", nn.Parameter(torch.zeros(32, 8)))]
+
+    def custom(groups, *, num_ranks):
+        return MatrixAssignment({"l0.w": 1}, {"l0.heads": (1, 3)})
+
+    specs = materialize_dist_muon_buckets(named, FakeMesh(2), initial=[], blocks=[["l0"]], final=[],
+                                          num_blocks_of=lambda n, p: 4 if n.endswith("heads") else 1,
+                                          assignment_fn=custom)
+    pls = specs[0].placement_fn(named, FakeMesh(2))
+    assert pls["l0.w"].member.segments[0][0] == 1
+    assert isinstance(pls["l0.heads"].member, BlockShard) and tuple(pls["l0.heads"].member.blocks_per_rank) == (1, 3)
