@@ -3,9 +3,45 @@ mesh, and the ``placement_fn`` that stores a matrix in whole head blocks (so tha
 own heads with no exchange). Parity: ``dist_muon/placement.py:26-222`` of the reference."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 from ..placements.block_shard import BlockShard
 from ..placements.mixed_bucket import make_mixed_placement_fn
 from ..placements.shard import shard_placement_fn
+
+
+@dataclass(frozen=True)
+class BlockShardPlan:
+    """Equal matrices packed one under the other along dim 0 of a 2-D parameter (attention heads, say):
+    ``num_matrices`` of them.  The checks name the parameter.  Parity: ``dist_muon/placement.py:26-66`` of the
+    reference."""
+
+    num_matrices: int
+
+    def __post_init__(self):
+        if isinstance(self.num_matrices, bool) or not isinstance(self.num_matrices, int) or self.num_matrices <= 0:
+            raise ValueError("num_matrices must be a positive integer")
+
+    def validate_parameter(self, fqn: str, param) -> None:
+        if param.ndim != 2:
+            raise ValueError(f"matrix-sharded parameter {fqn!r} must be 2-D, but has shape {tuple(param.shape)}")
+        if param.shape[0] % self.num_matrices:
+            raise ValueError(f"matrix-sharded parameter {fqn!r} must have a dim 0 divisible by its "
+                             f"{self.num_matrices} matrices, but has shape {tuple(param.shape)}")
+
+    def matrix_rows(self, fqn: str, param) -> int:
+        self.validate_parameter(fqn, param)
+        return param.shape[0] // self.num_matrices
+
+    def validate_matrix_extent(self, fqn: str, param, expected_matrix_extent: int) -> None:
+        rows = self.matrix_rows(fqn, param)
+        if rows != expected_matrix_extent:
+            raise ValueError(f"matrix-sharded parameter {fqn!r} has matrices of {rows} rows, expected "
+                             f"{expected_matrix_extent}")
+
+    def blocks_per_rank(self, world_size: int) -> tuple[int, ...]:
+        """Whole matrices per rank when they are dealt out as evenly as possible."""
+        return get_dim0_block_partitions(self.num_matrices, world_size)
 
 
 def get_mesh_rank_groups(world_size: int, group_size: int) -> list[list[int]]:
@@ -43,5 +79,5 @@ def make_bucketed_block_placement_fn(num_blocks_of):
 
 
 shard0_placement_fn = shard_placement_fn(0)
-__all__ = ["get_mesh_rank_groups", "get_strided_rank_groups", "get_dim0_block_partitions", "make_mixed_placement_fn",
+__all__ = ["BlockShardPlan", "get_mesh_rank_groups", "get_strided_rank_groups", "get_dim0_block_partitions", "make_mixed_placement_fn",
            "shard0_placement_fn", "make_bucketed_block_placement_fn"]

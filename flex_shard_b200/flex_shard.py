@@ -262,10 +262,16 @@ def _hook_modules_for(root: nn.Module, spec: BucketSpec, fqns: Sequence[str]):
     return [mod], False, name or "<root>"
 
 
-def _unwrap_placements(result) -> dict:
+def _unwrap_placements(result, named=()) -> dict:
     """A placement function maps FQN -> Placement; the reference's functions return one-element tuples
-    ``(placement,)`` (one entry per mesh dimension of a 1-D mesh), which are accepted as well."""
-    return {f: (v[0] if isinstance(v, (tuple, list)) and len(v) == 1 else v) for f, v in dict(result).items()}
+    ``(placement,)`` (one entry per mesh dimension of a 1-D mesh), which are accepted as well.  A placement that
+    describes the whole bucket (``BucketedOwned`` built from ``{fqn: segments}``) is narrowed to each parameter."""
+    out = {f: (v[0] if isinstance(v, (tuple, list)) and len(v) == 1 else v) for f, v in dict(result).items()}
+    shapes = {f: tuple(getattr(p, "_fsb_global_shape", None) or p.shape) for f, p in named}
+    for f, v in out.items():
+        if f in shapes and hasattr(v, "for_param"):
+            out[f] = v.for_param(f, shapes[f])
+    return out
 
 
 def _validate_bucket(spec: BucketSpec, named, placements, comm) -> None:
@@ -359,7 +365,7 @@ def flex_shard(module: nn.Module, buckets: Sequence[BucketSpec], *,
         if spec.fsdp2_compatible:
             group = fsdp2_param_order(module, group)
         fn = spec.placement_fn or shard_placement_fn(0)
-        placements = _unwrap_placements(fn(group, spec.mesh))
+        placements = _unwrap_placements(fn(group, spec.mesh), group)
         _validate_bucket(spec, group, placements, comm)
         # every name of a tied parameter counts: the bucket must be gathered around all the modules that use it
         all_names = [n for f, _ in group for n in (f, *shared.get(f, ()))]
@@ -421,7 +427,7 @@ def relayout_bucket(module: nn.Module, storage: ShardedBucketStorage, placement_
             from .placement_contract import set_partial_grad_group
 
             set_partial_grad_group(p, info.partial_grad_group)
-    placements = _unwrap_placements(placement_fn(named, storage.mesh))
+    placements = _unwrap_placements(placement_fn(named, storage.mesh), named)
     _validate_bucket(storage.spec, named, placements, comm)
     shared = {info.fqn: info.shared_fqns for info in storage.infos}
     new = ShardedBucketStorage.from_bucket(storage.spec, named, placements, storage.mesh, comm, storage.device,

@@ -13,7 +13,10 @@ from .bucketed_block_shard import BucketedBlockShard, FlatBucketPlan, make_bucke
 from .mixed_bucket import MixedBucketPlacement, ShardSlice, make_mixed_placement_fn
 from .owned import (
     BucketedOwned,
+    BucketedOwnedSegmentSpec,
     make_bucketed_owned_expert_block_placement_fn,
+    make_bucketed_owned_expert_block_segments,
+    make_bucketed_owned_full_param_segments,
     make_bucketed_owned_full_param_placement_fn,
     newton_schulz_cost,
 )
@@ -34,7 +37,8 @@ def per_param_placements(named_params, mesh):
 __all__ = [
     "BlockShard", "BlockwiseQuantBucketedBlockShard", "Fp8BucketedBlockShard", "make_fp8_bucketed_block_shard_placement_fn",
     "Mxfp8BucketedBlockShard", "make_mxfp8_bucketed_block_shard_placement_fn",
-    "partition_min_max", "plan_row_ranges", "BucketedBlockShard", "BucketedOwned", "FlatBucketPlan", "make_bucketed_block_shard_placement_fn", "MixedBucketPlacement", "Shard", "ShardSlice",
+    "partition_min_max", "plan_row_ranges", "BucketedBlockShard", "BucketedOwned", "BucketedOwnedSegmentSpec",
+    "make_bucketed_owned_expert_block_segments", "make_bucketed_owned_full_param_segments", "FlatBucketPlan", "make_bucketed_block_shard_placement_fn", "MixedBucketPlacement", "Shard", "ShardSlice",
     "make_block_shard_placement_fn", "make_bucketed_owned_expert_block_placement_fn",
     "make_bucketed_owned_full_param_placement_fn", "make_mixed_placement_fn", "newton_schulz_cost",
     "shard_placement_fn", "make_shard_placement_fn", "per_param_placements", "make_bucketed_block_placement_fn",

@@ -12,14 +12,33 @@ loads ``:393-495``, expert-block segments ``:505-583``).
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 from typing import Mapping, Sequence
 
 from ..utils.validation import assign_to_hosts_then_ranks, mesh_rank_hosts
 from .sliced import Piece, SlicedPlacement
 
 
+@dataclass(frozen=True)
+class BucketedOwnedSegmentSpec:
+    """A flat slice of one parameter and the rank that owns it: the bucket-level description of ownership
+    (``{fqn: [specs]}``) that ``BucketedOwned`` also accepts.  ``param_offset`` and ``numel`` count elements of the
+    row-major parameter and must cover whole dim-0 rows; ``storage_order`` orders the owners' storage.
+    Parity: ``custom_placements/owned.py:39-48`` of the reference."""
+
+    name: str
+    fqn: str
+    param_offset: int
+    numel: int
+    owner_rank: int
+    storage_order: int = 0
+
+
 class BucketedOwned(SlicedPlacement):
     """One parameter's ownership: ``segments`` = ((rank, start, length), ...) over dim 0.
+
+    Also takes the bucket-level form ``{fqn: [BucketedOwnedSegmentSpec, ...]}``: one object for every parameter of
+    the bucket, from which ``flex_shard`` takes each parameter's own placement (``for_param``).
 
     ``view_kind == "full_param"``: a single segment covering the parameter on its owner.
     ``view_kind == "expert_block"``: dim-0 slabs (e.g. experts of a stacked weight) with
@@ -28,11 +47,20 @@ class BucketedOwned(SlicedPlacement):
 
     owner_style = True
 
-    def __init__(self, segments: Sequence[tuple[int, int, int]], view_kind: str = "full_param"):
+    def __init__(self, segments, view_kind: str = "full_param"):
         if view_kind not in ("full_param", "expert_block"):
             raise ValueError(f"unknown view_kind {view_kind!r}")
-        self.segments = tuple((int(r), int(s), int(l)) for r, s, l in segments)
         self.view_kind = view_kind
+        self.segments_by_fqn = None
+        if isinstance(segments, Mapping):
+            for fqn, specs in segments.items():
+                if not specs or any(not isinstance(sp, BucketedOwnedSegmentSpec) or sp.fqn != fqn for sp in specs):
+                    raise ValueError(f"segments of {fqn!r} must be a non-empty list of BucketedOwnedSegmentSpec "
+                                     "naming that parameter")
+            self.segments_by_fqn = {f: tuple(specs) for f, specs in segments.items()}
+            self.segments, self._extent = (), 0
+            return
+        self.segments = tuple((int(r), int(s), int(l)) for r, s, l in segments)
         pos = 0
         for _, s, l in sorted(self.segments, key=lambda t: t[1]):
             if s != pos or l <= 0:
@@ -40,11 +68,30 @@ class BucketedOwned(SlicedPlacement):
             pos += l
         self._extent = pos
 
+    def for_param(self, fqn: str, shape: Sequence[int]) -> "BucketedOwned":
+        """The placement of one parameter: this object itself, or, for the bucket-level form, the dim-0 row
+        segments that the parameter's flat slices amount to."""
+        if self.segments_by_fqn is None:
+            return self
+        specs = self.segments_by_fqn.get(fqn)
+        if specs is None:
+            raise ValueError(f"BucketedOwned has no segments for {fqn!r} (it describes {sorted(self.segments_by_fqn)})")
+        row = math.prod(shape[1:]) if len(shape) > 1 else 1
+        rows = []
+        for sp in sorted(specs, key=lambda sp: sp.param_offset):
+            if sp.param_offset % row or sp.numel % row or sp.numel <= 0:
+                raise ValueError(f"segment {sp.name!r} of {fqn!r} (offset {sp.param_offset}, {sp.numel} elements) does "
+                                 f"not cover whole dim-0 rows of {row} elements")
+            rows.append((sp.owner_rank, sp.param_offset // row, sp.numel // row))
+        return BucketedOwned(rows, self.view_kind)
+
     def __eq__(self, other):
-        return isinstance(other, BucketedOwned) and (other.segments, other.view_kind) == (self.segments, self.view_kind)
+        return isinstance(other, BucketedOwned) and (other.segments, other.view_kind, other.segments_by_fqn) == (
+            self.segments, self.view_kind, self.segments_by_fqn)
 
     def __hash__(self):
-        return hash(("BucketedOwned", self.segments, self.view_kind))
+        by_fqn = None if self.segments_by_fqn is None else tuple(sorted(self.segments_by_fqn.items()))
+        return hash(("BucketedOwned", self.segments, self.view_kind, by_fqn))
 
     def __repr__(self):
         return f"BucketedOwned(segments={self.segments}, view_kind={self.view_kind!r})"
@@ -54,6 +101,8 @@ class BucketedOwned(SlicedPlacement):
         return tuple(sorted({r for r, _, _ in self.segments}))
 
     def pieces(self, global_shape, rank, world_size):
+        if self.segments_by_fqn is not None:
+            raise ValueError("a bucket-level BucketedOwned describes several parameters: use for_param(fqn, shape)")
         if global_shape[0] != self._extent:
             raise ValueError(f"segments cover {self._extent} rows, the parameter has {global_shape[0]}")
         mine = sorted((s, l) for r, s, l in self.segments if r == rank)
@@ -117,6 +166,58 @@ def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_
 
     fn.reset_loads = carried.clear
     return fn
+
+
+def make_bucketed_owned_full_param_segments(named_params, world_size: int, *, hosts: Sequence[int] | None = None,
+                                            carried_loads: Sequence[float] | None = None
+                                            ) -> dict[str, list[BucketedOwnedSegmentSpec]]:
+    """One whole-parameter segment per parameter; owners by longest-processing-time on the element count, hosts
+    first when ``hosts`` gives each rank's host, on top of ``carried_loads`` (each rank's elements from earlier
+    buckets; a list is updated in place).  Parity: ``custom_placements/owned.py:425-462`` of the reference."""
+    if world_size <= 0:
+        raise ValueError(f"world_size must be positive, got {world_size}")
+    if hosts is not None and len(hosts) != world_size:
+        raise ValueError(f"hosts must give each of the {world_size} ranks a host")
+    if carried_loads is not None and len(carried_loads) != world_size:
+        raise ValueError(f"carried_loads must give each of the {world_size} ranks a load")
+    named_params = list(named_params)
+    loads = carried_loads if isinstance(carried_loads, list) else list(carried_loads or [0.0] * world_size)
+    owners = assign_to_hosts_then_ranks([float(p.numel()) for _, p in named_params],
+                                        list(hosts) if hosts is not None else [0] * world_size, loads)
+    return {f: [BucketedOwnedSegmentSpec(f"{f}#full", f, 0, p.numel(), r, order)]
+            for order, ((f, p), r) in enumerate(zip(named_params, owners))}
+
+
+def make_bucketed_owned_expert_block_segments(named_params, world_size: int, *,
+                                              suffix_order: tuple[str, ...] = (".w1", ".w3", ".w2")
+                                              ) -> dict[str, list[BucketedOwnedSegmentSpec]]:
+    """One segment per expert of stacked expert weights ``[E, ...]``; experts go to the ranks in contiguous runs, as
+    evenly as possible, the same run for every weight; ``suffix_order`` orders the weights of one expert in the
+    owner's storage.  Parity: ``custom_placements/owned.py:505-583`` of the reference."""
+    if world_size <= 0:
+        raise ValueError(f"world_size must be positive, got {world_size}")
+    if not suffix_order:
+        raise ValueError("suffix_order must contain at least one suffix")
+    named_params = list(named_params)
+    bad = [(f, tuple(p.shape)) for f, p in named_params if p.dim() < 3 or not f.endswith(tuple(suffix_order))]
+    if bad:
+        raise ValueError(f"expert-block segments need stacked weights of at least 3 dims whose names end in one of "
+                         f"{suffix_order}: {bad}")
+    if not named_params:
+        return {}
+    E = named_params[0][1].shape[0]
+    if any(p.shape[0] != E for _, p in named_params):
+        raise ValueError("stacked expert weights of one bucket must hold the same number of experts")
+    per = [E // world_size + (1 if r < E % world_size else 0) for r in range(world_size)]
+    owner_of = [r for r, n in enumerate(per) for _ in range(n)]
+    rank_of_suffix = {sfx: i for i, sfx in enumerate(suffix_order)}
+    out: dict[str, list[BucketedOwnedSegmentSpec]] = {}
+    for f, p in named_params:
+        slab = p.numel() // E
+        which = next(rank_of_suffix[sfx] for sfx in suffix_order if f.endswith(sfx))
+        out[f] = [BucketedOwnedSegmentSpec(f"{f}#expert{e}", f, e * slab, slab, owner_of[e],
+                                           e * len(suffix_order) + which) for e in range(E)]
+    return out
 
 
 def make_bucketed_owned_expert_block_placement_fn(experts_per_rank: Sequence[int] | None = None):

@@ -37,6 +37,13 @@ def _placement_fn(kind):
         from flex_shard_b200.placements import make_bucketed_block_shard_placement_fn
 
         return make_bucketed_block_shard_placement_fn((1, 3))
+    if kind == "owned_segments":    # the bucket-level form: one BucketedOwned built from {fqn: segment specs}
+        from flex_shard_b200.placements import make_bucketed_owned_full_param_segments
+
+        def fn(named, mesh):
+            whole = BucketedOwned(make_bucketed_owned_full_param_segments(named, 2))
+            return {f: (whole,) for f, _ in named}
+        return fn
     if kind == "mixed_owned":      # every member whole on one owner: gradients accumulate in one mirror buffer
         return lambda named, mesh: {f: MixedBucketPlacement(BucketedOwned(((i % 2, 0, p.shape[0]),)))
                                     for i, (f, p) in enumerate(named)}
@@ -64,7 +71,8 @@ def _train(rank, world, kind, steps):
     ref.load_state_dict(model.state_dict())
     flex_shard(model, [BucketSpec(["*"], placement_fn=_placement_fn(kind))])
     st = model.sharded_bucket_storages[0]
-    assert st.placement.reduces_grads_in_param_layout(st.infos) == (kind in ("owned", "mixed_owned", "flat", "flat_uneven"))
+    assert st.placement.reduces_grads_in_param_layout(st.infos) == (
+        kind in ("owned", "owned_segments", "mixed_owned", "flat", "flat_uneven"))
     opt = torch.optim.SGD(model.parameters(), lr=0.1)
     ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
     for s in range(steps):
@@ -85,7 +93,7 @@ def _train(rank, world, kind, steps):
     return err, sizes, model.sharded_bucket_storages[0].total_bytes
 
 
-@pytest.mark.parametrize("kind", ["block", "owned", "mixed", "mixed_owned", "flat", "flat_uneven"])
+@pytest.mark.parametrize("kind", ["block", "owned", "owned_segments", "mixed", "mixed_owned", "flat", "flat_uneven"])
 def test_sliced_placements_train_like_unsharded(kind):
     res = run_ranks(_train, 2, kind, 3)
     for err, sizes, nbytes in res:
@@ -95,6 +103,48 @@ def test_sliced_placements_train_like_unsharded(kind):
         total = sum(p.numel() for p in MLP().parameters())
         assert sum(res[0][1]) + sum(res[1][1]) == total
         assert all(a == 0 or b == 0 for a, b in zip(res[0][1], res[1][1]))
+
+
+def test_owner_segment_specs():
+    """The bucket-level description of ownership: whole parameters by element count (hosts first, carried loads),
+    experts of stacked weights in contiguous runs, and the narrowing to one parameter's dim-0 rows.
+    Parity: ``custom_placements/owned.py:39-48, 425-583`` of the reference."""
+    from flex_shard_b200.placements import (BucketedOwned, BucketedOwnedSegmentSpec,
+                                            make_bucketed_owned_expert_block_segments,
+                                            make_bucketed_owned_full_param_segments)
+
+    named = [("big", torch.zeros(8, 8)), ("mid", torch.zeros(4, 8)), ("small", torch.zeros(8))]
+    segs = make_bucketed_owned_full_param_segments(named, 2)
+    assert {f: (s[0].owner_rank, s[0].param_offset, s[0].numel, s[0].storage_order) for f, s in segs.items()} == {
+        "big": (0, 0, 64, 0), "mid": (1, 0, 32, 1), "small": (1, 0, 8, 2)}
+    loads = [100.0, 0.0]
+    carried = make_bucketed_owned_full_param_segments(named[:1], 2, carried_loads=loads)
+    assert carried["big"][0].owner_rank == 1 and loads == [100.0, 64.0]
+    for kwargs in (dict(hosts=(0,)), dict(carried_loads=(0, 0, 0))):
+        with pytest.raises(ValueError):
+            make_bucketed_owned_full_param_segments(named, 2, **kwargs)
+    whole = BucketedOwned(segs)
+    assert whole.for_param("mid", (4, 8)).segments == ((1, 0, 4),)
+    with pytest.raises(ValueError, match="no segments"):
+        whole.for_param("other", (4, 8))
+    with pytest.raises(ValueError, match="for_param"):
+        whole.pieces((4, 8), 0, 2)
+    ragged = BucketedOwned({"w": [BucketedOwnedSegmentSpec("w#0", "w", 0, 12, 0)]})
+    with pytest.raises(ValueError, match="whole dim-0 rows"):
+        ragged.for_param("w", (4, 8))
+
+    experts = [("moe.w1", torch.zeros(5, 4, 2)), ("moe.w2", torch.zeros(5, 2, 4))]
+    es = make_bucketed_owned_expert_block_segments(experts, 2)
+    assert [s.owner_rank for s in es["moe.w1"]] == [0, 0, 0, 1, 1] == [s.owner_rank for s in es["moe.w2"]]
+    assert [(s.param_offset, s.numel) for s in es["moe.w1"]][:2] == [(0, 8), (8, 8)]
+    # one expert's weights sit together in the owner's storage, in suffix order (.w1, .w3, .w2)
+    assert es["moe.w1"][1].storage_order < es["moe.w2"][1].storage_order < es["moe.w1"][2].storage_order
+    per_param = BucketedOwned(es, view_kind="expert_block").for_param("moe.w2", (5, 2, 4))
+    assert per_param.view_kind == "expert_block" and per_param.pieces((5, 2, 4), 1, 2)[0].start == 3
+    with pytest.raises(ValueError, match="at least 3 dims"):
+        make_bucketed_owned_expert_block_segments([("moe.w1", torch.zeros(4, 2))], 2)
+    with pytest.raises(ValueError, match="suffix"):
+        make_bucketed_owned_expert_block_segments(experts, 2, suffix_order=())
 
 
 def test_owner_rows_hold_no_padding_golden():
