@@ -4,6 +4,8 @@ from .blockwise_quant import (
     BlockwiseQuantBucketedBlockShard,
     Fp8BucketedBlockShard,
     Mxfp8BucketedBlockShard,
+    BlockwiseFp8WeightFactory,
+    BlockwiseMxfp8WeightFactory,
     make_mxfp8_bucketed_block_shard_placement_fn,
     make_fp8_bucketed_block_shard_placement_fn,
     partition_min_max,
@@ -43,4 +45,5 @@ __all__ = [
     "make_bucketed_owned_full_param_placement_fn", "make_mixed_placement_fn", "newton_schulz_cost",
     "shard_placement_fn", "make_shard_placement_fn", "per_param_placements", "make_bucketed_block_placement_fn",
     "make_fp8_bucketed_block_placement_fn", "make_mxfp8_bucketed_block_placement_fn",
+    "BlockwiseFp8WeightFactory", "BlockwiseMxfp8WeightFactory",
 ]

@@ -22,7 +22,7 @@ only and no tile is split between ranks.
 from __future__ import annotations
 
 import math
-from typing import Callable, Sequence
+from typing import Callable, Protocol, Sequence
 
 import torch
 
@@ -84,11 +84,16 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
     shard_block_rows = 128
     allows_mixed_dtypes = False
 
-    def __init__(self, row_ranges: Sequence[tuple[int, int]]):
+    def __init__(self, row_ranges: Sequence[tuple[int, int]], weight_factory: Callable | None = None):
+        if weight_factory is not None and not callable(weight_factory):
+            raise TypeError("weight_factory must be callable")
         self.row_ranges = tuple((int(a), int(b)) for a, b in row_ranges)
+        # builds the tensor the consumer sees from the gathered operands (default: this library's wrapper class)
+        self.weight_factory = weight_factory
 
     def __eq__(self, other):
-        return type(other) is type(self) and other.row_ranges == self.row_ranges
+        return (type(other) is type(self) and other.row_ranges == self.row_ranges
+                and other.weight_factory is self.weight_factory)
 
     def __hash__(self):
         return hash((type(self).__name__, self.row_ranges))
@@ -125,7 +130,7 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
     def quantize_into(self, w: torch.Tensor, qdata_bytes: torch.Tensor, scale_bytes: torch.Tensor) -> None:
         raise NotImplementedError
 
-    def make_weight(self, qdata_bytes: torch.Tensor, scale_bytes: torch.Tensor, shape, dtype):
+    def make_weight(self, qdata_bytes: torch.Tensor, scale_bytes: torch.Tensor, shape, dtype, requires_grad=True):
         raise NotImplementedError
 
     # ---- payload geometry
@@ -246,7 +251,8 @@ class BlockwiseQuantBucketedBlockShard(SlicedPlacement):
             # compact buffer with one segment-copy launch; the weight wrappers (which may derive further
             # scale tensors from the gathered bytes) are built afterwards
             run_segment_ops(copies)
-            outs = [pl.make_weight(q, sc, info.global_shape, info.param_dtype) for pl, q, sc, info in outs]
+            outs = [pl.make_weight(q, sc, info.global_shape, info.param_dtype, info.requires_grad)
+                    for pl, q, sc, info in outs]
         if not prepared.extra.get("cached") and "key" in prepared.extra:
             self._payload_cache = (prepared.extra["key"], recv)
         return PlacementUnshardResult(outs, keepalive=[])
@@ -274,14 +280,19 @@ class Fp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
         s = scale_bytes.view(torch.float32).view(-(-rows // 128), -(-cols // 128))
         quantize_blockwise(w.contiguous(), out_q=q, out_scale=s)
 
-    def make_weight(self, qdata_bytes, scale_bytes, shape, dtype):
+    def make_weight(self, qdata_bytes, scale_bytes, shape, dtype, requires_grad=True):
         from ..ops.fp8 import FP8
         from ..quant.weight import BlockwiseFp8Weight
 
         rows, cols = math.prod(shape[:-1]), shape[-1]
-        return BlockwiseFp8Weight(qdata_bytes.view(FP8).view(rows, cols),
-                                  scale_bytes.view(torch.float32).view(-(-rows // 128), -(-cols // 128)),
-                                  shape, dtype)
+        q = qdata_bytes.view(FP8).view(rows, cols)
+        scale = scale_bytes.view(torch.float32).view(-(-rows // 128), -(-cols // 128))
+        if self.weight_factory is not None:
+            # the consumer's own tensor: data in the parameter's shape, one reciprocal scale per 128x128 block of
+            # the [prod(shape[:-1]), shape[-1]] matrix; it must view (not copy) both, which are refilled in place
+            return self.weight_factory(q.view(tuple(shape)), scale, self.block_size, orig_dtype=dtype,
+                                       requires_grad=requires_grad)
+        return BlockwiseFp8Weight(q, scale, shape, dtype)
 
 
 class Mxfp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
@@ -294,10 +305,10 @@ class Mxfp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
 
     block_size = 32
 
-    def __init__(self, row_ranges, scaling_mode: str = "rceil"):
+    def __init__(self, row_ranges, scaling_mode: str = "rceil", weight_factory: Callable | None = None):
         if scaling_mode != "rceil":
             raise ValueError(f"unsupported MXFP8 scaling mode {scaling_mode!r} (only 'rceil': round the scale up)")
-        super().__init__(row_ranges)
+        super().__init__(row_ranges, weight_factory)
         self.scaling_mode = scaling_mode
 
     def qdata_nbytes(self, rows, cols):
@@ -313,13 +324,18 @@ class Mxfp8BucketedBlockShard(BlockwiseQuantBucketedBlockShard):
         mx_quantize_weight(w.contiguous(), out_q=qdata_bytes.view(FP8).view(rows, cols),
                            out_e=scale_bytes.view(-(-rows // 32), -(-cols // 32)))
 
-    def make_weight(self, qdata_bytes, scale_bytes, shape, dtype):
+    def make_weight(self, qdata_bytes, scale_bytes, shape, dtype, requires_grad=True):
         from ..ops.mxfp8 import FP8
         from ..quant.weight import BlockwiseMxfp8Weight
 
         rows, cols = math.prod(shape[:-1]), shape[-1]
-        return BlockwiseMxfp8Weight.from_tile_exponents(qdata_bytes.view(FP8).view(rows, cols),
-                                                        scale_bytes.view(-(-rows // 32), -(-cols // 32)), shape, dtype)
+        w = BlockwiseMxfp8Weight.from_tile_exponents(qdata_bytes.view(FP8).view(rows, cols),
+                                                     scale_bytes.view(-(-rows // 32), -(-cols // 32)), shape, dtype)
+        if self.weight_factory is not None:
+            # the consumer's own tensor from the data (parameter's shape) and the two blocked scale tensors
+            return self.weight_factory(w.qdata.view(tuple(shape)), w.fwd_scale, w.dgrad_scale, orig_dtype=dtype,
+                                       requires_grad=requires_grad)
+        return w
 
 
 def plan_row_ranges(shapes: Sequence[tuple[int, ...]], world_size: int, block_rows: int,
@@ -359,9 +375,30 @@ def _check_quantisable(fqn: str, p, block_rows: int, who: str) -> None:
                          f"of {block_rows} rows, so that no quantisation block straddles two of them")
 
 
-def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
+class BlockwiseFp8WeightFactory(Protocol):
+    """``weight_factory`` of the FP8 placement: builds the consumer's tensor from the gathered operands, which it
+    must view rather than copy.  Parity: ``custom_placements/fp8_bucketed_block_shard.py:43-65`` of the reference."""
+
+    def __call__(self, fp8_data: torch.Tensor, recip_scale: torch.Tensor, block_size: int, *,
+                 orig_dtype: torch.dtype, requires_grad: bool) -> torch.Tensor: ...
+
+
+class BlockwiseMxfp8WeightFactory(Protocol):
+    """``weight_factory`` of the MXFP8 placement (data, forward-orientation and input-gradient-orientation blocked
+    scales).  Parity: ``custom_placements/mxfp8_bucketed_block_shard.py:68-90`` of the reference."""
+
+    def __call__(self, fp8_data: torch.Tensor, fwd_scale: torch.Tensor, dgrad_scale: torch.Tensor, *,
+                 orig_dtype: torch.dtype, requires_grad: bool) -> torch.Tensor: ...
+
+
+def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128, *, weight_factory=None,
+                                               fp8_dtype: torch.dtype = torch.float8_e4m3fn):
     """Placement function for FP8 buckets: 2-D weights ``[out, in]`` or stacked weights ``[*stack, out, in]``
-    whose ``out`` is a multiple of the block size."""
+    whose ``out`` is a multiple of the block size.  ``weight_factory``: see ``BlockwiseFp8WeightFactory``."""
+    if block_size != 128:
+        raise ValueError(f"the FP8 kernels quantise in 128x128 blocks, got block_size={block_size}")
+    if fp8_dtype != torch.float8_e4m3fn:
+        raise ValueError(f"the FP8 kernels use torch.float8_e4m3fn, got {fp8_dtype}")
 
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
@@ -372,14 +409,15 @@ def make_fp8_bucketed_block_shard_placement_fn(block_size: int = 128):
             _check_quantisable(f, p, block_size, "Fp8BucketedBlockShard")
         cost = lambda rows, cols: rows * cols + -(-rows // block_size) * -(-cols // block_size) * 4
         ranges = plan_row_ranges(shapes, W, block_size, cost)
-        return {f: Fp8BucketedBlockShard(ranges[i]) for i, (f, _) in enumerate(named_params)}
+        return {f: Fp8BucketedBlockShard(ranges[i], weight_factory) for i, (f, _) in enumerate(named_params)}
 
     return fn
 
 
-def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil"):
+def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil", *, weight_factory=None):
     """Placement function for MXFP8 buckets: 2-D weights (rows handed out in whole 128-row units) or stacked
-    weights ``[*stack, out, in]`` with ``out`` a multiple of 128 (handed out matrix by matrix)."""
+    weights ``[*stack, out, in]`` with ``out`` a multiple of 128 (handed out matrix by matrix).
+    ``weight_factory``: see ``BlockwiseMxfp8WeightFactory``."""
 
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
@@ -390,6 +428,7 @@ def make_mxfp8_bucketed_block_shard_placement_fn(scaling_mode: str = "rceil"):
             _check_quantisable(f, p, 128, "Mxfp8BucketedBlockShard")
         cost = lambda rows, cols: rows * cols + -(-rows // 32) * -(-cols // 32)
         ranges = plan_row_ranges(shapes, W, 128, cost)
-        return {f: Mxfp8BucketedBlockShard(ranges[i], scaling_mode) for i, (f, _) in enumerate(named_params)}
+        return {f: Mxfp8BucketedBlockShard(ranges[i], scaling_mode, weight_factory)
+                for i, (f, _) in enumerate(named_params)}
 
     return fn

@@ -4,6 +4,7 @@ from .linear import (
     FlexShardFloat8BlockwiseStackedLinear,
     FlexShardMxfp8BlockwiseLinear,
     FlexShardPrequantizedLinear,
+    PrequantizedLinearGemms,
     convert_to_flex_shard_float8_blockwise_linear,
     convert_to_flex_shard_mxfp8_blockwise_linear,
     convert_to_flex_shard_prequantized_linear,

@@ -1,5 +1,6 @@
 """Fp8BucketedBlockShard on 2 gloo ranks: planner goldens, FP8 payload smaller than bf16, gathered
 weight bitwise equal to quantise-after-gather, training equal to the unsharded twin."""
+import pytest
 import torch
 import torch.nn as nn
 
@@ -39,15 +40,28 @@ def _init(m):
             p.copy_((0.05 * torch.randn(p.shape, generator=g)).to(p.dtype))
 
 
-def _run(rank, world, steps):
+_factory_calls = []
+
+
+def _consumer_weight(fp8_data, recip_scale, block_size, *, orig_dtype, requires_grad):
+    """A ``weight_factory``: the consumer builds its own tensor from the gathered operands (views, not copies)."""
+    from flex_shard_b200.quant import BlockwiseFp8Weight
+
+    _factory_calls.append((tuple(fp8_data.shape), tuple(recip_scale.shape), block_size, orig_dtype, requires_grad))
+    rows = fp8_data.numel() // fp8_data.shape[-1]
+    return BlockwiseFp8Weight(fp8_data.view(rows, fp8_data.shape[-1]), recip_scale, fp8_data.shape, orig_dtype)
+
+
+def _run(rank, world, steps, factory=False):
     from flex_shard_b200 import BucketSpec, flex_shard
-    from flex_shard_b200.placements import make_fp8_bucketed_block_shard_placement_fn
+    from flex_shard_b200.placements import make_fp8_bucketed_block_placement_fn
     from flex_shard_b200.ops.fp8 import quantize_blockwise
 
     model, twin = Net(), Net()
     _init(model)
     _init(twin)
-    flex_shard(model, [BucketSpec(["*"], placement_fn=make_fp8_bucketed_block_shard_placement_fn())])
+    fn = make_fp8_bucketed_block_placement_fn(weight_factory=_consumer_weight if factory else None)
+    flex_shard(model, [BucketSpec(["*"], placement_fn=fn)])
     st = model.sharded_bucket_storages[0]
     sizes = [sp.numel() * 2 for sp in st.sharded_params]
     opt = torch.optim.SGD(model.parameters(), lr=0.05)
@@ -76,12 +90,19 @@ def _run(rank, world, steps):
         topt.zero_grad()
     out["bf16_bytes"] = sum(p.numel() for p in twin.parameters()) * 2 // world
     out["master_dtype"] = str(st.sharded_params[0].dtype)
+    out["factory_calls"] = sorted(set(_factory_calls))
     return out
 
 
-def test_fp8_bucket_trains_like_gather_then_quantize():
-    res = run_ranks(_run, 2, 3)
+@pytest.mark.parametrize("factory", [False, True])
+def test_fp8_bucket_trains_like_gather_then_quantize(factory):
+    """Also with a consumer's ``weight_factory`` (parity: ``custom_placements/fp8_bucketed_block_shard.py:43-65`` of
+    the reference): it receives the data in the parameter's shape, one scale per 128x128 block, the block size, the
+    compute dtype and whether the parameter trains."""
+    res = run_ranks(_run, 2, 3, factory)
     for r in res:
+        assert r["factory_calls"] == ([((128, 384), (1, 3), 128, torch.bfloat16, True),
+                                       ((384, 256), (3, 2), 128, torch.bfloat16, True)] if factory else [])
         assert all(r["bitwise"]), r
         assert r["equal_logits"][0] is True            # identical weights -> identical logits
         assert r["send_bytes"] < r["bf16_bytes"]       # FP8 + scales is smaller than a bf16 shard

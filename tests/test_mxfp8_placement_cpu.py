@@ -1,6 +1,7 @@
 """Mxfp8BucketedBlockShard on 2 gloo ranks: payload smaller than bf16, gathered weight bitwise equal
 to quantise-after-gather, training equal to the unsharded twin; the MXFP8 linear against a
 high-precision reference; the weight wrapper's invariants."""
+import pytest
 import torch
 import torch.nn as nn
 
@@ -26,15 +27,29 @@ def _init(m):
             p.copy_((0.05 * torch.randn(p.shape, generator=g)).to(p.dtype))
 
 
-def _run(rank, world, steps):
+_factory_calls = []
+
+
+def _consumer_weight(fp8_data, fwd_scale, dgrad_scale, *, orig_dtype, requires_grad):
+    """A ``weight_factory``: the consumer's own tensor from the gathered data and the two blocked scale tensors."""
+    from flex_shard_b200.quant import BlockwiseMxfp8Weight
+
+    _factory_calls.append((tuple(fp8_data.shape), fwd_scale.dtype, dgrad_scale.dtype, orig_dtype, requires_grad))
+    rows = fp8_data.numel() // fp8_data.shape[-1]
+    return BlockwiseMxfp8Weight(fp8_data.view(rows, fp8_data.shape[-1]), fwd_scale, fp8_data.shape, orig_dtype,
+                                dgrad_scale=dgrad_scale)
+
+
+def _run(rank, world, steps, factory=False):
     from flex_shard_b200 import BucketSpec, flex_shard
     from flex_shard_b200.ops.mxfp8 import mx_expand_scales, mx_quantize_weight
-    from flex_shard_b200.placements import make_mxfp8_bucketed_block_shard_placement_fn
+    from flex_shard_b200.placements import make_mxfp8_bucketed_block_placement_fn
 
     model, twin = Net(), Net()
     _init(model)
     _init(twin)
-    flex_shard(model, [BucketSpec(["*"], placement_fn=make_mxfp8_bucketed_block_shard_placement_fn())])
+    fn = make_mxfp8_bucketed_block_placement_fn(weight_factory=_consumer_weight if factory else None)
+    flex_shard(model, [BucketSpec(["*"], placement_fn=fn)])
     st = model.sharded_bucket_storages[0]
     opt = torch.optim.SGD(model.parameters(), lr=0.05)
     topt = torch.optim.SGD(twin.parameters(), lr=0.05)
@@ -64,12 +79,17 @@ def _run(rank, world, steps):
         topt.zero_grad()
     out["bf16_bytes"] = sum(p.numel() for p in twin.parameters()) * 2 // world
     out["master_dtype"] = str(st.sharded_params[0].dtype)
+    out["factory_calls"] = len(_factory_calls)
     return out
 
 
-def test_mxfp8_bucket_trains_like_gather_then_quantize():
-    res = run_ranks(_run, 2, 3)
+@pytest.mark.parametrize("factory", [False, True])
+def test_mxfp8_bucket_trains_like_gather_then_quantize(factory):
+    """Also with a consumer's ``weight_factory`` (parity: ``custom_placements/mxfp8_bucketed_block_shard.py:68-90``
+    of the reference)."""
+    res = run_ranks(_run, 2, 3, factory)
     for r in res:
+        assert (r["factory_calls"] > 0) == factory
         assert all(r["bitwise"]), r
         assert all(r["equal_logits"]), r
         assert r["send_bytes"] < r["bf16_bytes"]
