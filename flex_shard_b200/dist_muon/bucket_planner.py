@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import fnmatch
 from dataclasses import dataclass
-from typing import Mapping, Protocol, Sequence
+from typing import Any, Mapping, Protocol, Sequence
 
 import torch.distributed as dist
 
@@ -77,6 +77,28 @@ class MatrixAssignmentFn(Protocol):
     """A custom balancer: runs on every rank and must give the same answer everywhere."""
 
     def __call__(self, groups: Sequence[AssignmentGroup], *, num_ranks: int) -> MatrixAssignment: ...
+
+
+@dataclass(frozen=True)
+class PackedParameterPlan:
+    """A 2-D parameter that packs ``block_plan.num_matrices`` equal matrices along dim 0 (attention heads); every
+    matrix gets its own owner and the parameter is stored in whole matrices (``BlockShard``)."""
+    fqn: str
+    parameter: Any
+    block_plan: Any      # BlockShardPlan
+
+
+@dataclass(frozen=True)
+class ParameterBucketPlan:
+    """One step of a recipe (a transformer block): ``mixed_fqns`` go into one mixed bucket on the assignment mesh, in
+    which ``owned_parameters`` are whole on an owner, ``packed_parameters`` are stored matrix by matrix and the rest is
+    ``Shard(0)``; ``partitioned_parameters`` (stacked ``[blocks, ...]`` weights that an outer mesh axis already
+    partitions, e.g. experts under expert parallelism) go into a flat block bucket on the partition's own ranks."""
+    mixed_fqns: tuple = ()
+    owned_parameters: tuple = ()
+    packed_parameters: tuple = ()
+    partitioned_parameters: tuple = ()
+    partition_group_name_prefix: str = "partition#"
 
 
 def _assign_groups(groups: Sequence[AssignmentGroup], num_ranks: int, hosts: Sequence[int] | None) -> MatrixAssignment:
@@ -219,15 +241,171 @@ def assign_matrices(groups, num_ranks: int, *, ranks_per_host: int | None = None
     return out
 
 
-def materialize_dist_muon_buckets(named_params, mesh, *, initial: Sequence[str], blocks: Sequence[Sequence[str]],
-                                  final: Sequence[str], is_matrix=None, num_blocks_of=None,
-                                  mp_policy: MixedPrecisionPolicy | None = None, carry_loads: bool = True,
-                                  ranks_per_host: int | None = None, assignment_fn=None) -> list[BucketSpec]:
+def _partition_rank_groups(assignment_mesh, partition_mesh, rank_axis: str, partition_axis: str):
+    """For every partition (index along ``partition_axis``) the ranks that share it, as positions in the flat
+    assignment mesh, ordered along ``rank_axis``."""
+    names = partition_mesh.mesh_dim_names
+    if names is None or set(names) != {rank_axis, partition_axis} or len(names) != 2:
+        raise ValueError(f"the partition mesh must have exactly the axes {rank_axis!r} and {partition_axis!r}, "
+                         f"got {names}")
+    flat = [int(r) for r in assignment_mesh.mesh.flatten().tolist()]
+    grid = partition_mesh.mesh
+    if sorted(int(r) for r in grid.flatten().tolist()) != sorted(flat):
+        raise ValueError("the assignment mesh and the partition mesh must hold the same ranks")
+    position = {g: i for i, g in enumerate(flat)}
+    by_axis = grid.permute(names.index(rank_axis), names.index(partition_axis))
+    return tuple(tuple(position[int(g)] for g in by_axis[:, part].tolist()) for part in range(by_axis.shape[1]))
+
+
+def _partition_blocks(fqn_params, num_partitions: int, partition_index: int) -> tuple[int, int]:
+    """(blocks held by one partition, elements of one block over all the parameters) of stacked weights that the
+    partition axis cuts evenly along dim 0; with more than one partition every parameter must declare that layout."""
+    import math
+
+    from ..placement_contract import GlobalLayout, get_global_layout
+
+    shapes = [tuple(p.shape) for _, p in fqn_params]
+    if any(len(s) < 3 for s in shapes):
+        raise ValueError("partitioned block parameters must have at least 3 dims ([blocks, rows, cols])")
+    n = shapes[0][0]
+    if n <= 0 or any(s[0] != n for s in shapes):
+        raise ValueError("partitioned block parameters of one plan must hold the same, positive number of blocks")
+    if num_partitions > 1:
+        for (fqn, p), shape in zip(fqn_params, shapes):
+            want = GlobalLayout((n * num_partitions, *shape[1:]), ((partition_index * n, *(0,) * (len(shape) - 1)),),
+                                ((0,) * len(shape),), (shape,))
+            if get_global_layout(p) != want:
+                raise ValueError(f"partitioned block parameter {fqn!r} must declare a global layout that cuts dim 0 "
+                                 f"evenly into {num_partitions} partitions, this rank holding partition "
+                                 f"{partition_index} (set_global_layout)")
+    return n, sum(math.prod(s[1:]) for s in shapes)
+
+
+def _check_plan_assignment(groups: Sequence[AssignmentGroup], answer, num_ranks: int) -> None:
+    if not isinstance(answer, MatrixAssignment):
+        raise TypeError(f"the assignment function must return a MatrixAssignment, got {type(answer).__name__}")
+    want_m = {m.name for g in groups for m in g.matrices}
+    want_b = {b.name: b for g in groups for b in g.block_groups}
+    if set(answer.rank_by_matrix) != want_m:
+        raise ValueError(f"Matrix assignment names do not match the recipe: missing "
+                         f"{sorted(want_m - set(answer.rank_by_matrix))}, unexpected "
+                         f"{sorted(set(answer.rank_by_matrix) - want_m)}")
+    if set(answer.blocks_per_rank_by_group) != set(want_b):
+        raise ValueError(f"Block group names do not match the recipe: missing "
+                         f"{sorted(set(want_b) - set(answer.blocks_per_rank_by_group))}, unexpected "
+                         f"{sorted(set(answer.blocks_per_rank_by_group) - set(want_b))}")
+    for name, r in answer.rank_by_matrix.items():
+        if isinstance(r, bool) or not isinstance(r, int) or not 0 <= r < num_ranks:
+            raise ValueError(f"owner of {name!r} must be a rank in [0, {num_ranks}), got {r!r}")
+    for name, counts in answer.blocks_per_rank_by_group.items():
+        b = want_b[name]
+        if (len(counts) != len(b.eligible_ranks) or any(isinstance(c, bool) or not isinstance(c, int) or c < 0
+                                                        for c in counts) or sum(counts) != b.num_blocks):
+            raise ValueError(f"block group {name!r} needs {len(b.eligible_ranks)} non-negative block counts that sum "
+                             f"to {b.num_blocks}, got {tuple(counts)!r}")
+
+
+def _materialize_from_plans(*, bucket_plans, assignment_name_by_fqn, initial_sharded_fqns, final_sharded_fqn_groups,
+                            assignment_mesh, partition_mesh, partition_rank_axis_name, partition_axis_name, mp_policy,
+                            assignment_fn) -> list[BucketSpec]:
+    """The recipe form of ``materialize_dist_muon_buckets`` (parity: ``dist_muon/bucket_planner.py:328-517`` of the
+    reference): initial ``Shard(0)`` bucket, per plan a mixed bucket (owned + packed + ``Shard(0)``) and a flat block
+    bucket of its partitioned weights on the partition's ranks, final ``Shard(0)`` buckets that stay gathered; all
+    buckets sum their gradients."""
+    from ..placements.bucketed_block_shard import make_bucketed_block_shard_placement_fn
+    from ..placements.mixed_bucket import make_mixed_placement_fn
+
+    W = int(assignment_mesh.size())
+    if partition_mesh is None:
+        storage_mesh, rank_groups, mine = assignment_mesh, (tuple(range(W)),), 0
+    else:
+        storage_mesh = partition_mesh[partition_rank_axis_name]
+        rank_groups = _partition_rank_groups(assignment_mesh, partition_mesh, partition_rank_axis_name,
+                                             partition_axis_name)
+        mine = int(partition_mesh.get_local_rank(partition_axis_name))
+    groups, group_names, matrix_to_packed, owned_fqns = [], [], {}, []
+    for plan in bucket_plans:
+        matrices = []
+        for fqn, p in plan.owned_parameters:
+            matrices.append(WholeMatrixSpec(assignment_name_by_fqn[fqn], p.numel()))
+            owned_fqns.append(fqn)
+        for packed in sorted(plan.packed_parameters, key=lambda sp: assignment_name_by_fqn[sp.fqn]):
+            packed.block_plan.validate_parameter(packed.fqn, packed.parameter)
+            k = packed.block_plan.num_matrices
+            for i in range(k):
+                name = f"{assignment_name_by_fqn[packed.fqn]}#matrix{i}"
+                matrices.append(WholeMatrixSpec(name, packed.parameter.numel() // k))
+                matrix_to_packed[name] = packed.fqn
+        block_groups = ()
+        if plan.partitioned_parameters:
+            n, numel = _partition_blocks(plan.partitioned_parameters, len(rank_groups), mine)
+            block_groups = tuple(MatrixBlockGroupSpec(f"{plan.partition_group_name_prefix}{i}", n, numel, ranks)
+                                 for i, ranks in enumerate(rank_groups))
+        groups.append(AssignmentGroup(tuple(matrices), block_groups))
+        group_names.append(tuple(b.name for b in block_groups))
+    if assignment_fn is None:
+        answer = _assign_groups(groups, W, mesh_rank_hosts(W))
+    else:
+        _assign_groups(groups, W, None)            # the same input checks a built-in run would make
+        answer = assignment_fn(tuple(groups), num_ranks=W)
+    _check_plan_assignment(groups, answer, W)
+    owned_rank = {f: answer.rank_by_matrix[assignment_name_by_fqn[f]] for f in owned_fqns}
+    counts_by_fqn: dict[str, list[int]] = {}
+    for name, fqn in matrix_to_packed.items():
+        counts_by_fqn.setdefault(fqn, [0] * W)[answer.rank_by_matrix[name]] += 1
+    kw = dict(mp_policy=mp_policy, gradient_reduce_op=dist.ReduceOp.SUM)
+    specs = []
+    if initial_sharded_fqns:
+        specs.append(BucketSpec(tuple(initial_sharded_fqns), placement_fn=shard_placement_fn(0), mesh=assignment_mesh,
+                                reshard_after_forward=True, **kw))
+    for plan, names in zip(bucket_plans, group_names):
+        if plan.mixed_fqns:
+            inside = set(plan.mixed_fqns)
+            fn = make_mixed_placement_fn({f: r for f, r in owned_rank.items() if f in inside},
+                                         {f: tuple(c) for f, c in counts_by_fqn.items() if f in inside})
+            specs.append(BucketSpec(tuple(plan.mixed_fqns), placement_fn=fn, mesh=assignment_mesh,
+                                    reshard_after_forward=True, **kw))
+        if plan.partitioned_parameters:
+            counts = answer.blocks_per_rank_by_group[names[mine]]
+            specs.append(BucketSpec(tuple(f for f, _ in plan.partitioned_parameters),
+                                    placement_fn=make_bucketed_block_shard_placement_fn(tuple(counts)),
+                                    mesh=storage_mesh, reshard_after_forward=True, **kw))
+    for fqns in final_sharded_fqn_groups:
+        if fqns:
+            specs.append(BucketSpec(tuple(fqns), placement_fn=shard_placement_fn(0), mesh=assignment_mesh,
+                                    reshard_after_forward=False, **kw))
+    return specs
+
+
+def materialize_dist_muon_buckets(named_params=None, mesh=None, *, initial: Sequence[str] = (),
+                                  blocks: Sequence[Sequence[str]] = (), final: Sequence[str] = (), is_matrix=None,
+                                  num_blocks_of=None, mp_policy: MixedPrecisionPolicy | None = None,
+                                  carry_loads: bool = True, ranks_per_host: int | None = None, assignment_fn=None,
+                                  bucket_plans=None, assignment_name_by_fqn: Mapping[str, str] | None = None,
+                                  initial_sharded_fqns: Sequence[str] = (),
+                                  final_sharded_fqn_groups: Sequence[Sequence[str]] = (), assignment_mesh=None,
+                                  partition_mesh=None, partition_rank_axis_name: str = "",
+                                  partition_axis_name: str = "") -> list[BucketSpec]:
     """BucketSpecs for a Muon-trained model: ``initial`` / ``final`` pattern groups stay ``Shard(0)``
     (AdamW parameters); each entry of ``blocks`` becomes one mixed bucket whose matrices are owned
     whole (or block-sharded when ``num_blocks_of`` says so) and whose vectors are ``Shard(0)``.
     All buckets sum gradients (``ReduceOp.SUM``), as the reference's recipe does.  ``assignment_fn(groups,
-    num_ranks=W) -> {fqn: rank | blocks per rank}`` replaces the built-in balancer."""
+    num_ranks=W) -> {fqn: rank | blocks per rank}`` replaces the built-in balancer.
+
+    With ``bucket_plans`` (``ParameterBucketPlan``s) the call takes the reference's recipe form instead
+    (``assignment_name_by_fqn``, ``initial_sharded_fqns``, ``final_sharded_fqn_groups``, ``assignment_mesh``,
+    ``partition_mesh`` and its two axis names): see ``_materialize_from_plans``."""
+    if bucket_plans is not None:
+        if assignment_name_by_fqn is None or assignment_mesh is None:
+            raise ValueError("the recipe form needs assignment_name_by_fqn and assignment_mesh")
+        return _materialize_from_plans(
+            bucket_plans=tuple(bucket_plans), assignment_name_by_fqn=assignment_name_by_fqn,
+            initial_sharded_fqns=initial_sharded_fqns, final_sharded_fqn_groups=final_sharded_fqn_groups,
+            assignment_mesh=assignment_mesh, partition_mesh=partition_mesh,
+            partition_rank_axis_name=partition_rank_axis_name, partition_axis_name=partition_axis_name,
+            mp_policy=mp_policy or MixedPrecisionPolicy(), assignment_fn=assignment_fn)
+    if named_params is None:
+        raise ValueError("materialize_dist_muon_buckets needs named_params and mesh, or bucket_plans")
     from ..parallel.comm import mesh_group
 
     _, _, W, _ = mesh_group(mesh)

@@ -70,8 +70,32 @@ class MixedBucketPlacement(SlicedPlacement):
             and i.param_dtype == (i.bucket_reduce_dtype or i.reduce_dtype) for i in infos))
 
 
-def make_mixed_placement_fn(member_fn):
-    """Wrap the placements returned by ``member_fn`` so that they may share one bucket."""
+def make_mixed_placement_fn(member_fn, blocks_per_rank_by_fqn=None):
+    """Wrap the placements returned by ``member_fn`` so that they may share one bucket.
+
+    Also takes the reference's form ``make_mixed_placement_fn(owned_rank_by_fqn, blocks_per_rank_by_fqn)``
+    (``dist_muon/placement.py:164-199`` there): the named parameters are whole on their owner rank, or stored in
+    whole dim-0 blocks with the given blocks per rank; every other parameter of the bucket is ``Shard(0)``."""
+    from collections.abc import Mapping
+
+    if isinstance(member_fn, Mapping):
+        owned, blocks = dict(member_fn), dict(blocks_per_rank_by_fqn or {})
+
+        def by_name(named_params, mesh):
+            from .block_shard import BlockShard
+            from .owned import BucketedOwned
+
+            out = {}
+            for f, p in named_params:
+                if f in blocks:
+                    out[f] = MixedBucketPlacement(BlockShard(tuple(blocks[f]), 0))
+                elif f in owned:
+                    out[f] = MixedBucketPlacement(BucketedOwned(((int(owned[f]), 0, p.shape[0]),)))
+                else:
+                    out[f] = MixedBucketPlacement(Shard(0))
+            return out
+
+        return by_name
 
     def fn(named_params, mesh):
         return {f: MixedBucketPlacement(pl) for f, pl in member_fn(named_params, mesh).items()}

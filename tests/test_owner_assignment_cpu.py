@@ -208,3 +208,110 @@ def test_recipe_types_of_the_reference_are_accepted():
     pls = specs[0].placement_fn(named, FakeMesh(2))
     assert pls["l0.w"].member.segments[0][0] == 1
     assert isinstance(pls["l0.heads"].member, BlockShard) and tuple(pls["l0.heads"].member.blocks_per_rank) == (1, 3)
+
+
+class _Mesh:
+    """Stand-in for a DeviceMesh in planner tests: ranks as a tensor, axis names, this rank's coordinates."""
+
+    def __init__(self, ranks, names=None, coords=None):
+        import torch
+
+        self.mesh = torch.tensor(ranks)
+        self.mesh_dim_names = names
+        self._coords = coords or {}
+        self.world_size, self.rank, self.ndim, self.device = self.mesh.numel(), 0, self.mesh.dim(), "cpu"
+
+    def size(self):
+        return self.mesh.numel()
+
+    def get_local_rank(self, axis=None):
+        return self._coords.get(axis, 0)
+
+    def __getitem__(self, axis):
+        i = self.mesh_dim_names.index(axis)
+        other = 1 - i
+        line = self.mesh.select(other, self._coords[self.mesh_dim_names[other]])
+        return _Mesh(line.tolist(), (axis,), {axis: self._coords[axis]})
+
+
+def test_recipe_form_of_the_bucket_materializer():
+    """``bucket_plans``: owned + packed parameters in a mixed bucket, partitioned expert weights in a flat block
+    bucket on the partition's own ranks, ``Shard(0)`` around them, every bucket summing its gradients.  Restated from
+    ``tests/test_matrix_assignment.py:41-71,166-260`` of the reference."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    from flex_shard_b200 import GlobalLayout, set_global_layout
+    from flex_shard_b200.dist_muon import (BlockShardPlan, MatrixAssignment, PackedParameterPlan, ParameterBucketPlan,
+                                           materialize_dist_muon_buckets)
+    from flex_shard_b200.placements import BlockShard, BucketedBlockShard, BucketedOwned, Shard
+
+    owned, blocks = nn.Parameter(torch.empty(2, 2)), nn.Parameter(torch.empty(4, 2, 3))
+    plan = ParameterBucketPlan(mixed_fqns=("owned",), owned_parameters=(("owned", owned),),
+                               partitioned_parameters=(("blocks", blocks),), partition_group_name_prefix="blocks#")
+    common = dict(bucket_plans=(plan,), assignment_name_by_fqn={"owned": "matrix"}, initial_sharded_fqns=(),
+                  final_sharded_fqn_groups=(), assignment_mesh=_Mesh([0, 1]), partition_mesh=None,
+                  partition_rank_axis_name="rank", partition_axis_name="partition")
+    seen = {}
+
+    def custom(groups, *, num_ranks):
+        seen["n"], seen["groups"] = num_ranks, groups
+        return MatrixAssignment({"matrix": 1}, {"blocks#0": (1, 3)})
+
+    specs = materialize_dist_muon_buckets(**common, assignment_fn=custom)
+    assert seen["n"] == 2 and len(seen["groups"]) == 1
+    assert seen["groups"][0].block_groups[0].block_numel == 6 and seen["groups"][0].block_groups[0].num_blocks == 4
+    assert [s.gradient_reduce_op for s in specs] == [dist.ReduceOp.SUM] * 2
+    pl = specs[0].placement_fn([("owned", owned)], common["assignment_mesh"])["owned"]
+    assert isinstance(pl.member, BucketedOwned) and pl.member.segments == ((1, 0, 2),)
+    bp = specs[1].placement_fn([("blocks", blocks)], common["assignment_mesh"])["blocks"]
+    assert isinstance(bp, BucketedBlockShard) and tuple(bp.blocks_per_rank) == (1, 3)
+    for bad, msg in ((MatrixAssignment({}, {"blocks#0": (1, 3)}), "Matrix assignment names"),
+                     (MatrixAssignment({"matrix": 1}, {}), "Block group names"),
+                     (MatrixAssignment({"matrix": 2}, {"blocks#0": (1, 3)}), "rank in"),
+                     (MatrixAssignment({"matrix": 1}, {"blocks#0": (1, 2)}), "sum to 4"),
+                     (MatrixAssignment({"matrix": 1}, {"blocks#0": (4,)}), "2 non-negative")):
+        with pytest.raises(ValueError, match=msg):
+            materialize_dist_muon_buckets(**common, assignment_fn=lambda g, *, num_ranks, bad=bad: bad)
+    with pytest.raises(TypeError, match="MatrixAssignment"):
+        materialize_dist_muon_buckets(**common, assignment_fn=lambda g, *, num_ranks: {"matrix": 1})
+
+    # the built-in balancer, a packed parameter (4 heads of 2 rows) and the buckets around the blocks
+    heads = nn.Parameter(torch.empty(8, 3))
+    plan2 = ParameterBucketPlan(mixed_fqns=("owned", "heads", "norm"), owned_parameters=(("owned", owned),),
+                                packed_parameters=(PackedParameterPlan("heads", heads, BlockShardPlan(4)),))
+    specs = materialize_dist_muon_buckets(bucket_plans=(plan2,), assignment_name_by_fqn={"owned": "o", "heads": "h"},
+                                          initial_sharded_fqns=("emb",), final_sharded_fqn_groups=(("norm_f",), ()),
+                                          assignment_mesh=_Mesh([0, 1]))
+    assert [s.patterns for s in specs] == [("emb",), ("owned", "heads", "norm"), ("norm_f",)]
+    assert [s.reshard_after_forward for s in specs] == [True, True, False]
+    pls = specs[1].placement_fn([("owned", owned), ("heads", heads), ("norm", nn.Parameter(torch.empty(3)))], None)
+    assert isinstance(pls["heads"].member, BlockShard) and sum(pls["heads"].member.blocks_per_rank) == 4
+    assert isinstance(pls["norm"].member, Shard) or pls["norm"].member.__class__.__name__ == "ShardSlice"
+    with pytest.raises(ValueError, match="divisible"):
+        materialize_dist_muon_buckets(
+            bucket_plans=(ParameterBucketPlan(packed_parameters=(PackedParameterPlan("heads", heads, BlockShardPlan(3)),)),),
+            assignment_name_by_fqn={"heads": "h"}, assignment_mesh=_Mesh([0, 1]))
+
+    # experts cut by an outer axis: 4 ranks as efsdp x ep = 2 x 2, this rank at (efsdp 1, ep 1)
+    flat = _Mesh([0, 1, 2, 3])
+    grid = _Mesh([[0, 1], [2, 3]], ("efsdp", "ep"), {"efsdp": 1, "ep": 1})
+    experts = nn.Parameter(torch.empty(4, 2, 3))           # this partition's 4 of 8 experts
+    eplan = ParameterBucketPlan(partitioned_parameters=(("experts", experts),), partition_group_name_prefix="e#")
+    args = dict(bucket_plans=(eplan,), assignment_name_by_fqn={}, assignment_mesh=flat, partition_mesh=grid,
+                partition_rank_axis_name="efsdp", partition_axis_name="ep")
+    with pytest.raises(ValueError, match="set_global_layout"):
+        materialize_dist_muon_buckets(**args)
+    set_global_layout(experts, GlobalLayout((8, 2, 3), ((4, 0, 0),), ((0, 0, 0),), ((4, 2, 3),)))
+
+    def spy(groups, *, num_ranks):
+        seen["eligible"] = [b.eligible_ranks for b in groups[0].block_groups]
+        return MatrixAssignment({}, {"e#0": (4, 0), "e#1": (1, 3)})
+
+    (spec,) = materialize_dist_muon_buckets(**args, assignment_fn=spy)
+    assert seen["eligible"] == [(0, 2), (1, 3)]              # ranks sharing ep 0, ranks sharing ep 1
+    assert spec.mesh.mesh.tolist() == [1, 3]                 # stored on this partition's ranks
+    assert tuple(spec.placement_fn([("experts", experts)], spec.mesh)["experts"].blocks_per_rank) == (1, 3)
+    with pytest.raises(ValueError, match="exactly the axes"):
+        materialize_dist_muon_buckets(**{**args, "partition_axis_name": "pp"})
