@@ -11,6 +11,7 @@ from typing import Mapping, Sequence
 import torch.nn as nn
 
 from ..placements.block_shard import BlockShard
+from ..placements.bucketed_block_shard import BucketedBlockShard
 from ..placements.mixed_bucket import MixedBucketPlacement, ShardSlice
 from ..placements.owned import BucketedOwned
 from ..placements.shard import Shard
@@ -87,6 +88,17 @@ def get_flex_shard_muon_compute_layouts(module: nn.Module,
                     pattern = head_rows or ((pl.block_size(gshape),) if pl.block_size(gshape) else None)
                     blocks = _repeat(info.fqn, pattern, info.local_shape[0]) if pattern else ()
                     out[info.fqn] = LocalMuonComputeLayout("row_blocks", block_rows=blocks, global_shape=gshape)
+            elif isinstance(pl, BucketedBlockShard):
+                # a flat block bucket cuts every parameter on whole dim-0 entries: whole matrices of a stacked
+                # weight (experts), whole rows of a 2-D one
+                if len(gshape) >= 3:
+                    out[info.fqn] = LocalMuonComputeLayout("matrix_batch", global_shape=gshape)
+                elif head_rows is not None:
+                    out[info.fqn] = LocalMuonComputeLayout(
+                        "row_blocks", block_rows=_repeat(info.fqn, head_rows, info.local_shape[0]), global_shape=gshape)
+                else:
+                    raise ValueError(f"{info.fqn!r} is stored in a flat block bucket, which cuts a 2-D parameter between "
+                                     "any two rows: give its block rows (block_rows_by_fqn) or store it another way")
             elif isinstance(pl, (Shard, ShardSlice)) and pl.dim == 0:
                 if W == 1:
                     out[info.fqn] = LocalMuonComputeLayout("owned", global_shape=gshape)
