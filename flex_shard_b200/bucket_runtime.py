@@ -584,7 +584,7 @@ class BucketRuntime:
             self._set_unsharded_grad_dtypes(defer_upcast=True)
             hook = self.storage.spec.pre_backward_hook
             if hook is not None:
-                hook(self.storage)
+                hook(self._hook_args())
             elif self.storage.placement.reduces_grads_in_param_layout(self.storage.infos):
                 from .utils.validation import alloc_grads_in_param_layout
 
@@ -592,6 +592,12 @@ class BucketRuntime:
             elif getattr(self.storage.placement, "wants_grad_bucket", lambda infos: False)(self.storage.infos):
                 self.storage.placement.alloc_grad_bucket(self.storage, self.unsharded_params)
             self._prefetch(forward=False)
+
+    def _hook_args(self):
+        from .bucket_storage import BucketHookArgs
+
+        pairs = [(i.fqn, u) for i, u in zip(self.storage.infos, self.unsharded_params or ())]
+        return BucketHookArgs(self.storage, pairs)
 
     def on_input_grads(self) -> None:
         self._triggers_fired += 1
@@ -710,7 +716,7 @@ class BucketRuntime:
         self.needs_sync = False
         if grads is None or not grads:
             if hook is not None:
-                hook(st)
+                hook(self._hook_args())
             return
         reduce_dtype = st.bucket_reduce_dtype
         for g in grads:
@@ -721,7 +727,7 @@ class BucketRuntime:
         ctx.stats["reduces"] += 1
         ctx.pending_reduces.append(state)
         if hook is not None:
-            hook(st)
+            hook(self._hook_args())
 
     def accumulate_sharded_grads(self, result) -> None:
         st = self.storage

@@ -35,7 +35,22 @@ from .placement_contract import (
 from .sharded_param import set_sharding_info
 
 PlacementFn = Callable[[list[tuple[str, nn.Parameter]], Any], Mapping[str, Placement]]
-BucketHook = Callable[["ShardedBucketStorage"], None]
+class BucketHookArgs(list):
+    """What a bucket hook is called with: the bucket's ``(fqn, unsharded parameter)`` pairs, as in the reference
+    (``flex_shard/bucket_storage.py:48-49`` there), which also answer for the bucket's storage: ``args.storage`` is the
+    ``ShardedBucketStorage`` and its attributes (``name``, ``infos``, ...) can be read from ``args`` directly."""
+
+    def __init__(self, storage, pairs):
+        super().__init__(pairs)
+        self.storage = storage
+
+    def __getattr__(self, name):
+        if name == "storage":
+            raise AttributeError(name)
+        return getattr(self.storage, name)
+
+
+BucketHook = Callable[[BucketHookArgs], None]
 
 
 # --------------------------------------------------------------------------- policies

@@ -14,7 +14,9 @@ import torch
 def alloc_grads_in_param_layout(storage) -> None:
     """Give every unsharded parameter of ``storage`` a ``.grad`` that is a view of one
     bucket-shaped buffer (the Megatron ``main_grad`` idea), so the reduction can send the
-    buffer as it is. No-op when the grads already exist."""
+    buffer as it is. No-op when the grads already exist.  Usable as a ``BucketSpec.pre_backward_hook`` as it is (a
+    hook's argument carries the storage)."""
+    storage = getattr(storage, "storage", storage)
     rt = storage.runtime
     if rt is None or rt.unsharded_params is None:
         return

@@ -81,6 +81,34 @@ def test_dtype_overrides_span_the_buckets_that_share_the_policy():
         flex_shard(root_first[0], [BucketSpec(["*"])])
 
 
+def test_bucket_hooks_receive_named_unsharded_parameters():
+    """Hooks are called with the bucket's ``(fqn, unsharded parameter)`` pairs, as in the reference
+    (``flex_shard/bucket_storage.py:48-49, 207-227`` there); the argument also answers for the storage, and
+    ``alloc_grads_in_param_layout`` can be the pre-backward hook as it is."""
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.utils.validation import alloc_grads_in_param_layout
+
+    seen = []
+
+    def pre(named):
+        seen.append(("pre", [(fqn, tuple(p.shape), p.grad is None) for fqn, p in named], named.name))
+        for _, p in named:
+            p.marker = "set in pre-backward"
+
+    def post(named):
+        seen.append(("post", [fqn for fqn, _ in named], [getattr(p, "marker", None) for _, p in named],
+                     [p.grad is None for _, p in named]))
+
+    torch.manual_seed(0)
+    m = Net()
+    flex_shard(m, [BucketSpec(["a.*"], pre_backward_hook=pre, post_reduce_hook=post),
+                   BucketSpec(["b.*"], pre_backward_hook=alloc_grads_in_param_layout)])
+    m(torch.randn(3, 8)).sum().backward()
+    assert seen[0] == ("pre", [("a.weight", (16, 8), True), ("a.bias", (16,), True)], "a")
+    assert seen[1] == ("post", ["a.weight", "a.bias"], ["set in pre-backward"] * 2, [True, True])
+    assert all(p.grad is not None for p in m.parameters())
+
+
 def test_flex_shard_applies_once():
     from flex_shard_b200 import BucketSpec, flex_shard
 
