@@ -153,31 +153,33 @@ class FlexShardModule:
         return st
 
     # ---- settings broadcast to every bucket
-    def set_gradient_reduce_op(self, op) -> None:
+    # The setters keep the reference's signatures (``flex_shard/flex_shard.py:262-394`` there).  ``recurse`` selects
+    # the sharded modules below this one as well; nested wrapping is refused, so this module's buckets are all there are.
+    def set_gradient_reduce_op(self, op, *, recurse: bool = True) -> None:
         for st in self.sharded_bucket_storages:
             st.set_gradient_reduce_op(op)
 
-    def set_gradient_divide_factor(self, factor) -> None:
+    def set_gradient_divide_factor(self, factor, *, recurse: bool = True) -> None:
         for st in self.sharded_bucket_storages:
             st.set_gradient_divide_factor(factor)
 
-    def set_requires_gradient_sync(self, value: bool) -> None:
+    def set_requires_gradient_sync(self, requires_gradient_sync: bool, *, recurse: bool = True) -> None:
         for st in self.sharded_bucket_storages:
-            st.set_requires_gradient_sync(value)
+            st.set_requires_gradient_sync(requires_gradient_sync)
 
-    def set_reshard_after_backward(self, value: bool) -> None:
+    def set_reshard_after_backward(self, reshard_after_backward: bool, *, recurse: bool = True) -> None:
         for st in self.sharded_bucket_storages:
-            st.set_reshard_after_backward(value)
+            st.set_reshard_after_backward(reshard_after_backward)
 
-    def set_reshard_after_forward(self, value: bool) -> None:
+    def set_reshard_after_forward(self, reshard_after_forward: bool, *, recurse: bool = True) -> None:
         for st in self.sharded_bucket_storages:
-            st.set_reshard_after_forward(value)
+            st.set_reshard_after_forward(reshard_after_forward)
 
-    def set_separate_reduce_scatter_group(self, enabled: bool = True) -> None:
+    def set_separate_reduce_scatter_group(self, enable: bool = True, *, recurse: bool = True) -> None:
         """Run reduce-scatters on a second communicator so they can overlap all-gathers."""
         made: dict[int, Any] = {}
         for st in self.sharded_bucket_storages:
-            if not enabled:
+            if not enable:
                 st.reduce_comm = st.comm
                 continue
             if st.reduce_comm is not st.comm:
@@ -187,10 +189,10 @@ class FlexShardModule:
                 made[key] = st.comm.new_like()
             st.reduce_comm = made[key]
 
-    def set_max_pending_reduce_grads(self, n: int) -> None:
-        if n < 1:
+    def set_max_pending_reduce_grads(self, max_pending_reduce_grads: int = 1, *, recurse: bool = True) -> None:
+        if max_pending_reduce_grads < 1:
             raise ValueError("max_pending_reduce_grads must be >= 1")
-        self._fsb_ctx().max_pending_reduce_grads = int(n)
+        self._fsb_ctx().max_pending_reduce_grads = int(max_pending_reduce_grads)
 
 
 # --------------------------------------------------------------------------- helpers

@@ -109,6 +109,51 @@ def test_bucket_hooks_receive_named_unsharded_parameters():
     assert all(p.grad is not None for p in m.parameters())
 
 
+def test_reference_call_forms_are_accepted():
+    """Setters take the reference's keyword names and ``recurse``; ``init_from_full(local, layout, init_fn)`` and
+    ``set_sharding_info(tensor, placements, global_shape, global_stride, mesh)`` take its positional forms
+    (``flex_shard/flex_shard.py:262-394``, ``param_init.py:18``, ``sharded_param.py:57`` there)."""
+    from flex_shard_b200 import (GlobalLayout, get_flex_shard_global_layouts, get_global_shape, get_placements,
+                                 init_from_full, is_flex_shard_param)
+    from flex_shard_b200.placements import Shard
+    from flex_shard_b200.sharded_param import set_sharding_info
+
+    m = _sharded()
+    m.set_requires_gradient_sync(requires_gradient_sync=False, recurse=True)
+    assert not any(st.requires_gradient_sync for st in m.sharded_bucket_storages)
+    m.set_requires_gradient_sync(True, recurse=False)
+    m.set_reshard_after_backward(reshard_after_backward=False)
+    m.set_gradient_divide_factor(2.0, recurse=True)
+    m.set_gradient_divide_factor(None)
+    m.set_gradient_reduce_op(dist.ReduceOp.SUM, recurse=True)
+    m.set_separate_reduce_scatter_group(enable=False)
+    m.set_max_pending_reduce_grads(max_pending_reduce_grads=2, recurse=True)
+    m.set_max_pending_reduce_grads()
+    m.unshard(async_op=False)
+    m.reshard()
+
+    layouts = get_flex_shard_global_layouts(m)
+    w = dict(m.named_parameters())["a.weight"]
+    init_from_full(w, layouts["a.weight"], lambda full: full.fill_(3.0))
+    assert bool((w.detach() == 3.0).all())
+    init_from_full(w, lambda full: full.fill_(4.0))
+    assert bool((w.detach() == 4.0).all())
+    half = torch.zeros(2, 4)      # rows 2..3 of a [4, 4] tensor
+    init_from_full(half, GlobalLayout((4, 4), ((2, 0),), ((0, 0),), ((2, 4),)),
+                   lambda full: full.copy_(torch.arange(16.0).view(4, 4)))
+    assert half.tolist() == [[8, 9, 10, 11], [12, 13, 14, 15]]
+    with pytest.raises(TypeError):
+        init_from_full(half, "not a layout", lambda full: None)
+
+    t = torch.zeros(2, 3)
+    set_sharding_info(t, (Shard(0),), torch.Size((4, 3)), (3, 1), None)
+    assert is_flex_shard_param(t) and get_placements(t) == (Shard(0),) and tuple(get_global_shape(t)) == (4, 3)
+    with pytest.raises(TypeError):
+        set_sharding_info(t, (Shard(0),), (4, 3), (3, 1), None, placement=Shard(0))
+    with pytest.raises(ValueError, match="1-D"):
+        set_sharding_info(t, (Shard(0), Shard(1)), (4, 3), (3, 1), None)
+
+
 def test_flex_shard_applies_once():
     from flex_shard_b200 import BucketSpec, flex_shard
 
