@@ -296,7 +296,11 @@ class BucketedBlockShard(Placement):
         return PlacementReduceGradResult(grads=grads, output=out)
 
 
-def make_bucketed_block_shard_placement_fn(blocks_per_rank: Sequence[int] | None = None):
+def make_bucketed_block_shard_placement_fn(blocks_per_rank: Sequence[int] | None = None, *,
+                                           dims: Sequence[int] = (0,)):
+    if tuple(dims) != (0,):
+        raise ValueError("BucketedBlockShard supports dims=(0,) (row-major flat buckets)")
+
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
 

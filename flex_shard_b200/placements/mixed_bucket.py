@@ -37,15 +37,53 @@ class ShardSlice(SlicedPlacement):
 
 
 class MixedBucketPlacement(SlicedPlacement):
-    """Wraps one member placement of a mixed bucket."""
+    """Wraps one member placement of a mixed bucket.
+
+    ``MixedBucketPlacement({fqn: [BucketedOwnedSegmentSpec]})``, the reference's form
+    (``custom_placements/mixed_bucket.py`` there), describes the bucket's owned parameters instead and hands out the
+    members: ``.shard0``, ``.block_shard(blocks_per_rank, dim=0)`` and ``.bucketed_owned`` (narrowed to each
+    parameter's own segments when ``flex_shard`` applies it)."""
 
     def __init__(self, member):
+        from collections.abc import Mapping
+
+        self._segments_by_fqn = None
+        if isinstance(member, Mapping):
+            from .owned import BucketedOwned
+
+            self._segments_by_fqn = dict(member)
+            member = BucketedOwned(self._segments_by_fqn) if self._segments_by_fqn else ShardSlice(0)
         if isinstance(member, Shard):
             member = ShardSlice(member.dim)
         if not isinstance(member, SlicedPlacement):
             raise TypeError(f"{member!r} cannot be a member of a mixed bucket")
         self.member = member
         self.owner_style = getattr(member, "owner_style", False)
+
+    # ---- the reference's way of building the members of one bucket
+    @property
+    def shard0(self) -> "MixedBucketPlacement":
+        return MixedBucketPlacement(Shard(0))
+
+    def block_shard(self, blocks_per_rank, dim: int = 0) -> "MixedBucketPlacement":
+        from .block_shard import BlockShard
+
+        return MixedBucketPlacement(BlockShard(tuple(blocks_per_rank), dim))
+
+    @property
+    def bucketed_owned(self) -> "MixedBucketPlacement":
+        from .owned import BucketedOwned
+
+        if not self._segments_by_fqn:
+            raise ValueError("this MixedBucketPlacement was built without owner segments")
+        return MixedBucketPlacement(BucketedOwned(self._segments_by_fqn))
+
+    def for_param(self, fqn: str, shape) -> "MixedBucketPlacement":
+        narrow = getattr(self.member, "for_param", None)
+        if narrow is None:
+            return self
+        member = narrow(fqn, shape)
+        return self if member is self.member else MixedBucketPlacement(member)
 
     def __eq__(self, other):
         return isinstance(other, MixedBucketPlacement) and other.member == self.member

@@ -44,6 +44,22 @@ def _placement_fn(kind):
             whole = BucketedOwned(make_bucketed_owned_full_param_segments(named, 2))
             return {f: (whole,) for f, _ in named}
         return fn
+    if kind == "mixed_factory":     # the reference's way: one MixedBucketPlacement per bucket hands out the members
+        from flex_shard_b200.placements import make_bucketed_owned_full_param_segments
+
+        def fn(named, mesh):
+            owned = [(f, p) for f, p in named if f == "a.weight"]
+            mixed = MixedBucketPlacement(make_bucketed_owned_full_param_segments(owned, 2))
+            out = {}
+            for f, p in named:
+                if f == "a.weight":
+                    out[f] = (mixed.bucketed_owned,)
+                elif p.dim() == 2:
+                    out[f] = (mixed.block_shard(blocks_per_rank=(1, 1), dim=0),)
+                else:
+                    out[f] = (mixed.shard0,)
+            return out
+        return fn
     if kind == "mixed_owned":      # every member whole on one owner: gradients accumulate in one mirror buffer
         return lambda named, mesh: {f: MixedBucketPlacement(BucketedOwned(((i % 2, 0, p.shape[0]),)))
                                     for i, (f, p) in enumerate(named)}
@@ -93,7 +109,8 @@ def _train(rank, world, kind, steps):
     return err, sizes, model.sharded_bucket_storages[0].total_bytes
 
 
-@pytest.mark.parametrize("kind", ["block", "owned", "owned_segments", "mixed", "mixed_owned", "flat", "flat_uneven"])
+@pytest.mark.parametrize("kind", ["block", "owned", "owned_segments", "mixed", "mixed_factory", "mixed_owned", "flat",
+                                  "flat_uneven"])
 def test_sliced_placements_train_like_unsharded(kind):
     res = run_ranks(_train, 2, kind, 3)
     for err, sizes, nbytes in res:
