@@ -104,7 +104,8 @@ class ParameterBucketPlan:
 def _assign_groups(groups: Sequence[AssignmentGroup], num_ranks: int, hosts: Sequence[int] | None) -> MatrixAssignment:
     """Groups are balanced one after the other on top of the loads the earlier ones left.  Whole matrices of a group:
     without ``hosts``, packed into one pile per rank (largest first onto the lightest pile), then the heaviest pile
-    goes to the rank that carries least so far; with ``hosts``, host first and then rank (``assign_to_hosts_then_ranks``).
+    goes to the rank that carries least so far; with ``hosts``, the piles go to hosts first and then to their ranks, one
+    pile per rank (``assign_to_hosts_then_ranks`` with earlier loads as tie-break).
     Blocks of a block group go one by one to the least loaded eligible rank (ties: the earlier eligible rank)."""
     if num_ranks <= 0:
         raise ValueError("num_ranks must be positive")
@@ -131,21 +132,25 @@ def _assign_groups(groups: Sequence[AssignmentGroup], num_ranks: int, hosts: Seq
     whole: dict[str, int] = {}
     blocks: dict[str, tuple[int, ...]] = {}
     for g in groups:
-        if g.matrices and hosts is None:
+        if g.matrices:
             piles = [[0.0, []] for _ in range(num_ranks)]
             for m in sorted(g.matrices, key=lambda m: -m.numel):
                 pile = min(piles, key=lambda p: p[0])          # min keeps the first of equals: the lowest pile index
                 pile[0] += m.numel
                 pile[1].append(m.name)
-            lightest_first = sorted(range(num_ranks), key=lambda r: loads[r])
-            for pile, r in zip(sorted(piles, key=lambda p: -p[0]), lightest_first):
+            if hosts is None:
+                # the heaviest pile to the rank that carries least so far
+                lightest_first = sorted(range(num_ranks), key=lambda r: loads[r])
+                pairs = zip(sorted(piles, key=lambda p: -p[0]), lightest_first)
+            else:
+                # one pile per rank, hosts first: heavy and light hosts alternate in rank order
+                ranks = assign_to_hosts_then_ranks([p[0] for p in piles], list(hosts), carried_loads=loads,
+                                                   one_per_rank=True)
+                pairs = zip(piles, ranks)
+            for pile, r in list(pairs):
                 for name in pile[1]:
                     whole[name] = r
                 loads[r] += pile[0]
-        elif g.matrices:
-            owners = assign_to_hosts_then_ranks([float(m.numel) for m in g.matrices], list(hosts), loads)
-            for m, r in zip(g.matrices, owners):
-                whole[m.name] = r
         for b in g.block_groups:
             counts = [0] * len(b.eligible_ranks)
             for _ in range(b.num_blocks):

@@ -171,9 +171,12 @@ def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_
 def make_bucketed_owned_full_param_segments(named_params, world_size: int, *, hosts: Sequence[int] | None = None,
                                             carried_loads: Sequence[float] | None = None
                                             ) -> dict[str, list[BucketedOwnedSegmentSpec]]:
-    """One whole-parameter segment per parameter; owners by longest-processing-time on the element count, hosts
-    first when ``hosts`` gives each rank's host, on top of ``carried_loads`` (each rank's elements from earlier
-    buckets; a list is updated in place).  Parity: ``custom_placements/owned.py:425-462`` of the reference."""
+    """One whole-parameter segment per parameter; owners by longest-processing-time on the element count.  Without
+    ``hosts``: the largest parameter first onto the rank that carries least, ``carried_loads`` (each rank's elements
+    from earlier buckets) counted in.  With ``hosts`` (each rank's host, ``mesh_rank_hosts``): hosts first, then the
+    ranks of the host, the bucket balanced by itself and ``carried_loads`` breaking ties.  ``carried_loads`` is not
+    changed: the caller adds what this bucket placed.  Parity: ``custom_placements/owned.py:393-462`` of the
+    reference."""
     if world_size <= 0:
         raise ValueError(f"world_size must be positive, got {world_size}")
     if hosts is not None and len(hosts) != world_size:
@@ -181,9 +184,16 @@ def make_bucketed_owned_full_param_segments(named_params, world_size: int, *, ho
     if carried_loads is not None and len(carried_loads) != world_size:
         raise ValueError(f"carried_loads must give each of the {world_size} ranks a load")
     named_params = list(named_params)
-    loads = carried_loads if isinstance(carried_loads, list) else list(carried_loads or [0.0] * world_size)
-    owners = assign_to_hosts_then_ranks([float(p.numel()) for _, p in named_params],
-                                        list(hosts) if hosts is not None else [0] * world_size, loads)
+    sizes = [float(p.numel()) for _, p in named_params]
+    if hosts is not None:
+        owners = assign_to_hosts_then_ranks(sizes, list(hosts), carried_loads=list(carried_loads or [0.0] * world_size))
+    else:
+        load = list(carried_loads or [0.0] * world_size)
+        owners = [0] * len(sizes)
+        for i in sorted(range(len(sizes)), key=lambda i: -sizes[i]):
+            r = min(range(world_size), key=lambda r: load[r])        # the first of equals: the lowest rank
+            owners[i] = r
+            load[r] += sizes[i]
     return {f: [BucketedOwnedSegmentSpec(f"{f}#full", f, 0, p.numel(), r, order)]
             for order, ((f, p), r) in enumerate(zip(named_params, owners))}
 

@@ -315,3 +315,59 @@ def test_recipe_form_of_the_bucket_materializer():
     assert tuple(spec.placement_fn([("experts", experts)], spec.mesh)["experts"].blocks_per_rank) == (1, 3)
     with pytest.raises(ValueError, match="exactly the axes"):
         materialize_dist_muon_buckets(**{**args, "partition_axis_name": "pp"})
+
+
+_MOE_LAYER = (7168 * 16384, 1536 * 7168, 2048 * 7168, 2048 * 7168, 7168 * 2048, 256 * 7168)
+
+
+def test_two_level_owner_goldens_of_the_reference(monkeypatch):
+    """Hosts first, then ranks, through the reference's call forms; goldens restated from
+    ``tests/test_matrix_assignment.py:266-360`` of the reference (one MoE layer of DeepSeek-V3 671B: attention ``wo``
+    and ``wq_a``, the shared experts' three matrices, the router)."""
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200.dist_muon import AssignmentGroup, WholeMatrixSpec, assign_matrices
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_segments
+    from flex_shard_b200.utils.validation import assign_to_hosts_then_ranks, mesh_rank_hosts
+
+    assert mesh_rank_hosts(range(8), 4) == (0, 0, 0, 0, 1, 1, 1, 1)
+    assert mesh_rank_hosts((64, 65, 72, 73), 8) == (0, 0, 1, 1)      # global ranks of a sub-mesh, hosts in mesh order
+    assert mesh_rank_hosts(range(4), 1) == (0, 1, 2, 3)
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")
+    assert mesh_rank_hosts(range(4)) == (0, 0, 1, 1)
+    monkeypatch.delenv("LOCAL_WORLD_SIZE")
+
+    # four MoE layers on 64 ranks of 8 hosts: each wo exceeds a host's share, so the hosts that hold one alternate
+    # with the others in rank order, and a second bucket on top of the carried loads flips them
+    hosts = mesh_rank_hosts(range(64), 8)
+    group = AssignmentGroup(tuple(WholeMatrixSpec(f"layer{l}.m{i}", n) for l in range(4) for i, n in enumerate(_MOE_LAYER)))
+    a = assign_matrices((group,), num_ranks=64, hosts=hosts)
+    assert sorted(hosts[a.rank_by_matrix[f"layer{l}.m0"]] for l in range(4)) == [0, 2, 4, 6]
+    per_host = [0] * 8
+    for m in group.matrices:
+        per_host[hosts[a.rank_by_matrix[m.name]]] += m.numel
+    assert per_host[0::2] == [_MOE_LAYER[0]] * 4 and per_host[1::2] == [sum(_MOE_LAYER) - _MOE_LAYER[0]] * 4
+    carried = [sum(m.numel for m in group.matrices if a.rank_by_matrix[m.name] == r) for r in range(64)]
+    second = assign_to_hosts_then_ranks([m.numel for m in group.matrices], hosts, carried_loads=carried, one_per_rank=True)
+    assert sorted(hosts[second[6 * l]] for l in range(4)) == [1, 3, 5, 7]
+
+    eight = AssignmentGroup(tuple(WholeMatrixSpec(f"m{i}", n) for i, n in enumerate((100,) * 4 + (10,) * 4)))
+    one_host = assign_matrices((eight,), num_ranks=8, hosts=(0,) * 8)
+    assert sorted(one_host.rank_by_matrix[f"m{i}"] for i in range(4)) == [0, 2, 4, 6]
+
+    six = AssignmentGroup(tuple(WholeMatrixSpec(f"m{i}", n) for i, n in enumerate((100, 100, 10, 10, 10, 10))))
+    two_level = assign_matrices((six,), num_ranks=8, hosts=mesh_rank_hosts(range(8), 4))
+    rank_order = assign_matrices((six,), num_ranks=8)
+    assert {two_level.rank_by_matrix[m] for m in ("m0", "m1")} == {0, 4}
+    assert {rank_order.rank_by_matrix[m] for m in ("m0", "m1")} == {0, 1}
+
+    named = [(f"p{i}", nn.Parameter(torch.empty(n))) for i, n in enumerate((100, 100, 10, 10))]
+    hosts_first = make_bucketed_owned_full_param_segments(named, 8, hosts=mesh_rank_hosts(range(8), 4))
+    plain = make_bucketed_owned_full_param_segments(named, 8)
+    assert {hosts_first[p][0].owner_rank for p in ("p0", "p1")} == {0, 4}
+    assert {plain[p][0].owner_rank for p in ("p0", "p1")} == {0, 1}
+    with pytest.raises(ValueError, match="one per rank"):
+        assign_to_hosts_then_ranks([1, 1, 1], (0, 0), one_per_rank=True)
+    with pytest.raises(ValueError, match="numbered"):
+        assign_to_hosts_then_ranks([1], (0, 2), carried_loads=[0, 0])

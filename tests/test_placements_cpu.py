@@ -136,7 +136,7 @@ def test_owner_segment_specs():
         "big": (0, 0, 64, 0), "mid": (1, 0, 32, 1), "small": (1, 0, 8, 2)}
     loads = [100.0, 0.0]
     carried = make_bucketed_owned_full_param_segments(named[:1], 2, carried_loads=loads)
-    assert carried["big"][0].owner_rank == 1 and loads == [100.0, 64.0]
+    assert carried["big"][0].owner_rank == 1 and loads == [100.0, 0.0]       # the caller adds what was placed
     for kwargs in (dict(hosts=(0,)), dict(carried_loads=(0, 0, 0))):
         with pytest.raises(ValueError):
             make_bucketed_owned_full_param_segments(named, 2, **kwargs)
