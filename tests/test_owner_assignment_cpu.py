@@ -371,3 +371,33 @@ def test_two_level_owner_goldens_of_the_reference(monkeypatch):
         assign_to_hosts_then_ranks([1, 1, 1], (0, 0), one_per_rank=True)
     with pytest.raises(ValueError, match="numbered"):
         assign_to_hosts_then_ranks([1], (0, 2), carried_loads=[0, 0])
+
+
+def test_sixteen_identical_blocks_on_64_ranks(monkeypatch):
+    """16 identical buckets of a DeepSeek-V3 MoE block's owned matrices on 64 ranks of 8 hosts: placed one at a time
+    every bucket gets the same 6 owners; carrying the loads spreads them, each rank owning at most one ``wo`` and
+    about a fair share in all.  Restated from ``tests/test_matrix_assignment.py:361-404`` of the reference."""
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200.placements import make_bucketed_owned_full_param_placement_fn
+    from tests.common import FakeMesh
+
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    shapes = ((7168, 16384), (1536, 7168), (576, 7168), (256, 7168), (2, 2048, 7168), (7168, 2048))
+
+    def owned_numel(fn):
+        loads = [0] * 64
+        for block in range(16):
+            named = [(f"layers.{block}.m{i}", nn.Parameter(torch.empty(s, device="meta"))) for i, s in enumerate(shapes)]
+            sizes = {f: p.numel() for f, p in named}
+            for f, pl in fn(named, FakeMesh(64)).items():
+                for r, _, _ in pl.segments:
+                    loads[r] += sizes[f]
+        return loads
+
+    per_bucket = owned_numel(make_bucketed_owned_full_param_placement_fn())
+    carried = owned_numel(make_bucketed_owned_full_param_placement_fn(carry_loads=True))
+    assert sum(load > 0 for load in per_bucket) == 6 and max(per_bucket) == 16 * 7168 * 16384
+    assert sum(load > 0 for load in carried) >= 60
+    assert max(carried) <= 7168 * 16384 + sum(carried) // 64
