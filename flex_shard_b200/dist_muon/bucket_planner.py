@@ -23,6 +23,7 @@ from ..placements.mixed_bucket import MixedBucketPlacement
 from ..placements.owned import BucketedOwned, newton_schulz_cost
 from ..placements.shard import Shard, shard_placement_fn
 from ..utils.validation import assign_to_hosts_then_ranks, mesh_rank_hosts
+from .placement import get_dim0_block_partitions, get_mesh_rank_groups
 
 
 @dataclass(frozen=True)
@@ -246,46 +247,6 @@ def assign_matrices(groups, num_ranks: int, *, ranks_per_host: int | None = None
     return out
 
 
-def _partition_rank_groups(assignment_mesh, partition_mesh, rank_axis: str, partition_axis: str):
-    """For every partition (index along ``partition_axis``) the ranks that share it, as positions in the flat
-    assignment mesh, ordered along ``rank_axis``."""
-    names = partition_mesh.mesh_dim_names
-    if names is None or set(names) != {rank_axis, partition_axis} or len(names) != 2:
-        raise ValueError(f"the partition mesh must have exactly the axes {rank_axis!r} and {partition_axis!r}, "
-                         f"got {names}")
-    flat = [int(r) for r in assignment_mesh.mesh.flatten().tolist()]
-    grid = partition_mesh.mesh
-    if sorted(int(r) for r in grid.flatten().tolist()) != sorted(flat):
-        raise ValueError("the assignment mesh and the partition mesh must hold the same ranks")
-    position = {g: i for i, g in enumerate(flat)}
-    by_axis = grid.permute(names.index(rank_axis), names.index(partition_axis))
-    return tuple(tuple(position[int(g)] for g in by_axis[:, part].tolist()) for part in range(by_axis.shape[1]))
-
-
-def _partition_blocks(fqn_params, num_partitions: int, partition_index: int) -> tuple[int, int]:
-    """(blocks held by one partition, elements of one block over all the parameters) of stacked weights that the
-    partition axis cuts evenly along dim 0; with more than one partition every parameter must declare that layout."""
-    import math
-
-    from ..placement_contract import GlobalLayout, get_global_layout
-
-    shapes = [tuple(p.shape) for _, p in fqn_params]
-    if any(len(s) < 3 for s in shapes):
-        raise ValueError("partitioned block parameters must have at least 3 dims ([blocks, rows, cols])")
-    n = shapes[0][0]
-    if n <= 0 or any(s[0] != n for s in shapes):
-        raise ValueError("partitioned block parameters of one plan must hold the same, positive number of blocks")
-    if num_partitions > 1:
-        for (fqn, p), shape in zip(fqn_params, shapes):
-            want = GlobalLayout((n * num_partitions, *shape[1:]), ((partition_index * n, *(0,) * (len(shape) - 1)),),
-                                ((0,) * len(shape),), (shape,))
-            if get_global_layout(p) != want:
-                raise ValueError(f"partitioned block parameter {fqn!r} must declare a global layout that cuts dim 0 "
-                                 f"evenly into {num_partitions} partitions, this rank holding partition "
-                                 f"{partition_index} (set_global_layout)")
-    return n, sum(math.prod(s[1:]) for s in shapes)
-
-
 def _check_plan_assignment(groups: Sequence[AssignmentGroup], answer, num_ranks: int) -> None:
     if not isinstance(answer, MatrixAssignment):
         raise TypeError(f"the assignment function must return a MatrixAssignment, got {type(answer).__name__}")
@@ -325,8 +286,8 @@ def _materialize_from_plans(*, bucket_plans, assignment_name_by_fqn, initial_sha
         storage_mesh, rank_groups, mine = assignment_mesh, (tuple(range(W)),), 0
     else:
         storage_mesh = partition_mesh[partition_rank_axis_name]
-        rank_groups = _partition_rank_groups(assignment_mesh, partition_mesh, partition_rank_axis_name,
-                                             partition_axis_name)
+        rank_groups = get_mesh_rank_groups(assignment_mesh, partition_mesh, rank_axis_name=partition_rank_axis_name,
+                                           partition_axis_name=partition_axis_name)
         mine = int(partition_mesh.get_local_rank(partition_axis_name))
     groups, group_names, matrix_to_packed, owned_fqns = [], [], {}, []
     for plan in bucket_plans:
@@ -343,7 +304,8 @@ def _materialize_from_plans(*, bucket_plans, assignment_name_by_fqn, initial_sha
                 matrix_to_packed[name] = packed.fqn
         block_groups = ()
         if plan.partitioned_parameters:
-            n, numel = _partition_blocks(plan.partitioned_parameters, len(rank_groups), mine)
+            (n, numel), *_ = get_dim0_block_partitions(plan.partitioned_parameters, num_partitions=len(rank_groups),
+                                                       partition_index=mine)
             block_groups = tuple(MatrixBlockGroupSpec(f"{plan.partition_group_name_prefix}{i}", n, numel, ranks)
                                  for i, ranks in enumerate(rank_groups))
         groups.append(AssignmentGroup(tuple(matrices), block_groups))

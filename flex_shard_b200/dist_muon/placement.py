@@ -44,8 +44,27 @@ class BlockShardPlan:
         return get_dim0_block_partitions(self.num_matrices, world_size)
 
 
-def get_mesh_rank_groups(world_size: int, group_size: int) -> list[list[int]]:
-    """Consecutive groups of ``group_size`` ranks (e.g. the expert-parallel groups of a job)."""
+def get_mesh_rank_groups(world_size, group_size, *, rank_axis_name: str | None = None,
+                         partition_axis_name: str | None = None):
+    """``get_mesh_rank_groups(world_size, group_size)``: consecutive groups of ``group_size`` ranks (e.g. the
+    expert-parallel groups of a job).
+
+    ``get_mesh_rank_groups(flat_mesh, partitioned_mesh, rank_axis_name=..., partition_axis_name=...)``, the reference's
+    form (``dist_muon/placement.py:69-104`` there): for every partition (index along ``partition_axis_name`` of the
+    2-D mesh) the ranks that share it, as positions in the flat mesh, ordered along ``rank_axis_name``."""
+    if not isinstance(world_size, int):
+        flat_mesh, grid_mesh = world_size, group_size
+        names = grid_mesh.mesh_dim_names
+        if names is None or len(names) != 2 or set(names) != {rank_axis_name, partition_axis_name}:
+            raise ValueError(f"the partition mesh must have exactly the axes {rank_axis_name!r} and "
+                             f"{partition_axis_name!r}, got {names}")
+        flat = [int(r) for r in flat_mesh.mesh.flatten().tolist()]
+        grid = grid_mesh.mesh
+        if sorted(int(r) for r in grid.flatten().tolist()) != sorted(flat):
+            raise ValueError("the flat mesh and the partition mesh must hold the same ranks")
+        position = {g: i for i, g in enumerate(flat)}
+        by_axis = grid.permute(names.index(rank_axis_name), names.index(partition_axis_name))
+        return tuple(tuple(position[int(g)] for g in by_axis[:, part].tolist()) for part in range(by_axis.shape[1]))
     if group_size <= 0 or world_size % group_size:
         raise ValueError(f"group size {group_size} does not divide the world size {world_size}")
     return [list(range(i, i + group_size)) for i in range(0, world_size, group_size)]
@@ -58,11 +77,41 @@ def get_strided_rank_groups(world_size: int, group_size: int) -> list[list[int]]
     return [list(range(o, world_size, group_size)) for o in range(group_size)]
 
 
-def get_dim0_block_partitions(num_blocks: int, world_size: int) -> tuple[int, ...]:
-    """Blocks per rank when ``num_blocks`` whole blocks are dealt to ``world_size`` ranks as evenly as possible
-    (the first ``num_blocks % world_size`` ranks hold one more)."""
-    base, rem = divmod(num_blocks, world_size)
-    return tuple(base + (1 if r < rem else 0) for r in range(world_size))
+def get_dim0_block_partitions(num_blocks, world_size: int | None = None, *, num_partitions: int | None = None,
+                              partition_index: int | None = None):
+    """``get_dim0_block_partitions(num_blocks, world_size)``: blocks per rank when ``num_blocks`` whole blocks are
+    dealt to ``world_size`` ranks as evenly as possible (the first ``num_blocks % world_size`` ranks hold one more).
+
+    ``get_dim0_block_partitions(named_params, num_partitions=..., partition_index=...)``, the reference's form
+    (``dist_muon/placement.py:107-161`` there): for stacked weights ``[blocks, ...]`` that an outer mesh axis cuts evenly
+    along dim 0, ``((blocks of one partition, elements of one block over all the parameters),) * num_partitions``; with
+    more than one partition every parameter must declare that layout (``set_global_layout``), this rank holding
+    partition ``partition_index``."""
+    if isinstance(num_blocks, int):
+        base, rem = divmod(num_blocks, world_size)
+        return tuple(base + (1 if r < rem else 0) for r in range(world_size))
+    import math
+
+    from ..placement_contract import GlobalLayout, get_global_layout
+
+    fqn_params = list(num_blocks)
+    if num_partitions is None or partition_index is None:
+        raise TypeError("the parameter form needs num_partitions and partition_index")
+    shapes = [tuple(p.shape) for _, p in fqn_params]
+    if any(len(s) < 3 for s in shapes):
+        raise ValueError("dimension-0 block parameters must have at least 3 dims ([blocks, rows, cols])")
+    n = shapes[0][0]
+    if n <= 0 or any(s[0] != n for s in shapes):
+        raise ValueError("dimension-0 block parameters of one plan must hold the same, positive number of blocks")
+    if num_partitions > 1:
+        for (fqn, p), shape in zip(fqn_params, shapes):
+            want = GlobalLayout((n * num_partitions, *shape[1:]), ((partition_index * n, *(0,) * (len(shape) - 1)),),
+                                ((0,) * len(shape),), (shape,))
+            if get_global_layout(p) != want:
+                raise ValueError(f"partitioned block parameter {fqn!r} must declare a global layout that cuts dim 0 "
+                                 f"evenly into {num_partitions} partitions, this rank holding partition "
+                                 f"{partition_index} (set_global_layout)")
+    return ((n, sum(math.prod(s[1:]) for s in shapes)),) * num_partitions
 
 
 def make_bucketed_block_placement_fn(num_blocks_of):

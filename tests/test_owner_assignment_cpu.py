@@ -401,3 +401,40 @@ def test_sixteen_identical_blocks_on_64_ranks(monkeypatch):
     assert sum(load > 0 for load in per_bucket) == 6 and max(per_bucket) == 16 * 7168 * 16384
     assert sum(load > 0 for load in carried) >= 60
     assert max(carried) <= 7168 * 16384 + sum(carried) // 64
+
+
+def test_rank_group_and_block_partition_helpers_take_both_forms():
+    """Parity: ``dist_muon/placement.py:69-161`` of the reference (mesh form) next to this library's integer form."""
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200 import GlobalLayout, set_global_layout
+    from flex_shard_b200.dist_muon.placement import (get_dim0_block_partitions, get_mesh_rank_groups,
+                                                     get_strided_rank_groups)
+
+    assert get_mesh_rank_groups(8, 4) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert get_strided_rank_groups(8, 4) == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert get_dim0_block_partitions(10, 4) == (3, 3, 2, 2)
+    # a pipeline stage's ranks 8..15 as efsdp x ep = 2 x 4: positions in the flat mesh, one group per ep index
+    flat, grid = _Mesh(list(range(8, 16))), _Mesh([[8, 9, 10, 11], [12, 13, 14, 15]], ("efsdp", "ep"))
+    groups = get_mesh_rank_groups(flat, grid, rank_axis_name="efsdp", partition_axis_name="ep")
+    assert groups == ((0, 4), (1, 5), (2, 6), (3, 7))
+    swapped = _Mesh([[8, 12], [9, 13], [10, 14], [11, 15]], ("ep", "efsdp"))
+    assert get_mesh_rank_groups(flat, swapped, rank_axis_name="efsdp", partition_axis_name="ep") == groups
+    with pytest.raises(ValueError, match="same ranks"):
+        get_mesh_rank_groups(_Mesh(list(range(8))), grid, rank_axis_name="efsdp", partition_axis_name="ep")
+
+    w1, w2 = nn.Parameter(torch.empty(4, 2, 3)), nn.Parameter(torch.empty(4, 3, 2))
+    assert get_dim0_block_partitions([("w1", w1), ("w2", w2)], num_partitions=1, partition_index=0) == ((4, 12),)
+    with pytest.raises(ValueError, match="set_global_layout"):
+        get_dim0_block_partitions([("w1", w1)], num_partitions=2, partition_index=1)
+    for w, shape in ((w1, (2, 3)), (w2, (3, 2))):
+        set_global_layout(w, GlobalLayout((8, *shape), ((4, 0, 0),), ((0, 0, 0),), ((4, *shape),)))
+    assert get_dim0_block_partitions([("w1", w1), ("w2", w2)], num_partitions=2, partition_index=1) == ((4, 12),) * 2
+    with pytest.raises(ValueError, match="set_global_layout"):       # declared for partition 1, asked for partition 0
+        get_dim0_block_partitions([("w1", w1)], num_partitions=2, partition_index=0)
+    with pytest.raises(ValueError, match="3 dims"):
+        get_dim0_block_partitions([("m", nn.Parameter(torch.empty(4, 2)))], num_partitions=1, partition_index=0)
+    with pytest.raises(ValueError, match="same, positive number"):
+        get_dim0_block_partitions([("w1", w1), ("x", nn.Parameter(torch.empty(3, 2, 2)))], num_partitions=1,
+                                  partition_index=0)
