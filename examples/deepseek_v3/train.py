@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--aux-loss-coeff", type=float, default=0.0, help="weight of the sequence-wise router balance loss")
     ap.add_argument("--no-explicit-prefetch", action="store_true",
                     help="leave prefetching to the learned order instead of block-by-block prefetch lists")
+    ap.add_argument("--attention", choices=["sdpa"], default="sdpa",
+                    help="attention implementation: PyTorch SDPA with a block-diagonal mask for packed documents (the "
+                         "reference's other choice, FlexAttention, needs torch.compile, which this library does not use)")
     ap.add_argument("--muon-split", choices=["head", "role"], default="head",
                     help="Muon's matrices inside the attention projections: one per head, or one per head and role "
                          "(no-position / rotary / value rows apart, the Kimi-K2 recipe)")
