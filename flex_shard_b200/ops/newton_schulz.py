@@ -138,8 +138,25 @@ def ns_iterations_batched(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS) -> 
     return x
 
 
+def _newton_schulz_cpu(g: torch.Tensor, steps: int, coeffs, eps: float) -> torch.Tensor:
+    """The CPU statement of the iteration, in the very operations ``torch.optim.Muon`` uses (bf16 norm and division,
+    bf16 ``matmul`` / ``addmm``), so that on CPU an owner-stored matrix steps bitwise like that optimizer."""
+    a, b, c = coeffs
+    x = g.to(torch.bfloat16)
+    tall = g.size(0) > g.size(1)
+    if tall:
+        x = x.T
+    x = x / x.norm().clamp(min=eps)
+    for _ in range(steps):
+        gram = x @ x.T
+        x = torch.addmm(x, torch.addmm(gram, gram, gram, beta=b, alpha=c), x, beta=a)
+    return x.T if tall else x
+
+
 def newton_schulz(g: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
     """Approximate polar factor of ``g`` ([rows, cols] or batched [n, rows, cols]); returns bf16."""
+    if g.dim() == 2 and not g.is_cuda:
+        return _newton_schulz_cpu(g, steps, coeffs, eps)
     if g.dim() == 3:
         if batched_ns_supported(g):
             x = g.to(torch.bfloat16)
@@ -169,9 +186,7 @@ def muon_direction_(momentum: torch.Tensor, grad: torch.Tensor, mu: float, neste
     if not grad.is_cuda:
         momentum.lerp_(grad.float(), 1 - mu)
         u = grad.float().lerp(momentum, mu) if nesterov else momentum
-        x = u.to(torch.bfloat16)
-        x = x / x.float().norm().clamp_min(eps).to(torch.bfloat16)
-        return ns_iterations(x.contiguous(), steps, coeffs)
+        return _newton_schulz_cpu(u, steps, coeffs, eps)
     _ensure()
     lib = _lib.load()
     g = grad.contiguous()

@@ -45,6 +45,42 @@ def test_muon_owned_matches_reference_math():
         torch.testing.assert_close(p.detach(), ref_p, rtol=0, atol=2e-2)
 
 
+def test_owner_stored_matrices_step_bitwise_like_torch_muon_across_a_state_dict_round_trip():
+    """On CPU the step of a matrix that sits whole on its rank equals ``torch.optim.Muon`` bit for bit (same
+    operations), also after the optimizer's state went through ``state_dict`` into an optimizer built with other
+    hyper-parameters, which the loaded groups replace.  Restated from
+    ``tests/test_dist_muon_optimizer.py:48-249`` of the reference."""
+    import warnings
+
+    from flex_shard_b200.dist_muon import DistMuon
+
+    warnings.simplefilter("ignore")
+    torch.manual_seed(0)
+    for mode in ("match_rms_adamw", "original"):
+        shapes = [(32, 64), (96, 32), (48, 48)]
+        ours = [nn.Parameter(torch.randn(*s)) for s in shapes]
+        theirs = [nn.Parameter(p.detach().clone()) for p in ours]
+        kw = dict(lr=0.02, weight_decay=0.1, momentum=0.95, nesterov=True, adjust_lr_fn=mode)
+        a = DistMuon(ours, param_names=[f"w{i}" for i in range(3)], **kw)
+        b = torch.optim.Muon(theirs, **kw)
+
+        def step(opt_a):
+            for p, q in zip(ours, theirs):
+                g = torch.randn(*p.shape)
+                p.grad, q.grad = g.clone(), g.clone()
+            opt_a.step()
+            b.step()
+
+        step(a)
+        step(a)
+        fresh = DistMuon(ours, param_names=[f"w{i}" for i in range(3)], lr=1.0, ns_steps=3, adjust_lr_fn=mode)
+        fresh.load_state_dict(a.state_dict())
+        assert fresh.param_groups[0]["ns_steps"] == 5 and fresh.param_groups[0]["lr"] == 0.02
+        step(fresh)
+        for p, q in zip(ours, theirs):
+            assert torch.equal(p.detach(), q.detach()), (mode, tuple(p.shape))
+
+
 def test_missing_grad_rejects_before_any_update():
     from flex_shard_b200.dist_muon import DistMuon
 
