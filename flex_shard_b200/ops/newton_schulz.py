@@ -153,6 +153,14 @@ def _newton_schulz_cpu(g: torch.Tensor, steps: int, coeffs, eps: float) -> torch
     return x.T if tall else x
 
 
+def newton_schulz_kernel_reference(g: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
+    """CPU restatement of the arithmetic of the GPU kernels for one matrix (norm in fp32, the scaled matrix rounded to
+    bf16 once, every product accumulated in fp32 and rounded once): the oracle the GPU tests compare against."""
+    x = g.detach().cpu().to(torch.bfloat16)
+    x = x / x.float().norm().clamp_min(eps).to(torch.bfloat16)
+    return ns_iterations(x.contiguous(), steps, coeffs)
+
+
 def newton_schulz(g: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float = 1e-7) -> torch.Tensor:
     """Approximate polar factor of ``g`` ([rows, cols] or batched [n, rows, cols]); returns bf16."""
     if g.dim() == 2 and not g.is_cuda:
