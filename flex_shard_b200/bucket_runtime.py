@@ -38,6 +38,24 @@ from .utils.checkpointing import outside_selective_checkpoint
 from .utils.profiling import record
 
 
+def _outside_inference_mode(fn):
+    """Run ``fn`` as in ordinary mode when the caller is under ``torch.inference_mode()`` (an evaluation pass before
+    training): the gathered parameters and the buffers behind them outlive the call, and tensors created under
+    inference mode (dtype views of the byte storage among them) could neither be saved by a later backward nor be
+    refilled in place outside it.  Parity: the reference's "first unshard may run under inference_mode"
+    (``tests/test_flex_shard_runtime.py:409-541`` there)."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if torch.is_inference_mode_enabled():
+            with torch.inference_mode(False):
+                return fn(*args, **kwargs)
+        return fn(*args, **kwargs)
+
+    return wrapper
+
+
 def _in_backward() -> bool:
     return torch._C._current_graph_task_id() != -1
 
@@ -391,6 +409,7 @@ class BucketRuntime:
             up.grad = None
 
     # ------------------------------------------------------------------ unshard / reshard
+    @_outside_inference_mode
     def begin_unshard(self, prefetch: bool = False) -> None:
         if self.is_unsharded or self.pending is not None:
             return
@@ -408,6 +427,7 @@ class BucketRuntime:
             self.pending = begin_bucket_unshard(st, persistent, stream)
         self.context.stats["unshards"] += 1
 
+    @_outside_inference_mode
     def finish_unshard(self) -> None:
         p = self.pending
         assert p is not None
@@ -464,6 +484,7 @@ class BucketRuntime:
             handle.wait()
         return handle
 
+    @_outside_inference_mode
     def swap_in_unsharded(self) -> None:
         for up, slots in zip(self.unsharded_params, self.storage.param_slots):
             for mod, attr in slots:

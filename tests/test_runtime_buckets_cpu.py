@@ -2,6 +2,7 @@
 one gathered bucket at a time with ``reshard_after_forward``, persistent unsharded parameters whose storage is freed
 and refilled, a head applied chunk by chunk, and the per-bucket switches.
 Parity: the behaviours pinned by the reference's ``tests/test_flex_shard_runtime.py:348-407,409-569,709-870,921-970``."""
+import pytest
 import torch
 import torch.nn as nn
 
@@ -109,3 +110,37 @@ def test_per_bucket_runtime_contracts():
         assert r["freed"] and r["same_objects_refilled"]
         assert r["reduces"] == 4 and r["chunked_head_grad"] and r["idle"]
         assert r["partial_sync_reduces"] == 3 and r["kept_bucket_has_no_sharded_grad"] and r["kept_bucket_reduced_later"]
+
+
+def _inference_first(rank, world, kind):
+    import torch.nn as nn
+
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.placements import (make_bucketed_block_shard_placement_fn,
+                                            make_bucketed_owned_full_param_placement_fn)
+
+    fn = {"shard": None, "owned": make_bucketed_owned_full_param_placement_fn(),
+          "flat": make_bucketed_block_shard_placement_fn()}[kind]
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 4))
+    ref = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 4))
+    ref.load_state_dict(m.state_dict())
+    flex_shard(m, [BucketSpec(["0.*"], placement_fn=fn), BucketSpec(["2.*"], placement_fn=fn)])
+    x = torch.randn(3, 8)
+    with torch.inference_mode():
+        first = m(x)                    # the first unshard of every bucket happens here
+    ok = bool(torch.allclose(first, ref(x), atol=1e-6))
+    for _ in range(2):                  # training afterwards saves and refills the same gathered parameters
+        m(x).sum().backward()
+    with torch.inference_mode():
+        again = m(x)
+    return ok, all(p.grad is not None for p in m.parameters()), bool(torch.allclose(again, first, atol=1e-6))
+
+
+@pytest.mark.parametrize("kind", ["shard", "owned", "flat"])
+def test_first_unshard_may_happen_under_inference_mode(kind):
+    """An evaluation pass under ``torch.inference_mode()`` before training leaves ordinary gathered parameters behind
+    (parity: ``tests/test_flex_shard_runtime.py:409-541`` of the reference)."""
+    for world in (1, 2):
+        for ok, grads, same in run_ranks(_inference_first, world, kind):
+            assert ok and grads and same
