@@ -144,3 +144,42 @@ def test_first_unshard_may_happen_under_inference_mode(kind):
     for world in (1, 2):
         for ok, grads, same in run_ranks(_inference_first, world, kind):
             assert ok and grads and same
+
+
+class _WithUnused(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a, self.b, self.unused = nn.Linear(8, 8), nn.Linear(8, 4), nn.Linear(8, 8)
+
+    def forward(self, x):
+        return self.b(torch.relu(self.a(x)))
+
+
+def _user_hooks_and_freezing(rank, world):
+    from flex_shard_b200 import BucketSpec, flex_shard
+
+    torch.manual_seed(0)
+    m = _WithUnused()
+    seen = []
+    m.a.register_forward_pre_hook(lambda mod, args: seen.append(tuple(mod.weight.shape)))   # before flex_shard
+    flex_shard(m, [BucketSpec(["a.*", "unused.*"]), BucketSpec(["b.*"])])
+    x = torch.randn(3, 8)
+    m(x).sum().backward()
+    out = {"hook_saw": seen[:], "unused": [float(p.grad.abs().sum()) for p in m.unused.parameters()]}
+    for p in m.parameters():
+        p.grad = None
+    m.a.weight.requires_grad_(False)            # freezing a local shard takes effect at the next unshard
+    m(x).sum().backward()
+    out["frozen_has_no_grad"] = m.a.weight.grad is None and m.a.bias.grad is not None
+    out["repr"] = all("ShardedBucketStorage" in repr(st) for st in m.sharded_bucket_storages)   # while resharded
+    return out
+
+
+def test_user_hooks_unused_parameters_and_freezing_after_wrap():
+    """A pre-forward hook registered before ``flex_shard`` sees the gathered parameter, trainable parameters that the
+    forward does not use get zero gradients, a shard frozen after wrapping stops getting one, and ``repr`` of a
+    resharded bucket reads no freed storage (parity: ``tests/test_flex_shard_runtime.py:409-541, 921-971`` of the
+    reference)."""
+    for out in run_ranks(_user_hooks_and_freezing, 2):
+        assert out["hook_saw"] == [(8, 8)] and out["unused"] == [0.0, 0.0]
+        assert out["frozen_has_no_grad"] and out["repr"]
