@@ -204,6 +204,7 @@ class DistMuon(torch.optim.Optimizer):
         steps = group["ns_steps"]
         buckets = []
         self.owners = {}
+        row_plans: dict = {}     # identical layers (same shape, same storage rows, same owners) share one row plan
         for cfg, members in zip(configs, bound):
             if not members:
                 continue
@@ -246,7 +247,10 @@ class DistMuon(torch.optim.Optimizer):
                                      f"{storage_rows[rank]} of rank {rank}")
                 mats = [(lo, hi, owner_of[(it.name, b)]) for b, (lo, hi) in enumerate(res.blocks)]
                 self.owners[it.name] = tuple(o for _, _, o in mats)
-                plans.append(plan_rows(res.logical_shape, storage_rows, mats))
+                key = (tuple(res.logical_shape), tuple(storage_rows), tuple(mats))
+                if key not in row_plans:
+                    row_plans[key] = plan_rows(res.logical_shape, storage_rows, mats)
+                plans.append(row_plans[key])
             digest = plan_digest(plans, [(it.name, str(self.payload_dtype)) for it in members])
             buckets.append(RedistributedBucket(
                 items=tuple(moving), plans=tuple(plans), to_compute=packed_schedule(plans, rank, True),

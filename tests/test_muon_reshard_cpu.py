@@ -308,3 +308,30 @@ def test_runtime_buffers_are_reserved_once_for_the_largest_bucket():
     rt.reserve([bucket(2, 2)])
     assert [s.send.data_ptr() for s in rt.slots] == ptrs and len(rt.slots) == 2
     assert math.prod((8, 4)) == rt._reserved[0]
+
+
+def _identical_layers(rank, world):
+    from unittest import mock
+
+    from flex_shard_b200.dist_muon import BlockShard, BucketConfig, ComputeLayout, DistMuon, LocalMuonComputeLayout
+    from flex_shard_b200.dist_muon import reshard_plan
+    from flex_shard_b200.placements import Shard
+
+    # three layers whose 12 x 4 weight holds three 4-row matrices: the 6-row storage shards cut the middle one, so
+    # every layer needs the same redistribution
+    names = [f"layers.{i}.weight" for i in range(3)]
+    lo, hi = Shard(0)._range(12, rank, world)
+    params = [torch.nn.Parameter(torch.randn(hi - lo, 4)) for _ in names]
+    lays = {n: LocalMuonComputeLayout("row_shard", global_shape=(12, 4), row_range=(lo, hi)) for n in names}
+    with mock.patch.object(reshard_plan, "plan_rows", wraps=reshard_plan.plan_rows) as build:
+        opt = DistMuon(params, param_names=names, compute_layouts=lays,
+                       compute_sharding_by_fqn={n: ComputeLayout({"dp": BlockShard(0, (4,))}) for n in names},
+                       bucket_configs=[BucketConfig((n,)) for n in names])
+        buckets = opt.bucket_plans
+    return build.call_count, len(buckets), buckets[0].plans[0] is buckets[2].plans[0]
+
+
+def test_identical_layers_share_one_row_plan():
+    """Parity: ``tests/test_optimizer_reshard_schedule.py:23-70`` of the reference."""
+    for calls, n_buckets, shared in run_ranks(_identical_layers, 2):
+        assert calls == 1 and n_buckets == 3 and shared
