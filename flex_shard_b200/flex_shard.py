@@ -397,9 +397,10 @@ def flex_shard(module: nn.Module, buckets: Sequence[BucketSpec], *,
 
 
 @torch.no_grad()
-def relayout_bucket(module: nn.Module, storage: ShardedBucketStorage, placement_fn) -> ShardedBucketStorage:
+def relayout_bucket(module: nn.Module, bucket_storage: ShardedBucketStorage, placement_fn) -> ShardedBucketStorage:
     """Move one bucket to a new placement, bitwise (gathers in the storage dtype, repacks, frees the
     old buffer). Must run before the first unshard of the bucket and before optimizers are built."""
+    storage = bucket_storage
     state: _FlexShardState = getattr(module, _STATE_ATTR)
     if not any(s is storage for s in state.storages):
         raise ValueError("relayout_bucket(): the storage is not one of the module's bucket storages")
