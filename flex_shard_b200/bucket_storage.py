@@ -155,6 +155,31 @@ class ParamInfo:
         what ``reduce_dtype`` resolves to when the bucket is built."""
         return self.reduce_dtype
 
+    # ---- names of the reference's ParamInfo
+    @property
+    def placements(self) -> tuple:
+        return (self.placement,)
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.storage_dtype
+
+    @property
+    def unsharded_dtype(self) -> torch.dtype:
+        return self.param_dtype
+
+    @property
+    def grad_reduce_dtype(self) -> torch.dtype:
+        return self.bucket_reduce_dtype or self.reduce_dtype
+
+    @property
+    def has_explicit_grad_dtype(self) -> bool:
+        return self.grad_dtype is not None
+
+    @property
+    def grad_dtype_override(self) -> torch.dtype | None:
+        return self.grad_dtype
+
     @property
     def local_numel(self) -> int:
         return math.prod(self.local_shape)
@@ -339,6 +364,47 @@ class ShardedBucketStorage:
 
     def set_reshard_after_backward(self, value: bool) -> None:
         self.reshard_after_backward = bool(value)
+
+    # ---- read-only names the reference's storage offers (``flex_shard/bucket_storage.py:742-800, 961-969`` there)
+    @property
+    def flat_storage(self) -> torch.Tensor:
+        return self.byte_storage
+
+    @property
+    def numel(self) -> int:
+        """Bytes of the sharded storage."""
+        return self.byte_storage.numel()
+
+    @property
+    def param_infos(self) -> dict[str, ParamInfo]:
+        return {info.fqn: info for info in self.infos}
+
+    @property
+    def gradient_reduction(self) -> GradientReduction:
+        return self.reduction
+
+    @property
+    def gradient_reduce_op(self):
+        return self.reduction.op
+
+    @property
+    def gradient_divide_factor(self) -> float | None:
+        return self.reduction.divide_factor
+
+    @property
+    def world_size(self) -> int:
+        return self.comm.world_size
+
+    @property
+    def reduce_mesh(self):
+        """What the bucket reduce-scatters over: its mesh, or the process group of the communicator that
+        ``set_separate_reduce_scatter_group`` gave the reduce-scatters (a group, not a ``DeviceMesh``)."""
+        return self.mesh if self.reduce_comm is self.comm else self.reduce_comm.group
+
+    def get_local_view(self, fqn: str) -> torch.Tensor:
+        """The local tensor of parameter ``fqn`` as a view of the sharded storage."""
+        info = self.param_infos[fqn]
+        return info.placement.make_local_storage_view(info, self.byte_storage)
 
     def set_requires_gradient_sync(self, value: bool) -> None:
         self.requires_gradient_sync = bool(value)

@@ -154,6 +154,31 @@ def test_reference_call_forms_are_accepted():
         set_sharding_info(t, (Shard(0), Shard(1)), (4, 3), (3, 1), None)
 
 
+def test_storage_and_param_info_answer_to_the_reference_names():
+    """Read-only names of the reference's ``ShardedBucketStorage`` and ``ParamInfo``
+    (``flex_shard/bucket_storage.py:283-340, 742-800, 961-969`` there)."""
+    from flex_shard_b200 import BucketSpec, MixedPrecisionPolicy, flex_shard
+
+    m = Net()
+    m.a.weight.grad_dtype = torch.float64
+    flex_shard(m, [BucketSpec(["a.*"], mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16)),
+                   BucketSpec(["b.*"], gradient_divide_factor=4.0)])
+    a, b = m.sharded_bucket_storages
+    assert a.flat_storage is a.byte_storage and a.numel == a.total_bytes == a.byte_storage.numel()
+    assert list(a.param_infos) == ["a.weight", "a.bias"] and a.world_size == 1
+    assert b.gradient_reduce_op == dist.ReduceOp.AVG and b.gradient_divide_factor == 4.0
+    assert b.gradient_reduction.divide_factor == 4.0 and a.gradient_divide_factor is None
+    assert a.reduce_mesh is a.mesh
+    assert a.get_local_view("a.bias").shape == (16,) and a.get_local_view("a.bias").data_ptr() == m.a.bias.data_ptr()
+    info = a.param_infos["a.weight"]
+    assert info.placements == (info.placement,) and info.dtype == torch.float32
+    assert info.unsharded_dtype == torch.bfloat16 and info.has_explicit_grad_dtype
+    assert info.grad_dtype_override == torch.float64 and info.grad_reduce_dtype == torch.float64
+    plain = b.param_infos["b.weight"]
+    assert not plain.has_explicit_grad_dtype and plain.grad_dtype_override is None
+    assert plain.unsharded_dtype == plain.grad_reduce_dtype == torch.float32
+
+
 def test_flex_shard_applies_once():
     from flex_shard_b200 import BucketSpec, flex_shard
 
