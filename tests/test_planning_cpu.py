@@ -149,6 +149,32 @@ def test_adapters():
     assert lay.global_shape == (8, 8) and lay.global_offsets == ((4, 0),)
 
 
+def test_spmd_annotations_on_a_module_become_layouts_and_partial_groups():
+    """Parity: ``layout_adapters/spmd_types.py:20-127`` and ``tests/test_flex_shard_spmd_types_layout.py:34`` of the
+    reference (annotations come from parameter attributes here)."""
+    import pytest
+    import torch
+    import torch.nn as nn
+
+    from flex_shard_b200 import get_global_layout, get_partial_grad_group
+    from flex_shard_b200.layout_adapters import spmd_types_to_global_layout
+
+    m = nn.Module()
+    m.w = nn.Parameter(torch.zeros(4, 8))
+    m.norm = nn.Parameter(torch.zeros(8))
+    m.plain = nn.Parameter(torch.zeros(2))
+    m.w.spmd_sharding, m.w.spmd_mesh = {"tp": ("shard", 0), "dp": ("replicate",)}, {"tp": (1, 2), "dp": (0, 4)}
+    m.norm.spmd_sharding, m.norm.spmd_mesh = {"tp": ("partial",)}, {"tp": (1, 2)}
+    with pytest.raises(ValueError, match="no group was given"):
+        spmd_types_to_global_layout(m)
+    group = object()
+    assert spmd_types_to_global_layout(m, {"tp": group}) is m
+    lay = get_global_layout(m.w)
+    assert (lay.global_shape, lay.global_offsets, lay.local_sizes) == ((8, 8), ((4, 0),), ((4, 8),))
+    assert get_partial_grad_group(m.norm) is group and get_global_layout(m.norm).global_shape == (8,)
+    assert get_global_layout(m.plain) is None and get_partial_grad_group(m.w) is None
+
+
 def test_router_reference_gradients_match_autograd_of_the_plain_formula():
     import torch
     from flex_shard_b200.ops import moe
