@@ -311,7 +311,8 @@ def _materialize_from_plans(*, bucket_plans, assignment_name_by_fqn, initial_sha
         groups.append(AssignmentGroup(tuple(matrices), block_groups))
         group_names.append(tuple(b.name for b in block_groups))
     if assignment_fn is None:
-        answer = _assign_groups(groups, W, mesh_rank_hosts(W))
+        # hosts from the mesh's global ranks (a sub-mesh, e.g. one pipeline stage, does not start at rank 0)
+        answer = _assign_groups(groups, W, mesh_rank_hosts([int(r) for r in assignment_mesh.mesh.flatten().tolist()]))
     else:
         _assign_groups(groups, W, None)            # the same input checks a built-in run would make
         answer = assignment_fn(tuple(groups), num_ranks=W)
