@@ -130,6 +130,19 @@ def newton_schulz_cost(shape: Sequence[int], ns_steps: int = 5) -> float:
     return float(ns_steps * s * s * (2 * l + s) * math.prod(shape[:-2]))
 
 
+def _global_ranks(mesh, group, world_size: int):
+    """The mesh's global ranks in mesh order when they can be known (a sub-mesh need not start at rank 0 nor be
+    contiguous, and hosts follow the global ranks), else the mesh size."""
+    ranks = getattr(mesh, "mesh", None)
+    if ranks is not None and hasattr(ranks, "flatten"):
+        return [int(r) for r in ranks.flatten().tolist()]
+    if group is not None and world_size > 1:
+        import torch.distributed as dist
+
+        return list(dist.get_process_group_ranks(group))
+    return world_size
+
+
 def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_fn=None,
                                                 owner_by_fqn: Mapping[str, int] | None = None,
                                                 ranks_per_host: int | None = None):
@@ -142,8 +155,8 @@ def make_bucketed_owned_full_param_placement_fn(carry_loads: bool = False, cost_
     def fn(named_params, mesh):
         from ..parallel.comm import mesh_group
 
-        _, _, W, _ = mesh_group(mesh)
-        hosts = mesh_rank_hosts(W, ranks_per_host)
+        group, _, W, _ = mesh_group(mesh)
+        hosts = mesh_rank_hosts(_global_ranks(mesh, group, W), ranks_per_host)
         if carry_loads:
             if len(carried) != W:
                 carried[:] = [0.0] * W
