@@ -158,8 +158,30 @@ def _walk(d, path=()):
         yield path, d
 
 
+def _agree(error: BaseException | None, what: str, group) -> None:
+    """End of a collective save / load: every rank learns whether any rank failed, so that a failure on one rank (a
+    shard that the files do not cover, a full disk) raises everywhere instead of leaving the others in a barrier."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        failed: list = [None] * dist.get_world_size(group)
+        dist.all_gather_object(failed, None if error is None else f"{type(error).__name__}: {error}", group=group)
+        if error is None and any(f is not None for f in failed):
+            bad = {r: f for r, f in enumerate(failed) if f is not None}
+            raise RuntimeError(f"checkpoint {what} failed on rank(s) {sorted(bad)}: {next(iter(bad.values()))}")
+    if error is not None:
+        raise error
+
+
 def save(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
     """Write this rank's part of a (nested) state dict of tagged tensors."""
+    error = None
+    try:
+        _save_rank_file(state_dict, checkpoint_id, group)
+    except Exception as e:            # agreed on below
+        error = e
+    _agree(error, "save", group)
+
+
+def _save_rank_file(state_dict: Mapping[str, Any], checkpoint_id: str, group) -> None:
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     os.makedirs(checkpoint_id, exist_ok=True)
@@ -187,8 +209,6 @@ def save(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
     tmp = os.path.join(checkpoint_id, f"rank{rank}.pt.tmp")
     torch.save({"world_size": world, "entries": entries}, tmp)
     os.replace(tmp, os.path.join(checkpoint_id, f"rank{rank}.pt"))
-    if dist.is_initialized():
-        dist.barrier(group)
 
 
 def load(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
@@ -244,13 +264,18 @@ def load(state_dict: Mapping[str, Any], checkpoint_id: str, group=None) -> None:
                 if src is not None and src["kind"] == "object":
                     d[k] = src["value"]
 
-    recurse(state_dict, ())
-    if dist.is_initialized():
-        dist.barrier(group)
+    error = None
+    try:
+        recurse(state_dict, ())
+    except Exception as e:            # agreed on below
+        error = e
+    _agree(error, "load", group)
 
 
 @torch.no_grad()
 def _fill_boxes(v: torch.Tensor, lay: GlobalLayout, key: str, blobs) -> None:
+    if not any(key in b["entries"] for b in blobs):
+        raise KeyError(f"{key} not in checkpoint")
     covered = 0
     want = 0
     for goff, loff, size in zip(lay.global_offsets, lay.local_offsets, lay.local_sizes):
@@ -262,6 +287,10 @@ def _fill_boxes(v: torch.Tensor, lay: GlobalLayout, key: str, blobs) -> None:
             e = b["entries"].get(key)
             if e is None:
                 continue
+            saved_shape = tuple(e["tensor"].shape) if e["kind"] == "replicated" else tuple(e["global_shape"])
+            if saved_shape != tuple(lay.global_shape):
+                raise RuntimeError(f"size mismatch for {key}: the checkpoint holds shape {saved_shape}, the model "
+                                   f"expects {tuple(lay.global_shape)}")
             if e["kind"] == "replicated":
                 src = e["tensor"]
                 for d, (g, s) in enumerate(zip(goff, size)):

@@ -291,3 +291,46 @@ def test_round_trip_of_a_checkpoint_wrapped_submodule_and_of_tied_weights(world,
         assert out["layout"] == ((5, 4), ((lo, 0),), ((hi - lo, 4),))
         assert out["wrapped_ok"] and out["tied_ok"] and out["still_shared"]
         assert out["tied_layouts"] == [True, True]
+
+
+def _load_failures(rank, world, path):
+    from flex_shard_b200 import BucketSpec, checkpoint, flex_shard
+
+    def tagged(m):
+        sd = m.state_dict()
+        checkpoint.set_state_dict_global_layouts(m, sd)
+        return sd
+
+    saved = flex_shard(nn.Linear(4, 6), [BucketSpec(["*"])])
+    checkpoint.save(tagged(saved), path)
+    out = {}
+
+    def attempt(name, sd):
+        try:
+            checkpoint.load(sd, path)
+            out[name] = "loaded"
+        except Exception as e:
+            out[name] = f"{type(e).__name__}: {e}"
+
+    # rows 0..3 of the taller weight are all in the files, rows 4..7 are not: without the shape check only rank 1 failed
+    attempt("taller", tagged(flex_shard(nn.Linear(4, 8), [BucketSpec(["*"])])))
+    attempt("renamed", tagged(flex_shard(nn.Sequential(nn.Linear(4, 6)), [BucketSpec(["*"])])))
+    one_sided = tagged(saved)
+    if rank == 1:
+        one_sided["extra"] = torch.zeros(2)          # only this rank asks for a tensor the files do not have
+    attempt("one_sided", one_sided)
+    attempt("good", tagged(saved))
+    return out
+
+
+def test_load_failures_are_named_and_raise_on_every_rank(tmp_path):
+    """A shape that differs from the saved one is a "size mismatch" (parity:
+    ``tests/test_flex_shard_state_dict.py:68-75`` of the reference), a missing key is named, and a failure on one rank
+    raises on the others too instead of leaving them in the closing barrier."""
+    res = run_ranks(_load_failures, 2, str(tmp_path / "ckpt"))
+    for rank, out in enumerate(res):
+        assert "size mismatch for weight" in out["taller"] and "(6, 4)" in out["taller"], out
+        assert out["renamed"].startswith("KeyError") and "0.weight not in checkpoint" in out["renamed"]
+        assert out["good"] == "loaded"
+    assert res[1]["one_sided"].startswith("KeyError") and "extra not in checkpoint" in res[1]["one_sided"]
+    assert "failed on rank(s) [1]" in res[0]["one_sided"] and "extra not in checkpoint" in res[0]["one_sided"]
