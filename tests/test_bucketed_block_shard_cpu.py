@@ -126,3 +126,37 @@ def test_mixed_block_configurations_cannot_share_a_bucket():
     with pytest.raises(ValueError, match="mixes incompatible placements"):
         flex_shard(m, [BucketSpec(["*"], placement_fn=lambda named, mesh: {
             f: BucketedBlockShard((1,) if i % 2 else (2,)) for i, (f, _) in enumerate(named)})])
+
+
+def _padding_only_ranks(rank, world):
+    from flex_shard_b200 import BucketSpec, flex_shard
+    from flex_shard_b200.placements import make_bucketed_block_shard_placement_fn
+
+    torch.manual_seed(0)
+    m, ref = nn.Linear(8, 1, bias=False), nn.Linear(8, 1, bias=False)
+    ref.load_state_dict(m.state_dict())
+    flex_shard(m, [BucketSpec(["*"], placement_fn=make_bucketed_block_shard_placement_fn())])
+    held = m.weight.numel()
+    opt, ropt = torch.optim.SGD(m.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    for s in range(2):
+        xs = [torch.randn(3, 8, generator=torch.Generator().manual_seed(10 * s + r)) for r in range(world)]
+        m(xs[rank]).square().mean().backward()
+        opt.step()
+        opt.zero_grad()
+        sum(ref(x).square().mean() for x in xs).div(world).backward()
+        ropt.step()
+        ropt.zero_grad()
+    m.unshard()
+    err = float((m.weight.detach() - ref.weight.detach()).abs().max())
+    m.reshard()
+    return held, err
+
+
+def test_ranks_that_hold_only_padding_train_with_the_others():
+    """One row on four ranks: three ranks store nothing and still take part in every collective; the result equals
+    the unsharded model (the reference refuses such a rank, ``tests/test_flex_shard_block_shard.py:203-246`` there)."""
+    from tests.common import run_ranks
+
+    res = run_ranks(_padding_only_ranks, 4)
+    assert sorted(h for h, _ in res) == [0, 0, 0, 8]
+    assert all(err < 1e-6 for _, err in res)
